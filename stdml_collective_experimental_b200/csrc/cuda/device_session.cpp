@@ -1,0 +1,370 @@
+#include "device_session.hpp"
+
+#include <algorithm>
+#include <cstring>
+
+#include <cuda_runtime.h>
+
+namespace stdml::collective::cuda
+{
+namespace
+{
+constexpr size_t kElemSize[12] = {1, 2, 4, 8, 1, 2, 4, 8, 2, 2, 4, 8};
+
+size_t elem_size(int dt)
+{
+    if (dt < 0 || dt >= 12) { throw std::invalid_argument("device session: bad dtype"); }
+    return kElemSize[dt];
+}
+
+void rt_check(cudaError_t e, const char *what)
+{
+    if (e != cudaSuccess) {
+        throw std::runtime_error(std::string("CUDA runtime: ") + what + ": " +
+                                 cudaGetErrorString(e));
+    }
+}
+
+void launch_check(int rc, const char *what)
+{
+    if (rc != 0) {
+        throw std::runtime_error(std::string("device session: launch of ") + what + " failed: " +
+                                 cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    }
+}
+}  // namespace
+
+DeviceSession::DeviceSession(std::unique_ptr<DeviceWorld> world) : world_(std::move(world)) {}
+
+DeviceSession::~DeviceSession()
+{
+    for (void *p : table_mem_) { (void)cudaFree(p); }
+    table_mem_.clear();
+    (void)cudaGetLastError();
+}
+
+void DeviceSession::check()
+{
+    const DeviceStatus s = world_->poll_status();
+    if (s.code != 0) {
+        throw DeviceTimeout("device collective gave up: rank " + std::to_string(s.rank) +
+                                " block " + std::to_string(s.block) + " waited for rank " +
+                                std::to_string(s.peer) + " (barrier " + std::to_string(s.phase) +
+                                ", want " + std::to_string(s.want) + ", have " +
+                                std::to_string(s.have) + "); call recover() on every rank",
+                            s);
+    }
+}
+
+void DeviceSession::launch_ar(AllReduceCall &c, void *stream)
+{
+    launch_check(world_->all_reduce(c, stream), "all_reduce");
+    ++launches_;
+}
+
+void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t count, int dt,
+                               int op, double scale, int algo, void *stream)
+{
+    check();
+    if (count == 0) { return; }
+    const size_t es = elem_size(dt);
+    const int vr = world_->vranks();
+    AllReduceCall c;
+    c.dt = dt;
+    c.op = op;
+    c.algo = algo;
+    c.has_scale = scale != 1.0;
+    c.scale = static_cast<float>(scale);
+
+    // zero-copy: the buffer lives at the same arena offset on every rank
+    size_t off = world_->offset_of(in[0], 0);
+    bool symmetric = off != SIZE_MAX && off % 16 == 0;
+    bool in_place = true;
+    for (int v = 0; v < vr && symmetric; ++v) {
+        symmetric = world_->offset_of(in[v], v) == off;
+        in_place = in_place && (in[v] == out[v]);
+    }
+    if (symmetric && in_place) {
+        c.off = off;
+        c.count = count;
+        if (c.algo == kAlgoOneShot || c.algo == kAlgoNvlsOneShot) {
+            throw std::invalid_argument(
+                "all_reduce: one-shot algorithms cannot run in place on a symmetric buffer");
+        }
+        if (c.algo < 0) { c.algo = world_->pick_algo(count * es, dt, op, true); }
+        launch_ar(c, stream);
+        return;
+    }
+    const bool small = count * es <= 256u << 10;
+    if (symmetric && small && algo != kAlgoTwoShot && algo != kAlgoNvls) {
+        // read the symmetric input in place, write the user's output; the end
+        // barrier keeps the input stable until every peer has read it
+        c.off = off;
+        c.count = count;
+        c.dst = out;
+        c.end_barrier = true;
+        if (c.algo < 0) { c.algo = world_->pick_algo(count * es, dt, op, false); }
+        launch_ar(c, stream);
+        return;
+    }
+
+    // staged: pack into a staging slot inside the launch, one slot per chunk
+    const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
+    std::vector<const void *> src(vr);
+    std::vector<void *> dst(vr);
+    for (size_t done = 0; done < count; done += slot_elems) {
+        const size_t n = std::min(slot_elems, count - done);
+        for (int v = 0; v < vr; ++v) {
+            src[v] = static_cast<const char *>(in[v]) + done * es;
+            dst[v] = static_cast<char *>(out[v]) + done * es;
+        }
+        AllReduceCall k = c;
+        k.off = world_->next_staging_slot();
+        k.src = src.data();
+        k.dst = dst.data();
+        k.count = n;
+        launch_ar(k, stream);
+    }
+}
+
+void DeviceSession::reduce(const void *const *in, void *const *out, size_t count, int dt, int op,
+                           int root, double scale, void *stream)
+{
+    check();
+    if (count == 0) { return; }
+    if (root < 0 || root >= world_->world()) { throw std::invalid_argument("reduce: bad root"); }
+    const size_t es = elem_size(dt);
+    const int vr = world_->vranks();
+    const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
+    std::vector<const void *> src(vr);
+    std::vector<void *> dst(vr);
+    for (size_t done = 0; done < count; done += slot_elems) {
+        const size_t n = std::min(slot_elems, count - done);
+        for (int v = 0; v < vr; ++v) {
+            src[v] = static_cast<const char *>(in[v]) + done * es;
+            dst[v] = (out != nullptr && out[v] != nullptr)
+                         ? static_cast<char *>(out[v]) + done * es
+                         : nullptr;
+        }
+        AllReduceCall k;
+        k.dt = dt;
+        k.op = op;
+        k.root = root;
+        k.has_scale = scale != 1.0;
+        k.scale = static_cast<float>(scale);
+        k.off = world_->next_staging_slot();
+        k.src = src.data();
+        k.dst = dst.data();
+        k.count = n;
+        // small: root pulls everything; large: owners reduce their shard and
+        // store it to root only, which spreads the reads over all links
+        k.algo = (n * es <= (1u << 20) || world_->world() == 1) ? kAlgoOneShot : kAlgoTwoShot;
+        launch_ar(k, stream);
+    }
+}
+
+const DeviceSession::GroupPlan &DeviceSession::plan_group(size_t n, const void *const *ins,
+                                                          void *const *outs,
+                                                          const size_t *counts, int dt,
+                                                          int user_dt)
+{
+    const int vr = world_->vranks();
+    std::string key;
+    key.reserve((2 * vr * n + n + 2) * sizeof(void *));
+    key.append(reinterpret_cast<const char *>(ins), sizeof(void *) * n * vr);
+    key.append(reinterpret_cast<const char *>(outs), sizeof(void *) * n * vr);
+    key.append(reinterpret_cast<const char *>(counts), sizeof(size_t) * n);
+    key.append(reinterpret_cast<const char *>(&dt), sizeof(dt));
+    key.append(reinterpret_cast<const char *>(&user_dt), sizeof(user_dt));
+    auto it = plans_.find(key);
+    if (it != plans_.end()) { return it->second; }
+    if (plans_.size() >= 64) {  // bounded cache; cudaFree waits for work in flight
+        for (void *p : table_mem_) { (void)cudaFree(p); }
+        table_mem_.clear();
+        plans_.clear();
+    }
+
+    const size_t es = elem_size(dt);                          // wire element
+    const size_t ues = user_dt >= 0 ? elem_size(user_dt) : es;  // user element
+    const size_t lanes = 16 / es;
+    const size_t cap = world_->staging_bytes() / 16;  // vectors per slot
+
+    // Cut the flat sequence of tensors into slot-sized chunks; a tensor that
+    // does not fit is split at a vector boundary.
+    struct Piece {
+        size_t tensor, first_elem, count, voff;
+    };
+    std::vector<std::vector<Piece>> chunks(1);
+    size_t fill = 0;
+    for (size_t i = 0; i < n; ++i) {
+        size_t done = 0;
+        while (done < counts[i]) {
+            if (fill == cap) {
+                chunks.emplace_back();
+                fill = 0;
+            }
+            const size_t room = (cap - fill) * lanes;
+            const size_t take = std::min(room, counts[i] - done);
+            chunks.back().push_back(Piece{i, done, take, fill});
+            fill += (take + lanes - 1) / lanes;
+            done += take;
+        }
+    }
+
+    GroupPlan plan;
+    for (const auto &pieces : chunks) {
+        if (pieces.empty()) { continue; }
+        std::vector<Table> per_rank(vr);
+        size_t nvec = 0;
+        for (const auto &p : pieces) { nvec = std::max(nvec, p.voff + (p.count + lanes - 1) / lanes); }
+        for (int v = 0; v < vr; ++v) {
+            std::vector<GroupEntry> host(pieces.size());
+            for (size_t j = 0; j < pieces.size(); ++j) {
+                const Piece &p = pieces[j];
+                const char *s = static_cast<const char *>(ins[v * n + p.tensor]);
+                char *d = static_cast<char *>(outs[v * n + p.tensor]);
+                host[j].src = s + p.first_elem * ues;
+                host[j].dst = d + p.first_elem * ues;
+                host[j].voff = p.voff;
+                host[j].count = p.count;
+            }
+            void *dev = nullptr;
+            rt_check(cudaMalloc(&dev, host.size() * sizeof(GroupEntry)), "cudaMalloc(table)");
+            table_mem_.push_back(dev);
+            rt_check(cudaMemcpy(dev, host.data(), host.size() * sizeof(GroupEntry),
+                                cudaMemcpyHostToDevice),
+                     "cudaMemcpy(table)");
+            per_rank[v].dev = static_cast<GroupEntry *>(dev);
+            per_rank[v].n = static_cast<int>(host.size());
+            per_rank[v].nvec = nvec;
+        }
+        plan.chunks.push_back(std::move(per_rank));
+    }
+    return plans_.emplace(std::move(key), std::move(plan)).first->second;
+}
+
+void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *const *outs,
+                                     const size_t *counts, int dt, int op, int user_dt,
+                                     double scale, int algo, void *stream)
+{
+    check();
+    if (n == 0) { return; }
+    const size_t es = elem_size(dt);
+    const int vr = world_->vranks();
+    if (user_dt == dt) { user_dt = -1; }
+
+    // zero-copy: tensors sit back to back (16-byte granules) at the same arena
+    // offsets on every rank and are reduced in place -> one flat all_reduce
+    bool flat = user_dt < 0;
+    size_t first = SIZE_MAX, total = 0;
+    for (int v = 0; v < vr && flat; ++v) {
+        size_t expect = SIZE_MAX;
+        for (size_t i = 0; i < n && flat; ++i) {
+            const size_t off = world_->offset_of(ins[v * n + i], v);
+            flat = off != SIZE_MAX && off % 16 == 0 && ins[v * n + i] == outs[v * n + i] &&
+                   (expect == SIZE_MAX || off == expect);
+            if (i == 0) {
+                if (v == 0) { first = off; }
+                flat = flat && off == first;
+            }
+            expect = off + (counts[i] * es + 15) / 16 * 16;
+        }
+        if (flat) { total = expect - first; }
+    }
+    if (flat && total > 0) {
+        AllReduceCall c;
+        c.dt = dt;
+        c.op = op;
+        c.off = first;
+        c.count = total / es;
+        c.has_scale = scale != 1.0;
+        c.scale = static_cast<float>(scale);
+        c.algo = algo;
+        if (c.algo == kAlgoOneShot || c.algo == kAlgoNvlsOneShot) { c.algo = -1; }
+        if (c.algo < 0) { c.algo = world_->pick_algo(total, dt, op, true); }
+        launch_ar(c, stream);
+        return;
+    }
+
+    const GroupPlan &plan = plan_group(n, ins, outs, counts, dt, user_dt);
+    std::vector<const GroupEntry *> tabs(vr);
+    for (const auto &chunk : plan.chunks) {
+        for (int v = 0; v < vr; ++v) { tabs[v] = chunk[v].dev; }
+        AllReduceCall c;
+        c.dt = dt;
+        c.op = op;
+        c.user_dtype = user_dt;
+        c.off = world_->next_staging_slot();
+        c.table = tabs.data();
+        c.ntable = chunk[0].n;
+        c.count = chunk[0].nvec * (16 / es);
+        c.has_scale = scale != 1.0;
+        c.scale = static_cast<float>(scale);
+        c.algo = algo;
+        launch_ar(c, stream);
+    }
+}
+
+void DeviceSession::all_gather(const void *const *in, void *const *out, size_t count, int dt,
+                               void *stream)
+{
+    check();
+    const size_t bytes = count * elem_size(dt);
+    if (bytes == 0) { return; }
+    const int vr = world_->vranks();
+    const size_t slot = world_->staging_bytes();
+    std::vector<const void *> src(vr);
+    std::vector<void *> dst(vr);
+    for (size_t done = 0; done < bytes; done += slot) {
+        const size_t nbytes = std::min(slot, bytes - done);
+        for (int v = 0; v < vr; ++v) {
+            src[v] = static_cast<const char *>(in[v]) + done;
+            dst[v] = static_cast<char *>(out[v]) + done;
+        }
+        GatherCall g;
+        g.off = world_->next_staging_slot();
+        g.src = src.data();
+        g.dst = dst.data();
+        g.bytes = nbytes;
+        g.stride = bytes;
+        launch_check(world_->gather(g, stream), "all_gather");
+        ++launches_;
+    }
+}
+
+void DeviceSession::broadcast(const void *const *in, void *const *out, size_t count, int dt,
+                              int root, void *stream)
+{
+    check();
+    if (root < 0 || root >= world_->world()) { throw std::invalid_argument("broadcast: bad root"); }
+    const size_t bytes = count * elem_size(dt);
+    if (bytes == 0) { return; }
+    const int vr = world_->vranks();
+    const size_t slot = world_->staging_bytes();
+    std::vector<const void *> src(vr);
+    std::vector<void *> dst(vr);
+    for (size_t done = 0; done < bytes; done += slot) {
+        const size_t nbytes = std::min(slot, bytes - done);
+        for (int v = 0; v < vr; ++v) {
+            src[v] = (in != nullptr && in[v] != nullptr) ? static_cast<const char *>(in[v]) + done
+                                                          : nullptr;
+            dst[v] = static_cast<char *>(out[v]) + done;
+        }
+        GatherCall g;
+        g.off = world_->next_staging_slot();
+        g.src = src.data();
+        g.dst = dst.data();
+        g.bytes = nbytes;
+        g.root = root;
+        launch_check(world_->gather(g, stream), "broadcast");
+        ++launches_;
+    }
+}
+
+void DeviceSession::barrier(void *stream)
+{
+    check();
+    launch_check(world_->barrier(stream), "barrier");
+    ++launches_;
+}
+}  // namespace stdml::collective::cuda

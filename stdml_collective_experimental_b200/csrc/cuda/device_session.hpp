@@ -1,0 +1,88 @@
+// DeviceSession: the collective front-end for CUDA buffers.  It decides, per
+// call, between zero-copy (buffers that live in the symmetric heap) and staged
+// execution (arbitrary device pointers packed into one of two staging slots
+// inside the same kernel launch), splits messages larger than a slot, builds
+// and caches the descriptor tables of fused groups, and turns a device-side
+// timeout into an exception.
+//
+// It plays the role of the reference's session for device memory
+// (include/stdml/bits/collective/session.hpp:25-178): all_reduce,
+// group_all_reduce, all_gather, broadcast (any root; the reference fixes
+// root 0), plus reduce, which the reference only declares
+// (include/stdml/bits/collective/algorithm.hpp:16-18).
+//
+// Pointer arguments are arrays with one entry per virtual rank (`vranks()`):
+// one entry for a real multi-GPU world, `world` entries for a loopback world.
+#pragma once
+#include <cstddef>
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "device_world.hpp"
+
+namespace stdml::collective::cuda
+{
+struct DeviceTimeout : std::runtime_error {
+    DeviceStatus status;
+    DeviceTimeout(const std::string &what, const DeviceStatus &s)
+        : std::runtime_error(what), status(s)
+    {
+    }
+};
+
+class DeviceSession
+{
+  public:
+    explicit DeviceSession(std::unique_ptr<DeviceWorld> world);
+    ~DeviceSession();
+
+    DeviceWorld &world() { return *world_; }
+    int rank() const { return world_->rank(); }
+    int size() const { return world_->world(); }
+    int vranks() const { return world_->vranks(); }
+
+    // out[i] = scale * (in_0[i] op in_1[i] op ... ), scale == 1 means none.
+    // algo < 0 picks by size.  In-place (in == out) is allowed.
+    void all_reduce(const void *const *in, void *const *out, size_t count, int dt, int op,
+                    double scale, int algo, void *stream);
+    // Only `root` receives the result; `out` of other ranks may be null.
+    void reduce(const void *const *in, void *const *out, size_t count, int dt, int op, int root,
+                double scale, void *stream);
+    // n tensors, ins/outs laid out [vrank][tensor].  user_dt < 0: tensors have
+    // the wire type `dt`; otherwise tensors are f32 and travel as bf16/f16.
+    void group_all_reduce(size_t n, const void *const *ins, void *const *outs,
+                          const size_t *counts, int dt, int op, int user_dt, double scale,
+                          int algo, void *stream);
+    void all_gather(const void *const *in, void *const *out, size_t count, int dt, void *stream);
+    void broadcast(const void *const *in, void *const *out, size_t count, int dt, int root,
+                   void *stream);
+    void barrier(void *stream);
+
+    // Throws DeviceTimeout if a kernel reported a wait that ran out.
+    void check();
+    // Kernel launches issued so far (all kinds).
+    unsigned long long launches() const { return launches_; }
+
+  private:
+    struct Table {
+        GroupEntry *dev = nullptr;
+        int n = 0;
+        size_t nvec = 0;
+    };
+    struct GroupPlan {
+        std::vector<std::vector<Table>> chunks;  // [chunk][vrank]
+    };
+
+    void launch_ar(AllReduceCall &c, void *stream);
+    const GroupPlan &plan_group(size_t n, const void *const *ins, void *const *outs,
+                                const size_t *counts, int dt, int user_dt);
+
+    std::unique_ptr<DeviceWorld> world_;
+    std::map<std::string, GroupPlan> plans_;
+    std::vector<void *> table_mem_;
+    unsigned long long launches_ = 0;
+};
+}  // namespace stdml::collective::cuda

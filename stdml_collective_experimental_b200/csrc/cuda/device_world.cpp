@@ -1,0 +1,881 @@
+#include "device_world.hpp"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <new>
+#include <stdexcept>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include "local_rendezvous.hpp"
+
+namespace stdml::collective::cuda
+{
+namespace
+{
+// ------------------------------------------------------------------ helpers
+void rt_check(cudaError_t e, const char *what)
+{
+    if (e != cudaSuccess) {
+        throw std::runtime_error(std::string("CUDA runtime: ") + what + ": " +
+                                 cudaGetErrorString(e));
+    }
+}
+
+size_t round_up(size_t x, size_t m) { return (x + m - 1) / m * m; }
+
+// The driver API is reached through cudaGetDriverEntryPoint so that this
+// library loads (and its host parts run) on machines without libcuda.
+struct Driver {
+    decltype(&cuGetErrorString) GetErrorString = nullptr;
+    decltype(&cuDeviceGet) DeviceGet = nullptr;
+    decltype(&cuDeviceGetAttribute) DeviceGetAttribute = nullptr;
+    decltype(&cuMemGetAllocationGranularity) MemGetAllocationGranularity = nullptr;
+    decltype(&cuMemCreate) MemCreate = nullptr;
+    decltype(&cuMemRelease) MemRelease = nullptr;
+    decltype(&cuMemAddressReserve) MemAddressReserve = nullptr;
+    decltype(&cuMemAddressFree) MemAddressFree = nullptr;
+    decltype(&cuMemMap) MemMap = nullptr;
+    decltype(&cuMemUnmap) MemUnmap = nullptr;
+    decltype(&cuMemSetAccess) MemSetAccess = nullptr;
+    decltype(&cuMemExportToShareableHandle) MemExportToShareableHandle = nullptr;
+    decltype(&cuMemImportFromShareableHandle) MemImportFromShareableHandle = nullptr;
+    decltype(&cuMulticastCreate) MulticastCreate = nullptr;
+    decltype(&cuMulticastAddDevice) MulticastAddDevice = nullptr;
+    decltype(&cuMulticastBindMem) MulticastBindMem = nullptr;
+    decltype(&cuMulticastUnbind) MulticastUnbind = nullptr;
+    decltype(&cuMulticastGetGranularity) MulticastGetGranularity = nullptr;
+    bool ok = false;
+    bool multicast = false;
+
+    template <typename F>
+    bool load(const char *name, F &fn)
+    {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        fn = reinterpret_cast<F>(p);
+        return true;
+    }
+
+    Driver()
+    {
+        ok = load("cuGetErrorString", GetErrorString) && load("cuDeviceGet", DeviceGet) &&
+             load("cuDeviceGetAttribute", DeviceGetAttribute) &&
+             load("cuMemGetAllocationGranularity", MemGetAllocationGranularity) &&
+             load("cuMemCreate", MemCreate) && load("cuMemRelease", MemRelease) &&
+             load("cuMemAddressReserve", MemAddressReserve) &&
+             load("cuMemAddressFree", MemAddressFree) && load("cuMemMap", MemMap) &&
+             load("cuMemUnmap", MemUnmap) && load("cuMemSetAccess", MemSetAccess) &&
+             load("cuMemExportToShareableHandle", MemExportToShareableHandle) &&
+             load("cuMemImportFromShareableHandle", MemImportFromShareableHandle);
+        multicast = ok && load("cuMulticastCreate", MulticastCreate) &&
+                    load("cuMulticastAddDevice", MulticastAddDevice) &&
+                    load("cuMulticastBindMem", MulticastBindMem) &&
+                    load("cuMulticastUnbind", MulticastUnbind) &&
+                    load("cuMulticastGetGranularity", MulticastGetGranularity);
+    }
+
+    std::string err(CUresult r) const
+    {
+        const char *s = nullptr;
+        if (GetErrorString != nullptr && GetErrorString(r, &s) == CUDA_SUCCESS && s != nullptr) {
+            return s;
+        }
+        return "CUresult " + std::to_string(static_cast<int>(r));
+    }
+};
+
+Driver &driver()
+{
+    static Driver d;
+    return d;
+}
+
+struct DrvError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+void drv_check(CUresult r, const char *what)
+{
+    if (r != CUDA_SUCCESS) {
+        throw DrvError(std::string("CUDA driver: ") + what + ": " + driver().err(r));
+    }
+}
+
+// First-fit free-list allocator over [base, base + size).  Deterministic, so
+// ranks that make the same calls get the same offsets.
+class OffsetHeap
+{
+    std::map<size_t, size_t> free_;  // offset -> length
+    std::map<size_t, size_t> used_;
+
+  public:
+    void reset(size_t base, size_t size)
+    {
+        free_.clear();
+        used_.clear();
+        if (size > 0) { free_[base] = size; }
+    }
+
+    size_t alloc(size_t bytes)
+    {
+        bytes = round_up(std::max<size_t>(bytes, 1), 256);
+        for (auto it = free_.begin(); it != free_.end(); ++it) {
+            if (it->second >= bytes) {
+                const size_t off = it->first;
+                const size_t rest = it->second - bytes;
+                free_.erase(it);
+                if (rest > 0) { free_[off + bytes] = rest; }
+                used_[off] = bytes;
+                return off;
+            }
+        }
+        throw std::bad_alloc();
+    }
+
+    void release(size_t off)
+    {
+        auto it = used_.find(off);
+        if (it == used_.end()) { throw std::invalid_argument("release: unknown arena offset"); }
+        size_t len = it->second;
+        used_.erase(it);
+        auto next = free_.lower_bound(off);
+        if (next != free_.end() && off + len == next->first) {
+            len += next->second;
+            next = free_.erase(next);
+        }
+        if (next != free_.begin()) {
+            auto prev = std::prev(next);
+            if (prev->first + prev->second == off) {
+                prev->second += len;
+                return;
+            }
+        }
+        free_[off] = len;
+    }
+};
+
+struct Mapping {
+    CUdeviceptr va = 0;
+    CUmemGenericAllocationHandle handle = 0;
+    bool mapped = false;
+    bool have_handle = false;
+};
+
+class World final : public DeviceWorld
+{
+    DeviceWorldOptions opt_;
+    int vranks_;
+    size_t arena_bytes_ = 0;
+    size_t staging_off_[2] = {0, 0};
+    unsigned long long staged_ops_ = 0;
+    OffsetHeap heap_;
+    std::string backend_;
+
+    std::vector<char *> base_;  // per rank
+    char *mc_base_ = nullptr;
+
+    // vmm state
+    std::vector<Mapping> maps_;
+    Mapping mc_map_;
+    bool mc_bound_ = false;
+    CUdevice cudev_ = 0;
+    // ipc / loopback state
+    std::vector<void *> owned_;   // cudaMalloc'd
+    std::vector<void *> opened_;  // cudaIpcOpenMemHandle'd
+
+    StatusBlock *status_host_ = nullptr;
+    StatusBlock *status_dev_ = nullptr;
+
+    std::unique_ptr<LocalRendezvous> rdv_;
+    int num_sms_ = 148;
+    int max_blocks_ = 64;
+    size_t oneshot_max_ = 256u << 10;
+    size_t nvls_oneshot_max_ = 128u << 10;
+    unsigned long long wait_timeout_ns_;
+
+  public:
+    explicit World(const DeviceWorldOptions &o)
+        : opt_(o), vranks_(o.loopback ? o.world : 1),
+          wait_timeout_ns_(o.wait_timeout_ms * 1000000ull)
+    {
+        if (o.world < 1 || o.world > kMaxRanks) {
+            throw std::invalid_argument("device world: world size must be in [1, " +
+                                        std::to_string(kMaxRanks) + "]");
+        }
+        if (!o.loopback && (o.rank < 0 || o.rank >= o.world)) {
+            throw std::invalid_argument("device world: bad rank");
+        }
+        rt_check(cudaSetDevice(o.device), "cudaSetDevice");
+        rt_check(cudaFree(nullptr), "context creation");
+        cudaDeviceProp prop;
+        rt_check(cudaGetDeviceProperties(&prop, o.device), "cudaGetDeviceProperties");
+        num_sms_ = prop.multiProcessorCount;
+        if (const char *e = std::getenv("STDML_COLLECTIVE_MAX_BLOCKS")) {
+            max_blocks_ = std::max(1, std::min(kMaxBlocks, std::atoi(e)));
+        }
+        if (const char *e = std::getenv("STDML_COLLECTIVE_ONESHOT_MAX_BYTES")) {
+            oneshot_max_ = static_cast<size_t>(std::atoll(e));
+        }
+        if (const char *e = std::getenv("STDML_COLLECTIVE_NVLS_ONESHOT_MAX_BYTES")) {
+            nvls_oneshot_max_ = static_cast<size_t>(std::atoll(e));
+        }
+
+        const size_t staging = round_up(std::max<size_t>(o.staging_bytes, 4096), 4096);
+        staging_off_[0] = kDataOffset;
+        staging_off_[1] = kDataOffset + staging;
+        const size_t heap_off = kDataOffset + 2 * staging;
+        arena_bytes_ = heap_off + round_up(o.heap_bytes, 4096);
+        opt_.staging_bytes = staging;
+
+        rt_check(cudaHostAlloc(reinterpret_cast<void **>(&status_host_), sizeof(StatusBlock),
+                               cudaHostAllocMapped),
+                 "cudaHostAlloc(status)");
+        std::memset(status_host_, 0, sizeof(StatusBlock));
+        rt_check(cudaHostGetDevicePointer(reinterpret_cast<void **>(&status_dev_), status_host_, 0),
+                 "cudaHostGetDevicePointer");
+
+        base_.assign(o.world, nullptr);
+        try {
+            if (o.loopback) {
+                setup_loopback();
+            } else {
+                if (o.world > 1) {
+                    rdv_ = std::make_unique<LocalRendezvous>(o.key, o.rank, o.world,
+                                                             o.setup_timeout_ms);
+                }
+                setup_real();
+            }
+        } catch (...) {
+            teardown();
+            throw;
+        }
+        heap_.reset(heap_off, arena_bytes_ - heap_off);
+    }
+
+    ~World() override { teardown(); }
+
+    // ------------------------------------------------------------ accessors
+    int rank() const override { return opt_.loopback ? 0 : opt_.rank; }
+    int world() const override { return opt_.world; }
+    int vranks() const override { return vranks_; }
+    int device() const override { return opt_.device; }
+    bool has_nvls() const override { return mc_base_ != nullptr; }
+    const char *backend() const override { return backend_.c_str(); }
+    size_t arena_bytes() const override { return arena_bytes_; }
+    size_t staging_bytes() const override { return opt_.staging_bytes; }
+
+    void *ptr(int r, size_t off) const override
+    {
+        if (r < 0 || r >= opt_.world || off > arena_bytes_) {
+            throw std::out_of_range("device world: ptr()");
+        }
+        return base_[r] + off;
+    }
+
+    void *mc_ptr(size_t off) const override
+    {
+        return mc_base_ == nullptr ? nullptr : mc_base_ + off;
+    }
+
+    size_t offset_of(const void *p, int vr) const override
+    {
+        const int r = opt_.loopback ? vr : opt_.rank;
+        const char *c = static_cast<const char *>(p);
+        if (c >= base_[r] && c < base_[r] + arena_bytes_) {
+            return static_cast<size_t>(c - base_[r]);
+        }
+        return SIZE_MAX;
+    }
+
+    size_t alloc(size_t bytes) override { return heap_.alloc(bytes); }
+    void release(size_t off) override { heap_.release(off); }
+
+    size_t next_staging_slot() override { return staging_off_[(staged_ops_++) & 1ull]; }
+
+    void set_wait_timeout_ms(unsigned long long ms) override { wait_timeout_ns_ = ms * 1000000ull; }
+
+    void set_tuning(int max_blocks, size_t oneshot_max_bytes,
+                    size_t nvls_oneshot_max_bytes) override
+    {
+        if (max_blocks > 0) { max_blocks_ = std::min(max_blocks, kMaxBlocks); }
+        if (oneshot_max_bytes != SIZE_MAX) { oneshot_max_ = oneshot_max_bytes; }
+        if (nvls_oneshot_max_bytes != SIZE_MAX) { nvls_oneshot_max_ = nvls_oneshot_max_bytes; }
+    }
+
+    // ------------------------------------------------------- algorithm table
+    int pick_algo(size_t bytes, int dt, int op, bool need_owner) const override
+    {
+        const bool nvls = has_nvls() && nvls_supported(dt, op);
+        if (opt_.world == 1) { return need_owner ? kAlgoTwoShot : kAlgoOneShot; }
+        if (nvls) {
+            if (!need_owner && bytes <= nvls_oneshot_max_) { return kAlgoNvlsOneShot; }
+            return kAlgoNvls;
+        }
+        if (!need_owner && bytes <= oneshot_max_) { return kAlgoOneShot; }
+        return kAlgoTwoShot;
+    }
+
+    int pick_blocks(size_t nvec, int algo) const override
+    {
+        const bool owner = (algo == kAlgoTwoShot || algo == kAlgoNvls);
+        const size_t work = owner ? (nvec + opt_.world - 1) / opt_.world : nvec;
+        const size_t per_block = static_cast<size_t>(kThreads) * 4;
+        size_t b = (work + per_block - 1) / per_block;
+        size_t cap = static_cast<size_t>(max_blocks_);
+        if (vranks_ > 1) { cap = std::min<size_t>(cap, std::max(1, num_sms_ / vranks_)); }
+        b = std::max<size_t>(1, std::min(b, cap));
+        return static_cast<int>(b);
+    }
+
+    // --------------------------------------------------------------- launches
+    CommCtx make_ctx() const
+    {
+        CommCtx ctx;
+        std::memset(&ctx, 0, sizeof(ctx));
+        for (int r = 0; r < opt_.world; ++r) { ctx.base[r] = base_[r]; }
+        ctx.mc_base = mc_base_;
+        ctx.status = status_dev_;
+        ctx.timeout_ns = wait_timeout_ns_;
+        ctx.max_spins = 1u << 30;
+        ctx.world = opt_.world;
+        ctx.rank = opt_.loopback ? 0 : opt_.rank;
+        return ctx;
+    }
+
+    int all_reduce(const AllReduceCall &c, void *stream) override
+    {
+        if (c.dt < 0 || c.dt > DT_F64_) { throw std::invalid_argument("all_reduce: bad dtype"); }
+        if (c.op < 0 || c.op > 4) { throw std::invalid_argument("all_reduce: bad op"); }
+        if (c.op == 4 && c.dt >= 8) {
+            throw std::invalid_argument("all_reduce: bit_xor is not defined for floating point");
+        }
+        if (c.count == 0) { return 0; }
+        static const size_t sizes[12] = {1, 2, 4, 8, 1, 2, 4, 8, 2, 2, 4, 8};
+        const size_t esize = sizes[c.dt];
+        const size_t bytes = c.count * esize;
+        const size_t nvec = (bytes + 15) / 16;
+        if (c.off % 16 != 0 || c.off < kDataOffset || c.off + nvec * 16 > arena_bytes_) {
+            throw std::invalid_argument("all_reduce: symmetric buffer outside the arena");
+        }
+        const int user_dt = c.user_dtype < 0 ? c.dt : c.user_dtype;
+        if (user_dt != c.dt && !((c.dt == 8 || c.dt == 9) && user_dt == 10)) {
+            throw std::invalid_argument(
+                "all_reduce: only f32 user tensors may differ from a bf16/f16 wire type");
+        }
+        bool any_dst_null = false;
+        for (int v = 0; v < vranks_; ++v) {
+            const bool has_dst = (c.table != nullptr && c.table[v] != nullptr) ||
+                                 (c.dst != nullptr && c.dst[v] != nullptr);
+            any_dst_null = any_dst_null || !has_dst;
+        }
+        int algo = c.algo;
+        if (algo < 0) { algo = pick_algo(bytes, c.dt, c.op, any_dst_null); }
+        const bool owner = (algo == kAlgoTwoShot || algo == kAlgoNvls);
+        const bool nvls = (algo == kAlgoNvls || algo == kAlgoNvlsOneShot);
+        if (!owner && any_dst_null && c.table == nullptr && c.root < 0) {
+            throw std::invalid_argument("all_reduce: one-shot algorithms need a destination");
+        }
+        if (nvls && (!has_nvls() || !nvls_supported(c.dt, c.op))) {
+            throw std::invalid_argument("all_reduce: NVLS not available for this dtype/op/world");
+        }
+        int blocks = c.blocks > 0 ? c.blocks : pick_blocks(nvec, algo);
+        if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
+        blocks = std::min(blocks, kMaxBlocks);
+
+        AllReduceArgs a;
+        std::memset(&a, 0, sizeof(a));
+        for (int v = 0; v < vranks_; ++v) {
+            a.src[v] = c.src != nullptr ? c.src[v] : nullptr;
+            a.dst[v] = c.dst != nullptr ? c.dst[v] : nullptr;
+            a.table[v] = c.table != nullptr ? c.table[v] : nullptr;
+        }
+        a.off = c.off;
+        a.count = c.count;
+        a.nvec = nvec;
+        a.ntable = c.ntable;
+        a.algo = algo;
+        a.user_dtype = user_dt;
+        a.end_barrier = c.end_barrier ? 1 : 0;
+        a.root = c.root;
+        a.has_scale = c.has_scale ? 1 : 0;
+        a.scale = c.scale;
+        const CommCtx ctx = make_ctx();
+        const int rc = launch_all_reduce(ctx, a, c.dt, c.op, blocks, vranks_, stream);
+        if (rc < 0) { throw std::invalid_argument("all_reduce: (dtype, op) not built"); }
+        return rc;
+    }
+
+    int gather(const GatherCall &c, void *stream) override
+    {
+        if (c.bytes == 0) { return 0; }
+        const size_t nvec = (c.bytes + 15) / 16;
+        if (c.off % 16 != 0 || c.off < kDataOffset || c.off + nvec * 16 > arena_bytes_) {
+            throw std::invalid_argument("gather: symmetric buffer outside the arena");
+        }
+        GatherArgs a;
+        std::memset(&a, 0, sizeof(a));
+        for (int v = 0; v < vranks_; ++v) {
+            a.src[v] = c.src != nullptr ? c.src[v] : nullptr;
+            a.dst[v] = c.dst != nullptr ? c.dst[v] : nullptr;
+        }
+        a.off = c.off;
+        a.bytes = c.bytes;
+        a.stride = c.stride != 0 ? c.stride : c.bytes;
+        a.root = c.root;
+        a.end_barrier = c.end_barrier ? 1 : 0;
+        int blocks = c.blocks > 0 ? c.blocks : pick_blocks(nvec, kAlgoOneShot);
+        if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
+        return launch_gather(make_ctx(), a, blocks, vranks_, stream);
+    }
+
+    int barrier(void *stream) override
+    {
+        launch_barrier(make_ctx(), vranks_, stream);
+        return static_cast<int>(cudaGetLastError());
+    }
+
+    int barrier_rows(int rows, void *stream) override
+    {
+        if (!opt_.loopback || rows < 1 || rows > vranks_) {
+            throw std::invalid_argument("barrier_rows: loopback world and 1 <= rows <= world");
+        }
+        launch_barrier(make_ctx(), rows, stream);
+        return static_cast<int>(cudaGetLastError());
+    }
+
+    DeviceStatus poll_status() const override
+    {
+        DeviceStatus s;
+        const volatile StatusBlock *v = status_host_;
+        s.code = v->code;
+        if (s.code != 0) {
+            s.rank = v->rank;
+            s.block = v->block;
+            s.peer = v->peer;
+            s.phase = v->phase;
+            s.want = v->want;
+            s.have = v->have;
+        }
+        return s;
+    }
+
+    void recover() override
+    {
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        if (rdv_) { rdv_->barrier(); }
+        if (opt_.loopback) {
+            for (int r = 0; r < opt_.world; ++r) {
+                rt_check(cudaMemset(base_[r], 0, kDataOffset), "cudaMemset(pad)");
+            }
+        } else {
+            rt_check(cudaMemset(base_[opt_.rank], 0, kDataOffset), "cudaMemset(pad)");
+        }
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        std::memset(status_host_, 0, sizeof(StatusBlock));
+        staged_ops_ = 0;
+        if (rdv_) { rdv_->barrier(); }
+    }
+
+  private:
+    static constexpr int DT_F64_ = 11;
+
+    void setup_loopback()
+    {
+        backend_ = "loopback";
+        for (int r = 0; r < opt_.world; ++r) {
+            void *p = nullptr;
+            rt_check(cudaMalloc(&p, arena_bytes_), "cudaMalloc(arena)");
+            owned_.push_back(p);
+            rt_check(cudaMemset(p, 0, kDataOffset), "cudaMemset(pad)");
+            base_[r] = static_cast<char *>(p);
+        }
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    }
+
+    void setup_real()
+    {
+        const bool want_vmm = opt_.backend == "auto" || opt_.backend == "vmm";
+        bool vmm_ok = false;
+        std::string why;
+        if (want_vmm) {
+            try {
+                vmm_ok = setup_vmm_local(why);
+            } catch (const std::exception &e) {
+                vmm_ok = false;
+                why = e.what();
+            }
+        }
+        // every rank must take the same path
+        if (rdv_) { vmm_ok = rdv_->all_agree(vmm_ok); }
+        if (vmm_ok) {
+            backend_ = "vmm";
+            exchange_vmm();
+            if (opt_.enable_nvls && opt_.world > 1) { setup_multicast(); }
+        } else {
+            if (opt_.backend == "vmm") {
+                throw std::runtime_error("device world: VMM backend unavailable: " + why);
+            }
+            release_vmm();
+            backend_ = "ipc";
+            setup_ipc();
+        }
+        if (rdv_) { rdv_->barrier(); }
+    }
+
+    // ------------------------------------------------------------------ VMM
+    CUmemAllocationProp alloc_prop() const
+    {
+        CUmemAllocationProp prop;
+        std::memset(&prop, 0, sizeof(prop));
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = opt_.device;
+        prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        return prop;
+    }
+
+    void map_rw(CUdeviceptr va, size_t size) const
+    {
+        CUmemAccessDesc acc;
+        std::memset(&acc, 0, sizeof(acc));
+        acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        acc.location.id = opt_.device;
+        acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        drv_check(driver().MemSetAccess(va, size, &acc, 1), "cuMemSetAccess");
+    }
+
+    bool multicast_capable() const
+    {
+        Driver &d = driver();
+        if (!d.multicast) { return false; }
+        int v = 0;
+        if (d.DeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, cudev_) !=
+            CUDA_SUCCESS) {
+            return false;
+        }
+        return v != 0;
+    }
+
+    bool setup_vmm_local(std::string &why)
+    {
+        Driver &d = driver();
+        if (!d.ok) {
+            why = "driver entry points missing";
+            return false;
+        }
+        drv_check(d.DeviceGet(&cudev_, opt_.device), "cuDeviceGet");
+        int fd_ok = 0;
+        drv_check(d.DeviceGetAttribute(
+                      &fd_ok, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED,
+                      cudev_),
+                  "cuDeviceGetAttribute");
+        if (!fd_ok) {
+            why = "POSIX fd handles unsupported";
+            return false;
+        }
+        const CUmemAllocationProp prop = alloc_prop();
+        size_t gran = 0;
+        drv_check(d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED),
+                  "cuMemGetAllocationGranularity");
+        size_t size = round_up(arena_bytes_, gran);
+        if (opt_.enable_nvls && opt_.world > 1 && multicast_capable()) {
+            CUmulticastObjectProp mp;
+            std::memset(&mp, 0, sizeof(mp));
+            mp.numDevices = static_cast<unsigned int>(opt_.world);
+            mp.size = size;
+            mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+            size_t mg = 0;
+            if (d.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) ==
+                    CUDA_SUCCESS &&
+                mg > 0) {
+                size = round_up(size, std::max(gran, mg));
+            }
+        }
+        arena_bytes_ = size;  // the heap grows into the rounding slack
+        maps_.assign(opt_.world, Mapping{});
+        Mapping &me = maps_[opt_.rank];
+        drv_check(d.MemCreate(&me.handle, size, &prop, 0), "cuMemCreate");
+        me.have_handle = true;
+        drv_check(d.MemAddressReserve(&me.va, size, gran, 0, 0), "cuMemAddressReserve");
+        drv_check(d.MemMap(me.va, size, 0, me.handle, 0), "cuMemMap");
+        me.mapped = true;
+        map_rw(me.va, size);
+        base_[opt_.rank] = reinterpret_cast<char *>(me.va);
+        rt_check(cudaMemset(base_[opt_.rank], 0, kDataOffset), "cudaMemset(pad)");
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        return true;
+    }
+
+    void exchange_vmm()
+    {
+        if (opt_.world == 1) { return; }
+        Driver &d = driver();
+        // sizes can differ only if devices differ; insist on one size
+        std::vector<std::vector<char>> sizes;
+        const unsigned long long mine = arena_bytes_;
+        rdv_->all_gather(&mine, sizeof(mine), sizes);
+        for (const auto &s : sizes) {
+            unsigned long long v;
+            std::memcpy(&v, s.data(), sizeof(v));
+            if (v != mine) { throw std::runtime_error("device world: arena sizes differ"); }
+        }
+        int my_fd = -1;
+        drv_check(d.MemExportToShareableHandle(&my_fd, maps_[opt_.rank].handle,
+                                               CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+                  "cuMemExportToShareableHandle");
+        std::vector<int> fds = rdv_->all_gather_fd(my_fd);
+        ::close(my_fd);
+        const CUmemAllocationProp prop = alloc_prop();
+        size_t gran = 0;
+        drv_check(d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED),
+                  "cuMemGetAllocationGranularity");
+        std::string first_error;
+        for (int p = 0; p < opt_.world; ++p) {
+            if (p == opt_.rank) { continue; }
+            Mapping &m = maps_[p];
+            try {
+                drv_check(d.MemImportFromShareableHandle(
+                              &m.handle, reinterpret_cast<void *>(static_cast<uintptr_t>(fds[p])),
+                              CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
+                          "cuMemImportFromShareableHandle");
+                m.have_handle = true;
+                drv_check(d.MemAddressReserve(&m.va, arena_bytes_, gran, 0, 0),
+                          "cuMemAddressReserve(peer)");
+                drv_check(d.MemMap(m.va, arena_bytes_, 0, m.handle, 0), "cuMemMap(peer)");
+                m.mapped = true;
+                map_rw(m.va, arena_bytes_);
+                base_[p] = reinterpret_cast<char *>(m.va);
+            } catch (const std::exception &e) {
+                if (first_error.empty()) { first_error = e.what(); }
+            }
+            ::close(fds[p]);
+        }
+        if (!rdv_->all_agree(first_error.empty())) {
+            throw std::runtime_error("device world: peer mapping failed: " +
+                                     (first_error.empty() ? std::string("on another rank")
+                                                          : first_error));
+        }
+    }
+
+    // Builds the NVLS multicast mapping.  Any failure, on any rank, leaves all
+    // ranks without it (peer loads still work); it never throws.
+    void setup_multicast()
+    {
+        Driver &d = driver();
+        bool ok = multicast_capable();
+        if (!rdv_->all_agree(ok)) { return; }
+        CUmulticastObjectProp mp;
+        std::memset(&mp, 0, sizeof(mp));
+        mp.numDevices = static_cast<unsigned int>(opt_.world);
+        mp.size = arena_bytes_;
+        mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        size_t mg = 0;
+        ok = d.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) ==
+                 CUDA_SUCCESS &&
+             mg > 0 && arena_bytes_ % mg == 0;
+
+        // rank 0 creates and exports; everybody else imports
+        int fd = -1;
+        if (opt_.rank == 0) {
+            if (ok) {
+                ok = d.MulticastCreate(&mc_map_.handle, &mp) == CUDA_SUCCESS;
+                mc_map_.have_handle = ok;
+            }
+            if (ok) {
+                ok = d.MemExportToShareableHandle(&fd, mc_map_.handle,
+                                                  CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR,
+                                                  0) == CUDA_SUCCESS;
+            }
+            const char flag = ok ? 1 : 0;
+            for (int p = 1; p < opt_.world; ++p) {
+                rdv_->send_bytes(p, &flag, 1);
+                if (ok) { rdv_->send_fd(p, fd); }
+            }
+            if (fd >= 0) { ::close(fd); }
+        } else {
+            char flag = 0;
+            rdv_->recv_bytes(0, &flag, 1);
+            if (flag) {
+                fd = rdv_->recv_fd(0);
+                if (ok) {
+                    ok = d.MemImportFromShareableHandle(
+                             &mc_map_.handle, reinterpret_cast<void *>(static_cast<uintptr_t>(fd)),
+                             CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) == CUDA_SUCCESS;
+                    mc_map_.have_handle = ok;
+                }
+                ::close(fd);
+            } else {
+                ok = false;
+            }
+        }
+        if (ok) { ok = d.MulticastAddDevice(mc_map_.handle, cudev_) == CUDA_SUCCESS; }
+        // every device must have been added before any memory is bound
+        if (!rdv_->all_agree(ok)) {
+            drop_multicast();
+            return;
+        }
+        ok = d.MulticastBindMem(mc_map_.handle, 0, maps_[opt_.rank].handle, 0, arena_bytes_, 0) ==
+             CUDA_SUCCESS;
+        mc_bound_ = ok;
+        if (ok) {
+            ok = d.MemAddressReserve(&mc_map_.va, arena_bytes_, mg, 0, 0) == CUDA_SUCCESS;
+        }
+        if (ok) {
+            ok = d.MemMap(mc_map_.va, arena_bytes_, 0, mc_map_.handle, 0) == CUDA_SUCCESS;
+            mc_map_.mapped = ok;
+        }
+        if (ok) {
+            try {
+                map_rw(mc_map_.va, arena_bytes_);
+            } catch (const std::exception &) {
+                ok = false;
+            }
+        }
+        if (!rdv_->all_agree(ok)) {
+            drop_multicast();
+            return;
+        }
+        mc_base_ = reinterpret_cast<char *>(mc_map_.va);
+    }
+
+    void drop_multicast()
+    {
+        Driver &d = driver();
+        mc_base_ = nullptr;
+        if (mc_map_.mapped) {
+            d.MemUnmap(mc_map_.va, arena_bytes_);
+            mc_map_.mapped = false;
+        }
+        if (mc_map_.va != 0) {
+            d.MemAddressFree(mc_map_.va, arena_bytes_);
+            mc_map_.va = 0;
+        }
+        if (mc_bound_) {
+            d.MulticastUnbind(mc_map_.handle, cudev_, 0, arena_bytes_);
+            mc_bound_ = false;
+        }
+        if (mc_map_.have_handle) {
+            d.MemRelease(mc_map_.handle);
+            mc_map_.have_handle = false;
+        }
+    }
+
+    void release_vmm()
+    {
+        Driver &d = driver();
+        if (!d.ok) { return; }
+        drop_multicast();
+        for (size_t p = 0; p < maps_.size(); ++p) {
+            Mapping &m = maps_[p];
+            if (m.mapped) { d.MemUnmap(m.va, arena_bytes_); }
+            if (m.va != 0) { d.MemAddressFree(m.va, arena_bytes_); }
+            if (m.have_handle) { d.MemRelease(m.handle); }
+            m = Mapping{};
+        }
+        maps_.clear();
+    }
+
+    // ------------------------------------------------------------------ IPC
+    void setup_ipc()
+    {
+        void *p = nullptr;
+        rt_check(cudaMalloc(&p, arena_bytes_), "cudaMalloc(arena)");
+        owned_.push_back(p);
+        rt_check(cudaMemset(p, 0, kDataOffset), "cudaMemset(pad)");
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        base_[opt_.rank] = static_cast<char *>(p);
+        if (opt_.world == 1) { return; }
+        cudaIpcMemHandle_t h;
+        rt_check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle");
+        std::vector<std::vector<char>> all;
+        rdv_->all_gather(&h, sizeof(h), all);
+        std::string first_error;
+        for (int r = 0; r < opt_.world; ++r) {
+            if (r == opt_.rank) { continue; }
+            cudaIpcMemHandle_t ph;
+            std::memcpy(&ph, all[r].data(), sizeof(ph));
+            void *q = nullptr;
+            const cudaError_t e = cudaIpcOpenMemHandle(&q, ph, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                (void)cudaGetLastError();
+                if (first_error.empty()) {
+                    first_error = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e);
+                }
+                continue;
+            }
+            opened_.push_back(q);
+            base_[r] = static_cast<char *>(q);
+        }
+        if (!rdv_->all_agree(first_error.empty())) {
+            throw std::runtime_error("device world: " + (first_error.empty()
+                                                             ? std::string("IPC failed on a peer")
+                                                             : first_error));
+        }
+    }
+
+    void teardown()
+    {
+        // Nothing of ours may be in flight when mappings go away.
+        (void)cudaSetDevice(opt_.device);
+        (void)cudaDeviceSynchronize();
+        if (rdv_) {
+            try {
+                rdv_->barrier();  // peers have stopped touching our memory
+            } catch (const std::exception &) {
+                // a peer is gone; carry on with local cleanup
+            }
+        }
+        release_vmm();
+        for (void *q : opened_) { (void)cudaIpcCloseMemHandle(q); }
+        opened_.clear();
+        for (void *p : owned_) { (void)cudaFree(p); }
+        owned_.clear();
+        if (status_host_ != nullptr) {
+            (void)cudaFreeHost(status_host_);
+            status_host_ = nullptr;
+        }
+        (void)cudaGetLastError();
+        rdv_.reset();
+    }
+};
+}  // namespace
+
+std::unique_ptr<DeviceWorld> DeviceWorld::create(const DeviceWorldOptions &opt)
+{
+    return std::make_unique<World>(opt);
+}
+
+int cuda_device_count()
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+bool cuda_available() { return cuda_device_count() > 0; }
+
+int pointer_kind(const void *p)
+{
+    if (p == nullptr || !cuda_available()) { return 0; }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) ? 1 : 0;
+}
+}  // namespace stdml::collective::cuda

@@ -1,0 +1,135 @@
+// DeviceWorld: the symmetric-memory manager and kernel launcher of the NVLink
+// data plane.  One per (process, GPU).  It owns
+//   * this rank's arena (signal pad + two staging slots + a symmetric heap),
+//     allocated with the CUDA VMM API and exported as a POSIX file descriptor
+//     (or, as a fallback, cudaMalloc + CUDA IPC handles),
+//   * the mappings of every peer's arena into this process,
+//   * the NVLS multicast object bound over all arenas (when the box has it),
+//   * a host-mapped status block that kernels write when a bounded wait runs out.
+// A "loopback" world hosts all ranks on one GPU in one process; its kernels run
+// as one cooperative launch with one grid row per virtual rank.  This is how
+// the kernels are tested on a single GPU.
+//
+// The reference keeps the equivalent state (mailbox, slotbox, client pool) in
+// `peer` (include/stdml/bits/collective/peer.hpp:26-32); it has no device
+// memory of any kind.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "comm.cuh"
+
+namespace stdml::collective::cuda
+{
+struct DeviceWorldOptions {
+    int rank = 0;
+    int world = 1;
+    int device = 0;
+    bool loopback = false;            // all ranks virtual, on `device`
+    size_t heap_bytes = 1ull << 30;   // symmetric heap for user buffers
+    size_t staging_bytes = 64ull << 20;  // each of the two staging slots
+    std::string key = "default";      // rendezvous key (same on all ranks)
+    std::string backend = "auto";     // auto | vmm | ipc
+    bool enable_nvls = true;
+    int setup_timeout_ms = 120000;
+    unsigned long long wait_timeout_ms = 20000;  // device-side bounded waits
+};
+
+struct DeviceStatus {
+    int code = 0;
+    int rank = 0, block = 0, peer = 0, phase = 0;
+    unsigned int want = 0, have = 0;
+};
+
+// What to run.  Pointers are per virtual rank: arrays of `vranks()` entries
+// (1 for a real world, `world` for a loopback world).
+struct AllReduceCall {
+    size_t off = 0;  // arena byte offset of the symmetric buffer
+    const void *const *src = nullptr;
+    void *const *dst = nullptr;
+    const GroupEntry *const *table = nullptr;  // device pointers, one per vrank
+    int ntable = 0;
+    size_t count = 0;  // elements; for a group: flat length in wire elements
+    int dt = 0;
+    int op = 0;
+    int user_dtype = -1;  // -1: same as dt
+    int algo = -1;        // -1: pick by size
+    int blocks = 0;       // 0: pick by size
+    int root = -1;
+    bool end_barrier = false;
+    bool has_scale = false;
+    float scale = 1.0f;
+};
+
+struct GatherCall {
+    size_t off = 0;
+    const void *const *src = nullptr;
+    void *const *dst = nullptr;
+    size_t bytes = 0;
+    size_t stride = 0;  // all_gather: distance between rank blocks in dst (0: bytes)
+    int root = -1;
+    int blocks = 0;
+    bool end_barrier = false;
+};
+
+class DeviceWorld
+{
+  public:
+    static std::unique_ptr<DeviceWorld> create(const DeviceWorldOptions &opt);
+    virtual ~DeviceWorld() = default;
+
+    virtual int rank() const = 0;
+    virtual int world() const = 0;
+    virtual int vranks() const = 0;
+    virtual int device() const = 0;
+    virtual bool has_nvls() const = 0;
+    virtual const char *backend() const = 0;
+    virtual size_t arena_bytes() const = 0;
+    virtual size_t staging_bytes() const = 0;
+
+    // Address of arena offset `off` of rank `r` as mapped here / of the
+    // multicast mapping (nullptr without NVLS).
+    virtual void *ptr(int r, size_t off) const = 0;
+    virtual void *mc_ptr(size_t off) const = 0;
+    // Offset of `p` inside the arena of virtual rank `vr`, or SIZE_MAX.
+    virtual size_t offset_of(const void *p, int vr = 0) const = 0;
+
+    // Symmetric heap: every rank must make the same calls in the same order.
+    // Returns an arena offset (256-byte aligned).  Throws std::bad_alloc.
+    virtual size_t alloc(size_t bytes) = 0;
+    virtual void release(size_t off) = 0;
+    // Staging slot for the next staged operation (alternates between two).
+    virtual size_t next_staging_slot() = 0;
+
+    virtual int pick_algo(size_t bytes, int dt, int op, bool need_owner) const = 0;
+    virtual int pick_blocks(size_t nvec, int algo) const = 0;
+
+    // Launches.  Return 0 or a cudaError_t; throw std::invalid_argument on
+    // arguments that the kernels could not run.
+    virtual int all_reduce(const AllReduceCall &c, void *stream) = 0;
+    virtual int gather(const GatherCall &c, void *stream) = 0;
+    virtual int barrier(void *stream) = 0;
+    // Loopback worlds only: launch the barrier for the first `rows` virtual
+    // ranks.  With rows < world the missing ranks never arrive, so the wait
+    // runs out and the status block reports it; this is how the bounded wait
+    // is exercised without any faulting code.
+    virtual int barrier_rows(int rows, void *stream) = 0;
+
+    // Bounded-wait status: poll_status() never blocks.
+    virtual DeviceStatus poll_status() const = 0;
+    // After a timeout: all ranks quiesce, clear their pads and meet again.
+    virtual void recover() = 0;
+    virtual void set_wait_timeout_ms(unsigned long long ms) = 0;
+    virtual void set_tuning(int max_blocks, size_t oneshot_max_bytes,
+                            size_t nvls_oneshot_max_bytes) = 0;
+};
+
+// true when a usable CUDA device is present (never throws)
+bool cuda_available();
+int cuda_device_count();
+// memory kind of a pointer: 0 host/unknown, 1 device
+int pointer_kind(const void *p);
+}  // namespace stdml::collective::cuda

@@ -1,0 +1,130 @@
+// Barrier, all_gather and broadcast kernels, and the (dtype, op) dispatcher of
+// the all-reduce kernels.
+//
+// all_gather replaces the reference's full-mesh exchange
+// (src/stdml/collective/all_gather.cpp:16-56); broadcast replaces the walk of
+// the broadcast graph from rank 0 (src/stdml/collective/session.cpp:49-62);
+// the barrier replaces all_reduce(uint32 1) (src/stdml/collective/session.cpp:130-134).
+#include "ar_kernel.cuh"
+
+namespace stdml::collective::cuda
+{
+int launch_all_reduce_f(const CommCtx &, const AllReduceArgs &, int, int, int, int, void *);
+int launch_all_reduce_i(const CommCtx &, const AllReduceArgs &, int, int, int, int, void *);
+int launch_all_reduce_u(const CommCtx &, const AllReduceArgs &, int, int, int, int, void *);
+
+int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op, int blocks,
+                      int vranks, void *stream)
+{
+    if (dt >= DT_BF16 && dt <= DT_F64) {
+        return launch_all_reduce_f(ctx, a, dt, op, blocks, vranks, stream);
+    }
+    if (dt >= DT_I8 && dt <= DT_I64) {
+        return launch_all_reduce_i(ctx, a, dt, op, blocks, vranks, stream);
+    }
+    if (dt >= DT_U8 && dt <= DT_U64) {
+        return launch_all_reduce_u(ctx, a, dt, op, blocks, vranks, stream);
+    }
+    return -1;
+}
+
+bool nvls_supported(int dt, int op)
+{
+    if (dt == DT_F32) { return op == OP_SUM; }
+    if (dt == DT_BF16 || dt == DT_F16) { return op == OP_SUM || op == OP_MIN || op == OP_MAX; }
+    return false;
+}
+
+__global__ void __launch_bounds__(kThreads) barrier_kernel(const __grid_constant__ CommCtx ctx)
+{
+    __shared__ BlockSync sync;
+    const int rank = ctx.rank + static_cast<int>(blockIdx.y);
+    sync_begin(ctx, rank, &sync);
+    if (!peer_barrier(ctx, rank, &sync)) { return; }
+    sync_end(ctx, rank, &sync);
+}
+
+void launch_barrier(const CommCtx &ctx, int vranks, void *stream)
+{
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (vranks > 1) {
+        void *params[1] = {const_cast<CommCtx *>(&ctx)};
+        cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(&barrier_kernel),
+                                    dim3(1, vranks, 1), dim3(kThreads), params, 0, s);
+        return;
+    }
+    barrier_kernel<<<1, kThreads, 0, s>>>(ctx);
+}
+
+// One block per rank of `bytes` bytes.  all_gather: every rank packs its block
+// into its arena slot, then pulls every peer's slot into dst + peer * bytes.
+// broadcast: only `root` packs, everybody pulls root's slot into dst.
+__global__ void __launch_bounds__(kThreads)
+    gather_kernel(const __grid_constant__ CommCtx ctx, const __grid_constant__ GatherArgs a)
+{
+    __shared__ BlockSync sync;
+    const int vr = static_cast<int>(blockIdx.y);
+    const int rank = ctx.rank + vr;
+    const int world = ctx.world;
+    const int nb = static_cast<int>(gridDim.x);
+    const int b = static_cast<int>(blockIdx.x);
+    sync_begin(ctx, rank, &sync);
+
+    const unsigned long long nvec = (a.bytes + 15ull) / 16ull;
+    const Span sp = span_of(nvec, 1, 0, nb, b);
+    char *mine = ctx.base[rank] + a.off;
+    const void *src = a.src[vr];
+    if (src != nullptr && (a.root < 0 || a.root == rank)) {
+        const bool al = ptr_aligned16(src);
+        for (unsigned long long v = sp.lo + threadIdx.x; v < sp.hi; v += kThreads) {
+            st_arena_v4(mine + v * 16ull, load_user_vec<DT_U8>(src, false, v, a.bytes, al));
+        }
+    }
+
+    if (!peer_barrier(ctx, rank, &sync)) { return; }
+
+    char *dst = static_cast<char *>(a.dst[vr]);
+    if (dst != nullptr) {
+        const int first = a.root < 0 ? 0 : a.root;
+        const int last = a.root < 0 ? world : a.root + 1;
+        for (int i = first; i < last; ++i) {
+            // start with the next rank so that peers do not all read the same GPU first
+            const int p = a.root < 0 ? (rank + 1 + i) % world : i;
+            char *out = a.root < 0 ? dst + static_cast<unsigned long long>(p) * a.stride : dst;
+            const char *from = ctx.base[p] + a.off;
+            const bool al = ptr_aligned16(out);
+            unsigned long long v = sp.lo + threadIdx.x;
+            for (; v + 3ull * kThreads < sp.hi; v += 4ull * kThreads) {
+                uint4 x[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { x[u] = ld_arena_v4(from + (v + u * kThreads) * 16ull); }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    store_user_vec<DT_U8>(out, false, v + u * kThreads, a.bytes, al, x[u]);
+                }
+            }
+            for (; v < sp.hi; v += kThreads) {
+                store_user_vec<DT_U8>(out, false, v, a.bytes, al, ld_arena_v4(from + v * 16ull));
+            }
+        }
+    }
+
+    if (a.end_barrier) {
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+    }
+    sync_end(ctx, rank, &sync);
+}
+
+int launch_gather(const CommCtx &ctx, const GatherArgs &a, int blocks, int vranks, void *stream)
+{
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    dim3 grid(blocks, vranks, 1);
+    if (vranks > 1) {
+        void *params[2] = {const_cast<CommCtx *>(&ctx), const_cast<GatherArgs *>(&a)};
+        return static_cast<int>(cudaLaunchCooperativeKernel(
+            reinterpret_cast<const void *>(&gather_kernel), grid, dim3(kThreads), params, 0, s));
+    }
+    gather_kernel<<<grid, kThreads, 0, s>>>(ctx, a);
+    return static_cast<int>(cudaGetLastError());
+}
+}  // namespace stdml::collective::cuda

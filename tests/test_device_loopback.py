@@ -1,0 +1,282 @@
+"""Device kernels on ONE GPU: all ranks are emulated as rows of one cooperative
+launch (a loopback world), results are compared bit for bit with the native
+host reducer (rank-ascending order, one rounding for 16-bit floats)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from stdml_collective_experimental_b200 import DeviceSession, DeviceTimeoutError  # noqa: E402
+from stdml_collective_experimental_b200.ops.device import (ALGO_ONESHOT,  # noqa: E402
+                                                           ALGO_TWOSHOT)
+from stdml_collective_experimental_b200.utils.oracle import reduce_many  # noqa: E402
+
+FLOATS = [torch.float32, torch.float64, torch.bfloat16, torch.float16]
+INTS = [torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8]
+
+
+def make_inputs(world, n, dtype, seed, small=False):
+    g = torch.Generator().manual_seed(seed)
+    outs = []
+    for r in range(world):
+        if dtype.is_floating_point:
+            x = torch.rand(n, generator=g) * 2 - 1
+            if small:
+                x = x * 0.5 + 1.0  # keeps products away from 0 and inf
+            outs.append(x.to(dtype))
+        else:
+            info = torch.iinfo(dtype)
+            lo, hi = max(info.min, -100), min(info.max, 100)
+            outs.append(torch.randint(lo, hi + 1, (n,), generator=g).to(dtype))
+    return outs
+
+
+@pytest.fixture(scope="module", params=[1, 2, 4, 8])
+def sess(request):
+    s = DeviceSession.loopback(request.param, heap_bytes=32 << 20, staging_bytes=1 << 20)
+    yield s
+    s.close()
+
+
+def same(a, b):
+    if a.dtype.is_floating_point:
+        return torch.equal(a.view(torch.uint8), b.view(torch.uint8)) or torch.equal(a, b)
+    return torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", FLOATS + INTS)
+@pytest.mark.parametrize("op", ["sum", "min", "max", "prod", "bit_xor"])
+def test_all_reduce_matrix(sess, dtype, op):
+    if op == "bit_xor" and dtype.is_floating_point:
+        with pytest.raises(ValueError):
+            x = [torch.zeros(4, dtype=dtype, device="cuda") for _ in range(sess.world)]
+            sess.all_reduce(x if sess.vranks > 1 else x[0], op=op)
+        return
+    for n in [1, 2, 3, 5, 7, 8, 9, 15, 16, 17, 31, 33, 100, 1024, 4099]:
+        host = make_inputs(sess.world, n, dtype, seed=n, small=(op == "prod"))
+        want = reduce_many(host, op)
+        dev = [h.cuda() for h in host]
+        out = [torch.empty_like(d) for d in dev]
+        arg = (dev, out) if sess.vranks > 1 else (dev[0], out[0])
+        sess.all_reduce(arg[0], out=arg[1], op=op)
+        torch.cuda.synchronize()
+        sess.check()
+        for r in range(sess.world):
+            assert same(out[r].cpu(), want), (dtype, op, n, r)
+            assert same(dev[r].cpu(), host[r]), "input was modified"
+        # in place
+        sess.all_reduce(arg[0], op=op)
+        torch.cuda.synchronize()
+        for r in range(sess.world):
+            assert same(dev[r].cpu(), want), (dtype, op, n, r, "in place")
+
+
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_all_reduce_large_chunked_and_scaled(sess, algo, dtype):
+    # 3 MiB+ of data through 1 MiB staging slots: several launches, alternating slots
+    n = (3 << 20) // torch.empty((), dtype=dtype).element_size() + 13
+    host = make_inputs(sess.world, n, dtype, seed=3)
+    scale = 1.0 / sess.world
+    want = reduce_many(host, "sum", scale)
+    dev = [h.cuda() for h in host]
+    arg = dev if sess.vranks > 1 else dev[0]
+    sess.all_reduce(arg, op="sum", scale=scale, algo=algo)
+    torch.cuda.synchronize()
+    sess.check()
+    for r in range(sess.world):
+        assert same(dev[r].cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+def test_symmetric_zero_copy_in_place(sess, dtype):
+    n = 70001
+    host = make_inputs(sess.world, n, dtype, seed=11)
+    want = reduce_many(host, "sum")
+    sym = sess.symm_empty(n, dtype)
+    syms = sym if sess.vranks > 1 else [sym]
+    for r in range(sess.world):
+        syms[r].copy_(host[r])
+    before = sess.launches
+    sess.all_reduce(sym)
+    torch.cuda.synchronize()
+    sess.check()
+    assert sess.launches == before + 1
+    for r in range(sess.world):
+        assert same(syms[r].cpu(), want)
+    sess.symm_free(sym)
+
+
+def test_raw_algorithms_agree(sess):
+    n = 50000
+    host = make_inputs(sess.world, n, torch.float32, seed=5)
+    want = reduce_many(host, "sum", 0.5)
+    sym = sess.symm_empty(n, torch.float32)
+    syms = sym if sess.vranks > 1 else [sym]
+    for blocks in (1, 3, 16):
+        src = [h.cuda() for h in host]
+        dst = [torch.empty(n, device="cuda") for _ in host]
+        a = (src, dst) if sess.vranks > 1 else (src[0], dst[0])
+        sess.raw_all_reduce(sym, src=a[0], dst=a[1], algo=ALGO_ONESHOT, blocks=blocks, scale=0.5)
+        torch.cuda.synchronize()
+        for r in range(sess.world):
+            assert same(dst[r].cpu(), want), ("oneshot", blocks)
+        dst2 = [torch.empty(n, device="cuda") for _ in host]
+        a = (src, dst2) if sess.vranks > 1 else (src[0], dst2[0])
+        sess.raw_all_reduce(sym, src=a[0], dst=a[1], algo=ALGO_TWOSHOT, blocks=blocks, scale=0.5)
+        torch.cuda.synchronize()
+        for r in range(sess.world):
+            assert same(dst2[r].cpu(), want), ("twoshot", blocks)
+            assert same(syms[r].cpu(), want), ("twoshot leaves the result in the arena", blocks)
+    sess.check()
+    sess.symm_free(sym)
+
+
+def _grad_set(world, sizes, dtype, seed):
+    return [[t for t in make_inputs(1, n, dtype, seed + 1000 * r + i)] for r in range(world)
+            for i, n in enumerate(sizes)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_group_all_reduce_fused(sess, dtype):
+    sizes = [1, 7, 768, 3, 2304, 590_000, 5, 64, 1000, 123_457, 2, 768]
+    g = torch.Generator().manual_seed(1)
+    host = [[(torch.rand(n, generator=g) * 2 - 1).to(dtype) for n in sizes]
+            for _ in range(sess.world)]
+    scale = 1.0 / sess.world
+    want = [reduce_many([host[r][i] for r in range(sess.world)], "sum", scale)
+            for i in range(len(sizes))]
+    dev = [[t.cuda() for t in host[r]] for r in range(sess.world)]
+    before = sess.launches
+    sess.group_all_reduce(dev if sess.vranks > 1 else dev[0], scale=scale)
+    torch.cuda.synchronize()
+    sess.check()
+    launches = sess.launches - before
+    total_bytes = sum((n * host[0][0].element_size() + 15) // 16 * 16 for n in sizes)
+    assert launches == -(-total_bytes // sess.staging_bytes), "one launch per staging slot"
+    for r in range(sess.world):
+        for i in range(len(sizes)):
+            assert same(dev[r][i].cpu(), want[i]), (r, i)
+    # second call hits the cached descriptor table
+    sess.group_all_reduce(dev if sess.vranks > 1 else dev[0])
+    torch.cuda.synchronize()
+    sess.check()
+
+
+def test_group_all_reduce_bf16_wire_for_f32_grads(sess):
+    sizes = [5, 4096, 33, 100_000]
+    g = torch.Generator().manual_seed(2)
+    host = [[torch.rand(n, generator=g) * 2 - 1 for n in sizes] for _ in range(sess.world)]
+    scale = 1.0 / sess.world
+    dev = [[t.cuda() for t in host[r]] for r in range(sess.world)]
+    sess.group_all_reduce(dev if sess.vranks > 1 else dev[0], scale=scale,
+                          wire_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    sess.check()
+    for i in range(len(sizes)):
+        want = reduce_many([host[r][i].to(torch.bfloat16) for r in range(sess.world)], "sum",
+                           scale).float()
+        for r in range(sess.world):
+            assert torch.equal(dev[r][i].cpu(), want), (r, i)
+
+
+def test_group_zero_copy_flat(sess):
+    sizes = [8, 100, 4, 50_000]  # every tensor a multiple of 16 bytes: back to back
+    flat = sess.symm_empty(sum(sizes), torch.float32)
+    flats = flat if sess.vranks > 1 else [flat]
+    g = torch.Generator().manual_seed(7)
+    host = [torch.rand(sum(sizes), generator=g) for _ in range(sess.world)]
+    for r in range(sess.world):
+        flats[r].copy_(host[r])
+    views = [list(torch.split(f, sizes)) for f in flats]
+    before = sess.launches
+    sess.group_all_reduce(views if sess.vranks > 1 else views[0], scale=0.25)
+    torch.cuda.synchronize()
+    sess.check()
+    assert sess.launches == before + 1
+    want = reduce_many(host, "sum", 0.25)
+    for r in range(sess.world):
+        assert same(flats[r].cpu(), want)
+    sess.symm_free(flat)
+
+
+@pytest.mark.parametrize("n", [1, 2, 10, 1000, 300_001])
+def test_all_gather(sess, n):
+    host = make_inputs(sess.world, n, torch.int32, seed=n)
+    dev = [h.cuda() for h in host]
+    out = [torch.empty(n * sess.world, dtype=torch.int32, device="cuda") for _ in dev]
+    a = (dev, out) if sess.vranks > 1 else (dev[0], out[0])
+    sess.all_gather(a[0], a[1])
+    torch.cuda.synchronize()
+    sess.check()
+    want = torch.cat(host)
+    for r in range(sess.world):
+        assert torch.equal(out[r].cpu(), want)
+
+
+def test_all_gather_odd_bytes(sess):
+    n = 37  # 37 bytes per rank: unaligned destinations
+    host = make_inputs(sess.world, n, torch.uint8, seed=9)
+    dev = [h.cuda() for h in host]
+    out = [torch.empty(n * sess.world, dtype=torch.uint8, device="cuda") for _ in dev]
+    a = (dev, out) if sess.vranks > 1 else (dev[0], out[0])
+    sess.all_gather(a[0], a[1])
+    torch.cuda.synchronize()
+    want = torch.cat(host)
+    for r in range(sess.world):
+        assert torch.equal(out[r].cpu(), want)
+
+
+@pytest.mark.parametrize("n", [1, 17, 300_001])
+def test_broadcast_and_reduce(sess, n):
+    host = make_inputs(sess.world, n, torch.float32, seed=n)
+    for root in sorted({0, sess.world - 1}):
+        dev = [h.cuda() for h in host]
+        out = [torch.empty_like(d) for d in dev]
+        a = (dev, out) if sess.vranks > 1 else (dev[0], out[0])
+        sess.broadcast(a[0], out=a[1], root=root)
+        torch.cuda.synchronize()
+        for r in range(sess.world):
+            assert torch.equal(out[r].cpu(), host[root])
+        red = [torch.full_like(d, -7.0) for d in dev]
+        a = (dev, red) if sess.vranks > 1 else (dev[0], red[0])
+        sess.reduce(a[0], out=a[1], op="sum", root=root)
+        torch.cuda.synchronize()
+        want = reduce_many(host, "sum")
+        for r in range(sess.world):
+            if r == root:
+                assert same(red[r].cpu(), want)
+            else:
+                assert torch.all(red[r] == -7.0)
+    sess.check()
+
+
+def test_barrier_and_launch_count(sess):
+    before = sess.launches
+    for _ in range(5):
+        sess.barrier()
+    torch.cuda.synchronize()
+    sess.check()
+    assert sess.launches == before + 5
+
+
+def test_bounded_wait_reports_and_recovers():
+    """A rank that never arrives: the wait runs out, the host reads a status, the
+    context stays usable, and after recover() collectives work again."""
+    s = DeviceSession.loopback(2, heap_bytes=1 << 20, staging_bytes=1 << 20, wait_timeout_ms=200)
+    try:
+        s.barrier_rows(1)  # rank 1 is not launched: nothing sets its flag
+        torch.cuda.synchronize()
+        code, rank, block, peer, phase, want, have = s.status()
+        assert code == 1 and rank == 0 and peer == 1 and want == have + 1
+        with pytest.raises(DeviceTimeoutError):
+            s.all_reduce([torch.ones(4, device="cuda"), torch.ones(4, device="cuda")])
+        s.recover()
+        assert s.status()[0] == 0
+        x = [torch.full((9,), 1.0, device="cuda"), torch.full((9,), 2.0, device="cuda")]
+        s.all_reduce(x)
+        torch.cuda.synchronize()
+        s.check()
+        assert torch.all(x[0] == 3.0) and torch.all(x[1] == 3.0)
+    finally:
+        s.close()
