@@ -1,0 +1,150 @@
+"""One rank of the multi-GPU device tests (launched by torchrun from
+test_device_multigpu.py, one process per GPU).  Every rank regenerates all
+ranks' inputs from seeds, so the expected result needs no communication."""
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from stdml_collective_experimental_b200 import DeviceSession  # noqa: E402
+from stdml_collective_experimental_b200.utils.oracle import reduce_many  # noqa: E402
+
+
+def inputs(world, n, dtype, seed, exact=False):
+    g = torch.Generator().manual_seed(seed)
+    outs = []
+    for _ in range(world):
+        if dtype.is_floating_point:
+            if exact:
+                x = torch.randint(-8, 9, (n,), generator=g).float()
+            else:
+                x = torch.rand(n, generator=g) * 2 - 1
+            outs.append(x.to(dtype))
+        else:
+            outs.append(torch.randint(-100, 101, (n,), generator=g).to(dtype))
+    return outs
+
+
+def bits_equal(a, b):
+    return torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    sess = DeviceSession.from_env(heap_bytes=256 << 20, staging_bytes=4 << 20,
+                                  wait_timeout_ms=20000)
+    assert sess.rank == rank and sess.world == world
+    info = f"backend={sess.backend} nvls={sess.has_nvls}"
+    algos = ["oneshot", "twoshot"] + (["nvls", "nvls_oneshot"] if sess.has_nvls else [])
+
+    # ---- all_reduce: dtype x op x size, default algorithm choice (staged path)
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int32,
+                  torch.int64, torch.uint8):
+        for op in ("sum", "min", "max", "prod"):
+            for n in (1, 7, 33, 4099, 300_001):
+                host = inputs(world, n, dtype, seed=n, exact=True)
+                if op == "prod":
+                    host = [(h.abs() % 2 + 1).to(dtype) for h in host]
+                want = reduce_many(host, op)
+                x = host[rank].cuda()
+                out = torch.empty_like(x)
+                sess.all_reduce(x, out=out, op=op)
+                torch.cuda.synchronize()
+                sess.check()
+                assert bits_equal(out.cpu(), want), (dtype, op, n)
+                sess.all_reduce(x, op=op)
+                torch.cuda.synchronize()
+                assert bits_equal(x.cpu(), want), (dtype, op, n, "in place")
+
+    # ---- every algorithm, random floats, with scale
+    for algo in algos:
+        for dtype in (torch.float32, torch.bfloat16):
+            for n in (5, 1000, 2_000_003):
+                host = inputs(world, n, dtype, seed=7 * n)
+                scale = 1.0 / world
+                want = reduce_many(host, "sum", scale)
+                x = host[rank].cuda()
+                sess.all_reduce(x, op="sum", scale=scale, algo=algo)
+                torch.cuda.synchronize()
+                sess.check()
+                got = x.cpu()
+                if algo.startswith("nvls"):
+                    tol = 1e-5 if dtype == torch.float32 else 2e-2
+                    assert torch.allclose(got.float(), want.float(), rtol=tol, atol=tol), (algo, n)
+                else:
+                    assert bits_equal(got, want), (algo, dtype, n)
+
+    # ---- zero-copy symmetric buffers, every owner algorithm
+    for algo in [a for a in algos if a in ("twoshot", "nvls")]:
+        n = 1_000_003
+        host = inputs(world, n, torch.float32, seed=99, exact=True)
+        want = reduce_many(host, "sum")
+        sym = sess.symm_empty(n, torch.float32)
+        sym.copy_(host[rank])
+        before = sess.launches
+        sess.all_reduce(sym, algo=algo)
+        torch.cuda.synchronize()
+        sess.check()
+        assert sess.launches == before + 1
+        assert bits_equal(sym.cpu(), want), algo
+        sess.symm_free(sym)
+
+    # ---- fused group, f32 and bf16-wire
+    sizes = [1, 7, 768, 3, 2304, 590_000, 5, 64, 1000, 1_234_567, 2, 768]
+    g = torch.Generator().manual_seed(1)
+    host = [[torch.rand(n, generator=g) * 2 - 1 for n in sizes] for _ in range(world)]
+    scale = 1.0 / world
+    for algo in algos:
+        dev = [t.cuda() for t in host[rank]]
+        sess.group_all_reduce(dev, scale=scale, algo=algo)
+        torch.cuda.synchronize()
+        sess.check()
+        for i in range(len(sizes)):
+            want = reduce_many([host[r][i] for r in range(world)], "sum", scale)
+            if algo.startswith("nvls"):
+                assert torch.allclose(dev[i].cpu(), want, rtol=1e-5, atol=1e-6), (algo, i)
+            else:
+                assert bits_equal(dev[i].cpu(), want), (algo, i)
+    dev = [t.cuda() for t in host[rank]]
+    sess.group_all_reduce(dev, scale=scale, wire_dtype=torch.bfloat16, algo="twoshot")
+    torch.cuda.synchronize()
+    for i in range(len(sizes)):
+        want = reduce_many([host[r][i].to(torch.bfloat16) for r in range(world)], "sum",
+                           scale).float()
+        assert torch.equal(dev[i].cpu(), want), i
+
+    # ---- all_gather / broadcast / reduce / barrier
+    for n in (1, 10, 37, 1_000_001):
+        host = inputs(world, n, torch.int32, seed=n)
+        out = torch.empty(n * world, dtype=torch.int32, device="cuda")
+        sess.all_gather(host[rank].cuda(), out)
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), torch.cat(host))
+        for root in sorted({0, world - 1}):
+            b = host[rank].cuda()
+            sess.broadcast(b, root=root)
+            torch.cuda.synchronize()
+            assert torch.equal(b.cpu(), host[root])
+            r_out = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+            sess.reduce(host[rank].cuda(), out=r_out, root=root)
+            torch.cuda.synchronize()
+            if rank == root:
+                assert torch.equal(r_out.cpu(), reduce_many(host, "sum"))
+            else:
+                assert torch.all(r_out == -7)
+    for _ in range(10):
+        sess.barrier()
+    torch.cuda.synchronize()
+    sess.check()
+    sess.close()
+    print(f"OK rank {rank}/{world} {info}", flush=True)
+
+
+if __name__ == "__main__":
+    main()
