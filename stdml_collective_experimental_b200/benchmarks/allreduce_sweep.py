@@ -89,7 +89,9 @@ def main():
         sess.check()
         rows.append(row)
         if rank == 0:
-            print(json.dumps(row), flush=True)
+            cells = " ".join(f"{k}={v['busbw']:.1f}/{v['us']:.0f}us" for k, v in row.items()
+                             if isinstance(v, dict))
+            print(f"{nbytes:>11d} B  {cells}", flush=True)
         nbytes *= 2
     if rank == 0 and args.out:
         with open(args.out, "w") as f:

@@ -1,0 +1,174 @@
+// Rendezvous tables keyed by (source peer, message name).
+//   mailbox : eager messages.  The network thread allocates, reads the body and
+//             queues it; the receiver may come later.
+//   slotbox : rendezvous messages.  The receiver posts its destination pointer
+//             and blocks; the network thread reads the body straight into it.
+// Counterpart of include/stdml/bits/collective/mailbox.hpp:15-62.  Unlike the
+// reference, a slot is a FIFO of any depth on both sides and a body whose
+// destination is not posted yet is parked in a temporary buffer, so a network
+// thread never blocks behind one unposted buffer while it holds other tensors'
+// messages (the head-of-line blocking that deadlocks the reference's
+// group_all_reduce when ranks submit tensors in different orders).
+#pragma once
+#include <condition_variable>
+#include <cstring>
+#include <deque>
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <utility>
+
+#include <stdml/bits/collective/address.hpp>
+#include <stdml/bits/collective/buffer.hpp>
+#include <stdml/bits/collective/channel.hpp>
+
+namespace stdml::collective
+{
+// One rendezvous point.  The receiver posts a destination (pointer + capacity);
+// the network thread delivers a message body with put().  If a destination is
+// already posted the body is read straight into it (zero-copy); if not, the
+// body is read into a temporary buffer and handed over when the receiver
+// arrives, so the network thread never waits for the receiver.  A body longer
+// than the posted capacity is rejected (the reference trusts the sender's
+// length, src/stdml/collective/send_recv.cpp:6-12).
+class slot
+{
+    struct ticket {
+        void *ptr = nullptr;
+        size_t cap = 0;
+        bool done = false;
+        bool ok = false;
+    };
+    std::mutex mu_;
+    std::condition_variable finished_;
+    std::deque<std::shared_ptr<ticket>> waiting_;
+    std::deque<buffer> early_;
+
+    static bool deliver(ticket &t, const buffer &b)
+    {
+        if (b.len > t.cap) { return false; }
+        if (b.len > 0) { std::memcpy(t.ptr, b.data.get(), b.len); }
+        return true;
+    }
+
+    std::shared_ptr<ticket> post_ticket(void *ptr, size_t cap)
+    {
+        auto t = std::make_shared<ticket>();
+        t->ptr = ptr;
+        t->cap = cap;
+        std::lock_guard<std::mutex> lk(mu_);
+        if (!early_.empty()) {
+            t->ok = deliver(*t, early_.front());
+            t->done = true;
+            early_.pop_front();
+        } else {
+            waiting_.push_back(t);
+        }
+        return t;
+    }
+
+  public:
+    // Blocks until a body has been written into ptr; false if it did not fit.
+    bool get(void *ptr, size_t cap)
+    {
+        auto t = post_ticket(ptr, cap);
+        std::unique_lock<std::mutex> lk(mu_);
+        finished_.wait(lk, [&] { return t->done; });
+        return t->ok;
+    }
+
+    // Posts now; the returned function waits for the body.
+    std::function<bool()> post(void *ptr, size_t cap)
+    {
+        auto t = post_ticket(ptr, cap);
+        return [this, t] {
+            std::unique_lock<std::mutex> lk(mu_);
+            finished_.wait(lk, [&] { return t->done; });
+            return t->ok;
+        };
+    }
+
+    // Posts now; the returned function tells, without blocking, whether the
+    // body has arrived (for the polled task runtime).
+    std::function<bool()> post_polled(void *ptr, size_t cap)
+    {
+        auto t = post_ticket(ptr, cap);
+        return [this, t] {
+            std::lock_guard<std::mutex> lk(mu_);
+            return t->done;
+        };
+    }
+
+    // Network side: `read_body(dst)` must read exactly `len` bytes into dst.
+    void put(size_t len, const std::function<bool(void *)> &read_body)
+    {
+        std::shared_ptr<ticket> t;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            if (!waiting_.empty()) {
+                t = waiting_.front();
+                waiting_.pop_front();
+            }
+        }
+        if (t && len <= t->cap) {
+            const bool ok = read_body(t->ptr);
+            std::lock_guard<std::mutex> lk(mu_);
+            t->ok = ok;
+            t->done = true;
+            finished_.notify_all();
+            return;
+        }
+        buffer b = alloc_buffer(len);
+        const bool ok = read_body(b.data.get());
+        std::lock_guard<std::mutex> lk(mu_);
+        if (t) {  // posted, but too small: drained above, report failure
+            t->ok = false;
+            t->done = true;
+            finished_.notify_all();
+            return;
+        }
+        if (!ok) { return; }
+        if (!waiting_.empty()) {
+            t = waiting_.front();
+            waiting_.pop_front();
+            t->ok = deliver(*t, b);
+            t->done = true;
+            finished_.notify_all();
+        } else {
+            early_.push_back(std::move(b));
+        }
+    }
+};
+
+template <typename Box>
+class basic_mailbox
+{
+    using key = std::pair<uint64_t, std::string>;
+    std::mutex mu_;
+    std::map<key, std::unique_ptr<Box>> boxes_;
+
+  public:
+    Box *require(const peer_id &src, const std::string &name)
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        auto &b = boxes_[key(src.hash(), name)];
+        if (!b) { b.reset(new Box); }
+        return b.get();
+    }
+
+    size_t size()
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        return boxes_.size();
+    }
+};
+
+struct eager_box : channel<buffer> {
+    eager_box() : channel<buffer>(1u << 16) {}
+};
+
+using mailbox = basic_mailbox<eager_box>;
+using slotbox = basic_mailbox<slot>;
+}  // namespace stdml::collective
