@@ -95,15 +95,15 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
         launch_ar(c, stream);
         return;
     }
-    const bool small = count * es <= 256u << 10;
-    if (symmetric && small && algo != kAlgoTwoShot && algo != kAlgoNvls) {
+    int zc_algo = algo < 0 ? world_->pick_algo(count * es, dt, op, false) : algo;
+    if (symmetric && (zc_algo == kAlgoOneShot || zc_algo == kAlgoNvlsOneShot)) {
         // read the symmetric input in place, write the user's output; the end
         // barrier keeps the input stable until every peer has read it
         c.off = off;
         c.count = count;
         c.dst = out;
         c.end_barrier = true;
-        if (c.algo < 0) { c.algo = world_->pick_algo(count * es, dt, op, false); }
+        c.algo = zc_algo;
         launch_ar(c, stream);
         return;
     }

@@ -199,9 +199,9 @@ class World final : public DeviceWorld
 
     std::unique_ptr<LocalRendezvous> rdv_;
     int num_sms_ = 148;
-    int max_blocks_ = 64;
-    size_t oneshot_max_ = 256u << 10;
-    size_t nvls_oneshot_max_ = 128u << 10;
+    int max_blocks_ = 128;
+    size_t oneshot_max_ = 0;       // 0: measured default for this world size
+    size_t nvls_oneshot_max_ = 0;  // 0: measured default for this world size
     unsigned long long wait_timeout_ns_;
 
   public:
@@ -314,15 +314,31 @@ class World final : public DeviceWorld
     }
 
     // ------------------------------------------------------- algorithm table
+    // Thresholds below come from device-timed sweeps on 2, 4 and 8 B200s (f32
+    // sum, 4 KB ... 1 GiB, this library's four algorithms against each other).
+    size_t oneshot_limit() const
+    {
+        if (oneshot_max_ != 0) { return oneshot_max_; }
+        const size_t w = static_cast<size_t>(opt_.world);
+        return w <= 2 ? (8u << 20) : (16u << 20) / (w * w);
+    }
+
+    size_t nvls_oneshot_limit() const
+    {
+        if (nvls_oneshot_max_ != 0) { return nvls_oneshot_max_; }
+        return opt_.world <= 4 ? (256u << 10) : (64u << 10);
+    }
+
     int pick_algo(size_t bytes, int dt, int op, bool need_owner) const override
     {
-        const bool nvls = has_nvls() && nvls_supported(dt, op);
         if (opt_.world == 1) { return need_owner ? kAlgoTwoShot : kAlgoOneShot; }
+        // with two GPUs the switch has nothing to add: peer loads are faster
+        const bool nvls = has_nvls() && nvls_supported(dt, op) && opt_.world > 2;
         if (nvls) {
-            if (!need_owner && bytes <= nvls_oneshot_max_) { return kAlgoNvlsOneShot; }
+            if (!need_owner && bytes <= nvls_oneshot_limit()) { return kAlgoNvlsOneShot; }
             return kAlgoNvls;
         }
-        if (!need_owner && bytes <= oneshot_max_) { return kAlgoOneShot; }
+        if (!need_owner && bytes <= oneshot_limit()) { return kAlgoOneShot; }
         return kAlgoTwoShot;
     }
 
@@ -333,8 +349,13 @@ class World final : public DeviceWorld
         const size_t per_block = static_cast<size_t>(kThreads) * 4;
         size_t b = (work + per_block - 1) / per_block;
         size_t cap = static_cast<size_t>(max_blocks_);
+        if (algo == kAlgoNvls || algo == kAlgoNvlsOneShot) {
+            // the switch saturates with few CTAs; more only add contention
+            cap = std::min<size_t>(cap, nvec * 16 >= (16u << 20) ? 32 : 64);
+        }
+        if (opt_.world == 1) { cap = std::max<size_t>(cap, 4 * static_cast<size_t>(num_sms_)); }
         if (vranks_ > 1) { cap = std::min<size_t>(cap, std::max(1, num_sms_ / vranks_)); }
-        b = std::max<size_t>(1, std::min(b, cap));
+        b = std::max<size_t>(1, std::min(b, std::min<size_t>(cap, kMaxBlocks)));
         return static_cast<int>(b);
     }
 
@@ -858,12 +879,15 @@ std::unique_ptr<DeviceWorld> DeviceWorld::create(const DeviceWorldOptions &opt)
 
 int cuda_device_count()
 {
-    int n = 0;
-    if (cudaGetDeviceCount(&n) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return 0;
-    }
-    return n;
+    static const int count = [] {
+        int n = 0;
+        if (cudaGetDeviceCount(&n) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        return n;
+    }();
+    return count;
 }
 
 bool cuda_available() { return cuda_device_count() > 0; }

@@ -182,4 +182,7 @@ void reduce(void *x, const void *y, const void *z, size_t count, dtype dt,
 // the device kernels and by the host one-shot path.
 void reduce_many(void *out, const void *const *in, size_t n, size_t count,
                  dtype dt, reduce_op op, double scale = 1.0);
+
+// x[i] *= float(scale) for floating-point dtypes; integers are left alone.
+void scale_in_place(void *x, size_t count, dtype dt, double scale);
 }  // namespace stdml::collective

@@ -1,0 +1,91 @@
+// peer: the identity and lifetime of one process in the job.  Owns the
+// mailbox / slotbox, the rchan server and the client pool; creates sessions.
+// Same surface as the reference (include/stdml/bits/collective/peer.hpp:16-73).
+#pragma once
+#include <cstddef>
+#include <functional>
+#include <memory>
+#include <optional>
+
+#include <stdml/bits/collective/address.hpp>
+#include <stdml/bits/collective/config.hpp>
+#include <stdml/bits/collective/elastic.hpp>
+#include <stdml/bits/collective/mailbox.hpp>
+#include <stdml/bits/collective/rchan.hpp>
+#include <stdml/bits/collective/session.hpp>
+
+namespace stdml::collective
+{
+class peer
+{
+    system_config config_;
+    size_t init_version_;
+    peer_id self_;
+    peer_list init_peers_;
+    peer_list init_runners_;
+    strategy init_strategy_;
+
+    std::unique_ptr<mailbox> mailbox_;
+    std::unique_ptr<slotbox> slotbox_;
+    std::unique_ptr<rchan::conn_handler> handler_;
+    // the client pool goes away before the server
+    std::unique_ptr<rchan::server> server_;
+    std::unique_ptr<rchan::client_pool> client_pool_;
+
+    peer(system_config config, size_t init_version, peer_id self, peer_list init_peers,
+         peer_list init_runners, strategy init_strategy = star);
+
+  public:
+    peer(peer &&) noexcept;
+    ~peer();
+
+    // one process, no network
+    static peer single();
+    // KUNGFU_SELF_SPEC, KUNGFU_INIT_PEERS, KUNGFU_INIT_RUNNERS,
+    // KUNGFU_INIT_CLUSTER_VERSION, KUNGFU_ALLREDUCE_STRATEGY
+    static peer from_kungfu_env();
+    // OMPI_COMM_WORLD_SIZE / OMPI_COMM_WORLD_RANK -> 127.0.0.1:10000+rank, star
+    static peer from_ompi_env();
+    // RANK / WORLD_SIZE (torchrun) -> 127.0.0.1:(STDML_COLLECTIVE_BASE_PORT or 10000)+rank
+    static peer from_torchrun_env();
+    // KungFu, then OpenMPI, then torchrun variables, else single()
+    static peer from_env();
+    static peer from_fork(size_t rank, size_t size);
+    // explicit membership
+    static peer from_list(size_t rank, peer_list peers, strategy s = star, size_t version = 0,
+                          peer_list runners = {});
+
+    const system_config &config() const { return config_; }
+    const peer_id &self() const { return self_; }
+    size_t init_version() const { return init_version_; }
+    strategy init_strategy() const { return init_strategy_; }
+    rchan::client_pool *clients() const { return client_pool_.get(); }
+
+    void start();
+    void stop();
+
+    session join();
+    std::unique_ptr<session> join_elastic();
+
+    using config_prodiver = std::function<std::optional<cluster_config>()>;
+    using config_provider = config_prodiver;
+    using config_committer = std::function<void(cluster_config, int)>;
+
+    // Agree with the current members on the configuration that `get_config`
+    // returns (polling until all see the same one), commit it, and replace
+    // `sess` by a session of the new membership.  Survivors keep their process
+    // and connections; `detached` tells a removed rank to leave.
+    resize_result resize(std::unique_ptr<session> &sess, const config_prodiver &get_config);
+    // configuration from the config server ($KUNGFU_CONFIG_SERVER)
+    resize_result resize(std::unique_ptr<session> &sess);
+    // propose `new_size` to the config server first
+    resize_result resize(std::unique_ptr<session> &sess, size_t new_size);
+    resize_result resize(std::unique_ptr<session> &sess, const config_prodiver &get_config,
+                         const config_committer &commit);
+};
+
+// fork n ranks on this host (ports 10000 + i), run g in each, wait for all
+void prun(int n, const std::function<void(session &)> &g);
+
+strategy parse_kungfu_startegy(const char *s);
+}  // namespace stdml::collective

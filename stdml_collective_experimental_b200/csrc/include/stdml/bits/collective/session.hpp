@@ -1,0 +1,194 @@
+// session: the collective front-end.  One session = one fixed membership
+// (version, rank, peers).  Construction is collective and ends with a barrier.
+//
+// Same calls as the reference (include/stdml/bits/collective/session.hpp:25-178)
+// -- all_reduce, group_all_reduce, all_gather, broadcast (root 0), send, recv,
+// consistent -- plus reduce / gather to root 0 (the reference only declares
+// them, include/stdml/bits/collective/algorithm.hpp:16-18) and a public
+// barrier.  Every call accepts host pointers (TCP path: star / ring graphs,
+// 1 MiB chunks) and CUDA device pointers (NVLink path: fused sm_100a kernels;
+// all ranks on one box, one GPU per rank); the two kinds are told apart by
+// asking the CUDA runtime.  Device calls are enqueued on `stream` (the legacy
+// default stream when null) and return without waiting for the GPU.
+//
+// Messages are matched by (source peer, name): concurrent operations between
+// the same peers need distinct names, operations with one name are FIFO.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <future>
+#include <iterator>
+#include <memory>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include <stdml/bits/collective/address.hpp>
+#include <stdml/bits/collective/buffer.hpp>
+#include <stdml/bits/collective/config.hpp>
+#include <stdml/bits/collective/dtype.hpp>
+#include <stdml/bits/collective/mailbox.hpp>
+#include <stdml/bits/collective/rchan.hpp>
+#include <stdml/bits/collective/task.hpp>
+#include <stdml/bits/collective/thread_pool.hpp>
+#include <stdml/bits/collective/topology.hpp>
+
+namespace stdml::collective
+{
+namespace cuda
+{
+class DeviceSession;
+}
+
+class session
+{
+    std::unique_ptr<sync::thread_pool> pool_;
+    std::unique_ptr<runtime> async_runtime_;
+    std::unique_ptr<cuda::DeviceSession> device_;
+    bool device_tried_ = false;
+
+    const system_config config_;
+    const size_t version_;
+    const size_t rank_;
+    const peer_list peers_;
+    const peer_list runners_;
+    const strategy strategy_;
+
+    graph_pair_list all_reduce_topo_;
+
+    void run_chunk(const workspace &w, const graph *reduce_g, const graph *bcast_g);
+    task *chunk_task(const workspace &w, const graph *reduce_g, const graph *bcast_g);
+    cuda::DeviceSession *device();  // collective on first use
+    bool on_device(const void *a, const void *b) const;
+
+  public:
+    static constexpr size_t chunk_bytes = 1u << 20;
+
+    mailbox *mailbox_;                 // owned by peer
+    slotbox *slotbox_;                 // owned by peer
+    rchan::client_pool *client_pool_;  // owned by peer
+
+    session(system_config config, size_t version, size_t rank, peer_list peers, peer_list runners,
+            mailbox *mailbox, slotbox *slotbox, rchan::client_pool *client_pool,
+            strategy s = star);
+    ~session();
+
+    session(const session &) = delete;
+    session(session &&) noexcept;
+
+    size_t rank() const { return rank_; }
+    size_t size() const { return peers_.size(); }
+    const peer_list &peers() const { return peers_; }
+    const peer_list &runners() const { return runners_; }
+    sync::thread_pool *pool() const { return pool_.get(); }
+    runtime *async_rt() const { return async_runtime_.get(); }
+    cluster_config cluster() const { return cluster_config(runners_, peers_); }
+    size_t version() const { return version_; }
+    strategy get_strategy() const { return strategy_; }
+    const system_config &config() const { return config_; }
+
+    void barrier();
+
+    void all_reduce(const workspace &w, void *stream = nullptr);
+    // Blocks until every tensor is reduced.  Tensors may become ready in any
+    // order and in different orders on different ranks.
+    void group_all_reduce(std::vector<std::future<workspace>> ws);
+    // Same for tensors that are ready now; on device pointers this is ONE fused
+    // launch per staging slot, with `scale` applied in the kernel.
+    void group_all_reduce(const std::vector<workspace> &ws, double scale = 1.0,
+                          void *stream = nullptr);
+
+    void all_reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
+                    std::string name = "", void *stream = nullptr);
+    void reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
+                std::string name = "", void *stream = nullptr);
+    void all_gather(const void *input, void *output, size_t count, dtype dt,
+                    std::string name = "", void *stream = nullptr);
+    void gather(const void *input, void *output, size_t count, dtype dt, std::string name = "");
+    void broadcast(const void *input, void *output, size_t count, dtype dt,
+                   std::string name = "", void *stream = nullptr);
+    void recv(void *output, size_t count, dtype dt, size_t target, std::string name = "");
+    void send(const void *input, size_t count, dtype dt, size_t target, std::string name = "");
+
+    bool consistent(const void *ptr, size_t size);
+
+    // ------------------------------------------------------- typed overloads
+    template <typename R>
+    void all_reduce(const R *in, R *out, const size_t count, const std::string &name = "")
+    {
+        all_reduce(in, out, count, type<R>(), sum, name);
+    }
+
+    template <typename R>
+    void all_reduce(const R *in, R *out, const size_t count, reduce_op op,
+                    const std::string &name = "")
+    {
+        all_reduce(in, out, count, type<R>(), op, name);
+    }
+
+    template <typename R>
+    void all_reduce(const R *begin1, const R *end1, R *begin2)
+    {
+        all_reduce(begin1, begin2, static_cast<size_t>(std::distance(begin1, end1)), type<R>(),
+                   sum, "");
+    }
+
+    template <typename R>
+    void all_reduce(const R *begin1, const R *end1, R *begin2, const std::string &name)
+    {
+        all_reduce(begin1, begin2, static_cast<size_t>(std::distance(begin1, end1)), type<R>(),
+                   sum, name);
+    }
+
+    template <typename R>
+    void all_reduce(const R *begin1, const R *end1, R *begin2, reduce_op op,
+                    const std::string &name = "")
+    {
+        all_reduce(begin1, begin2, static_cast<size_t>(std::distance(begin1, end1)), type<R>(),
+                   op, name);
+    }
+
+    template <typename T>
+    T all_reduce(const T &x, reduce_op op = sum)
+    {
+        T y;
+        all_reduce(&x, &y, 1, type<T>(), op, "");
+        return y;
+    }
+
+    template <typename R>
+    void all_gather(const R *input, R *output, const size_t count, const std::string &name = "")
+    {
+        all_gather(input, output, count, type<R>(), name);
+    }
+
+    template <typename T>
+    bool consistent(const T &x)
+    {
+        return consistent(&x, sizeof(T));
+    }
+
+    template <typename R>
+    void broadcast(const R *begin1, const R *end1, R *begin2)
+    {
+        broadcast(begin1, begin2, static_cast<size_t>(std::distance(begin1, end1)), type<R>());
+    }
+
+    template <typename T>
+    T broadcast(const T &x)
+    {
+        T y;
+        broadcast(reinterpret_cast<const int8_t *>(&x), reinterpret_cast<int8_t *>(&y), sizeof(T),
+                  i8);
+        return y;
+    }
+};
+
+// Which graph pair (ring root) serves a chunk: sum of squared character codes
+// of its name, as the reference hashes it (src/stdml/collective/session.cpp:142-149),
+// so both implementations spread chunks over roots identically.
+size_t name_based_hash(const std::string &name);
+
+std::vector<std::pair<workspace, std::pair<const graph *, const graph *>>>
+split_work(const workspace &w, const graph_pair_list &gps, size_t chunk_size);
+}  // namespace stdml::collective

@@ -334,6 +334,33 @@ void reduce(void *x, const void *y, const void *z, size_t count, dtype dt,
 #undef STDML_CASE_INT
 }
 
+void scale_in_place(void *x, size_t count, dtype dt, double scale)
+{
+    const float s = static_cast<float>(scale);
+    switch (dt) {
+    case f32:
+        for (size_t i = 0; i < count; ++i) { static_cast<float *>(x)[i] *= s; }
+        return;
+    case f64:
+        for (size_t i = 0; i < count; ++i) { static_cast<double *>(x)[i] *= static_cast<double>(s); }
+        return;
+    case bf16:
+        for (size_t i = 0; i < count; ++i) {
+            uint16_t &v = static_cast<uint16_t *>(x)[i];
+            v = float_to_bf16(bf16_to_float(v) * s);
+        }
+        return;
+    case f16:
+        for (size_t i = 0; i < count; ++i) {
+            uint16_t &v = static_cast<uint16_t *>(x)[i];
+            v = float_to_f16(f16_to_float(v) * s);
+        }
+        return;
+    default:
+        return;  // integers are not scaled (same as the device kernels)
+    }
+}
+
 void reduce_many(void *out, const void *const *in, size_t n, size_t count,
                  dtype dt, reduce_op op, double scale)
 {

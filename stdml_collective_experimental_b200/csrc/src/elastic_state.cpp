@@ -1,0 +1,60 @@
+#include <stdml/bits/collective/elastic_state.hpp>
+#include <stdml/bits/collective/log.hpp>
+
+namespace stdml::collective
+{
+elastic_state::elastic_state(peer::config_prodiver get_config, std::optional<int64_t> max_progress)
+    : peer_(peer::from_env()), sess_(peer_.join_elastic()), max_progress_(max_progress),
+      get_config_(std::move(get_config))
+{
+}
+
+elastic_state::elastic_state(std::optional<int64_t> max_progress)
+    : elastic_state([] { return get_cluster_config(); }, max_progress)
+{
+}
+
+void elastic_state::sync()
+{
+    if (!synced_) {
+        progress_ = sess_->all_reduce(progress_, max);
+        synced_ = true;
+    }
+}
+
+void elastic_state::check_resize()
+{
+    const resize_result r = peer_.resize(sess_, get_config_);
+    if (r.detached) {
+        detached_ = true;
+        return;
+    }
+    if (r.changed) {
+        synced_ = false;
+        sync();
+        if (on_resize_) { on_resize_(*sess_); }
+    }
+}
+
+elastic_state::operator int64_t()
+{
+    sync();
+    return progress_;
+}
+
+void elastic_state::operator++()
+{
+    sync();
+    ++progress_;
+    check_resize();
+}
+
+bool elastic_state::should_stop()
+{
+    if (detached_) { return true; }
+    sync();
+    return max_progress_.has_value() && progress_ >= *max_progress_;
+}
+
+session &elastic_state::sess() { return *sess_; }
+}  // namespace stdml::collective

@@ -1,0 +1,293 @@
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+#include <thread>
+
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <stdml/bits/collective/affinity.hpp>
+#include <stdml/bits/collective/log.hpp>
+#include <stdml/bits/collective/peer.hpp>
+
+namespace stdml::collective
+{
+namespace
+{
+// Routes messages of collective connections into the mailbox (eager) or the
+// slotbox (rendezvous, flag wait_recv_buf); other connection types are drained.
+class collective_msg_handler final : public rchan::msg_handler
+{
+    mailbox *mailbox_;
+    slotbox *slotbox_;
+
+  public:
+    collective_msg_handler(mailbox *mb, slotbox *sb) : mailbox_(mb), slotbox_(sb) {}
+
+    bool operator()(const rchan::received_header &mh, rchan::message_reader *reader,
+                    const peer_id &src) override
+    {
+        if (mh.flags & rchan::message_header::wait_recv_buf) {
+            bool ok = true;
+            slotbox_->require(src, mh.name)->put(mh.len, [&](void *dst) {
+                ok = reader->read_body(dst);
+                return ok;
+            });
+            return ok;
+        }
+        buffer b = alloc_buffer(mh.len);
+        if (!reader->read_body(b.data.get())) { return false; }
+        mailbox_->require(src, mh.name)->put(std::move(b));
+        return true;
+    }
+};
+
+class drain_handler final : public rchan::msg_handler
+{
+  public:
+    bool operator()(const rchan::received_header &mh, rchan::message_reader *reader,
+                    const peer_id &) override
+    {
+        buffer b = alloc_buffer(mh.len);
+        return reader->read_body(b.data.get());
+    }
+};
+
+class peer_conn_handler final : public rchan::conn_handler
+{
+    collective_msg_handler collective_;
+    drain_handler drain_;
+
+  public:
+    peer_conn_handler(mailbox *mb, slotbox *sb) : collective_(mb, sb) {}
+
+    size_t operator()(std::unique_ptr<rchan::connection> conn) override
+    {
+        switch (conn->type()) {
+        case rchan::conn_collective:
+        case rchan::conn_peer_to_peer:
+        case rchan::conn_send:
+        case rchan::conn_recv:
+        case rchan::conn_mpi:
+            return handle_to_end(conn.get(), &collective_);
+        default:
+            return handle_to_end(conn.get(), &drain_);
+        }
+    }
+};
+}  // namespace
+
+strategy parse_kungfu_startegy(const char *s)
+{
+    // an unset variable means star (the reference dereferences a null pointer here)
+    if (s == nullptr) { return star; }
+    std::string v(s);
+    for (auto &c : v) { c = static_cast<char>(std::toupper(static_cast<unsigned char>(c))); }
+    return v == "RING" ? ring : star;
+}
+
+peer::peer(system_config config, size_t init_version, peer_id self, peer_list init_peers,
+           peer_list init_runners, strategy init_strategy)
+    : config_(std::move(config)), init_version_(init_version), self_(self),
+      init_peers_(std::move(init_peers)), init_runners_(std::move(init_runners)),
+      init_strategy_(init_strategy), mailbox_(new mailbox), slotbox_(new slotbox),
+      handler_(new peer_conn_handler(mailbox_.get(), slotbox_.get())),
+      client_pool_(new rchan::client_pool(self))
+{
+}
+
+peer::peer(peer &&) noexcept = default;
+
+peer::~peer() { stop(); }
+
+peer peer::single()
+{
+    const peer_list ps = peer_list::gen(1);
+    return peer(parse_system_config_from_env(), 0, ps[0], ps, {});
+}
+
+peer peer::from_list(size_t rank, peer_list peers, strategy s, size_t version, peer_list runners)
+{
+    if (rank >= peers.size()) { throw std::invalid_argument("peer: rank outside the peer list"); }
+    const peer_id self = peers[rank];
+    peer p(parse_system_config_from_env(), version, self, std::move(peers), std::move(runners), s);
+    p.start();
+    return p;
+}
+
+peer peer::from_kungfu_env()
+{
+    const auto self = parse_peer_id(safe_getenv("KUNGFU_SELF_SPEC"));
+    const auto peers = parse_peer_list(safe_getenv("KUNGFU_INIT_PEERS"));
+    const auto runners = parse_peer_list(safe_getenv("KUNGFU_INIT_RUNNERS"));
+    if (!self || !peers || !runners) { return single(); }
+    if (!peers->contains(*self)) {
+        throw std::runtime_error("KUNGFU_SELF_SPEC " + self->str() +
+                                 " is not listed in KUNGFU_INIT_PEERS");
+    }
+    const size_t version =
+        static_cast<size_t>(parse_env_int("KUNGFU_INIT_CLUSTER_VERSION").value_or(0));
+    peer p(parse_system_config_from_env(), version, *self, *peers, *runners,
+           parse_kungfu_startegy(std::getenv("KUNGFU_ALLREDUCE_STRATEGY")));
+    p.start();
+    return p;
+}
+
+peer peer::from_ompi_env()
+{
+    const auto size = parse_env_int("OMPI_COMM_WORLD_SIZE");
+    const auto rank = parse_env_int("OMPI_COMM_WORLD_RANK");
+    if (!size || !rank || *size <= 0 || *rank < 0 || *rank >= *size) { return single(); }
+    return from_fork(static_cast<size_t>(*rank), static_cast<size_t>(*size));
+}
+
+peer peer::from_torchrun_env()
+{
+    const auto size = parse_env_int("WORLD_SIZE");
+    const auto rank = parse_env_int("RANK");
+    if (!size || !rank || *size <= 0 || *rank < 0 || *rank >= *size) { return single(); }
+    const uint16_t base =
+        static_cast<uint16_t>(parse_env_int("STDML_COLLECTIVE_BASE_PORT").value_or(10000));
+    peer_list ps;
+    for (int64_t i = 0; i < *size; ++i) {
+        ps.push_back(peer_id{(127u << 24) | 1u, static_cast<uint16_t>(base + i)});
+    }
+    return from_list(static_cast<size_t>(*rank), ps,
+                     parse_kungfu_startegy(std::getenv("KUNGFU_ALLREDUCE_STRATEGY")));
+}
+
+peer peer::from_env()
+{
+    if (std::getenv("KUNGFU_SELF_SPEC") != nullptr) { return from_kungfu_env(); }
+    if (std::getenv("OMPI_COMM_WORLD_SIZE") != nullptr) { return from_ompi_env(); }
+    if (std::getenv("WORLD_SIZE") != nullptr && std::getenv("RANK") != nullptr) {
+        return from_torchrun_env();
+    }
+    return single();
+}
+
+peer peer::from_fork(size_t rank, size_t size)
+{
+    return from_list(rank, peer_list::gen(size),
+                     parse_kungfu_startegy(std::getenv("KUNGFU_ALLREDUCE_STRATEGY")));
+}
+
+void peer::start()
+{
+    if (!server_) {
+        server_ = rchan::server::New(self_, handler_.get());
+        server_->start();
+    }
+}
+
+void peer::stop()
+{
+    client_pool_.reset();
+    if (server_) {
+        server_->stop();
+        server_.reset();
+    }
+}
+
+session peer::join()
+{
+    if (!client_pool_) { client_pool_.reset(new rchan::client_pool(self_)); }
+    const size_t rank = init_peers_.rank(self_);
+    session s(config_, init_version_, rank, init_peers_, init_runners_, mailbox_.get(),
+              slotbox_.get(), client_pool_.get(), init_strategy_);
+    if (config_.use_affinity) { set_affinity(rank, init_peers_.size()); }
+    return s;
+}
+
+std::unique_ptr<session> peer::join_elastic()
+{
+    if (!client_pool_) { client_pool_.reset(new rchan::client_pool(self_)); }
+    const size_t rank = init_peers_.rank(self_);
+    return std::make_unique<session>(config_, init_version_, rank, init_peers_, init_runners_,
+                                     mailbox_.get(), slotbox_.get(), client_pool_.get(),
+                                     init_strategy_);
+}
+
+resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver &get_config,
+                           const config_committer &commit)
+{
+    using namespace std::chrono_literals;
+    std::optional<cluster_config> next;
+    for (int attempt = 0;; ++attempt) {
+        next = get_config();
+        // the proposal may reach ranks at different times: go on only when
+        // every current member has read the same configuration
+        const std::vector<std::byte> bytes = next ? next->bytes() : std::vector<std::byte>();
+        if (sess->consistent(bytes.data(), bytes.size())) { break; }
+        log() << "resize: members disagree on the new configuration, retrying";
+        std::this_thread::sleep_for(attempt < 20 ? 50ms : 1000ms);
+    }
+    if (!next || *next == sess->cluster()) { return {false, false}; }
+    const size_t new_version = sess->version() + 1;
+    const bool detached = !next->workers.contains(self_);
+    commit(*next, static_cast<int>(new_version));
+    if (detached) { return {true, true}; }
+    const peer_list removed = sess->peers() - next->workers;
+    const strategy s = sess->get_strategy();
+    sess.reset();  // releases device mappings of the old membership first
+    client_pool_->reset_peers(removed);
+    init_peers_ = next->workers;
+    init_runners_ = next->runners;
+    init_version_ = new_version;
+    // the constructor's barrier admits the joiners (they dial until we answer)
+    sess = std::make_unique<session>(config_, new_version, next->workers.rank(self_),
+                                     next->workers, next->runners, mailbox_.get(),
+                                     slotbox_.get(), client_pool_.get(), s);
+    return {true, false};
+}
+
+resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver &get_config)
+{
+    return resize(sess, get_config, [](cluster_config c, int v) {
+        commit_cluster_config(c, static_cast<size_t>(v));
+    });
+}
+
+resize_result peer::resize(std::unique_ptr<session> &sess)
+{
+    return resize(sess, [] { return get_cluster_config(); });
+}
+
+resize_result peer::resize(std::unique_ptr<session> &sess, size_t new_size)
+{
+    // one proposer is enough; everyone then converges on the server's answer
+    if (sess->rank() == 0) { propose_new_size(sess->cluster(), new_size); }
+    return resize(sess);
+}
+
+void prun(int n, const std::function<void(session &)> &g)
+{
+    std::vector<pid_t> kids;
+    for (int i = 0; i < n; ++i) {
+        const pid_t pid = ::fork();
+        if (pid < 0) { throw std::runtime_error("prun: fork failed"); }
+        if (pid == 0) {
+            int rc = 0;
+            try {
+                peer p = peer::from_fork(static_cast<size_t>(i), static_cast<size_t>(n));
+                session s = p.join();
+                g(s);
+            } catch (const std::exception &e) {
+                std::fprintf(stderr, "prun: rank %d failed: %s\n", i, e.what());
+                rc = 1;
+            }
+            std::fflush(nullptr);
+            ::_exit(rc);
+        }
+        kids.push_back(pid);
+    }
+    int failed = 0;
+    for (const pid_t pid : kids) {
+        int status = 0;
+        ::waitpid(pid, &status, 0);
+        if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) { ++failed; }
+    }
+    if (failed > 0) { throw std::runtime_error("prun: " + std::to_string(failed) + " rank(s) failed"); }
+}
+}  // namespace stdml::collective

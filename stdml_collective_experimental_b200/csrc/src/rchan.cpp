@@ -1,0 +1,417 @@
+// POSIX-socket implementation of the rchan endpoints.  One listening socket
+// per peer; one reader thread per inbound connection; one outgoing connection
+// per (type, target), dialled on first use.  TCP_NODELAY is set on every
+// socket: control messages are latency-bound (the reference leaves Nagle on,
+// src/stdml/collective/platforms/linux/socket_opt.c:41-45).
+#include <atomic>
+#include <cerrno>
+#include <chrono>
+#include <cstring>
+#include <list>
+#include <stdexcept>
+#include <thread>
+#include <vector>
+
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <poll.h>
+#include <sys/socket.h>
+#include <sys/uio.h>
+#include <unistd.h>
+
+#include <stdml/bits/collective/config.hpp>
+#include <stdml/bits/collective/log.hpp>
+#include <stdml/bits/collective/rchan.hpp>
+#include <stdml/bits/collective/stat.hpp>
+
+namespace stdml::collective::rchan
+{
+namespace
+{
+void tune_socket(int fd)
+{
+    int one = 1;
+    setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+    int buf = 4 << 20;
+    setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &buf, sizeof(buf));
+    setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &buf, sizeof(buf));
+}
+
+sockaddr_in to_sockaddr(const peer_id &id)
+{
+    sockaddr_in a;
+    std::memset(&a, 0, sizeof(a));
+    a.sin_family = AF_INET;
+    a.sin_port = htons(id.port);
+    a.sin_addr.s_addr = htonl(id.ipv4);
+    return a;
+}
+
+bool read_exact(int fd, void *data, size_t size)
+{
+    char *p = static_cast<char *>(data);
+    while (size > 0) {
+        const ssize_t n = ::recv(fd, p, size, 0);
+        if (n > 0) {
+            p += n;
+            size -= static_cast<size_t>(n);
+        } else if (n == 0) {
+            return false;
+        } else if (errno != EINTR) {
+            return false;
+        }
+    }
+    return true;
+}
+
+bool write_iov(int fd, iovec *iov, int cnt)
+{
+    while (cnt > 0) {
+        msghdr msg{};
+        msg.msg_iov = iov;
+        msg.msg_iovlen = static_cast<size_t>(cnt);
+        ssize_t n = ::sendmsg(fd, &msg, MSG_NOSIGNAL);
+        if (n < 0) {
+            if (errno == EINTR) { continue; }
+            return false;
+        }
+        while (cnt > 0 && n >= static_cast<ssize_t>(iov->iov_len)) {
+            n -= static_cast<ssize_t>(iov->iov_len);
+            ++iov;
+            --cnt;
+        }
+        if (cnt > 0 && n > 0) {
+            iov->iov_base = static_cast<char *>(iov->iov_base) + n;
+            iov->iov_len -= static_cast<size_t>(n);
+        }
+    }
+    return true;
+}
+
+class reader_impl final : public message_reader
+{
+    int fd_;
+    uint32_t len_ = 0;
+
+  public:
+    explicit reader_impl(int fd) : fd_(fd) {}
+
+    std::optional<received_header> read_header() override
+    {
+        STDML_COLLECTIVE_PROFILE_RATE("read_header", 0);
+        received_header h;
+        if (!read_exact(fd_, &h.name_len, 4)) { return {}; }
+        if (h.name_len > (1u << 20)) { return {}; }  // not our protocol
+        std::vector<char> rest(h.name_len + 8);
+        if (!read_exact(fd_, rest.data(), rest.size())) { return {}; }
+        h.name.assign(rest.data(), h.name_len);
+        std::memcpy(&h.flags, rest.data() + h.name_len, 4);
+        std::memcpy(&h.len, rest.data() + h.name_len + 4, 4);
+        len_ = h.len;
+        return h;
+    }
+
+    bool read_body(void *data) override
+    {
+        STDML_COLLECTIVE_PROFILE_RATE("read_body", len_);
+        return len_ == 0 || read_exact(fd_, data, len_);
+    }
+};
+
+class connection_impl final : public connection
+{
+    int fd_;
+    conn_type type_;
+    peer_id src_;
+    std::mutex send_mu_;
+
+  public:
+    connection_impl(int fd, conn_type type, peer_id src) : fd_(fd), type_(type), src_(src) {}
+
+    ~connection_impl() override
+    {
+        if (fd_ >= 0) { ::close(fd_); }
+    }
+
+    int fd() const { return fd_; }
+
+    void shutdown_now()
+    {
+        if (fd_ >= 0) { ::shutdown(fd_, SHUT_RDWR); }
+    }
+
+    conn_type type() const override { return type_; }
+    peer_id src() const override { return src_; }
+
+    std::unique_ptr<message_reader> next() override
+    {
+        return std::unique_ptr<message_reader>(new reader_impl(fd_));
+    }
+
+    void send(const char *name, const void *data, size_t size, uint32_t flags) override
+    {
+        STDML_COLLECTIVE_PROFILE_RATE("send", size);
+        if (size > 0xffffffffull) { throw std::length_error("rchan: message longer than 4 GiB"); }
+        const uint32_t name_len = static_cast<uint32_t>(std::strlen(name));
+        const uint32_t len = static_cast<uint32_t>(size);
+        iovec iov[5];
+        iov[0] = {&const_cast<uint32_t &>(name_len), 4};
+        iov[1] = {const_cast<char *>(name), name_len};
+        iov[2] = {&flags, 4};
+        iov[3] = {&const_cast<uint32_t &>(len), 4};
+        iov[4] = {const_cast<void *>(data), size};
+        std::lock_guard<std::mutex> lk(send_mu_);
+        if (!write_iov(fd_, iov, size > 0 ? 5 : 4)) {
+            throw std::runtime_error("rchan: send to " + src_.str() + " failed: " +
+                                     std::strerror(errno));
+        }
+    }
+};
+}  // namespace
+
+int64_t connect_timeout_ms()
+{
+    static const int64_t v =
+        parse_env_int("STDML_COLLECTIVE_CONNECT_TIMEOUT_MS").value_or(120000);
+    return v;
+}
+
+std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_type type,
+                                             const peer_id local)
+{
+    using clock = std::chrono::steady_clock;
+    const auto t0 = clock::now();
+    const int64_t limit = connect_timeout_ms();
+    const sockaddr_in addr = to_sockaddr(remote);
+    int wait_ms = 2;
+    for (;;) {
+        const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        if (fd < 0) { throw std::runtime_error("rchan: socket() failed"); }
+        if (::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr)) == 0) {
+            tune_socket(fd);
+            conn_header h{static_cast<uint16_t>(type), local.port, local.ipv4};
+            connection_ack ack{};
+            iovec iov{&h, sizeof(h)};
+            if (write_iov(fd, &iov, 1) && read_exact(fd, &ack, sizeof(ack))) {
+                return std::unique_ptr<connection>(new connection_impl(fd, type, remote));
+            }
+        }
+        ::close(fd);
+        const auto waited =
+            std::chrono::duration_cast<std::chrono::milliseconds>(clock::now() - t0).count();
+        if (limit > 0 && waited > limit) {
+            throw std::runtime_error("rchan: could not reach " + remote.str() + " within " +
+                                     std::to_string(limit) + " ms");
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(wait_ms));
+        wait_ms = std::min(wait_ms * 2, 200);  // the peer may simply not be up yet
+    }
+}
+
+bool conn_handler::handle_next(connection *conn, msg_handler *h)
+{
+    auto reader = conn->next();
+    const auto mh = reader->read_header();
+    if (!mh) { return false; }
+    return (*h)(*mh, reader.get(), conn->src());
+}
+
+size_t conn_handler::handle_to_end(connection *conn, msg_handler *h)
+{
+    size_t n = 0;
+    while (handle_next(conn, h)) { ++n; }
+    return n;
+}
+
+// ------------------------------------------------------------------- client
+namespace
+{
+class client_impl final : public client
+{
+    const peer_id self_;
+    const conn_type type_;
+    std::mutex mu_;
+    std::map<uint64_t, std::shared_ptr<connection>> conns_;
+
+    std::shared_ptr<connection> require(const peer_id &target)
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        auto &c = conns_[target.hash()];
+        if (!c) { c = connection::dial(target, type_, self_); }
+        return c;
+    }
+
+  public:
+    client_impl(peer_id self, conn_type type) : self_(self), type_(type) {}
+
+    void send(const peer_id target, const char *name, const void *data, size_t size,
+              uint32_t flags) override
+    {
+        require(target)->send(name, data, size, flags);
+    }
+
+    std::unique_ptr<connection> dial(peer_id target, conn_type type) override
+    {
+        return connection::dial(target, type, self_);
+    }
+
+    void reset_peers(const peer_list &ids) override
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        for (const auto &id : ids) { conns_.erase(id.hash()); }
+    }
+};
+}  // namespace
+
+std::unique_ptr<client> client::New(peer_id self, conn_type type)
+{
+    return std::unique_ptr<client>(new client_impl(self, type));
+}
+
+client *client_pool::require(conn_type type)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    auto &c = clients_[type];
+    if (!c) { c = client::New(self_, type); }
+    return c.get();
+}
+
+void client_pool::reset_peers(const peer_list &ids)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    for (auto &kv : clients_) { kv.second->reset_peers(ids); }
+}
+
+// ------------------------------------------------------------------- server
+namespace
+{
+class server_impl final : public server
+{
+    const peer_id self_;
+    conn_handler *handler_;
+    int listen_fd_ = -1;
+    std::atomic<bool> stopping_{false};
+    std::thread accept_thread_;
+    std::mutex mu_;
+    struct session {
+        std::thread th;
+        int wake_fd = -1;  // dup of the connection's socket, to shut it down from stop()
+        std::atomic<bool> finished{false};
+    };
+    std::list<session> sessions_;
+
+    void open()
+    {
+        listen_fd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        if (listen_fd_ < 0) { throw std::runtime_error("rchan: socket() failed"); }
+        int one = 1;
+        setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+        sockaddr_in a = to_sockaddr(self_);
+        a.sin_addr.s_addr = htonl(INADDR_ANY);
+        if (::bind(listen_fd_, reinterpret_cast<sockaddr *>(&a), sizeof(a)) != 0) {
+            const std::string why = std::strerror(errno);
+            ::close(listen_fd_);
+            listen_fd_ = -1;
+            throw std::runtime_error("rchan: cannot bind " + self_.str() + ": " + why);
+        }
+        if (::listen(listen_fd_, 128) != 0) { throw std::runtime_error("rchan: listen() failed"); }
+    }
+
+    void reap()
+    {
+        for (auto it = sessions_.begin(); it != sessions_.end();) {
+            if (it->finished.load()) {
+                it->th.join();
+                if (it->wake_fd >= 0) { ::close(it->wake_fd); }
+                it = sessions_.erase(it);
+            } else {
+                ++it;
+            }
+        }
+    }
+
+    void accept_loop()
+    {
+        while (!stopping_.load()) {
+            pollfd pfd{listen_fd_, POLLIN, 0};
+            const int r = ::poll(&pfd, 1, 100);
+            if (r <= 0) { continue; }
+            const int fd = ::accept4(listen_fd_, nullptr, nullptr, SOCK_CLOEXEC);
+            if (fd < 0) { continue; }
+            tune_socket(fd);
+            conn_header h{};
+            connection_ack ack{0};
+            iovec iov{&ack, sizeof(ack)};
+            if (!read_exact(fd, &h, sizeof(h)) || !write_iov(fd, &iov, 1)) {
+                ::close(fd);
+                continue;
+            }
+            std::lock_guard<std::mutex> lk(mu_);
+            if (stopping_.load()) {
+                ::close(fd);
+                break;
+            }
+            reap();
+            sessions_.emplace_back();
+            session &s = sessions_.back();
+            auto *conn = new connection_impl(fd, static_cast<conn_type>(h.type),
+                                             peer_id{h.src_ipv4, h.src_port});
+            s.wake_fd = ::dup(fd);
+            s.th = std::thread([this, conn, &s] {
+                try {
+                    (*handler_)(std::unique_ptr<connection>(conn));
+                } catch (const std::exception &e) {
+                    log(WARN) << "rchan: connection handler failed:" << e.what();
+                }
+                s.finished.store(true);
+            });
+        }
+    }
+
+  public:
+    server_impl(peer_id self, conn_handler *handler) : self_(self), handler_(handler) {}
+
+    ~server_impl() override { stop(); }
+
+    void serve() override
+    {
+        if (listen_fd_ < 0) { open(); }
+        accept_loop();
+    }
+
+    void start() override
+    {
+        if (listen_fd_ < 0) { open(); }
+        accept_thread_ = std::thread([this] { accept_loop(); });
+    }
+
+    void stop() override
+    {
+        if (stopping_.exchange(true)) { return; }
+        if (accept_thread_.joinable()) { accept_thread_.join(); }
+        {
+            // wake every reader thread: they see end-of-stream and return
+            std::lock_guard<std::mutex> lk(mu_);
+            for (auto &s : sessions_) {
+                if (s.wake_fd >= 0) { ::shutdown(s.wake_fd, SHUT_RDWR); }
+            }
+        }
+        for (auto &s : sessions_) {
+            if (s.th.joinable()) { s.th.join(); }
+            if (s.wake_fd >= 0) { ::close(s.wake_fd); }
+        }
+        sessions_.clear();
+        if (listen_fd_ >= 0) {
+            ::close(listen_fd_);
+            listen_fd_ = -1;
+        }
+    }
+};
+}  // namespace
+
+std::unique_ptr<server> server::New(const peer_id self, conn_handler *handler)
+{
+    return std::unique_ptr<server>(new server_impl(self, handler));
+}
+}  // namespace stdml::collective::rchan

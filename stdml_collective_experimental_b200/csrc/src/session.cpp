@@ -1,0 +1,506 @@
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <numeric>
+#include <stdexcept>
+#include <thread>
+
+#include <stdml/bits/collective/execution.hpp>
+#include <stdml/bits/collective/log.hpp>
+#include <stdml/bits/collective/session.hpp>
+#include <stdml/bits/collective/stat.hpp>
+
+#include "../cuda/device_session.hpp"
+
+namespace stdml::collective
+{
+using rchan::conn_collective;
+using rchan::message_header;
+
+size_t name_based_hash(const std::string &name)
+{
+    size_t h = 0;
+    for (const unsigned char c : name) { h += static_cast<size_t>(c) * c; }
+    return h;
+}
+
+std::vector<std::pair<workspace, std::pair<const graph *, const graph *>>>
+split_work(const workspace &w, const graph_pair_list &gps, size_t chunk_size)
+{
+    std::vector<std::pair<workspace, std::pair<const graph *, const graph *>>> out;
+    for (auto &part : w.split_by_bytes(chunk_size)) {
+        const auto gs = gps.choose(name_based_hash(part.name));
+        out.emplace_back(std::move(part), gs);
+    }
+    return out;
+}
+
+session::session(system_config config, size_t version, size_t rank, peer_list peers,
+                 peer_list runners, mailbox *mailbox, slotbox *slotbox,
+                 rchan::client_pool *client_pool, strategy s)
+    : config_(std::move(config)), version_(version), rank_(rank), peers_(std::move(peers)),
+      runners_(std::move(runners)), strategy_(s),
+      all_reduce_topo_(make_graph_pair_list(s, peers_.size())), mailbox_(mailbox),
+      slotbox_(slotbox), client_pool_(client_pool)
+{
+    if (rank_ >= peers_.size()) { throw std::invalid_argument("session: rank outside the peer list"); }
+    if (config_.thread_pool_size > 0 &&
+        (config_.rt == rt_thread_pool || config_.rt == rt_go)) {
+        pool_ = sync::thread_pool::make(config_.thread_pool_size);
+    }
+    async_runtime_.reset(runtime::New(8));
+    barrier();
+}
+
+session::~session() = default;
+session::session(session &&) noexcept = default;
+
+void session::barrier()
+{
+    uint32_t one = 1, all = 0;
+    all_reduce(&one, &all, 1, u32, sum, "stdml::barrier::v" + std::to_string(version_));
+}
+
+// ---------------------------------------------------------------- host path
+namespace
+{
+std::string versioned(const session &s, const std::string &name)
+{
+    // keeps messages of an old membership from matching operations of a new one
+    return s.version() == 0 ? name : name + "@v" + std::to_string(s.version());
+}
+}  // namespace
+
+void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
+{
+    workspace_state st(&w);
+    const std::string name = versioned(*this, w.name);
+    const size_t bytes = w.bytes();
+    rchan::client *out = client_pool_->require(conn_collective);
+
+    auto recv_reduce = [&](size_t src) {
+        buffer b = mailbox_->require(peers_[src], name)->get();
+        if (b.len != bytes) {
+            throw std::runtime_error("all_reduce: peer " + peers_[src].str() + " sent " +
+                                     std::to_string(b.len) + " bytes for '" + w.name +
+                                     "', expected " + std::to_string(bytes));
+        }
+        st.add_to(b.data.get());
+    };
+    auto send_partial = [&](size_t dst) {
+        out->send(peers_[dst], name.c_str(), st.effective_data(), bytes, 0);
+    };
+    auto recv_result = [&](size_t src) {
+        if (!slotbox_->require(peers_[src], name)->get(w.recv, bytes)) {
+            throw std::runtime_error("all_reduce: result for '" + w.name + "' did not fit");
+        }
+        st.replaced();
+    };
+    auto send_result = [&](size_t dst) {
+        out->send(peers_[dst], name.c_str(), w.recv, bytes, message_header::wait_recv_buf);
+    };
+
+    // reduce graph: accumulate what the predecessors send, pass the partial on
+    if (pool_) {
+        fmap(pool_.get(), recv_reduce, rg->prevs(rank_));
+        fmap(pool_.get(), send_partial, rg->nexts(rank_));
+    } else {
+        fmap(par, recv_reduce, rg->prevs(rank_));
+        fmap(par, send_partial, rg->nexts(rank_));
+    }
+    // broadcast graph: the root already holds the result
+    if (bg->prevs(rank_).empty()) {
+        if (st.received() == 0) { st.forward(); }
+    } else {
+        fmap(seq, recv_result, bg->prevs(rank_));
+    }
+    if (pool_) {
+        fmap(pool_.get(), send_result, bg->nexts(rank_));
+    } else {
+        fmap(par, send_result, bg->nexts(rank_));
+    }
+}
+
+// The same chunk as a polled task tree (rt_async): nothing in it blocks.
+task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
+{
+    struct shared {
+        workspace w;
+        workspace_state st;
+        std::string name;
+        explicit shared(const workspace &x) : w(x), st(&w) {}
+    };
+    auto sh = std::make_shared<shared>(w);
+    sh->name = versioned(*this, w.name);
+    const size_t bytes = w.bytes();
+    rchan::client *out = client_pool_->require(conn_collective);
+
+    task_builder recv1, send1, recv2, send2;
+    for (size_t src : rg->prevs(rank_)) {
+        auto *box = mailbox_->require(peers_[src], sh->name);
+        auto got = std::make_shared<buffer>();
+        recv1 << new poll_task(
+            [box, got] {
+                auto b = box->try_get();
+                if (!b) { return false; }
+                *got = std::move(*b);
+                return true;
+            },
+            [sh, got, bytes] {
+                if (got->len != bytes) { throw std::runtime_error("all_reduce: size mismatch"); }
+                sh->st.add_to(got->data.get());
+            });
+    }
+    for (size_t dst : rg->nexts(rank_)) {
+        const peer_id target = peers_[dst];
+        send1 << new simple_task([sh, out, target, bytes] {
+            out->send(target, sh->name.c_str(), sh->st.effective_data(), bytes, 0);
+        });
+    }
+    if (bg->prevs(rank_).empty()) {
+        recv2 << new simple_task([sh] {
+            if (sh->st.received() == 0) { sh->st.forward(); }
+        });
+    } else {
+        for (size_t src : bg->prevs(rank_)) {
+            auto *sl = slotbox_->require(peers_[src], sh->name);
+            auto done = std::make_shared<std::function<bool()>>();
+            recv2 << new poll_task([sl, sh, done, bytes] {
+                // the destination is posted on the first poll, i.e. after the
+                // reduce phase is over and recv no longer holds partial sums
+                if (!*done) { *done = sl->post_polled(sh->w.recv, bytes); }
+                return (*done)();
+            });
+        }
+    }
+    for (size_t dst : bg->nexts(rank_)) {
+        const peer_id target = peers_[dst];
+        send2 << new simple_task([sh, out, target, bytes] {
+            out->send(target, sh->name.c_str(), sh->w.recv, bytes, message_header::wait_recv_buf);
+        });
+    }
+    task_builder steps;
+    steps << recv1.par();
+    steps << send1.par();
+    steps << recv2.seq();
+    steps << send2.par();
+    return steps.seq();
+}
+
+void session::all_reduce(const workspace &w, void *stream)
+{
+    STDML_COLLECTIVE_PROFILE_RATE("all_reduce", w.bytes());
+    if (!reduce_supported(w.dt, w.op)) {
+        throw std::invalid_argument(std::string("all_reduce: ") + reduce_op_name(w.op) +
+                                    " is not defined for " + dtype_name(w.dt));
+    }
+    if (w.count == 0) { return; }
+    if (on_device(w.send, w.recv)) {
+        const void *in[1] = {w.send};
+        void *out[1] = {w.recv};
+        device()->all_reduce(in, out, w.count, w.dt, w.op, 1.0, -1, stream);
+        return;
+    }
+    if (peers_.size() == 1) {
+        w.forward();
+        return;
+    }
+    const auto work = split_work(w, all_reduce_topo_, chunk_bytes);
+    if (config_.rt == rt_async || config_.rt == rt_coro) {
+        std::vector<std::unique_ptr<task>> ts;
+        for (const auto &[part, gs] : work) {
+            ts.emplace_back(chunk_task(part, gs.first, gs.second));
+        }
+        std::unique_ptr<task> all(task::par(std::move(ts), async_runtime_.get()));
+        all->finish();
+        return;
+    }
+    for (const auto &[part, gs] : work) { run_chunk(part, gs.first, gs.second); }
+}
+
+void session::all_reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
+                         std::string name, void *stream)
+{
+    workspace w;
+    w.send = input;
+    w.recv = output;
+    w.count = count;
+    w.dt = dt;
+    w.op = op;
+    w.name = std::move(name);
+    all_reduce(w, stream);
+}
+
+void session::group_all_reduce(const std::vector<workspace> &ws, double scale, void *stream)
+{
+    if (ws.empty()) { return; }
+    bool dev = true, same = true;
+    for (const auto &w : ws) {
+        dev = dev && on_device(w.send, w.recv);
+        same = same && w.dt == ws[0].dt && w.op == ws[0].op;
+    }
+    if (dev && same) {
+        std::vector<const void *> ins;
+        std::vector<void *> outs;
+        std::vector<size_t> counts;
+        for (const auto &w : ws) {
+            ins.push_back(w.send);
+            outs.push_back(w.recv);
+            counts.push_back(w.count);
+        }
+        device()->group_all_reduce(ws.size(), ins.data(), outs.data(), counts.data(), ws[0].dt,
+                                   ws[0].op, -1, scale, -1, stream);
+        return;
+    }
+    std::vector<std::future<workspace>> fs;
+    for (const auto &w : ws) {
+        std::promise<workspace> p;
+        p.set_value(w);
+        fs.push_back(p.get_future());
+    }
+    group_all_reduce(std::move(fs));
+    if (scale != 1.0) {
+        for (const auto &w : ws) { scale_in_place(w.recv, w.count, w.dt, scale); }
+    }
+}
+
+void session::group_all_reduce(std::vector<std::future<workspace>> fs)
+{
+    // Tensors are handed to a small set of workers strictly in submission
+    // order, which is the same on every rank (futures are positional).  The
+    // earliest unfinished tensor is therefore always being worked on by every
+    // rank, whatever order the futures resolve in, so the group cannot
+    // deadlock (the reference runs each tensor on an ad-hoc pool of 76 threads
+    // as it becomes ready, which deadlocks for larger sets:
+    // src/stdml/collective/session.cpp:83-97).
+    const size_t n = fs.size();
+    if (n == 0) { return; }
+    size_t workers = 8;
+    if (pool_) {
+        const size_t fan = std::max<size_t>(1, peers_.size() - 1);
+        workers = std::max<size_t>(1, std::min<size_t>(8, pool_->size() / fan));
+    }
+    workers = std::min(workers, n);
+    std::atomic<size_t> next{0};
+    std::mutex err_mu;
+    std::exception_ptr err;
+    auto work = [&] {
+        for (;;) {
+            const size_t i = next.fetch_add(1);
+            if (i >= n) { return; }
+            try {
+                const workspace w = fs[i].get();
+                if (!err) { all_reduce(w); }
+            } catch (...) {
+                std::lock_guard<std::mutex> lk(err_mu);
+                if (!err) { err = std::current_exception(); }
+            }
+        }
+    };
+    std::vector<std::thread> ths;
+    for (size_t t = 1; t < workers; ++t) { ths.emplace_back(work); }
+    work();
+    for (auto &t : ths) { t.join(); }
+    if (err) { std::rethrow_exception(err); }
+}
+
+void session::reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
+                     std::string name, void *stream)
+{
+    if (count == 0) { return; }
+    if (!reduce_supported(dt, op)) { throw std::invalid_argument("reduce: undefined dtype/op"); }
+    if (on_device(input, output != nullptr ? output : input)) {
+        const void *in[1] = {input};
+        void *out[1] = {output};
+        device()->reduce(in, out, count, dt, op, 0, 1.0, stream);
+        return;
+    }
+    // root 0 gathers the operands in rank order and folds them left to right
+    const size_t bytes = count * dtype_size(dt);
+    const std::string tag = versioned(*this, "stdml::reduce::" + name);
+    if (rank_ != 0) {
+        client_pool_->require(conn_collective)
+            ->send(peers_[0], tag.c_str(), input, bytes, 0);
+        return;
+    }
+    if (output != input) { std::memcpy(output, input, bytes); }
+    for (size_t r = 1; r < peers_.size(); ++r) {
+        buffer b = mailbox_->require(peers_[r], tag)->get();
+        if (b.len != bytes) { throw std::runtime_error("reduce: size mismatch"); }
+        stdml::collective::reduce(output, output, b.data.get(), count, dt, op);
+    }
+}
+
+void session::all_gather(const void *input, void *output, size_t count, dtype dt,
+                         std::string name, void *stream)
+{
+    if (count == 0) { return; }
+    if (on_device(input, output)) {
+        const void *in[1] = {input};
+        void *out[1] = {output};
+        device()->all_gather(in, out, count, dt, stream);
+        return;
+    }
+    const size_t bytes = count * dtype_size(dt);
+    const std::string tag = versioned(*this, "stdml::all_gather::" + name);
+    char *out = static_cast<char *>(output);
+    // post every destination first, then send: the bodies land in place
+    std::vector<std::function<bool()>> waits;
+    for (size_t r = 0; r < peers_.size(); ++r) {
+        if (r == rank_) { continue; }
+        waits.push_back(slotbox_->require(peers_[r], tag)->post(out + r * bytes, bytes));
+    }
+    std::memmove(out + rank_ * bytes, input, bytes);
+    std::vector<size_t> others;
+    for (size_t r = 1; r < peers_.size(); ++r) { others.push_back((rank_ + r) % peers_.size()); }
+    rchan::client *cl = client_pool_->require(conn_collective);
+    auto send_to = [&](size_t r) {
+        cl->send(peers_[r], tag.c_str(), input, bytes, message_header::wait_recv_buf);
+    };
+    if (pool_) {
+        fmap(pool_.get(), send_to, others);
+    } else {
+        fmap(par, send_to, others);
+    }
+    for (auto &w : waits) {
+        if (!w()) { throw std::runtime_error("all_gather: a block did not fit"); }
+    }
+}
+
+void session::gather(const void *input, void *output, size_t count, dtype dt, std::string name)
+{
+    if (count == 0) { return; }
+    const size_t bytes = count * dtype_size(dt);
+    const std::string tag = versioned(*this, "stdml::gather::" + name);
+    if (rank_ != 0) {
+        client_pool_->require(conn_collective)
+            ->send(peers_[0], tag.c_str(), input, bytes, message_header::wait_recv_buf);
+        return;
+    }
+    char *out = static_cast<char *>(output);
+    std::memmove(out, input, bytes);
+    for (size_t r = 1; r < peers_.size(); ++r) {
+        if (!slotbox_->require(peers_[r], tag)->get(out + r * bytes, bytes)) {
+            throw std::runtime_error("gather: a block did not fit");
+        }
+    }
+}
+
+void session::broadcast(const void *input, void *output, size_t count, dtype dt,
+                        std::string name, void *stream)
+{
+    if (count == 0) { return; }
+    if (on_device(input, output)) {
+        const void *in[1] = {input};
+        void *out[1] = {output};
+        device()->broadcast(in, out, count, dt, 0, stream);
+        return;
+    }
+    const size_t bytes = count * dtype_size(dt);
+    const std::string tag = versioned(*this, "stdml::broadcast::" + name);
+    const graph &g = all_reduce_topo_.pairs[0].broadcast_graph;  // rooted at rank 0
+    if (g.prevs(rank_).empty()) {
+        if (output != input) { std::memcpy(output, input, bytes); }
+    } else {
+        for (size_t src : g.prevs(rank_)) {
+            if (!slotbox_->require(peers_[src], tag)->get(output, bytes)) {
+                throw std::runtime_error("broadcast: the message did not fit");
+            }
+        }
+    }
+    rchan::client *cl = client_pool_->require(conn_collective);
+    auto send_to = [&](size_t r) {
+        cl->send(peers_[r], tag.c_str(), output, bytes, message_header::wait_recv_buf);
+    };
+    fmap(par, send_to, g.nexts(rank_));
+}
+
+void session::send(const void *input, size_t count, dtype dt, size_t target, std::string name)
+{
+    if (target >= peers_.size()) { throw std::out_of_range("send: no such rank"); }
+    const std::string tag = versioned(*this, "stdml::p2p::" + name);
+    client_pool_->require(conn_collective)
+        ->send(peers_[target], tag.c_str(), input, count * dtype_size(dt),
+               message_header::wait_recv_buf);
+}
+
+void session::recv(void *output, size_t count, dtype dt, size_t target, std::string name)
+{
+    if (target >= peers_.size()) { throw std::out_of_range("recv: no such rank"); }
+    const std::string tag = versioned(*this, "stdml::p2p::" + name);
+    if (!slotbox_->require(peers_[target], tag)->get(output, count * dtype_size(dt))) {
+        throw std::length_error("recv: the message is longer than the posted buffer");
+    }
+}
+
+bool session::consistent(const void *ptr, size_t size)
+{
+    // everyone holds the same bytes iff min == max for the length and, given
+    // equal lengths, for every byte
+    const uint64_t n = size;
+    uint64_t lo = 0, hi = 0;
+    all_reduce(&n, &lo, 1, u64, min, "stdml::consistent::len::min");
+    all_reduce(&n, &hi, 1, u64, max, "stdml::consistent::len::max");
+    if (lo != hi) { return false; }
+    if (size == 0) { return true; }
+    std::vector<uint8_t> a(size), b(size);
+    all_reduce(ptr, a.data(), size, u8, min, "stdml::consistent::min");
+    all_reduce(ptr, b.data(), size, u8, max, "stdml::consistent::max");
+    return a == b;
+}
+
+// -------------------------------------------------------------- device path
+bool session::on_device(const void *a, const void *b) const
+{
+    const int ka = cuda::pointer_kind(a), kb = cuda::pointer_kind(b);
+    if (ka != kb) {
+        throw std::invalid_argument(
+            "collective: input and output must both be host or both be device memory");
+    }
+    return ka == 1;
+}
+
+cuda::DeviceSession *session::device()
+{
+    if (device_) { return device_.get(); }
+    if (device_tried_) { throw std::runtime_error("device collectives are unavailable"); }
+    device_tried_ = true;
+    cuda::DeviceWorldOptions o;
+    o.rank = static_cast<int>(rank_);
+    o.world = static_cast<int>(peers_.size());
+    // one GPU per rank on this host: the rank's position among the peers that
+    // share its address, unless STDML_COLLECTIVE_DEVICE_ID / LOCAL_RANK says otherwise
+    int local = 0;
+    for (size_t r = 0; r < rank_; ++r) {
+        if (peers_[r].ipv4 == peers_[rank_].ipv4) { ++local; }
+    }
+    if (const auto v = parse_env_int("STDML_COLLECTIVE_DEVICE_ID")) {
+        local = static_cast<int>(*v);
+    } else if (const auto l = parse_env_int("LOCAL_RANK")) {
+        local = static_cast<int>(*l);
+    }
+    const int ndev = cuda::cuda_device_count();
+    if (ndev <= 0) { throw std::runtime_error("device collectives need a CUDA device"); }
+    o.device = local % ndev;
+    for (const auto &p : peers_) {
+        if (p.ipv4 != peers_[0].ipv4) {
+            throw std::runtime_error(
+                "device collectives need all ranks on one box (one NVLink domain)");
+        }
+    }
+    o.key = peers_[0].str() + ".v" + std::to_string(version_);
+    if (const auto v = parse_env_int("STDML_COLLECTIVE_HEAP_MB")) {
+        o.heap_bytes = static_cast<size_t>(*v) << 20;
+    }
+    if (const auto v = parse_env_int("STDML_COLLECTIVE_STAGING_MB")) {
+        o.staging_bytes = static_cast<size_t>(*v) << 20;
+    }
+    o.enable_nvls = config_.use_nvls;
+    o.wait_timeout_ms = static_cast<unsigned long long>(config_.timeout_ms);
+    const std::string backend = safe_getenv("STDML_COLLECTIVE_SYMM");
+    if (!backend.empty()) { o.backend = backend; }
+    device_ = std::make_unique<cuda::DeviceSession>(cuda::DeviceWorld::create(o));
+    return device_.get();
+}
+}  // namespace stdml::collective
