@@ -29,6 +29,7 @@ class elastic_state
     int64_t progress_ = 0;
     bool synced_ = false;
     bool detached_ = false;
+    bool needs_state_ = false;
     peer::config_prodiver get_config_;
     std::function<void(session &)> on_resize_;
 
@@ -46,7 +47,9 @@ class elastic_state
     bool detached() const { return detached_; }
     session &sess();
     peer &get_peer() { return peer_; }
-    // called on every member of the new session right after a resize
+    // called on every member of a new session (survivors right after the
+    // resize, joiners at their first use of the state), after the progress
+    // counter has been synchronised
     void on_resize(std::function<void(session &)> f) { on_resize_ = std::move(f); }
 };
 }  // namespace stdml::collective

@@ -7,6 +7,8 @@ elastic_state::elastic_state(peer::config_prodiver get_config, std::optional<int
     : peer_(peer::from_env()), sess_(peer_.join_elastic()), max_progress_(max_progress),
       get_config_(std::move(get_config))
 {
+    // a process that joins a running job has to receive the state as well
+    needs_state_ = sess_->version() > 0;
 }
 
 elastic_state::elastic_state(std::optional<int64_t> max_progress)
@@ -19,6 +21,10 @@ void elastic_state::sync()
     if (!synced_) {
         progress_ = sess_->all_reduce(progress_, max);
         synced_ = true;
+        if (needs_state_) {
+            needs_state_ = false;
+            if (on_resize_) { on_resize_(*sess_); }
+        }
     }
 }
 
@@ -31,8 +37,8 @@ void elastic_state::check_resize()
     }
     if (r.changed) {
         synced_ = false;
+        needs_state_ = true;
         sync();
-        if (on_resize_) { on_resize_(*sess_); }
     }
 }
 

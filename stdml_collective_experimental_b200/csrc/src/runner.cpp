@@ -1,0 +1,301 @@
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+#include <thread>
+
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <stdml/bits/collective/json.hpp>
+#include <stdml/bits/collective/log.hpp>
+#include <stdml/bits/collective/runner.hpp>
+
+namespace stdml::collective
+{
+namespace
+{
+class control_msg_handler final : public rchan::msg_handler
+{
+    runner *runner_;
+
+  public:
+    explicit control_msg_handler(runner *r) : runner_(r) {}
+
+    bool operator()(const rchan::received_header &mh, rchan::message_reader *reader,
+                    const peer_id &) override
+    {
+        std::string body(mh.len, '\0');
+        if (!reader->read_body(body.data())) { return false; }
+        if (mh.name != "update") { return true; }
+        const auto v = json::parse(body);
+        if (!v) { return true; }
+        const json::value *ver = v->get("Version");
+        const json::value *cl = v->get("Cluster");
+        if (ver == nullptr || cl == nullptr) { return true; }
+        const auto next = cluster_config::from_json(cl->dump());
+        if (next) { runner_->on_update(static_cast<size_t>(ver->as_int()), *next); }
+        return true;
+    }
+};
+
+class control_conn_handler final : public rchan::conn_handler
+{
+    control_msg_handler h_;
+
+  public:
+    explicit control_conn_handler(runner *r) : h_(r) {}
+    size_t operator()(std::unique_ptr<rchan::connection> conn) override
+    {
+        return handle_to_end(conn.get(), &h_);
+    }
+};
+}  // namespace
+
+runner::runner(runner_options opt) : opt_(std::move(opt))
+{
+    peer_list workers;
+    for (size_t i = 0; i < opt_.np; ++i) {
+        workers.push_back(peer_id{opt_.self.ipv4, static_cast<uint16_t>(opt_.worker_base_port + i)});
+    }
+    cluster_ = cluster_config(peer_list{opt_.self}, workers);
+    stored_config_ = cluster_.json();
+}
+
+runner::~runner()
+{
+    if (server_) { server_->stop(); }
+    if (http_) { http_->stop(); }
+}
+
+std::string runner::config_url() const
+{
+    if (!opt_.config_server_url.empty()) { return opt_.config_server_url; }
+    if (http_) { return "http://127.0.0.1:" + std::to_string(http_->port()) + "/config"; }
+    return "";
+}
+
+void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t version)
+{
+    std::string peers;
+    for (size_t i = 0; i < cluster.workers.size(); ++i) {
+        peers += (i ? "," : "") + cluster.workers[i].str();
+    }
+    std::string runners;
+    for (size_t i = 0; i < cluster.runners.size(); ++i) {
+        runners += (i ? "," : "") + cluster.runners[i].str();
+    }
+    const std::string url = config_url();
+    const pid_t pid = ::fork();
+    if (pid < 0) { throw std::runtime_error("runner: fork failed"); }
+    if (pid == 0) {
+        ::setenv("KUNGFU_SELF_SPEC", worker.str().c_str(), 1);
+        ::setenv("KUNGFU_INIT_PEERS", peers.c_str(), 1);
+        ::setenv("KUNGFU_INIT_RUNNERS", runners.c_str(), 1);
+        ::setenv("KUNGFU_INIT_CLUSTER_VERSION", std::to_string(version).c_str(), 1);
+        ::setenv("KUNGFU_ALLREDUCE_STRATEGY", strategy_name(opt_.strat), 1);
+        if (!url.empty()) { ::setenv("KUNGFU_CONFIG_SERVER", url.c_str(), 1); }
+        // a worker keeps its GPU for life: the index follows its port, not its rank
+        ::setenv("STDML_COLLECTIVE_DEVICE_ID",
+                 std::to_string(worker.port - opt_.worker_base_port).c_str(), 1);
+        for (const auto &kv : opt_.extra_env) { ::setenv(kv.first.c_str(), kv.second.c_str(), 1); }
+        if (!opt_.logdir.empty()) {
+            ::mkdir(opt_.logdir.c_str(), 0755);
+            const std::string base = opt_.logdir + "/" + worker.hostname() + "." +
+                                     std::to_string(worker.port);
+            const int out = ::open((base + ".stdout.log").c_str(), O_WRONLY | O_CREAT | O_APPEND, 0644);
+            const int err = ::open((base + ".stderr.log").c_str(), O_WRONLY | O_CREAT | O_APPEND, 0644);
+            if (out >= 0) { ::dup2(out, 1); }
+            if (err >= 0) { ::dup2(err, 2); }
+        }
+        std::vector<char *> argv;
+        for (auto &a : opt_.command) { argv.push_back(const_cast<char *>(a.c_str())); }
+        argv.push_back(nullptr);
+        ::execvp(argv[0], argv.data());
+        std::fprintf(stderr, "runner: cannot exec %s: %s\n", argv[0], std::strerror(errno));
+        ::_exit(127);
+    }
+    pids_[worker.hash()] = pid;
+    if (!opt_.quiet) {
+        log(PRINT) << "[runner] started worker" << worker.str() << "pid" << pid << "version"
+                   << version;
+    }
+}
+
+void runner::reap(bool block)
+{
+    for (;;) {
+        int status = 0;
+        const pid_t pid = ::waitpid(-1, &status, block ? 0 : WNOHANG);
+        if (pid <= 0) { return; }
+        std::lock_guard<std::mutex> lk(mu_);
+        for (auto it = pids_.begin(); it != pids_.end(); ++it) {
+            if (it->second == pid) {
+                pids_.erase(it);
+                break;
+            }
+        }
+        if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) {
+            ++failed_;
+            if (!opt_.quiet) { log(PRINT) << "[runner] worker pid" << pid << "failed"; }
+        }
+        if (block) { return; }
+    }
+}
+
+void runner::on_update(size_t version, const cluster_config &next)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    if (version <= version_) { return; }  // every surviving worker sends the same update
+    version_ = version;
+    const cluster_config old = cluster_;
+    cluster_ = next;
+    stored_config_ = next.json();
+    if (!opt_.quiet) {
+        log(PRINT) << "[runner] version" << version << ":" << old.workers.size() << "->"
+                   << next.workers.size() << "workers";
+    }
+    for (const auto &w : next.workers) {
+        if (w.ipv4 != opt_.self.ipv4) { continue; }  // another host's runner starts it
+        if (old.workers.contains(w)) { continue; }
+        const auto running = pids_.find(w.hash());
+        if (running != pids_.end()) {
+            // an earlier incarnation of this worker was removed and is on its
+            // way out; its port is free only once it has exited
+            int status = 0;
+            if (::waitpid(running->second, &status, 0) == running->second &&
+                (!WIFEXITED(status) || WEXITSTATUS(status) != 0)) {
+                ++failed_;
+            }
+            pids_.erase(running);
+        }
+        spawn(w, next, version);
+    }
+    // removed workers learn `detached` from their own resize() and exit by themselves
+}
+
+int runner::run()
+{
+    if (opt_.command.empty()) { throw std::invalid_argument("runner: no program given"); }
+    if (opt_.config_port >= 0) {
+        http_ = std::make_unique<http_server>(
+            static_cast<uint16_t>(opt_.config_port), [this](const http_server::request &rq) {
+                http_response rs;
+                rs.status = 200;
+                std::lock_guard<std::mutex> lk(mu_);
+                if (rq.method == "PUT" || rq.method == "POST") {
+                    if (!cluster_config::from_json(rq.body)) {
+                        rs.status = 400;
+                        rs.body = "{\"error\":\"malformed cluster\"}";
+                        return rs;
+                    }
+                    stored_config_ = rq.body;
+                }
+                rs.body = stored_config_;
+                return rs;
+            });
+        http_->start();
+    }
+    if (opt_.watch) {
+        handler_ = std::make_unique<control_conn_handler>(this);
+        server_ = rchan::server::New(opt_.self, handler_.get());
+        server_->start();
+    }
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        for (const auto &w : cluster_.workers) { spawn(w, cluster_, 0); }
+    }
+    for (;;) {
+        reap(false);
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            if (pids_.empty()) { break; }
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    }
+    if (server_) { server_->stop(); }
+    if (http_) { http_->stop(); }
+    return failed_;
+}
+
+bool parse_runner_args(int argc, char *argv[], runner_options &o, std::string &error)
+{
+    int i = 1;
+    auto need = [&](const char *flag) -> const char * {
+        if (i + 1 >= argc) {
+            error = std::string("missing value for ") + flag;
+            return nullptr;
+        }
+        return argv[++i];
+    };
+    for (; i < argc; ++i) {
+        const std::string a = argv[i];
+        if (a == "-np") {
+            const char *v = need("-np");
+            if (!v) { return false; }
+            o.np = static_cast<size_t>(std::atoi(v));
+        } else if (a == "-H") {  // accepted for kungfu-run compatibility: ip:slots
+            if (!need("-H")) { return false; }
+        } else if (a == "-strategy") {
+            const char *v = need("-strategy");
+            if (!v) { return false; }
+            o.strat = std::string(v) == "RING" || std::string(v) == "ring" ? ring : star;
+        } else if (a == "-w") {
+            o.watch = true;
+        } else if (a == "-q") {
+            o.quiet = true;
+        } else if (a == "-builtin-config-port") {
+            const char *v = need("-builtin-config-port");
+            if (!v) { return false; }
+            o.config_port = std::atoi(v);
+        } else if (a == "-config-server") {
+            const char *v = need("-config-server");
+            if (!v) { return false; }
+            o.config_server_url = v;
+        } else if (a == "-logdir") {
+            const char *v = need("-logdir");
+            if (!v) { return false; }
+            o.logdir = v;
+        } else if (a == "-runner-port") {
+            const char *v = need("-runner-port");
+            if (!v) { return false; }
+            o.self.port = static_cast<uint16_t>(std::atoi(v));
+        } else if (a == "-port-range") {
+            const char *v = need("-port-range");
+            if (!v) { return false; }
+            o.worker_base_port = static_cast<uint16_t>(std::atoi(v));
+        } else if (a == "-env") {
+            const char *v = need("-env");
+            if (!v) { return false; }
+            const std::string kv = v;
+            const size_t eq = kv.find('=');
+            if (eq == std::string::npos) {
+                error = "-env wants NAME=VALUE";
+                return false;
+            }
+            o.extra_env.emplace_back(kv.substr(0, eq), kv.substr(eq + 1));
+        } else if (a == "--") {
+            ++i;
+            break;
+        } else if (!a.empty() && a[0] == '-') {
+            error = "unknown flag " + a;
+            return false;
+        } else {
+            break;
+        }
+    }
+    for (; i < argc; ++i) { o.command.push_back(argv[i]); }
+    if (o.np == 0) {
+        error = "-np must be positive";
+        return false;
+    }
+    if (o.command.empty()) {
+        error = "no program given";
+        return false;
+    }
+    return true;
+}
+}  // namespace stdml::collective

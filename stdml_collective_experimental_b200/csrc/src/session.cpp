@@ -216,7 +216,37 @@ void session::all_reduce(const workspace &w, void *stream)
         all->finish();
         return;
     }
-    for (const auto &[part, gs] : work) { run_chunk(part, gs.first, gs.second); }
+    // Chunks are independent (distinct names, spread over the ring roots), so a
+    // few of them are kept in flight; every rank starts them in the same order,
+    // which keeps the pipeline free of deadlocks (see group_all_reduce).  The
+    // reference runs the chunks of one tensor strictly one after another
+    // (src/stdml/collective/run_graph_pair_list_multi_thread.cpp:93-95).
+    // (a star has one root, whose links are already busy with one chunk)
+    const size_t lanes = strategy_ == ring ? std::min<size_t>(work.size(), 4) : 1;
+    if (lanes <= 1) {
+        for (const auto &[part, gs] : work) { run_chunk(part, gs.first, gs.second); }
+        return;
+    }
+    std::atomic<size_t> next{0};
+    std::mutex err_mu;
+    std::exception_ptr err;
+    auto lane = [&] {
+        for (;;) {
+            const size_t i = next.fetch_add(1);
+            if (i >= work.size()) { return; }
+            try {
+                run_chunk(work[i].first, work[i].second.first, work[i].second.second);
+            } catch (...) {
+                std::lock_guard<std::mutex> lk(err_mu);
+                if (!err) { err = std::current_exception(); }
+            }
+        }
+    };
+    std::vector<std::thread> ths;
+    for (size_t t = 1; t < lanes; ++t) { ths.emplace_back(lane); }
+    lane();
+    for (auto &t : ths) { t.join(); }
+    if (err) { std::rethrow_exception(err); }
 }
 
 void session::all_reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,

