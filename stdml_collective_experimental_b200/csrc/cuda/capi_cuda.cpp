@@ -38,6 +38,11 @@ int guarded(F f)
 DeviceSession *S(void *h) { return static_cast<DeviceSession *>(h); }
 }  // namespace
 
+namespace stdml::collective::cuda
+{
+void set_last_error(const std::string &msg) { g_error = msg; }
+}  // namespace stdml::collective::cuda
+
 extern "C" {
 const char *stdmlc_last_error() { return g_error.c_str(); }
 

@@ -1,4 +1,5 @@
 // C ABI of the host runtime (loaded from Python with ctypes).
+#include <cstdio>
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -37,5 +38,264 @@ int stdmlc_reduce(void *x, const void *y, const void *z, unsigned long long coun
     } catch (const std::exception &) {
         return 2;
     }
+}
+}
+
+// ------------------------------------------------------------ peer / session
+#include <memory>
+#include <optional>
+#include <vector>
+
+#include <stdml/bits/collective/peer.hpp>
+#include <stdml/bits/collective/stat.hpp>
+
+namespace stdml::collective::cuda
+{
+void set_last_error(const std::string &msg);  // cuda/capi_cuda.cpp
+}
+
+namespace
+{
+template <typename F>
+int host_guarded(F f)
+{
+    try {
+        f();
+        return 0;
+    } catch (const std::invalid_argument &e) {
+        sc::cuda::set_last_error(e.what());
+        return 2;
+    } catch (const std::exception &e) {
+        sc::cuda::set_last_error(e.what());
+        return 1;
+    }
+}
+
+struct session_box {
+    std::unique_ptr<sc::session> s;
+};
+
+sc::session &SS(void *h) { return *static_cast<session_box *>(h)->s; }
+}  // namespace
+
+extern "C" {
+int stdmlc_peer_from_env(void **out)
+{
+    *out = nullptr;
+    return host_guarded([&] { *out = new sc::peer(sc::peer::from_env()); });
+}
+
+int stdmlc_peer_create(void **out, int rank, const char *peers_csv, int strategy,
+                       unsigned long long version, const char *runners_csv)
+{
+    *out = nullptr;
+    return host_guarded([&] {
+        const auto peers = sc::parse_peer_list(peers_csv ? peers_csv : "");
+        const auto runners = sc::parse_peer_list(runners_csv ? runners_csv : "");
+        if (!peers || !runners || peers->empty()) {
+            throw std::invalid_argument("peer: malformed peer list");
+        }
+        *out = new sc::peer(sc::peer::from_list(static_cast<size_t>(rank), *peers,
+                                                strategy == 1 ? sc::ring : sc::star, version,
+                                                *runners));
+    });
+}
+
+int stdmlc_peer_destroy(void *p)
+{
+    return host_guarded([&] { delete static_cast<sc::peer *>(p); });
+}
+
+int stdmlc_peer_self(void *p, char *buf, unsigned long long size)
+{
+    return host_guarded([&] {
+        const std::string s = static_cast<sc::peer *>(p)->self().str();
+        std::snprintf(buf, size, "%s", s.c_str());
+    });
+}
+
+int stdmlc_peer_join(void *p, void **sess)
+{
+    *sess = nullptr;
+    return host_guarded([&] {
+        auto box = std::make_unique<session_box>();
+        box->s = static_cast<sc::peer *>(p)->join_elastic();
+        *sess = box.release();
+    });
+}
+
+int stdmlc_session_destroy(void *s)
+{
+    return host_guarded([&] { delete static_cast<session_box *>(s); });
+}
+
+// what: 0 rank, 1 size, 2 version, 3 strategy (0 star, 1 ring)
+int stdmlc_session_info(void *s, int what, unsigned long long *out)
+{
+    return host_guarded([&] {
+        sc::session &ss = SS(s);
+        switch (what) {
+        case 0:
+            *out = ss.rank();
+            break;
+        case 1:
+            *out = ss.size();
+            break;
+        case 2:
+            *out = ss.version();
+            break;
+        case 3:
+            *out = ss.get_strategy() == sc::ring ? 1 : 0;
+            break;
+        default:
+            throw std::invalid_argument("session_info: unknown item");
+        }
+    });
+}
+
+int stdmlc_session_cluster_json(void *s, char *buf, unsigned long long size)
+{
+    return host_guarded([&] {
+        const std::string js = SS(s).cluster().json();
+        if (js.size() + 1 > size) { throw std::invalid_argument("cluster_json: buffer too small"); }
+        std::snprintf(buf, size, "%s", js.c_str());
+    });
+}
+
+int stdmlc_session_all_reduce(void *s, const void *in, void *out, unsigned long long count, int dt,
+                              int op, const char *name, void *stream)
+{
+    return host_guarded([&] {
+        SS(s).all_reduce(in, out, count, static_cast<sc::dtype>(dt), static_cast<sc::reduce_op>(op),
+                         name ? name : "", stream);
+    });
+}
+
+int stdmlc_session_reduce(void *s, const void *in, void *out, unsigned long long count, int dt,
+                          int op, const char *name, void *stream)
+{
+    return host_guarded([&] {
+        SS(s).reduce(in, out, count, static_cast<sc::dtype>(dt), static_cast<sc::reduce_op>(op),
+                     name ? name : "", stream);
+    });
+}
+
+int stdmlc_session_group_all_reduce(void *s, unsigned long long n, const void *const *ins,
+                                    void *const *outs, const unsigned long long *counts, int dt,
+                                    int op, const char *const *names, double scale, void *stream)
+{
+    return host_guarded([&] {
+        std::vector<sc::workspace> ws(n);
+        for (size_t i = 0; i < n; ++i) {
+            ws[i].send = ins[i];
+            ws[i].recv = outs[i];
+            ws[i].count = counts[i];
+            ws[i].dt = static_cast<sc::dtype>(dt);
+            ws[i].op = static_cast<sc::reduce_op>(op);
+            ws[i].name = names != nullptr && names[i] != nullptr ? names[i]
+                                                                 : "tensor:" + std::to_string(i);
+        }
+        SS(s).group_all_reduce(ws, scale, stream);
+    });
+}
+
+int stdmlc_session_all_gather(void *s, const void *in, void *out, unsigned long long count, int dt,
+                              const char *name, void *stream)
+{
+    return host_guarded([&] {
+        SS(s).all_gather(in, out, count, static_cast<sc::dtype>(dt), name ? name : "", stream);
+    });
+}
+
+int stdmlc_session_gather(void *s, const void *in, void *out, unsigned long long count, int dt,
+                          const char *name)
+{
+    return host_guarded(
+        [&] { SS(s).gather(in, out, count, static_cast<sc::dtype>(dt), name ? name : ""); });
+}
+
+int stdmlc_session_broadcast(void *s, const void *in, void *out, unsigned long long count, int dt,
+                             const char *name, void *stream)
+{
+    return host_guarded([&] {
+        SS(s).broadcast(in, out, count, static_cast<sc::dtype>(dt), name ? name : "", stream);
+    });
+}
+
+int stdmlc_session_send(void *s, const void *in, unsigned long long count, int dt, int target,
+                        const char *name)
+{
+    return host_guarded([&] {
+        SS(s).send(in, count, static_cast<sc::dtype>(dt), static_cast<size_t>(target),
+                   name ? name : "");
+    });
+}
+
+int stdmlc_session_recv(void *s, void *out, unsigned long long count, int dt, int target,
+                        const char *name)
+{
+    return host_guarded([&] {
+        SS(s).recv(out, count, static_cast<sc::dtype>(dt), static_cast<size_t>(target),
+                   name ? name : "");
+    });
+}
+
+int stdmlc_session_barrier(void *s)
+{
+    return host_guarded([&] { SS(s).barrier(); });
+}
+
+int stdmlc_session_consistent(void *s, const void *data, unsigned long long size, int *same)
+{
+    return host_guarded([&] { *same = SS(s).consistent(data, size) ? 1 : 0; });
+}
+
+// new_size >= 0: propose it to the config server first; < 0: follow the server.
+// cluster_json != NULL: use this configuration instead of the config server.
+int stdmlc_peer_resize(void *p, void *sess, long long new_size, const char *cluster_json,
+                       int *changed, int *detached)
+{
+    return host_guarded([&] {
+        auto *peer = static_cast<sc::peer *>(p);
+        auto *box = static_cast<session_box *>(sess);
+        sc::resize_result r{false, false};
+        if (cluster_json != nullptr) {
+            const auto cfg = sc::cluster_config::from_json(cluster_json);
+            if (!cfg) { throw std::invalid_argument("resize: malformed cluster JSON"); }
+            r = peer->resize(box->s, [cfg] { return std::optional<sc::cluster_config>(*cfg); });
+        } else if (new_size >= 0) {
+            r = peer->resize(box->s, static_cast<size_t>(new_size));
+        } else {
+            r = peer->resize(box->s);
+        }
+        *changed = r.changed ? 1 : 0;
+        *detached = r.detached ? 1 : 0;
+    });
+}
+
+int stdmlc_cluster_resize_json(const char *cluster_json, unsigned long long new_size, char *buf,
+                               unsigned long long size)
+{
+    return host_guarded([&] {
+        const auto cfg = sc::cluster_config::from_json(cluster_json);
+        if (!cfg) { throw std::invalid_argument("malformed cluster JSON"); }
+        const std::string js = cfg->resize(new_size).json();
+        if (js.size() + 1 > size) { throw std::invalid_argument("buffer too small"); }
+        std::snprintf(buf, size, "%s", js.c_str());
+    });
+}
+
+void stdmlc_trace_enable(int on)
+{
+    if (on) {
+        sc::rchan::stat_enable();
+    } else {
+        sc::rchan::stat_disable();
+    }
+}
+
+int stdmlc_trace_write(const char *path)
+{
+    return sc::rchan::stat_write_chrome_trace(path) ? 0 : 1;
 }
 }

@@ -1,0 +1,278 @@
+"""Python face of the native peer / session model.
+
+    peer = Peer.from_env()          # KungFu, OpenMPI or torchrun variables
+    sess = peer.join()
+    sess.all_reduce(t)              # torch tensor, CPU (TCP path) or CUDA (NVLink kernels)
+
+Mirrors the reference's C++ API (include/stdml/bits/collective/peer.hpp:16-73,
+session.hpp:25-178): all_reduce / group_all_reduce / all_gather / broadcast /
+reduce / gather / send / recv / consistent / barrier and the elastic
+`peer.resize(sess, ...)`.  CUDA tensors are enqueued on the current CUDA stream.
+"""
+import ctypes
+import json
+
+import torch
+
+from .. import _native
+from ..ops.device import dtype_code, op_code
+
+_declared = False
+
+
+def _lib():
+    global _declared
+    lib = _native.lib()
+    if not _declared:
+        c = ctypes
+        vp, vpp, u64 = c.c_void_p, c.POINTER(c.c_void_p), c.c_ulonglong
+        lib.stdmlc_peer_from_env.argtypes = [vpp]
+        lib.stdmlc_peer_create.argtypes = [vpp, c.c_int, c.c_char_p, c.c_int, u64, c.c_char_p]
+        lib.stdmlc_peer_destroy.argtypes = [vp]
+        lib.stdmlc_peer_self.argtypes = [vp, c.c_char_p, u64]
+        lib.stdmlc_peer_join.argtypes = [vp, vpp]
+        lib.stdmlc_session_destroy.argtypes = [vp]
+        lib.stdmlc_session_info.argtypes = [vp, c.c_int, c.POINTER(u64)]
+        lib.stdmlc_session_cluster_json.argtypes = [vp, c.c_char_p, u64]
+        lib.stdmlc_session_all_reduce.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p, vp]
+        lib.stdmlc_session_reduce.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p, vp]
+        lib.stdmlc_session_group_all_reduce.argtypes = [
+            vp, u64, vpp, vpp, c.POINTER(u64), c.c_int, c.c_int, c.POINTER(c.c_char_p),
+            c.c_double, vp]
+        lib.stdmlc_session_all_gather.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p, vp]
+        lib.stdmlc_session_gather.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p]
+        lib.stdmlc_session_broadcast.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p, vp]
+        lib.stdmlc_session_send.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
+        lib.stdmlc_session_recv.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
+        lib.stdmlc_session_barrier.argtypes = [vp]
+        lib.stdmlc_session_consistent.argtypes = [vp, vp, u64, c.POINTER(c.c_int)]
+        lib.stdmlc_peer_resize.argtypes = [vp, vp, c.c_longlong, c.c_char_p, c.POINTER(c.c_int),
+                                           c.POINTER(c.c_int)]
+        lib.stdmlc_cluster_resize_json.argtypes = [c.c_char_p, u64, c.c_char_p, u64]
+        lib.stdmlc_trace_enable.argtypes = [c.c_int]
+        lib.stdmlc_trace_write.argtypes = [c.c_char_p]
+        _declared = True
+    return lib
+
+
+def _stream_of(t):
+    if t.is_cuda:
+        return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    return None
+
+
+def _checked(t, what):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{what}: torch tensor expected")
+    if not t.is_contiguous():
+        raise ValueError(f"{what}: contiguous tensor expected")
+    return t
+
+
+class Session:
+    """One fixed membership.  Created by Peer.join(); replaced in place by Peer.resize()."""
+
+    def __init__(self, handle):
+        self._h = handle
+        self._lib = _lib()
+
+    def _info(self, what):
+        v = ctypes.c_ulonglong()
+        _native.check(self._lib.stdmlc_session_info(self._h, what, ctypes.byref(v)))
+        return int(v.value)
+
+    @property
+    def rank(self):
+        return self._info(0)
+
+    @property
+    def size(self):
+        return self._info(1)
+
+    @property
+    def version(self):
+        return self._info(2)
+
+    @property
+    def strategy(self):
+        return "ring" if self._info(3) == 1 else "star"
+
+    @property
+    def cluster(self):
+        """{"Runners": [...], "Workers": [...]} of this session."""
+        buf = ctypes.create_string_buffer(1 << 16)
+        _native.check(self._lib.stdmlc_session_cluster_json(self._h, buf, len(buf)))
+        return json.loads(buf.value.decode())
+
+    def close(self):
+        if self._h is not None:
+            h, self._h = self._h, None
+            _native.check(self._lib.stdmlc_session_destroy(h))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------ collectives
+    def all_reduce(self, tensor, out=None, op="sum", name=""):
+        t = _checked(tensor, "all_reduce")
+        o = t if out is None else _checked(out, "all_reduce")
+        _native.check(self._lib.stdmlc_session_all_reduce(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), op_code(op),
+            name.encode(), _stream_of(t)))
+        return o
+
+    def reduce(self, tensor, out=None, op="sum", name=""):
+        """Result on rank 0 only (the reference's fixed root)."""
+        t = _checked(tensor, "reduce")
+        o = t if out is None else _checked(out, "reduce")
+        _native.check(self._lib.stdmlc_session_reduce(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), op_code(op),
+            name.encode(), _stream_of(t)))
+        return o
+
+    def group_all_reduce(self, tensors, outs=None, op="sum", scale=None, names=None):
+        """All tensors of a gradient set in one call (CUDA: one fused launch per
+        staging slot; CPU: pipelined, deadlock-free for any arrival order)."""
+        ts = [_checked(t, "group_all_reduce") for t in tensors]
+        os_ = ts if outs is None else [_checked(t, "group_all_reduce") for t in outs]
+        if not ts:
+            return tensors
+        n = len(ts)
+        ins = (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+        out_ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in os_])
+        counts = (ctypes.c_ulonglong * n)(*[t.numel() for t in ts])
+        cnames = None
+        if names is not None:
+            cnames = (ctypes.c_char_p * n)(*[s.encode() for s in names])
+        _native.check(self._lib.stdmlc_session_group_all_reduce(
+            self._h, n, ins, out_ptrs, counts, dtype_code(ts[0].dtype), op_code(op), cnames,
+            1.0 if scale is None else float(scale), _stream_of(ts[0])))
+        return outs if outs is not None else tensors
+
+    def all_gather(self, tensor, out, name=""):
+        t, o = _checked(tensor, "all_gather"), _checked(out, "all_gather")
+        if o.numel() != t.numel() * self.size:
+            raise ValueError("all_gather: out must hold size * tensor.numel() elements")
+        _native.check(self._lib.stdmlc_session_all_gather(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), name.encode(),
+            _stream_of(t)))
+        return o
+
+    def gather(self, tensor, out, name=""):
+        t, o = _checked(tensor, "gather"), _checked(out, "gather")
+        _native.check(self._lib.stdmlc_session_gather(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), name.encode()))
+        return o
+
+    def broadcast(self, tensor, out=None, name=""):
+        """From rank 0 to everyone."""
+        t = _checked(tensor, "broadcast")
+        o = t if out is None else _checked(out, "broadcast")
+        _native.check(self._lib.stdmlc_session_broadcast(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), name.encode(),
+            _stream_of(t)))
+        return o
+
+    def send(self, tensor, target, name=""):
+        t = _checked(tensor, "send")
+        _native.check(self._lib.stdmlc_session_send(
+            self._h, t.data_ptr(), t.numel(), dtype_code(t.dtype), target, name.encode()))
+
+    def recv(self, out, source, name=""):
+        o = _checked(out, "recv")
+        _native.check(self._lib.stdmlc_session_recv(
+            self._h, o.data_ptr(), o.numel(), dtype_code(o.dtype), source, name.encode()))
+        return o
+
+    def barrier(self):
+        _native.check(self._lib.stdmlc_session_barrier(self._h))
+
+    def consistent(self, data):
+        """True when every rank holds the same bytes."""
+        if isinstance(data, torch.Tensor):
+            t = data.detach().cpu().contiguous()
+            ptr, size = t.data_ptr(), t.numel() * t.element_size()
+            keep = t
+        else:
+            keep = ctypes.create_string_buffer(bytes(data), len(data))
+            ptr, size = ctypes.addressof(keep), len(data)
+        same = ctypes.c_int()
+        _native.check(self._lib.stdmlc_session_consistent(self._h, ptr, size, ctypes.byref(same)))
+        del keep
+        return bool(same.value)
+
+
+class Peer:
+    def __init__(self, handle):
+        self._h = handle
+        self._lib = _lib()
+
+    @classmethod
+    def from_env(cls):
+        h = ctypes.c_void_p()
+        _native.check(_lib().stdmlc_peer_from_env(ctypes.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def from_list(cls, rank, peers, strategy="star", version=0, runners=()):
+        """peers / runners: 'ip:port' strings."""
+        h = ctypes.c_void_p()
+        _native.check(_lib().stdmlc_peer_create(
+            ctypes.byref(h), rank, ",".join(peers).encode(), 1 if strategy == "ring" else 0,
+            version, ",".join(runners).encode()))
+        return cls(h)
+
+    @property
+    def self_id(self):
+        buf = ctypes.create_string_buffer(64)
+        _native.check(self._lib.stdmlc_peer_self(self._h, buf, len(buf)))
+        return buf.value.decode()
+
+    def join(self):
+        s = ctypes.c_void_p()
+        _native.check(self._lib.stdmlc_peer_join(self._h, ctypes.byref(s)))
+        return Session(s)
+
+    def resize(self, sess, new_size=None, cluster=None):
+        """Change the membership of `sess` in place.
+
+        new_size: propose that many workers to the config server, then follow it;
+        cluster: an explicit {"Runners": [...], "Workers": [...]} dict (no server);
+        neither: follow the config server.  Returns (changed, detached)."""
+        changed, detached = ctypes.c_int(), ctypes.c_int()
+        js = None if cluster is None else json.dumps(cluster).encode()
+        _native.check(self._lib.stdmlc_peer_resize(
+            self._h, sess._h, -1 if new_size is None else int(new_size), js,
+            ctypes.byref(changed), ctypes.byref(detached)))
+        return bool(changed.value), bool(detached.value)
+
+    def close(self):
+        if self._h is not None:
+            h, self._h = self._h, None
+            _native.check(self._lib.stdmlc_peer_destroy(h))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def resized_cluster(cluster, new_size):
+    """cluster_config::resize on a {"Runners", "Workers"} dict."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    _native.check(_lib().stdmlc_cluster_resize_json(json.dumps(cluster).encode(), new_size, buf,
+                                                    len(buf)))
+    return json.loads(buf.value.decode())
+
+
+def enable_trace(on=True):
+    _lib().stdmlc_trace_enable(1 if on else 0)
+
+
+def write_trace(path):
+    """Chrome-trace JSON of the recorded events."""
+    return _lib().stdmlc_trace_write(path.encode()) == 0

@@ -1,0 +1,68 @@
+"""One rank of the Python host-API test (spawned by test_python_api.py)."""
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from stdml_collective_experimental_b200.parallel import Peer, resized_cluster  # noqa: E402
+
+
+def main():
+    rank, n, base = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+    strategy = sys.argv[4]
+    peers = [f"127.0.0.1:{base + i}" for i in range(n)]
+    peer = Peer.from_list(rank, peers, strategy=strategy)
+    sess = peer.join()
+    assert (sess.rank, sess.size, sess.version, sess.strategy) == (rank, n, 0, strategy)
+
+    x = torch.arange(1000, dtype=torch.float32) + rank
+    y = torch.empty_like(x)
+    sess.all_reduce(x, out=y, name="x")
+    assert torch.equal(y, torch.arange(1000, dtype=torch.float32) * n + n * (n - 1) / 2)
+    h = torch.full((33,), rank + 0.5, dtype=torch.bfloat16)
+    sess.all_reduce(h, op="max")
+    assert torch.all(h == n - 0.5)
+
+    grads = [torch.full((k,), float(rank + i)) for i, k in enumerate([3, 70000, 1, 512])]
+    sess.group_all_reduce(grads, scale=1.0 / n, names=[f"g{i}" for i in range(4)])
+    for i, g in enumerate(grads):
+        assert torch.allclose(g, torch.full_like(g, (n - 1) / 2 + i))
+
+    out = torch.empty(n * 5, dtype=torch.int64)
+    sess.all_gather(torch.full((5,), rank, dtype=torch.int64), out)
+    assert out.tolist() == [r for r in range(n) for _ in range(5)]
+    b = torch.full((7,), float(rank))
+    sess.broadcast(b)
+    assert torch.all(b == 0)
+    r = torch.full((4,), float(rank))
+    ro = torch.full((4,), -1.0)
+    sess.reduce(r, out=ro)
+    assert torch.all(ro == (n * (n - 1) / 2 if rank == 0 else -1))
+    assert sess.consistent(b) and (n == 1 or not sess.consistent(torch.tensor([rank])))
+    if n > 1:
+        if rank == 0:
+            sess.send(torch.tensor([42.0]), 1, name="p2p")
+        elif rank == 1:
+            assert sess.recv(torch.zeros(1), 0, name="p2p").item() == 42.0
+    sess.barrier()
+
+    # elastic: shrink to n - 1 by explicit configuration; the last rank detaches
+    if n > 2:
+        smaller = resized_cluster(sess.cluster, n - 1)
+        changed, detached = peer.resize(sess, cluster=smaller)
+        assert changed
+        if rank == n - 1:
+            assert detached
+        else:
+            assert not detached and sess.size == n - 1 and sess.version == 1
+            assert sess.all_reduce(torch.ones(3))[0] == n - 1
+    sess.close()
+    peer.close()
+    print(f"rank {rank} OK", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -14,12 +14,12 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def run_world(n, port, extra_env=None, timeout=600):
+def run_world(n, port, extra_env=None, timeout=600, worker="multigpu_worker.py"):
     env = dict(os.environ)
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
-           os.path.join(HERE, "multigpu_worker.py")]
+           os.path.join(HERE, worker)]
     res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                          timeout=timeout)
     assert res.returncode == 0, res.stdout[-4000:]
@@ -39,3 +39,9 @@ def test_multigpu_ipc_backend_without_nvls():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_world(2, 29631, {"STDML_COLLECTIVE_SYMM": "ipc", "STDML_COLLECTIVE_NVLS": "0"})
+
+
+def test_data_parallel_matches_single_process_training():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_world(2, 29641, worker="ddp_worker.py")
