@@ -1,0 +1,61 @@
+"""A small, self-ending case of the fused all-reduce kernel on ONE GPU, sized for
+profilers: `--world` ranks emulated in one cooperative launch (loopback world),
+a symmetric buffer of `--mb` MiB per rank reduced in place, `--iters` launches.
+
+    python -m stdml_collective_experimental_b200.benchmarks.kernel_case --world 4 --mb 64 --algo twoshot
+
+Prints the device time per launch (CUDA events) and the bytes each launch must
+move through HBM, so that an achieved fraction of the copy bandwidth can be
+stated next to the profiler's counters.
+"""
+import argparse
+import json
+
+import torch
+
+from .. import DeviceSession
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--world", type=int, default=4)
+    ap.add_argument("--mb", type=int, default=64)
+    ap.add_argument("--dtype", default="f32")
+    ap.add_argument("--algo", default="twoshot")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--blocks", type=int, default=0)
+    args = ap.parse_args()
+    dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
+    es = 4 if args.dtype == "f32" else 2
+    n = (args.mb << 20) // es
+    sess = DeviceSession.loopback(args.world, heap_bytes=(args.mb << 20) + (8 << 20),
+                                  staging_bytes=1 << 20)
+    if args.blocks:
+        sess.set_tuning(max_blocks=args.blocks)
+    sym = sess.symm_empty(n, dtype)
+    bufs = sym if args.world > 1 else [sym]
+    for r, b in enumerate(bufs):
+        b.fill_(r + 1)
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(args.iters + 1)]
+    e[0].record()
+    for i in range(args.iters):
+        sess.all_reduce(sym, scale=1.0 / args.world, algo=args.algo)
+        e[i + 1].record()
+    torch.cuda.synchronize()
+    sess.check()
+    times = [e[i].elapsed_time(e[i + 1]) for i in range(args.iters)]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    # per launch: every rank's buffer is read once and written once
+    hbm_bytes = 2 * args.world * n * es
+    print(json.dumps({"world": args.world, "mb_per_rank": args.mb, "algo": args.algo,
+                      "ms_per_launch": times, "best_ms": best,
+                      "hbm_bytes_per_launch": hbm_bytes,
+                      "achieved_gb_s": hbm_bytes / (best * 1e-3) / 1e9}))
+    want = sum(range(1, args.world + 1)) / args.world
+    assert abs(float(bufs[0][0]) - want) < 1e-3 or args.iters > 1
+    sess.close()
+
+
+if __name__ == "__main__":
+    main()
