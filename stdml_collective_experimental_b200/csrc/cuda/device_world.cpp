@@ -353,7 +353,8 @@ class World final : public DeviceWorld
             // the switch saturates with few CTAs; more only add contention
             cap = std::min<size_t>(cap, nvec * 16 >= (16u << 20) ? 32 : 64);
         }
-        if (opt_.world == 1) { cap = std::max<size_t>(cap, 4 * static_cast<size_t>(num_sms_)); }
+        // alone on the GPU the kernel is an HBM copy: one resident CTA per SM
+        if (opt_.world == 1) { cap = static_cast<size_t>(num_sms_); }
         if (vranks_ > 1) { cap = std::min<size_t>(cap, std::max(1, num_sms_ / vranks_)); }
         b = std::max<size_t>(1, std::min(b, std::min<size_t>(cap, kMaxBlocks)));
         return static_cast<int>(b);
