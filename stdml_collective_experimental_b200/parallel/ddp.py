@@ -44,7 +44,14 @@ class DataParallel(torch.nn.Module):
         self.flat = sess.symm_empty(total, self.dtype)
         self.flat.zero_()
         for p, off in zip(self.params, offs):
-            p.grad = self.flat[off:off + p.numel()].view_as(p)
+            # same strides as the parameter (e.g. channels_last), so autograd
+            # accumulates in place without a layout conversion
+            dense = p.is_contiguous() or p.is_contiguous(memory_format=torch.channels_last) \
+                if p.dim() == 4 else p.is_contiguous()
+            if dense:
+                p.grad = torch.as_strided(self.flat, p.size(), p.stride(), off)
+            else:
+                p.grad = self.flat[off:off + p.numel()].view_as(p)
         # contiguous buckets of about equal bytes, in readiness order
         nb = max(1, min(buckets, len(self.params)))
         target = total / nb
