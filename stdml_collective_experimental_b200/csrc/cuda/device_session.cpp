@@ -156,9 +156,16 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         k.src = src.data();
         k.dst = dst.data();
         k.count = n;
-        // small: root pulls everything; large: owners reduce their shard and
-        // store it to root only, which spreads the reads over all links
-        k.algo = (n * es <= (1u << 20) || world_->world() == 1) ? kAlgoOneShot : kAlgoTwoShot;
+        // small (or two ranks): root pulls everything; large: the switch reduces
+        // for root, or owners reduce their shard and store it to root only,
+        // which spreads the reads over all links
+        if (n * es <= (1u << 20) || world_->world() <= 2) {
+            k.algo = kAlgoOneShot;
+        } else if (world_->has_nvls() && nvls_supported(dt, op)) {
+            k.algo = kAlgoNvlsOneShot;  // root alone pulls the switch-reduced data
+        } else {
+            k.algo = kAlgoTwoShot;
+        }
         launch_ar(k, stream);
     }
 }
