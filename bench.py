@@ -148,10 +148,13 @@ def run_ours(args):
                    str(29500 + os.getpid() % 400)] + sys.argv
             return subprocess.call(cmd)
         raise SystemExit(f"WORLD_SIZE={world} but --gpus {n}")
+    from stdml_collective_experimental_b200.utils.numa import bind_to_gpu_numa
+    numa_node = bind_to_gpu_numa(local)  # before any pinned allocation
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if n > 1:
         dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local)  # NVML set-up stays outside the timed region
 
     def host_barrier():
         if n > 1:
@@ -207,12 +210,12 @@ def run_ours(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    sampler.start()
     torch.cuda.synchronize()
     host_barrier()
-    sampler = ClockSampler(local).start()
+    sess.barrier()  # ranks leave the host barrier at different times: line them up on the device
     launches0 = sess.launches
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    torch.cuda.synchronize()
     ev[0].record()
     for i in range(args.steps):
         step()
@@ -258,7 +261,7 @@ def run_ours(args):
                    "set_bytes": set_bytes, "global_batch": None, "seq_len": None,
                    "parallelism": f"dp{n}", "op": "sum, scale 1/N fused",
                    "memory": "symmetric heap (zero-copy)", "nvls": sess.has_nvls,
-                   "backend": sess.backend,
+                   "backend": sess.backend, "numa_node": numa_node,
                    "l2": "inputs (438 MB per rank) are larger than the 126 MB L2; no flush"},
     }
     if rank == 0:

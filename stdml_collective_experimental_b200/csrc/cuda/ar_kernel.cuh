@@ -286,8 +286,21 @@ __global__ void __launch_bounds__(kThreads)
                                    unsigned long long hi) {
                                    if (e.src == nullptr) { return; }
                                    const bool al = ptr_aligned16(e.src);
-                                   for (unsigned long long v = lo + threadIdx.x; v < hi;
-                                        v += kThreads) {
+                                   unsigned long long v = lo + threadIdx.x;
+                                   for (; v + 3ull * kThreads < hi; v += 4ull * kThreads) {
+                                       uint4 x[4];
+#pragma unroll
+                                       for (int u = 0; u < 4; ++u) {
+                                           x[u] = load_user_vec<DT>(e.src, user_f32,
+                                                                    v + u * kThreads - e.voff,
+                                                                    e.count, al);
+                                       }
+#pragma unroll
+                                       for (int u = 0; u < 4; ++u) {
+                                           st_arena_v4(mine + (v + u * kThreads) * 16ull, x[u]);
+                                       }
+                                   }
+                                   for (; v < hi; v += kThreads) {
                                        st_arena_v4(mine + v * 16ull,
                                                    load_user_vec<DT>(e.src, user_f32, v - e.voff,
                                                                      e.count, al));
@@ -350,8 +363,21 @@ __global__ void __launch_bounds__(kThreads)
                                    unsigned long long hi) {
                                    if (e.dst == nullptr) { return; }
                                    const bool al = ptr_aligned16(e.dst);
-                                   for (unsigned long long v = lo + threadIdx.x; v < hi;
-                                        v += kThreads) {
+                                   unsigned long long v = lo + threadIdx.x;
+                                   for (; v + 3ull * kThreads < hi; v += 4ull * kThreads) {
+                                       uint4 x[4];
+#pragma unroll
+                                       for (int u = 0; u < 4; ++u) {
+                                           x[u] = ld_arena_v4(mine + (v + u * kThreads) * 16ull);
+                                       }
+#pragma unroll
+                                       for (int u = 0; u < 4; ++u) {
+                                           store_user_vec<DT>(e.dst, user_f32,
+                                                              v + u * kThreads - e.voff, e.count,
+                                                              al, x[u]);
+                                       }
+                                   }
+                                   for (; v < hi; v += kThreads) {
                                        store_user_vec<DT>(e.dst, user_f32, v - e.voff, e.count,
                                                           al, ld_arena_v4(mine + v * 16ull));
                                    }

@@ -103,6 +103,13 @@ struct GatherArgs {
     unsigned long long stride;  // distance between rank blocks in dst (all_gather)
     int root;                   // < 0: all_gather; >= 0: broadcast from `root`
     int end_barrier;
+    int algo;                   // broadcast only: see kBcast*
+};
+
+enum : int {
+    kBcastPull = 0,     // everybody reads root's slot (small messages)
+    kBcastNvls = 1,     // root multimem.st once, everybody copies its own slot
+    kBcastScatter = 2,  // rank r pulls slice r from root, then all ranks exchange slices
 };
 
 // kernels_misc.cu

@@ -326,7 +326,8 @@ class World final : public DeviceWorld
     size_t nvls_oneshot_limit() const
     {
         if (nvls_oneshot_max_ != 0) { return nvls_oneshot_max_; }
-        return opt_.world <= 4 ? (256u << 10) : (64u << 10);
+        return 2u << 20;  // only staged / out-of-place calls can take it; beats a
+                          // staged owner algorithm up to a few MB
     }
 
     int pick_algo(size_t bytes, int dt, int op, bool need_owner) const override
@@ -411,7 +412,19 @@ class World final : public DeviceWorld
         if (nvls && (!has_nvls() || !nvls_supported(c.dt, c.op))) {
             throw std::invalid_argument("all_reduce: NVLS not available for this dtype/op/world");
         }
+        bool staged = false;
+        for (int v = 0; v < vranks_; ++v) {
+            staged = staged || (c.table != nullptr && c.table[v] != nullptr) ||
+                     (c.src != nullptr && c.src[v] != nullptr);
+        }
         int blocks = c.blocks > 0 ? c.blocks : pick_blocks(nvec, algo);
+        if (c.blocks <= 0 && nvls && (staged || c.root >= 0)) {
+            // the pack / unpack phases are plain HBM copies and a root-only pull
+            // has the switch to itself: both want the full grid, not the small
+            // one that suits all ranks pulling through the switch together
+            blocks = std::max(blocks, pick_blocks(nvec, algo == kAlgoNvls ? kAlgoTwoShot
+                                                                          : kAlgoOneShot));
+        }
         if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
         blocks = std::min(blocks, kMaxBlocks);
 
@@ -456,6 +469,18 @@ class World final : public DeviceWorld
         a.stride = c.stride != 0 ? c.stride : c.bytes;
         a.root = c.root;
         a.end_barrier = c.end_barrier ? 1 : 0;
+        a.algo = kBcastPull;
+        if (c.root >= 0 && opt_.world > 2) {
+            // measured: pulling from root costs (n-1) copies on root's links
+            if (c.algo >= 0) {
+                a.algo = c.algo;
+            } else if (c.bytes >= (256u << 10)) {
+                a.algo = has_nvls() ? kBcastNvls : kBcastScatter;
+            }
+            if (a.algo == kBcastNvls && !has_nvls()) {
+                throw std::invalid_argument("broadcast: NVLS is not available");
+            }
+        }
         int blocks = c.blocks > 0 ? c.blocks : pick_blocks(nvec, kAlgoOneShot);
         if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
         return launch_gather(make_ctx(), a, blocks, vranks_, stream);

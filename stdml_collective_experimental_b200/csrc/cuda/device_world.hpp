@@ -72,6 +72,7 @@ struct GatherCall {
     size_t stride = 0;  // all_gather: distance between rank blocks in dst (0: bytes)
     int root = -1;
     int blocks = 0;
+    int algo = -1;  // broadcast: -1 pick, else kBcast*
     bool end_barrier = false;
 };
 

@@ -57,8 +57,27 @@ void launch_barrier(const CommCtx &ctx, int vranks, void *stream)
 }
 
 // One block per rank of `bytes` bytes.  all_gather: every rank packs its block
-// into its arena slot, then pulls every peer's slot into dst + peer * bytes.
-// broadcast: only `root` packs, everybody pulls root's slot into dst.
+// into its arena slot, then pulls every peer's slot into dst + peer * stride.
+// broadcast: three ways to get root's data to everybody, see kBcast*.
+__device__ __forceinline__ void copy_span_to_user(char *out, unsigned long long bytes,
+                                                  const char *from, const Span &sp)
+{
+    const bool al = ptr_aligned16(out);
+    unsigned long long v = sp.lo + threadIdx.x;
+    for (; v + 3ull * kThreads < sp.hi; v += 4ull * kThreads) {
+        uint4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { x[u] = ld_arena_v4(from + (v + u * kThreads) * 16ull); }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            store_user_vec<DT_U8>(out, false, v + u * kThreads, bytes, al, x[u]);
+        }
+    }
+    for (; v < sp.hi; v += kThreads) {
+        store_user_vec<DT_U8>(out, false, v, bytes, al, ld_arena_v4(from + v * 16ull));
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
     gather_kernel(const __grid_constant__ CommCtx ctx, const __grid_constant__ GatherArgs a)
 {
@@ -71,40 +90,68 @@ __global__ void __launch_bounds__(kThreads)
     sync_begin(ctx, rank, &sync);
 
     const unsigned long long nvec = (a.bytes + 15ull) / 16ull;
-    const Span sp = span_of(nvec, 1, 0, nb, b);
+    const Span whole = span_of(nvec, 1, 0, nb, b);
     char *mine = ctx.base[rank] + a.off;
     const void *src = a.src[vr];
-    if (src != nullptr && (a.root < 0 || a.root == rank)) {
-        const bool al = ptr_aligned16(src);
-        for (unsigned long long v = sp.lo + threadIdx.x; v < sp.hi; v += kThreads) {
-            st_arena_v4(mine + v * 16ull, load_user_vec<DT_U8>(src, false, v, a.bytes, al));
-        }
-    }
-
-    if (!peer_barrier(ctx, rank, &sync)) { return; }
-
     char *dst = static_cast<char *>(a.dst[vr]);
-    if (dst != nullptr) {
-        const int first = a.root < 0 ? 0 : a.root;
-        const int last = a.root < 0 ? world : a.root + 1;
-        for (int i = first; i < last; ++i) {
-            // start with the next rank so that peers do not all read the same GPU first
-            const int p = a.root < 0 ? (rank + 1 + i) % world : i;
-            char *out = a.root < 0 ? dst + static_cast<unsigned long long>(p) * a.stride : dst;
-            const char *from = ctx.base[p] + a.off;
-            const bool al = ptr_aligned16(out);
-            unsigned long long v = sp.lo + threadIdx.x;
-            for (; v + 3ull * kThreads < sp.hi; v += 4ull * kThreads) {
-                uint4 x[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) { x[u] = ld_arena_v4(from + (v + u * kThreads) * 16ull); }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    store_user_vec<DT_U8>(out, false, v + u * kThreads, a.bytes, al, x[u]);
+    const bool bcast = a.root >= 0;
+    const bool is_root = a.root == rank;
+
+    if (bcast && a.algo == kBcastNvls) {
+        // root stores every vector once; the switch replicates it into all slots
+        if (is_root) {
+            const bool al = src != nullptr && ptr_aligned16(src);
+            for (unsigned long long v = whole.lo + threadIdx.x; v < whole.hi; v += kThreads) {
+                const uint4 x = src != nullptr ? load_user_vec<DT_U8>(src, false, v, a.bytes, al)
+                                               : ld_arena_v4(mine + v * 16ull);
+                mm_st_v4(ctx.mc_base + a.off + v * 16ull, x);
+            }
+        }
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (dst != nullptr) { copy_span_to_user(dst, a.bytes, mine, whole); }
+    } else if (bcast && a.algo == kBcastScatter) {
+        // root packs; rank r fetches slice r from root; then everybody fetches
+        // every slice from its holder, so root's links carry ~2 copies, not n-1
+        if (is_root && src != nullptr) {
+            const bool al = ptr_aligned16(src);
+            for (int s = 0; s < world; ++s) {
+                const Span sp = span_of(nvec, world, s, nb, b);
+                for (unsigned long long v = sp.lo + threadIdx.x; v < sp.hi; v += kThreads) {
+                    st_arena_v4(mine + v * 16ull, load_user_vec<DT_U8>(src, false, v, a.bytes, al));
                 }
             }
-            for (; v < sp.hi; v += kThreads) {
-                store_user_vec<DT_U8>(out, false, v, a.bytes, al, ld_arena_v4(from + v * 16ull));
+        }
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (!is_root) {
+            const Span sp = span_of(nvec, world, rank, nb, b);
+            const char *from = ctx.base[a.root] + a.off;
+            for (unsigned long long v = sp.lo + threadIdx.x; v < sp.hi; v += kThreads) {
+                st_arena_v4(mine + v * 16ull, ld_arena_v4(from + v * 16ull));
+            }
+        }
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (dst != nullptr) {
+            for (int i = 0; i < world; ++i) {
+                const int s = (rank + i) % world;  // own slice first, then round the ranks
+                const Span sp = span_of(nvec, world, s, nb, b);
+                copy_span_to_user(dst, a.bytes, ctx.base[s] + a.off, sp);
+            }
+        }
+    } else {
+        if (src != nullptr && (!bcast || is_root)) {
+            const bool al = ptr_aligned16(src);
+            for (unsigned long long v = whole.lo + threadIdx.x; v < whole.hi; v += kThreads) {
+                st_arena_v4(mine + v * 16ull, load_user_vec<DT_U8>(src, false, v, a.bytes, al));
+            }
+        }
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (dst != nullptr) {
+            const int count = bcast ? 1 : world;
+            for (int i = 0; i < count; ++i) {
+                // start with the next rank so that peers do not all read the same GPU first
+                const int p = bcast ? a.root : (rank + 1 + i) % world;
+                char *out = bcast ? dst : dst + static_cast<unsigned long long>(p) * a.stride;
+                copy_span_to_user(out, a.bytes, ctx.base[p] + a.off, whole);
             }
         }
     }
