@@ -309,7 +309,15 @@ class server_impl final : public server
         setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
         sockaddr_in a = to_sockaddr(self_);
         a.sin_addr.s_addr = htonl(INADDR_ANY);
-        if (::bind(listen_fd_, reinterpret_cast<sockaddr *>(&a), sizeof(a)) != 0) {
+        // a predecessor on the same port (a rank that was removed and is being
+        // replaced, a previous job) may still be closing: give it a moment
+        int rc = -1;
+        for (int attempt = 0; attempt < 50; ++attempt) {
+            rc = ::bind(listen_fd_, reinterpret_cast<sockaddr *>(&a), sizeof(a));
+            if (rc == 0 || errno != EADDRINUSE) { break; }
+            std::this_thread::sleep_for(std::chrono::milliseconds(100));
+        }
+        if (rc != 0) {
             const std::string why = std::strerror(errno);
             ::close(listen_fd_);
             listen_fd_ = -1;
