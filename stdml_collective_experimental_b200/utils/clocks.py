@@ -14,7 +14,7 @@ _REASONS = {
 
 
 class ClockSampler:
-    def __init__(self, device_index=0, period_s=0.05):
+    def __init__(self, device_index=0, period_s=0.01):
         self.device_index = device_index
         self.period_s = period_s
         self.samples = []
@@ -33,9 +33,11 @@ class ClockSampler:
         except Exception:
             self._nvml = None
 
-    def _run(self):
+    def _sample(self):
         n = self._nvml
-        while not self._stop.is_set():
+        if n is None:
+            return
+        if True:
             try:
                 self.samples.append(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
                 mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle) if hasattr(
@@ -46,6 +48,10 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._sample()
             time.sleep(self.period_s)
 
     def start(self):
@@ -57,6 +63,7 @@ class ClockSampler:
 
     def stop(self):
         if self._thread is not None:
+            self._sample()  # one more while the GPU is still busy or just done
             self._stop.set()
             self._thread.join()
             self._thread = None
