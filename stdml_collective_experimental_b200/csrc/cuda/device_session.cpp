@@ -25,6 +25,20 @@ void rt_check(cudaError_t e, const char *what)
     }
 }
 
+// Inside a stream capture the two staging slots do not alternate across
+// replays (a graph with an odd number of staged calls would reuse one slot back
+// to back), so captured staged calls end with a barrier, which makes any reuse
+// of the slot safe.
+bool capturing(void *stream)
+{
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &st) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return st != cudaStreamCaptureStatusNone;
+}
+
 void launch_check(int rc, const char *what)
 {
     if (rc != 0) {
@@ -109,6 +123,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
     }
 
     // staged: pack into a staging slot inside the launch, one slot per chunk
+    const bool in_capture = capturing(stream);
     const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
     std::vector<const void *> src(vr);
     std::vector<void *> dst(vr);
@@ -123,6 +138,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
         k.src = src.data();
         k.dst = dst.data();
         k.count = n;
+        k.end_barrier = in_capture;
         launch_ar(k, stream);
     }
 }
@@ -156,6 +172,7 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         k.src = src.data();
         k.dst = dst.data();
         k.count = n;
+        k.end_barrier = capturing(stream);
         // small (or two ranks): root pulls everything; large: the switch reduces
         // for root, or owners reduce their shard and store it to root only,
         // which spreads the reads over all links
@@ -308,6 +325,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
         c.has_scale = scale != 1.0;
         c.scale = static_cast<float>(scale);
         c.algo = algo;
+        c.end_barrier = capturing(stream);
         launch_ar(c, stream);
     }
 }
@@ -334,6 +352,7 @@ void DeviceSession::all_gather(const void *const *in, void *const *out, size_t c
         g.dst = dst.data();
         g.bytes = nbytes;
         g.stride = bytes;
+        g.end_barrier = capturing(stream);
         launch_check(world_->gather(g, stream), "all_gather");
         ++launches_;
     }
@@ -363,6 +382,7 @@ void DeviceSession::broadcast(const void *const *in, void *const *out, size_t co
         g.dst = dst.data();
         g.bytes = nbytes;
         g.root = root;
+        g.end_barrier = capturing(stream);
         launch_check(world_->gather(g, stream), "broadcast");
         ++launches_;
     }

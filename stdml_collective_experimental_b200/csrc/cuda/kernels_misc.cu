@@ -101,7 +101,21 @@ __global__ void __launch_bounds__(kThreads)
         // root stores every vector once; the switch replicates it into all slots
         if (is_root) {
             const bool al = src != nullptr && ptr_aligned16(src);
-            for (unsigned long long v = whole.lo + threadIdx.x; v < whole.hi; v += kThreads) {
+            unsigned long long v = whole.lo + threadIdx.x;
+            for (; v + 3ull * kThreads < whole.hi; v += 4ull * kThreads) {
+                uint4 x[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const unsigned long long vu = v + u * kThreads;
+                    x[u] = src != nullptr ? load_user_vec<DT_U8>(src, false, vu, a.bytes, al)
+                                          : ld_arena_v4(mine + vu * 16ull);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    mm_st_v4(ctx.mc_base + a.off + (v + u * kThreads) * 16ull, x[u]);
+                }
+            }
+            for (; v < whole.hi; v += kThreads) {
                 const uint4 x = src != nullptr ? load_user_vec<DT_U8>(src, false, v, a.bytes, al)
                                                : ld_arena_v4(mine + v * 16ull);
                 mm_st_v4(ctx.mc_base + a.off + v * 16ull, x);

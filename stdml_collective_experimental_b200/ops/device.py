@@ -310,6 +310,46 @@ class DeviceSession:
     def barrier(self, stream=None):
         _native.check(self._lib.stdmlc_dw_barrier(self._h, self._stream(stream)))
 
+    # ---------------------------------------------------------- point to point
+    def _p2p_stream(self):
+        if getattr(self, "_p2p", None) is None:
+            self._p2p = torch.cuda.Stream(self.device)
+        return self._p2p
+
+    def send(self, tensor, dst):
+        """Point-to-point send of a CUDA tensor: NCCL p2p (torch.distributed) on a
+        stream of its own, so it overlaps the collectives of this session.  The
+        reference's send/recv (src/stdml/collective/send_recv.cpp:6-21) is the
+        rendezvous message of its TCP transport.  Returns a handle with wait()."""
+        return self._p2p_op(tensor, dst, True)
+
+    def recv(self, tensor, src):
+        return self._p2p_op(tensor, src, False)
+
+    def _p2p_op(self, tensor, peer, is_send):
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("send/recv of CUDA tensors needs torch.distributed (backend nccl)")
+        side = self._p2p_stream()
+        cur = torch.cuda.current_stream(self.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            if is_send:
+                dist.send(tensor, peer)
+            else:
+                dist.recv(tensor, peer)
+            done = torch.cuda.Event()
+            done.record(side)
+        tensor.record_stream(side)
+
+        class _Handle:
+            def wait(self_h, stream=None):
+                (stream or torch.cuda.current_stream(self.device)).wait_event(done)
+
+            def synchronize(self_h):
+                done.synchronize()
+        return _Handle()
+
     def barrier_rows(self, rows, stream=None):
         """Loopback only: barrier among the first `rows` emulated ranks.  With
         rows < world the others never arrive and the bounded wait runs out."""

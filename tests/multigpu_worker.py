@@ -142,6 +142,61 @@ def main():
         sess.barrier()
     torch.cuda.synchronize()
     sess.check()
+
+    # ---- the collectives as torch custom ops
+    from stdml_collective_experimental_b200.ops import torch_ops
+    torch_ops.set_default_session(sess)
+    t = torch.full((1000,), float(rank + 1), device="cuda")
+    torch.ops.stdml_collective.all_reduce_(t, "sum", 1.0 / world)
+    g = torch.ops.stdml_collective.all_gather(torch.full((3,), float(rank), device="cuda"))
+    torch.cuda.synchronize()
+    assert torch.allclose(t, torch.full_like(t, (world + 1) / 2))
+    assert g.tolist() == [float(r) for r in range(world) for _ in range(3)]
+
+    # ---- CUDA graph: a zero-copy all_reduce and a staged one, captured once, replayed
+    sym = sess.symm_empty(4096, torch.float32)
+    user = torch.empty(4096, device="cuda")
+    sess.all_reduce(sym)  # warm up outside the capture
+    sess.all_reduce(user)
+    sess.all_reduce(user)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    cap = torch.cuda.Stream()
+    with torch.cuda.stream(cap):
+        with torch.cuda.graph(graph, stream=cap):
+            sess.all_reduce(sym, stream=cap)
+            sess.all_reduce(user, stream=cap)
+            sess.all_reduce(user, stream=cap)
+    for it in range(3):
+        sym.fill_(rank + it)
+        user.fill_(1.0)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        sess.check()
+        assert torch.all(sym == world * (world - 1) / 2 + world * it), "graph replay (zero-copy)"
+        assert torch.all(user == float(world * world)), "graph replay (staged)"
+    sess.symm_free(sym)
+
+    # ---- point to point on NCCL's side stream, overlapping a collective
+    import torch.distributed as dist
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world > 1:
+        out = torch.full((1 << 20,), float(rank), device="cuda")
+        inn = torch.empty(1 << 20, device="cuda")
+        if rank % 2 == 0:
+            hs = sess.send(out, (rank + 1) % world)
+            hr = sess.recv(inn, (rank - 1) % world)
+        else:
+            hr = sess.recv(inn, (rank - 1) % world)
+            hs = sess.send(out, (rank + 1) % world)
+        busy = torch.ones(1 << 18, device="cuda")
+        sess.all_reduce(busy)
+        hs.wait()
+        hr.wait()
+        torch.cuda.synchronize()
+        assert torch.all(inn == float((rank - 1) % world)) and torch.all(busy == world)
+    dist.destroy_process_group()
     sess.close()
     print(f"OK rank {rank}/{world} {info}", flush=True)
 

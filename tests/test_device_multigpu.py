@@ -45,3 +45,28 @@ def test_data_parallel_matches_single_process_training():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_world(2, 29641, worker="ddp_worker.py")
+
+
+def test_elastic_resize_on_gpus():
+    """2 -> 1 -> 2 workers with CUDA tensors through Peer/Session: every membership
+    gets a fresh device world (arenas, mappings, multicast); the survivor keeps
+    its process; the joiner catches up (step by max, state by broadcast)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(HERE)
+    runner = os.path.join(root, "stdml_collective_experimental_b200", "csrc", "build", "bin",
+                          "stdml_collective_run")
+    if not os.path.exists(runner):
+        from stdml_collective_experimental_b200 import _native
+        _native.build()
+    env = dict(os.environ, PYTHONPATH=root, NCCL_NVLS_ENABLE="0")
+    cmd = [runner, "-q", "-np", "2", "-w", "-builtin-config-port", "0", "-runner-port", "38181",
+           "-port-range", "10300", sys.executable, "-m",
+           "stdml_collective_experimental_b200.benchmarks.elastic", "--model", "resnet50",
+           "--max-step", "12", "--schedule", "3:1,7:2", "--state-mb", "1"]
+    res = subprocess.run(cmd, env=env, cwd=root, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                         text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-4000:]
+    assert '"event": "detached"' in res.stdout
+    assert res.stdout.count('"event": "resized"') == 2
+    assert '"weights_ok": true' in res.stdout and '"size": 2, "version": 2' in res.stdout
