@@ -267,7 +267,13 @@ __global__ void __launch_bounds__(kThreads)
     const bool user_f32 = Tr<DT>::is_half && a.user_dtype == DT_F32;
     const bool computes = (a.root < 0 || a.root == rank);
 
-    sync_begin(ctx, rank, &sync);
+    // A launch may run only some phases: large staged messages are cut into
+    // chunks whose pack / reduce / unpack run as separate launches on three
+    // streams, so that the HBM copies of one chunk overlap the NVLink phase of
+    // another.  Only the reduce phase synchronises with peers.
+    const int phases = a.phases;
+    const bool do_reduce = (phases & kPhaseReduce) != 0;
+    if (do_reduce) { sync_begin(ctx, rank, &sync); }
 
     char *mine = ctx.base[rank] + a.off;
     const GroupEntry *tab = a.table[vr];
@@ -278,7 +284,7 @@ __global__ void __launch_bounds__(kThreads)
     single.count = a.count;
 
     // ---- pack: user memory -> own arena buffer (the parts peers' block b read)
-    if (tab != nullptr || single.src != nullptr) {
+    if ((phases & kPhasePack) != 0 && (tab != nullptr || single.src != nullptr)) {
         for (int s = 0; s < shards; ++s) {
             const Span sp = span_of(a.nvec, shards, s, nb, b);
             for_each_entry<DT>(tab, a.ntable, single, sp.lo, sp.hi,
@@ -309,10 +315,12 @@ __global__ void __launch_bounds__(kThreads)
         }
     }
 
-    if (!peer_barrier(ctx, rank, &sync)) { return; }
+    if (do_reduce && !peer_barrier(ctx, rank, &sync)) { return; }
 
     // ---- reduce
-    if (owner_algo) {
+    if (!do_reduce) {
+        // pack-only or unpack-only launch
+    } else if (owner_algo) {
         // the owner of shard `rank` reduces it and stores the result into every
         // rank's buffer (only into root's for reduce-to-root)
         const Span sp = span_of(a.nvec, shards, rank, nb, b);
@@ -350,12 +358,13 @@ __global__ void __launch_bounds__(kThreads)
             });
     }
 
-    if (owner_algo || a.end_barrier) {
+    if (do_reduce && (owner_algo || a.end_barrier)) {
         if (!peer_barrier(ctx, rank, &sync)) { return; }
     }
 
     // ---- unpack: own arena buffer -> user memory (two-shot / NVLS only)
-    if (owner_algo && computes && (tab != nullptr || single.dst != nullptr)) {
+    if ((phases & kPhaseUnpack) != 0 && owner_algo && computes &&
+        (tab != nullptr || single.dst != nullptr)) {
         for (int s = 0; s < shards; ++s) {
             const Span sp = span_of(a.nvec, shards, s, nb, b);
             for_each_entry<DT>(tab, a.ntable, single, sp.lo, sp.hi,
@@ -385,7 +394,7 @@ __global__ void __launch_bounds__(kThreads)
         }
     }
 
-    sync_end(ctx, rank, &sync);
+    if (do_reduce) { sync_end(ctx, rank, &sync); }
 }
 
 template <int DT, int OP>

@@ -93,7 +93,10 @@ struct AllReduceArgs {
     int root;         // >= 0: reduce-to-root (only `root` computes and stores)
     int has_scale;
     float scale;
+    int phases;       // bit 0 pack, bit 1 reduce (with its barriers), bit 2 unpack
 };
+
+enum : int { kPhasePack = 1, kPhaseReduce = 2, kPhaseUnpack = 4, kPhaseAll = 7 };
 
 struct GatherArgs {
     const void *src[kMaxRanks];  // nullptr: block already at arena offset `off`

@@ -1,6 +1,7 @@
 #include "device_session.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include <cuda_runtime.h>
@@ -48,10 +49,26 @@ void launch_check(int rc, const char *what)
 }
 }  // namespace
 
-DeviceSession::DeviceSession(std::unique_ptr<DeviceWorld> world) : world_(std::move(world)) {}
+DeviceSession::DeviceSession(std::unique_ptr<DeviceWorld> world) : world_(std::move(world))
+{
+    if (const char *e = std::getenv("STDML_COLLECTIVE_PIPELINE_MIN_BYTES")) {
+        pipeline_min_bytes_ = static_cast<size_t>(std::atoll(e));
+    }
+}
 
 DeviceSession::~DeviceSession()
 {
+    (void)cudaDeviceSynchronize();
+    if (pack_stream_ != nullptr) {
+        (void)cudaStreamDestroy(static_cast<cudaStream_t>(pack_stream_));
+        (void)cudaStreamDestroy(static_cast<cudaStream_t>(unpack_stream_));
+        (void)cudaEventDestroy(static_cast<cudaEvent_t>(entry_ev_));
+        for (int i = 0; i < 2; ++i) {
+            (void)cudaEventDestroy(static_cast<cudaEvent_t>(packed_ev_[i]));
+            (void)cudaEventDestroy(static_cast<cudaEvent_t>(reduced_ev_[i]));
+            (void)cudaEventDestroy(static_cast<cudaEvent_t>(unpacked_ev_[i]));
+        }
+    }
     for (void *p : table_mem_) { (void)cudaFree(p); }
     table_mem_.clear();
     (void)cudaGetLastError();
@@ -74,6 +91,73 @@ void DeviceSession::launch_ar(AllReduceCall &c, void *stream)
 {
     launch_check(world_->all_reduce(c, stream), "all_reduce");
     ++launches_;
+}
+
+void DeviceSession::ensure_pipeline()
+{
+    if (pack_stream_ != nullptr) { return; }
+    cudaStream_t a, b;
+    rt_check(cudaStreamCreateWithFlags(&a, cudaStreamNonBlocking), "cudaStreamCreate");
+    rt_check(cudaStreamCreateWithFlags(&b, cudaStreamNonBlocking), "cudaStreamCreate");
+    pack_stream_ = a;
+    unpack_stream_ = b;
+    auto make = [](void *&slot) {
+        cudaEvent_t e;
+        rt_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+        slot = e;
+    };
+    make(entry_ev_);
+    for (int i = 0; i < 2; ++i) {
+        make(packed_ev_[i]);
+        make(reduced_ev_[i]);
+        make(unpacked_ev_[i]);
+    }
+}
+
+void DeviceSession::run_pipelined(std::vector<AllReduceCall> &calls, void *stream)
+{
+    ensure_pipeline();
+    cudaStream_t main_s = static_cast<cudaStream_t>(stream);
+    cudaStream_t pack_s = static_cast<cudaStream_t>(pack_stream_);
+    cudaStream_t unpack_s = static_cast<cudaStream_t>(unpack_stream_);
+    auto ev = [](void *e) { return static_cast<cudaEvent_t>(e); };
+    // the inputs are ready when the caller's stream gets here
+    rt_check(cudaEventRecord(ev(entry_ev_), main_s), "cudaEventRecord");
+    rt_check(cudaStreamWaitEvent(pack_s, ev(entry_ev_), 0), "cudaStreamWaitEvent");
+    bool used[2] = {false, false};
+    for (AllReduceCall &c : calls) {
+        c.off = world_->next_staging_slot();
+        const int slot = static_cast<int>((c.off - kDataOffset) / world_->staging_bytes()) & 1;
+        // the slot is free once the chunk that used it before has been unpacked
+        if (used[slot]) {
+            rt_check(cudaStreamWaitEvent(pack_s, ev(unpacked_ev_[slot]), 0), "cudaStreamWaitEvent");
+        }
+        AllReduceCall pack = c;
+        pack.phases = kPhasePack;
+        launch_ar(pack, pack_s);
+        rt_check(cudaEventRecord(ev(packed_ev_[slot]), pack_s), "cudaEventRecord");
+
+        rt_check(cudaStreamWaitEvent(main_s, ev(packed_ev_[slot]), 0), "cudaStreamWaitEvent");
+        AllReduceCall red = c;
+        red.phases = kPhaseReduce;
+        // leave SMs to the copy phases of the neighbouring chunks
+        const size_t esz = kElemSize[c.dt];
+        red.blocks = std::min(64, world_->pick_blocks((c.count * esz + 15) / 16, c.algo));
+        launch_ar(red, main_s);
+        rt_check(cudaEventRecord(ev(reduced_ev_[slot]), main_s), "cudaEventRecord");
+
+        rt_check(cudaStreamWaitEvent(unpack_s, ev(reduced_ev_[slot]), 0), "cudaStreamWaitEvent");
+        AllReduceCall unpack = c;
+        unpack.phases = kPhaseUnpack;
+        launch_ar(unpack, unpack_s);
+        rt_check(cudaEventRecord(ev(unpacked_ev_[slot]), unpack_s), "cudaEventRecord");
+        used[slot] = true;
+    }
+    for (int i = 0; i < 2; ++i) {
+        if (used[i]) {
+            rt_check(cudaStreamWaitEvent(main_s, ev(unpacked_ev_[i]), 0), "cudaStreamWaitEvent");
+        }
+    }
 }
 
 void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t count, int dt,
@@ -124,7 +208,37 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
 
     // staged: pack into a staging slot inside the launch, one slot per chunk
     const bool in_capture = capturing(stream);
-    const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
+    size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
+    const size_t total_bytes = count * es;
+    if (world_->world() > 1 && total_bytes >= pipeline_min_bytes_ && !in_capture &&
+        (algo < 0 || algo == kAlgoTwoShot || algo == kAlgoNvls)) {
+        // large message: chunks of about 1/8 of it (8 MB at least, a slot at most)
+        const size_t lanes = 16 / es;
+        size_t chunk = std::max<size_t>((8u << 20) / es, (count / 8 + lanes - 1) / lanes * lanes);
+        chunk = std::min(chunk, slot_elems);
+        const int owner = algo >= 0 ? algo : world_->pick_algo(chunk * es, dt, op, true);
+        std::vector<std::vector<const void *>> srcs;
+        std::vector<std::vector<void *>> dsts;
+        std::vector<AllReduceCall> calls;
+        for (size_t done = 0; done < count; done += chunk) {
+            srcs.emplace_back(vr);
+            dsts.emplace_back(vr);
+            for (int v = 0; v < vr; ++v) {
+                srcs.back()[v] = static_cast<const char *>(in[v]) + done * es;
+                dsts.back()[v] = static_cast<char *>(out[v]) + done * es;
+            }
+            AllReduceCall k = c;
+            k.count = std::min(chunk, count - done);
+            k.algo = owner;
+            calls.push_back(k);
+        }
+        for (size_t i = 0; i < calls.size(); ++i) {
+            calls[i].src = srcs[i].data();
+            calls[i].dst = dsts[i].data();
+        }
+        run_pipelined(calls, stream);
+        return;
+    }
     std::vector<const void *> src(vr);
     std::vector<void *> dst(vr);
     for (size_t done = 0; done < count; done += slot_elems) {
@@ -311,6 +425,30 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
     }
 
     const GroupPlan &plan = plan_group(n, ins, outs, counts, dt, user_dt);
+    size_t plan_bytes = 0;
+    for (const auto &chunk : plan.chunks) { plan_bytes += chunk[0].nvec * 16; }
+    if (world_->world() > 1 && plan.chunks.size() >= 2 && plan_bytes >= pipeline_min_bytes_ &&
+        !capturing(stream) && (algo < 0 || algo == kAlgoTwoShot || algo == kAlgoNvls)) {
+        std::vector<std::vector<const GroupEntry *>> all_tabs;
+        std::vector<AllReduceCall> calls;
+        for (const auto &chunk : plan.chunks) {
+            all_tabs.emplace_back(vr);
+            for (int v = 0; v < vr; ++v) { all_tabs.back()[v] = chunk[v].dev; }
+            AllReduceCall c;
+            c.dt = dt;
+            c.op = op;
+            c.user_dtype = user_dt;
+            c.ntable = chunk[0].n;
+            c.count = chunk[0].nvec * (16 / es);
+            c.has_scale = scale != 1.0;
+            c.scale = static_cast<float>(scale);
+            c.algo = algo >= 0 ? algo : world_->pick_algo(chunk[0].nvec * 16, dt, op, true);
+            calls.push_back(c);
+        }
+        for (size_t i = 0; i < calls.size(); ++i) { calls[i].table = all_tabs[i].data(); }
+        run_pipelined(calls, stream);
+        return;
+    }
     std::vector<const GroupEntry *> tabs(vr);
     for (const auto &chunk : plan.chunks) {
         for (int v = 0; v < vr; ++v) { tabs[v] = chunk[v].dev; }

@@ -77,6 +77,11 @@ class DeviceSession
     };
 
     void launch_ar(AllReduceCall &c, void *stream);
+    // Runs staged calls (one per staging slot) with their pack, reduce and
+    // unpack phases on three streams, so that the HBM copies of one chunk
+    // overlap the NVLink phase of its neighbours.
+    void run_pipelined(std::vector<AllReduceCall> &calls, void *stream);
+    void ensure_pipeline();
     const GroupPlan &plan_group(size_t n, const void *const *ins, void *const *outs,
                                 const size_t *counts, int dt, int user_dt);
 
@@ -84,5 +89,13 @@ class DeviceSession
     std::map<std::string, GroupPlan> plans_;
     std::vector<void *> table_mem_;
     unsigned long long launches_ = 0;
+    size_t pipeline_min_bytes_ = 32u << 20;  // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
+    // pipeline resources (created on first use)
+    void *pack_stream_ = nullptr;
+    void *unpack_stream_ = nullptr;
+    void *entry_ev_ = nullptr;
+    void *packed_ev_[2] = {nullptr, nullptr};
+    void *reduced_ev_[2] = {nullptr, nullptr};
+    void *unpacked_ev_[2] = {nullptr, nullptr};
 };
 }  // namespace stdml::collective::cuda

@@ -445,6 +445,14 @@ class World final : public DeviceWorld
         a.root = c.root;
         a.has_scale = c.has_scale ? 1 : 0;
         a.scale = c.scale;
+        a.phases = c.phases;
+        if ((c.phases & kPhaseReduce) == 0) {
+            // a local copy phase: no peer waits, any grid will do
+            blocks = static_cast<int>(std::min<size_t>(
+                std::max<size_t>(1, nvec / (static_cast<size_t>(kThreads) * 4)),
+                static_cast<size_t>(2 * num_sms_)));
+            if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
+        }
         const CommCtx ctx = make_ctx();
         const int rc = launch_all_reduce(ctx, a, c.dt, c.op, blocks, vranks_, stream);
         if (rc < 0) { throw std::invalid_argument("all_reduce: (dtype, op) not built"); }

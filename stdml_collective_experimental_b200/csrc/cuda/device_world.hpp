@@ -62,6 +62,7 @@ struct AllReduceCall {
     bool end_barrier = false;
     bool has_scale = false;
     float scale = 1.0f;
+    int phases = 7;  // kPhasePack | kPhaseReduce | kPhaseUnpack
 };
 
 struct GatherCall {

@@ -143,6 +143,7 @@ extern "C" int stdmlc_all_reduce_noalloc(const void *const *in, void *const *out
     a.root = -1;
     a.has_scale = scale != 1.0 ? 1 : 0;
     a.scale = static_cast<float>(scale);
+    a.phases = kPhaseAll;
 
     // all rows of the grid wait on one another: they must be resident together
     const unsigned long long per_block = static_cast<unsigned long long>(kThreads) * 4;

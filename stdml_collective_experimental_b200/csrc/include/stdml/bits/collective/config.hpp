@@ -27,6 +27,9 @@ struct system_config {
     std::string device_algo = "auto";  // STDML_COLLECTIVE_ALGO: auto|oneshot|twoshot|nvls
     int64_t timeout_ms = 20000;        // STDML_COLLECTIVE_TIMEOUT_MS
     bool use_nvls = true;              // STDML_COLLECTIVE_NVLS
+    // ---- failure detection on the host path: how long a collective waits for a
+    // peer's message before it throws (0 = for ever, as the reference does)
+    int64_t host_timeout_ms = 0;       // STDML_COLLECTIVE_HOST_TIMEOUT_MS
 };
 
 std::ostream &operator<<(std::ostream &os, const system_config &c);

@@ -10,6 +10,7 @@
 // messages (the head-of-line blocking that deadlocks the reference's
 // group_all_reduce when ranks submit tensors in different orders).
 #pragma once
+#include <chrono>
 #include <condition_variable>
 #include <cstring>
 #include <deque>
@@ -77,6 +78,27 @@ class slot
         std::unique_lock<std::mutex> lk(mu_);
         finished_.wait(lk, [&] { return t->done; });
         return t->ok;
+    }
+
+    // Like get(), but gives up after `ms` milliseconds (ms <= 0: never): returns
+    // -1 on timeout, else 1 (delivered) or 0 (did not fit).  A ticket that
+    // timed out is withdrawn, so a late body is parked for the next receiver.
+    int get_for(void *ptr, size_t cap, long long ms)
+    {
+        if (ms <= 0) { return get(ptr, cap) ? 1 : 0; }
+        auto t = post_ticket(ptr, cap);
+        std::unique_lock<std::mutex> lk(mu_);
+        if (!finished_.wait_for(lk, std::chrono::milliseconds(ms), [&] { return t->done; })) {
+            for (auto it = waiting_.begin(); it != waiting_.end(); ++it) {
+                if (*it == t) {
+                    waiting_.erase(it);
+                    return -1;
+                }
+            }
+            // a network thread has taken the ticket and is filling it right now
+            finished_.wait(lk, [&] { return t->done; });
+        }
+        return t->ok ? 1 : 0;
     }
 
     // Posts now; the returned function waits for the body.

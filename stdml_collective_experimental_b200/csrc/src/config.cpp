@@ -78,6 +78,9 @@ system_config parse_system_config_from_env()
     if (const auto t = parse_env_int("STDML_COLLECTIVE_TIMEOUT_MS"); t && *t > 0) {
         c.timeout_ms = *t;
     }
+    if (const auto t = parse_env_int("STDML_COLLECTIVE_HOST_TIMEOUT_MS"); t && *t > 0) {
+        c.host_timeout_ms = *t;
+    }
     const std::string nvls = safe_getenv("STDML_COLLECTIVE_NVLS");
     if (nvls == "0" || nvls == "off" || nvls == "false") { c.use_nvls = false; }
     return c;

@@ -79,8 +79,20 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
     const size_t bytes = w.bytes();
     rchan::client *out = client_pool_->require(conn_collective);
 
+    const long long limit = config_.host_timeout_ms;
     auto recv_reduce = [&](size_t src) {
-        buffer b = mailbox_->require(peers_[src], name)->get();
+        buffer b;
+        if (limit > 0) {
+            auto got = mailbox_->require(peers_[src], name)->get_for(std::chrono::milliseconds(limit));
+            if (!got) {
+                throw std::runtime_error("all_reduce '" + w.name + "': nothing from peer " +
+                                         peers_[src].str() + " within " + std::to_string(limit) +
+                                         " ms (peer failed or left?)");
+            }
+            b = std::move(*got);
+        } else {
+            b = mailbox_->require(peers_[src], name)->get();
+        }
         if (b.len != bytes) {
             throw std::runtime_error("all_reduce: peer " + peers_[src].str() + " sent " +
                                      std::to_string(b.len) + " bytes for '" + w.name +
@@ -92,7 +104,13 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
         out->send(peers_[dst], name.c_str(), st.effective_data(), bytes, 0);
     };
     auto recv_result = [&](size_t src) {
-        if (!slotbox_->require(peers_[src], name)->get(w.recv, bytes)) {
+        const int rc = slotbox_->require(peers_[src], name)->get_for(w.recv, bytes, limit);
+        if (rc < 0) {
+            throw std::runtime_error("all_reduce '" + w.name + "': no result from peer " +
+                                     peers_[src].str() + " within " + std::to_string(limit) +
+                                     " ms (peer failed or left?)");
+        }
+        if (rc == 0) {
             throw std::runtime_error("all_reduce: result for '" + w.name + "' did not fit");
         }
         st.replaced();

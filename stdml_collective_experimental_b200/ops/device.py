@@ -234,10 +234,12 @@ class DeviceSession:
         ins = self._checked(self._per_rank(tensor, "tensor"), "all_reduce")
         outs = ins if out is None else self._checked(self._per_rank(out, "out"), "all_reduce")
         t0 = ins[0]
-        _native.check(self._lib.stdmlc_dw_all_reduce(
-            self._h, _ptr_array(ins), _ptr_array(outs), t0.numel(), dtype_code(t0.dtype),
-            op_code(op), 1.0 if scale is None else float(scale), _algo_code(algo),
-            self._stream(stream)))
+        self._profiled("all_reduce", t0.numel() * t0.element_size(), stream,
+                       lambda: _native.check(self._lib.stdmlc_dw_all_reduce(
+                           self._h, _ptr_array(ins), _ptr_array(outs), t0.numel(),
+                           dtype_code(t0.dtype), op_code(op),
+                           1.0 if scale is None else float(scale), _algo_code(algo),
+                           self._stream(stream))))
         return out if out is not None else tensor
 
     def reduce(self, tensor, out=None, op="sum", root=0, scale=None, stream=None):
@@ -281,9 +283,12 @@ class DeviceSession:
             wire, user = dtype_code(dt), -1
         else:
             wire, user = dtype_code(wire_dtype), dtype_code(dt)
-        _native.check(self._lib.stdmlc_dw_group_all_reduce(
-            self._h, n, _ptr_array(flat_in), _ptr_array(flat_out), counts, wire, op_code(op), user,
-            1.0 if scale is None else float(scale), _algo_code(algo), self._stream(stream)))
+        nbytes = sum(t.numel() * t.element_size() for t in per_rank[0])
+        self._profiled("group_all_reduce", nbytes, stream,
+                       lambda: _native.check(self._lib.stdmlc_dw_group_all_reduce(
+                           self._h, n, _ptr_array(flat_in), _ptr_array(flat_out), counts, wire,
+                           op_code(op), user, 1.0 if scale is None else float(scale),
+                           _algo_code(algo), self._stream(stream))))
         return outs if outs is not None else tensors
 
     def all_gather(self, tensor, out, stream=None):
@@ -293,18 +298,20 @@ class DeviceSession:
         t0 = ins[0]
         if outs[0].numel() != t0.numel() * self.world:
             raise ValueError("all_gather: out must hold world * tensor.numel() elements")
-        _native.check(self._lib.stdmlc_dw_all_gather(
-            self._h, _ptr_array(ins), _ptr_array(outs), t0.numel(), dtype_code(t0.dtype),
-            self._stream(stream)))
+        self._profiled("all_gather", t0.numel() * t0.element_size(), stream,
+                       lambda: _native.check(self._lib.stdmlc_dw_all_gather(
+                           self._h, _ptr_array(ins), _ptr_array(outs), t0.numel(),
+                           dtype_code(t0.dtype), self._stream(stream))))
         return out
 
     def broadcast(self, tensor, out=None, root=0, stream=None):
         ins = self._checked(self._per_rank(tensor, "tensor"), "broadcast")
         outs = ins if out is None else self._checked(self._per_rank(out, "out"), "broadcast")
         t0 = ins[0]
-        _native.check(self._lib.stdmlc_dw_broadcast(
-            self._h, _ptr_array(ins), _ptr_array(outs), t0.numel(), dtype_code(t0.dtype), root,
-            self._stream(stream)))
+        self._profiled("broadcast", t0.numel() * t0.element_size(), stream,
+                       lambda: _native.check(self._lib.stdmlc_dw_broadcast(
+                           self._h, _ptr_array(ins), _ptr_array(outs), t0.numel(),
+                           dtype_code(t0.dtype), root, self._stream(stream))))
         return out if out is not None else tensor
 
     def barrier(self, stream=None):
@@ -367,6 +374,47 @@ class DeviceSession:
             dtype_code(sy[0].dtype), op_code(op), algo, blocks, root, 1 if end_barrier else 0,
             0 if scale is None else 1, 1.0 if scale is None else float(scale),
             self._stream(stream)))
+
+    # --------------------------------------------------------------- profiling
+    def enable_profile(self, on=True):
+        """Record a CUDA event pair around every collective of this session (device
+        time per call, no host synchronisation until profile_summary()).  The
+        reference's counterpart is its STDML_COLLECTIVE_PROFILE_RATE scopes
+        (include/stdml/bits/collective/stat.hpp:196-202), which time the host."""
+        self._prof = [] if on else None
+
+    def _profiled(self, name, nbytes, stream, call):
+        prof = getattr(self, "_prof", None)
+        if prof is None:
+            return call()
+        s = torch.cuda.current_stream(self.device) if stream is None else stream
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        out = call()
+        e1.record(s)
+        prof.append((name, nbytes, e0, e1))
+        return out
+
+    def profile_summary(self, reset=True):
+        """{op: {calls, bytes, ms, algbw_gb_s, busbw_gb_s}}; waits for the recorded work."""
+        prof = getattr(self, "_prof", None) or []
+        out = {}
+        n = self.world
+        factor = {"all_reduce": 2 * (n - 1) / n, "group_all_reduce": 2 * (n - 1) / n,
+                  "all_gather": (n - 1), "broadcast": 1.0, "reduce": 1.0, "barrier": 0.0}
+        for name, nbytes, e0, e1 in prof:
+            e1.synchronize()
+            d = out.setdefault(name, {"calls": 0, "bytes": 0, "ms": 0.0})
+            d["calls"] += 1
+            d["bytes"] += nbytes
+            d["ms"] += e0.elapsed_time(e1)
+        for name, d in out.items():
+            sec = max(d["ms"], 1e-9) * 1e-3
+            d["algbw_gb_s"] = d["bytes"] / sec / 1e9
+            d["busbw_gb_s"] = d["algbw_gb_s"] * factor.get(name, 1.0)
+        if reset and getattr(self, "_prof", None) is not None:
+            self._prof = []
+        return out
 
     # ------------------------------------------------------------ failure path
     def status(self):

@@ -280,3 +280,77 @@ def test_bounded_wait_reports_and_recovers():
         assert torch.all(x[0] == 3.0) and torch.all(x[1] == 3.0)
     finally:
         s.close()
+
+
+def test_profile_summary_counts_device_time(sess):
+    sess.enable_profile()
+    x = [torch.ones(100_000, device="cuda") for _ in range(sess.world)]
+    arg = x if sess.vranks > 1 else x[0]
+    for _ in range(3):
+        sess.all_reduce(arg)
+    out = [torch.empty(100_000 * sess.world, device="cuda") for _ in range(sess.world)]
+    sess.all_gather(arg, out if sess.vranks > 1 else out[0])
+    summary = sess.profile_summary()
+    sess.enable_profile(False)
+    assert summary["all_reduce"]["calls"] == 3 and summary["all_reduce"]["bytes"] == 3 * 400_000
+    assert summary["all_reduce"]["ms"] > 0 and summary["all_gather"]["calls"] == 1
+    assert sess.profile_summary() == {}
+
+
+def test_cuda_graph_capture_and_replay():
+    """Collectives are plain kernel launches with device-side epochs: a captured
+    graph replays them (world 1: no cooperative launch inside the capture)."""
+    with DeviceSession.loopback(1, heap_bytes=1 << 20, staging_bytes=1 << 20) as s:
+        sym = s.symm_empty(1000, torch.float32)
+        user = torch.empty(1000, device="cuda")
+        s.all_reduce(sym, scale=0.5)
+        s.all_reduce(user, scale=2.0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        cap = torch.cuda.Stream()
+        with torch.cuda.stream(cap):
+            with torch.cuda.graph(g, stream=cap):
+                s.all_reduce(sym, scale=0.5, stream=cap)
+                s.all_reduce(user, scale=2.0, stream=cap)
+        for it in range(3):
+            sym.fill_(4.0 + it)
+            user.fill_(1.0 + it)
+            torch.cuda.synchronize()
+            g.replay()
+            torch.cuda.synchronize()
+            s.check()
+            assert torch.all(sym == (4.0 + it) / 2) and torch.all(user == 2.0 * (1.0 + it))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_large_staged_messages_are_pipelined_on_three_streams(world, monkeypatch):
+    """Above a size threshold staged calls run pack / reduce / unpack of successive
+    chunks on three streams; the result must not change."""
+    monkeypatch.setenv("STDML_COLLECTIVE_PIPELINE_MIN_BYTES", str(1 << 20))
+    with DeviceSession.loopback(world, heap_bytes=1 << 20, staging_bytes=1 << 20) as s:
+        n = (5 << 20) // 4 + 13
+        host = make_inputs(world, n, torch.float32, seed=21)
+        want = reduce_many(host, "sum", 0.5)
+        dev = [h.cuda() for h in host]
+        out = [torch.empty_like(d) for d in dev]
+        before = s.launches
+        s.all_reduce(dev, out=out, scale=0.5)
+        torch.cuda.synchronize()
+        s.check()
+        assert s.launches - before == 3 * 6, "6 slot-sized chunks, three launches each"
+        for r in range(world):
+            assert same(out[r].cpu(), want) and same(dev[r].cpu(), host[r])
+        # a fused group above the threshold takes the same route
+        sizes = [300_000, 7, 500_000, 64, 400_000]
+        g = torch.Generator().manual_seed(3)
+        hosts = [[torch.rand(k, generator=g) for k in sizes] for _ in range(world)]
+        devs = [[t.cuda() for t in hosts[r]] for r in range(world)]
+        s.group_all_reduce(devs, scale=1.0 / world)
+        s.all_reduce(dev)  # ordinary call right behind the pipeline
+        torch.cuda.synchronize()
+        s.check()
+        for i in range(len(sizes)):
+            w = reduce_many([hosts[r][i] for r in range(world)], "sum", 1.0 / world)
+            for r in range(world):
+                assert same(devs[r][i].cpu(), w), (r, i)
+        assert same(dev[0].cpu(), reduce_many(host, "sum"))

@@ -102,3 +102,13 @@ def test_elastic_state_follows_config_server():
               os.path.join(BIN, "example_elastic_state"), "--max-step=9", "2:4", "5:3",
               timeout=300)
     assert out.count("weight 45.0 (want 45.0) OK") == 3 and out.count("detached") == 1
+
+
+def test_shutdown_and_host_side_failure_detection():
+    # clean teardown after 100 collectives; a rank that leaves between steps and a rank
+    # that never joins both end in exceptions on the others, not in a hang
+    assert "test-shutdown np=3: OK" in run("test_shutdown", 3)
+
+
+def test_public_headers_compile_as_cxx17():
+    run("test_cxx17")
