@@ -54,6 +54,9 @@ DeviceSession::DeviceSession(std::unique_ptr<DeviceWorld> world) : world_(std::m
     if (const char *e = std::getenv("STDML_COLLECTIVE_PIPELINE_MIN_BYTES")) {
         pipeline_min_bytes_ = static_cast<size_t>(std::atoll(e));
     }
+    if (const char *e = std::getenv("STDML_COLLECTIVE_PIPELINE_CHUNK_BYTES")) {
+        pipeline_chunk_bytes_ = std::max<size_t>(1u << 16, static_cast<size_t>(std::atoll(e)));
+    }
 }
 
 DeviceSession::~DeviceSession()
@@ -214,7 +217,8 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
         (algo < 0 || algo == kAlgoTwoShot || algo == kAlgoNvls)) {
         // large message: chunks of about 1/8 of it (8 MB at least, a slot at most)
         const size_t lanes = 16 / es;
-        size_t chunk = std::max<size_t>((8u << 20) / es, (count / 8 + lanes - 1) / lanes * lanes);
+        size_t chunk = std::max<size_t>(pipeline_chunk_bytes_ / es,
+                                        (count / 8 + lanes - 1) / lanes * lanes);
         chunk = std::min(chunk, slot_elems);
         const int owner = algo >= 0 ? algo : world_->pick_algo(chunk * es, dt, op, true);
         std::vector<std::vector<const void *>> srcs;

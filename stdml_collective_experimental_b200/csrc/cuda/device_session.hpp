@@ -89,7 +89,8 @@ class DeviceSession
     std::map<std::string, GroupPlan> plans_;
     std::vector<void *> table_mem_;
     unsigned long long launches_ = 0;
-    size_t pipeline_min_bytes_ = 32u << 20;  // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
+    size_t pipeline_min_bytes_ = 512u << 20;   // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
+    size_t pipeline_chunk_bytes_ = 32u << 20;  // STDML_COLLECTIVE_PIPELINE_CHUNK_BYTES (smallest chunk)
     // pipeline resources (created on first use)
     void *pack_stream_ = nullptr;
     void *unpack_stream_ = nullptr;
