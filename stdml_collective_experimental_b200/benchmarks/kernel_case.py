@@ -16,6 +16,33 @@ import torch
 from .. import DeviceSession
 
 
+def staged_group(args, sess, dtype, es):
+    total = (args.mb << 20) // es
+    k = args.staged_group
+    # a few big tensors and many small ones, like a real gradient set
+    sizes = [total // 2, total // 4] + [max(1, (total // 4) // (k - 2))] * (k - 2)
+    ranks = [[torch.full((s,), float(r + 1), dtype=dtype, device="cuda") for s in sizes]
+             for r in range(args.world)]
+    arg = ranks if args.world > 1 else ranks[0]
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(args.iters + 1)]
+    e[0].record()
+    for i in range(args.iters):
+        sess.group_all_reduce(arg, scale=1.0 / args.world, algo=args.algo)
+        e[i + 1].record()
+    torch.cuda.synchronize()
+    sess.check()
+    times = [e[i].elapsed_time(e[i + 1]) for i in range(args.iters)]
+    nbytes = sum(sizes) * es
+    # per rank: pack (read + write), reduce (read world, write world, amortised: read + write), unpack (read + write)
+    hbm = 6 * args.world * nbytes
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(json.dumps({"world": args.world, "tensors": k, "set_mb": nbytes / 2**20, "algo": args.algo,
+                      "ms_per_call": times, "best_ms": best, "hbm_bytes_per_call": hbm,
+                      "achieved_gb_s": hbm / (best * 1e-3) / 1e9}))
+    sess.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--world", type=int, default=4)
@@ -24,14 +51,19 @@ def main():
     ap.add_argument("--algo", default="twoshot")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--blocks", type=int, default=0)
+    ap.add_argument("--staged-group", type=int, default=0,
+                    help="N > 0: reduce N separately allocated tensors per rank (pack + reduce + "
+                         "unpack through a descriptor table) instead of one symmetric buffer")
     args = ap.parse_args()
     dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
     es = 4 if args.dtype == "f32" else 2
     n = (args.mb << 20) // es
     sess = DeviceSession.loopback(args.world, heap_bytes=(args.mb << 20) + (8 << 20),
-                                  staging_bytes=1 << 20)
+                                  staging_bytes=(args.mb + 1) << 20 if args.staged_group else 1 << 20)
     if args.blocks:
         sess.set_tuning(max_blocks=args.blocks)
+    if args.staged_group > 0:
+        return staged_group(args, sess, dtype, es)
     sym = sess.symm_empty(n, dtype)
     bufs = sym if args.world > 1 else [sym]
     for r, b in enumerate(bufs):
