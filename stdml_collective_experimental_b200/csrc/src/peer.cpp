@@ -1,6 +1,7 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <iostream>
 #include <stdexcept>
 #include <thread>
 
@@ -10,6 +11,7 @@
 #include <stdml/bits/collective/affinity.hpp>
 #include <stdml/bits/collective/log.hpp>
 #include <stdml/bits/collective/peer.hpp>
+#include <stdml/bits/collective/stat.hpp>
 
 namespace stdml::collective
 {
@@ -276,6 +278,13 @@ void prun(int n, const std::function<void(session &)> &g)
             } catch (const std::exception &e) {
                 std::fprintf(stderr, "prun: rank %d failed: %s\n", i, e.what());
                 rc = 1;
+            }
+            // _exit skips static destructors, which is where a traced process
+            // prints its events
+            if (rchan::stat_enabled()) {
+                rchan::stat_report(std::cout);
+                rchan::stat_clear();
+                std::cout.flush();
             }
             std::fflush(nullptr);
             ::_exit(rc);

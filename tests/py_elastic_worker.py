@@ -1,0 +1,48 @@
+"""A worker of the Python ElasticState test (started by the native runner)."""
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from stdml_collective_experimental_b200.parallel.elastic import ElasticState  # noqa: E402
+from stdml_collective_experimental_b200.parallel.peer import resized_cluster  # noqa: E402
+import json  # noqa: E402
+import urllib.request  # noqa: E402
+
+
+def propose(sess, new_size):
+    body = json.dumps(resized_cluster(sess.cluster, new_size)).encode()
+    req = urllib.request.Request(os.environ["KUNGFU_CONFIG_SERVER"], data=body, method="PUT")
+    urllib.request.urlopen(req, timeout=5).read()
+
+
+def main():
+    max_step = int(sys.argv[1])
+    schedule = dict(tuple(map(int, a.split(":"))) for a in sys.argv[2:])
+    weights = torch.zeros(256)
+    state = ElasticState(max_progress=max_step)
+    state.on_resize(lambda s: s.broadcast(weights, name="state"))
+    while not state.should_stop():
+        step = int(state)
+        g = torch.full((256,), float(step + 1))
+        state.sess.all_reduce(g, name="grad")
+        weights += g / state.sess.size
+        if state.sess.rank == 0 and step in schedule:
+            propose(state.sess, schedule[step])
+        state.advance()
+    if state.detached:
+        print("detached", flush=True)
+        return
+    want = max_step * (max_step + 1) / 2
+    ok = float(weights[0]) == want
+    print(f"finished rank {state.sess.rank}/{state.sess.size} weight {float(weights[0])} "
+          f"{'OK' if ok else 'WRONG'}", flush=True)
+    state.close()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

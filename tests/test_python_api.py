@@ -17,3 +17,16 @@ def test_python_peer_session(n, strategy, base, native_lib):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
+
+
+def test_python_elastic_state_under_the_runner(native_lib):
+    from stdml_collective_experimental_b200 import _native
+    _native.build()
+    runner = os.path.join(_native.CSRC, "build", "bin", "stdml_collective_run")
+    cmd = [runner, "-q", "-np", "2", "-w", "-builtin-config-port", "0", "-runner-port", "38282",
+           "-port-range", "10500", sys.executable, os.path.join(HERE, "py_elastic_worker.py"),
+           "8", "2:3", "5:2"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:]
+    assert res.stdout.count("weight 36.0 OK") == 2 and res.stdout.count("detached") == 1

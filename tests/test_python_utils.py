@@ -1,0 +1,81 @@
+"""CPU tests of the pure-Python pieces: gradient-set shapes, trace parsing, NUMA
+list parsing, the clock sampler against a fake NVML, custom-op registration."""
+import os
+import subprocess
+import sys
+import types
+
+import torch
+
+from stdml_collective_experimental_b200.models import gradsets
+from stdml_collective_experimental_b200.models.resnet import ResNet50
+from stdml_collective_experimental_b200.utils import clocks, numa, timeline
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_gradient_sets_match_the_named_models(tmp_path):
+    r = gradsets.gradset_sizes("resnet50")
+    assert (len(r), sum(r)) == (161, 25_557_032)
+    v = gradsets.gradset_sizes("vgg16")
+    assert (len(v), sum(v)) == (32, 138_357_544) and max(v) == 25088 * 4096
+    b = gradsets.gradset_sizes("bert-base")
+    assert len(b) == 199 and 109_000_000 < sum(b) < 110_000_000
+    assert len(gradsets.gradset_sizes("bert-large")) == 391
+    assert gradsets.gradset_sizes("1024x100") == [1024] * 100
+    path = gradsets.write_sizes_file("resnet50", str(tmp_path / "r.txt"))
+    assert [int(x) for x in open(path).read().split()] == r
+    model = ResNet50()
+    assert sorted(p.numel() for p in model.parameters()) == sorted(r)
+
+
+def test_trace_lines_round_trip_through_the_native_runtime(tmp_path):
+    from stdml_collective_experimental_b200 import _native
+    _native.build()
+    env = dict(os.environ, STDML_COLLECTIVE_ENABLE_TRACE="1")
+    for k in ("KUNGFU_SELF_SPEC", "RANK", "WORLD_SIZE", "OMPI_COMM_WORLD_SIZE"):
+        env.pop(k, None)
+    out = subprocess.run([os.path.join(_native.CSRC, "build", "bin", "example_fork"), "2"], env=env,
+                         stdout=subprocess.PIPE, text=True, timeout=120).stdout
+    events = timeline.parse_log(out)
+    names = {e["name"] for e in events}
+    assert {"all_reduce", "send", "read_header"} <= names
+    s = timeline.summary(events)
+    assert s["all_reduce"]["calls"] >= 2 and s["send"]["bytes"] > 0
+    trace = timeline.to_chrome_trace({0: events})
+    assert trace["traceEvents"][0]["ph"] == "X"
+    timeline.write_chrome_trace({0: events}, str(tmp_path / "t.json"))
+
+
+def test_numa_cpulist_parsing():
+    assert numa._parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert numa._parse_cpulist("") == []
+    assert numa.bind_to_gpu_numa(0) is None or isinstance(numa.bind_to_gpu_numa(0), int)
+
+
+def test_clock_sampler_reads_but_never_sets(monkeypatch):
+    calls = []
+
+    fake = types.SimpleNamespace(
+        NVML_CLOCK_SM=1,
+        nvmlInit=lambda: calls.append("init"),
+        nvmlDeviceGetHandleByIndex=lambda i: ("h", i),
+        nvmlDeviceGetMaxClockInfo=lambda h, k: 1965,
+        nvmlDeviceGetClockInfo=lambda h, k: 1350,
+        nvmlDeviceGetCurrentClocksEventReasons=lambda h: 0x4,  # sw_power_cap
+    )
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    s = clocks.ClockSampler(0, period_s=0.001).start()
+    import time
+    time.sleep(0.02)
+    out = s.stop()
+    assert out["sm_mhz"] == 1350 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"]
+    assert out["samples"] >= 2 and calls == ["init"]
+    assert not [n for n in dir(fake) if "Set" in n or "Reset" in n]
+
+
+def test_custom_ops_are_registered():
+    from stdml_collective_experimental_b200.ops import torch_ops  # noqa: F401
+    assert hasattr(torch.ops.stdml_collective, "all_reduce_")
+    assert hasattr(torch.ops.stdml_collective, "group_all_reduce_")
+    assert hasattr(torch.ops.stdml_collective, "all_gather")
