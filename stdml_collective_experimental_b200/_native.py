@@ -36,9 +36,13 @@ def lib():
     with _lock:
         if _lib is None:
             if not os.path.exists(LIB_PATH):
-                raise ImportError(
-                    f"{LIB_PATH} is missing; build it with `make -C {CSRC}` "
-                    "or `python -c 'import __graft_entry__ as g; g.build()'`")
+                # a fresh checkout has sources only: compile once (needs nvcc, ~2 minutes)
+                try:
+                    build(target="lib")
+                except Exception as e:
+                    raise ImportError(
+                        f"{LIB_PATH} is missing and could not be built ({e}); build it with "
+                        f"`make -C {CSRC}`") from e
             _lib = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
             _declare(_lib)
         return _lib
