@@ -5,7 +5,7 @@
  * allocate device memory themselves or to trigger an allocation inside a
  * library call.  Typical cases: a plugin that runs inside a host application
  * whose device memory is owned entirely by that application's own allocator
- * (any cudaMalloc made behind its back breaks its memory budget or is simply
+ * (any cudaMalloc made behind its back breaks its memory accounting or is simply
  * forbidden by policy), and steady-state loops that must never hit the
  * implicit device-wide synchronisation that cudaMalloc / cudaFree perform.
  * The regular entry points (stdmlc_dw_create + stdmlc_dw_all_reduce) allocate a

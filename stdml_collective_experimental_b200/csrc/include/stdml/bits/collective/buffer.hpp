@@ -3,7 +3,7 @@
 // (include/stdml/bits/collective/buffer.hpp:49-187): alloc_buffer,
 // even_partition, workspace::{slice, split, forward}, workspace_state.
 // Differences: a zero-length workspace is defined (no chunks), and chunking is
-// by a byte budget so callers do not repeat the arithmetic.
+// by a byte limit so callers do not repeat the arithmetic.
 #pragma once
 #include <algorithm>
 #include <cstddef>
