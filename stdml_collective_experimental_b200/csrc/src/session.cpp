@@ -217,7 +217,7 @@ void session::all_reduce(const workspace &w, void *stream)
     if (on_device(w.send, w.recv)) {
         const void *in[1] = {w.send};
         void *out[1] = {w.recv};
-        device()->all_reduce(in, out, w.count, w.dt, w.op, 1.0, -1, stream);
+        device()->all_reduce(in, out, w.count, w.dt, w.op, 1.0, forced_algo(config_), stream);
         return;
     }
     if (peers_.size() == 1) {
@@ -298,7 +298,7 @@ void session::group_all_reduce(const std::vector<workspace> &ws, double scale, v
             counts.push_back(w.count);
         }
         device()->group_all_reduce(ws.size(), ins.data(), outs.data(), counts.data(), ws[0].dt,
-                                   ws[0].op, -1, scale, -1, stream);
+                                   ws[0].op, -1, scale, forced_algo(config_), stream);
         return;
     }
     std::vector<std::future<workspace>> fs;
@@ -499,6 +499,19 @@ bool session::consistent(const void *ptr, size_t size)
 }
 
 // -------------------------------------------------------------- device path
+namespace
+{
+// STDML_COLLECTIVE_ALGO: auto | oneshot | twoshot | nvls | nvls_oneshot
+int forced_algo(const system_config &c)
+{
+    if (c.device_algo == "oneshot") { return cuda::kAlgoOneShot; }
+    if (c.device_algo == "twoshot") { return cuda::kAlgoTwoShot; }
+    if (c.device_algo == "nvls") { return cuda::kAlgoNvls; }
+    if (c.device_algo == "nvls_oneshot") { return cuda::kAlgoNvlsOneShot; }
+    return -1;
+}
+}  // namespace
+
 bool session::on_device(const void *a, const void *b) const
 {
     const int ka = cuda::pointer_kind(a), kb = cuda::pointer_kind(b);

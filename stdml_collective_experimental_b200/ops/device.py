@@ -268,6 +268,23 @@ class DeviceSession:
         n = len(per_rank[0])
         if n == 0:
             return outs if outs is not None else tensors
+        dtypes = []
+        for t in per_rank[0]:
+            if t.dtype not in dtypes:
+                dtypes.append(t.dtype)
+        if len(dtypes) > 1:
+            # one fused call per dtype, each keeping the callers' order
+            for dt_ in dtypes:
+                idx = [i for i, t in enumerate(per_rank[0]) if t.dtype == dt_]
+                sub_in = [[pr[i] for i in idx] for pr in per_rank]
+                sub_out = [[pr[i] for i in idx] for pr in per_rank_out]
+                self.group_all_reduce(sub_in if self.vranks > 1 else sub_in[0],
+                                      outs=None if outs is None else
+                                      (sub_out if self.vranks > 1 else sub_out[0]),
+                                      op=op, scale=scale,
+                                      wire_dtype=wire_dtype if dt_ == torch.float32 else None,
+                                      algo=algo, stream=stream)
+            return outs if outs is not None else tensors
         dt = per_rank[0][0].dtype
         flat_in, flat_out = [], []
         for r in range(len(per_rank)):

@@ -354,3 +354,19 @@ def test_large_staged_messages_are_pipelined_on_three_streams(world, monkeypatch
             for r in range(world):
                 assert same(devs[r][i].cpu(), w), (r, i)
         assert same(dev[0].cpu(), reduce_many(host, "sum"))
+
+
+def test_group_with_mixed_dtypes_splits_per_dtype(sess):
+    g = torch.Generator().manual_seed(4)
+    kinds = [torch.float32, torch.bfloat16, torch.float32, torch.int32, torch.bfloat16]
+    sizes = [100, 33, 7, 64, 4096]
+    host = [[(torch.rand(n, generator=g) * 8).to(dt) for n, dt in zip(sizes, kinds)]
+            for _ in range(sess.world)]
+    dev = [[t.cuda() for t in host[r]] for r in range(sess.world)]
+    sess.group_all_reduce(dev if sess.vranks > 1 else dev[0])
+    torch.cuda.synchronize()
+    sess.check()
+    for i in range(len(sizes)):
+        want = reduce_many([host[r][i] for r in range(sess.world)], "sum")
+        for r in range(sess.world):
+            assert same(dev[r][i].cpu(), want), (r, i)
