@@ -36,6 +36,19 @@ split_work(const workspace &w, const graph_pair_list &gps, size_t chunk_size)
     return out;
 }
 
+namespace
+{
+// STDML_COLLECTIVE_ALGO: auto | oneshot | twoshot | nvls | nvls_oneshot
+int forced_algo(const system_config &c)
+{
+    if (c.device_algo == "oneshot") { return cuda::kAlgoOneShot; }
+    if (c.device_algo == "twoshot") { return cuda::kAlgoTwoShot; }
+    if (c.device_algo == "nvls") { return cuda::kAlgoNvls; }
+    if (c.device_algo == "nvls_oneshot") { return cuda::kAlgoNvlsOneShot; }
+    return -1;
+}
+}  // namespace
+
 session::session(system_config config, size_t version, size_t rank, peer_list peers,
                  peer_list runners, mailbox *mailbox, slotbox *slotbox,
                  rchan::client_pool *client_pool, strategy s)
@@ -499,18 +512,6 @@ bool session::consistent(const void *ptr, size_t size)
 }
 
 // -------------------------------------------------------------- device path
-namespace
-{
-// STDML_COLLECTIVE_ALGO: auto | oneshot | twoshot | nvls | nvls_oneshot
-int forced_algo(const system_config &c)
-{
-    if (c.device_algo == "oneshot") { return cuda::kAlgoOneShot; }
-    if (c.device_algo == "twoshot") { return cuda::kAlgoTwoShot; }
-    if (c.device_algo == "nvls") { return cuda::kAlgoNvls; }
-    if (c.device_algo == "nvls_oneshot") { return cuda::kAlgoNvlsOneShot; }
-    return -1;
-}
-}  // namespace
 
 bool session::on_device(const void *a, const void *b) const
 {
