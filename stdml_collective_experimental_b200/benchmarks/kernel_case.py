@@ -43,6 +43,38 @@ def staged_group(args, sess, dtype, es):
     sess.close()
 
 
+def other_collective(args, sess, dtype, es, n):
+    w = args.world
+    ins = [torch.full((n,), float(r + 1), dtype=dtype, device="cuda") for r in range(w)]
+    outs = [torch.empty(n * w if args.collective == "all_gather" else n, dtype=dtype,
+                        device="cuda") for _ in range(w)]
+    a_in = ins if w > 1 else ins[0]
+    a_out = outs if w > 1 else outs[0]
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(args.iters + 1)]
+    e[0].record()
+    for i in range(args.iters):
+        if args.collective == "all_gather":
+            sess.all_gather(a_in, a_out)
+        elif args.collective == "broadcast":
+            sess.broadcast(a_in, out=a_out, root=0)
+        else:
+            sess.barrier()
+        e[i + 1].record()
+    torch.cuda.synchronize()
+    sess.check()
+    times = [e[i].elapsed_time(e[i + 1]) for i in range(args.iters)]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    nbytes = n * es
+    # all_gather: pack (r+w) per rank, then every rank reads w blocks and writes w blocks
+    hbm = {"all_gather": w * nbytes * (2 + 2 * w), "broadcast": nbytes * (2 + 2 * w),
+           "barrier": 0}[args.collective]
+    print(json.dumps({"collective": args.collective, "world": w, "mb_per_rank": args.mb,
+                      "ms_per_launch": times, "best_ms": best, "hbm_bytes_per_launch": hbm,
+                      "achieved_gb_s": hbm / (best * 1e-3) / 1e9 if hbm else None}))
+    sess.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--world", type=int, default=4)
@@ -51,6 +83,8 @@ def main():
     ap.add_argument("--algo", default="twoshot")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--blocks", type=int, default=0)
+    ap.add_argument("--collective", default="all_reduce",
+                    help="all_reduce | all_gather | broadcast | barrier")
     ap.add_argument("--staged-group", type=int, default=0,
                     help="N > 0: reduce N separately allocated tensors per rank (pack + reduce + "
                          "unpack through a descriptor table) instead of one symmetric buffer")
@@ -59,11 +93,15 @@ def main():
     es = 4 if args.dtype == "f32" else 2
     n = (args.mb << 20) // es
     sess = DeviceSession.loopback(args.world, heap_bytes=(args.mb << 20) + (8 << 20),
-                                  staging_bytes=(args.mb + 1) << 20 if args.staged_group else 1 << 20)
+                                  staging_bytes=(args.mb + 1) << 20
+                                  if (args.staged_group or args.collective != "all_reduce")
+                                  else 1 << 20)
     if args.blocks:
         sess.set_tuning(max_blocks=args.blocks)
     if args.staged_group > 0:
         return staged_group(args, sess, dtype, es)
+    if args.collective != "all_reduce":
+        return other_collective(args, sess, dtype, es, n)
     sym = sess.symm_empty(n, dtype)
     bufs = sym if args.world > 1 else [sym]
     for r, b in enumerate(bufs):
