@@ -112,3 +112,32 @@ def test_shutdown_and_host_side_failure_detection():
 
 def test_public_headers_compile_as_cxx17():
     run("test_cxx17")
+
+
+@pytest.mark.parametrize("np_,strategy", [(16, "STAR"), (16, "RING"), (7, "RING")])
+def test_collectives_many_ranks(np_, strategy):
+    # the reference's CI sweeps np = 1..16 (t:37-57 there)
+    assert f"np={np_}: OK" in run("test_collectives", np_,
+                                  env={"KUNGFU_ALLREDUCE_STRATEGY": strategy})
+
+
+def test_host_runtime_under_address_and_thread_sanitizers():
+    """The host runtime rebuilt with -fsanitize=address / thread must run the unit
+    and integration programs without a report (compute-sanitizer's job for the
+    device code is done by exhaustive small cases against the CPU oracle)."""
+    if not os.path.exists("/usr/lib/gcc/x86_64-linux-gnu/13/libasan.so"):
+        pytest.skip("sanitizer runtimes not installed")
+    for san, opts in (("address", {"ASAN_OPTIONS": "detect_leaks=1:protect_shadow_gap=0"}),
+                      ("thread", {"TSAN_OPTIONS": "report_thread_leaks=0"})):
+        res = subprocess.run(["make", "-C", _native.CSRC, "-j8", "sanitize", f"SAN={san}"],
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        assert res.returncode == 0, res.stdout[-3000:]
+        sdir = os.path.join(_native.CSRC, "build", f"san-{san}", "bin")
+        for prog, args in (("test_unit", []), ("test_collectives", ["3"]), ("test_shutdown", ["3"])):
+            e = dict(os.environ, **opts)
+            for k in ("KUNGFU_SELF_SPEC", "OMPI_COMM_WORLD_SIZE", "RANK", "WORLD_SIZE"):
+                e.pop(k, None)
+            out = subprocess.run([os.path.join(sdir, prog), *args], env=e, stdout=subprocess.PIPE,
+                                 stderr=subprocess.STDOUT, text=True, timeout=900)
+            assert out.returncode == 0, (san, prog, out.stdout[-3000:])
+            assert "Sanitizer" not in out.stdout, (san, prog, out.stdout[-3000:])
