@@ -123,4 +123,7 @@ int launch_gather(const CommCtx &ctx, const GatherArgs &a, int blocks, int vrank
 int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op,
                       int blocks, int vranks, void *stream);
 bool nvls_supported(int dt, int op);
+// world of one GPU: dst = scale * src (integers: copy), no arena involved
+int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, float scale,
+                       int has_scale, int sms, void *stream);
 }  // namespace stdml::collective::cuda

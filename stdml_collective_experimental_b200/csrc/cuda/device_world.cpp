@@ -402,6 +402,16 @@ class World final : public DeviceWorld
                                  (c.dst != nullptr && c.dst[v] != nullptr);
             any_dst_null = any_dst_null || !has_dst;
         }
+        if (opt_.world == 1 && vranks_ == 1 && c.table == nullptr && user_dt == c.dt &&
+            c.phases == kPhaseAll) {
+            // alone on the GPU: one scaled copy, straight from the source to the
+            // destination (the arena buffer stands in for whichever is absent)
+            char *sym = base_[0] + c.off;
+            const void *from = (c.src != nullptr && c.src[0] != nullptr) ? c.src[0] : sym;
+            void *to = (c.dst != nullptr && c.dst[0] != nullptr) ? c.dst[0] : sym;
+            return launch_local_scale(from, to, c.count, c.dt, c.scale, c.has_scale ? 1 : 0,
+                                      num_sms_, stream);
+        }
         int algo = c.algo;
         if (algo < 0) { algo = pick_algo(bytes, c.dt, c.op, any_dst_null); }
         const bool owner = (algo == kAlgoTwoShot || algo == kAlgoNvls);

@@ -28,6 +28,86 @@ int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op
     return -1;
 }
 
+// A world of one GPU: all_reduce degenerates to out = scale * in.  No peers, no
+// barrier, no arena: a light grid-stride copy with many loads in flight.
+template <int DT>
+__global__ void __launch_bounds__(256)
+    local_scale_kernel(const void *src, void *dst,
+                       unsigned long long count, float scale, int has_scale)
+{
+    constexpr unsigned long long N = lanes_of<DT>();
+    const unsigned long long nvec = (count + N - 1) / N;
+    const bool al = ptr_aligned16(src) && ptr_aligned16(dst);
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    unsigned long long v = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    constexpr int U = 8;
+    for (; v + (U - 1) * stride < nvec; v += U * stride) {
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            x[u] = load_user_vec<DT>(src, false, v + u * stride, count, al);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if constexpr (Tr<DT>::is_float) {
+                if (has_scale) { x[u] = scale_vec<DT>(x[u], scale); }
+            }
+            store_user_vec<DT>(dst, false, v + u * stride, count, al, x[u]);
+        }
+    }
+    for (; v < nvec; v += stride) {
+        uint4 x = load_user_vec<DT>(src, false, v, count, al);
+        if constexpr (Tr<DT>::is_float) {
+            if (has_scale) { x = scale_vec<DT>(x, scale); }
+        }
+        store_user_vec<DT>(dst, false, v, count, al, x);
+    }
+}
+
+template <int DT>
+static int launch_local_dt(const void *src, void *dst, unsigned long long count, float scale,
+                           int has_scale, int sms, cudaStream_t s)
+{
+    constexpr unsigned long long N = lanes_of<DT>();
+    const unsigned long long nvec = (count + N - 1) / N;
+    unsigned long long blocks = (nvec + 256ull * 8 - 1) / (256ull * 8);
+    const unsigned long long cap = static_cast<unsigned long long>(sms) * 8;
+    if (blocks > cap) { blocks = cap; }
+    if (blocks < 1) { blocks = 1; }
+    local_scale_kernel<DT><<<static_cast<unsigned int>(blocks), 256, 0, s>>>(src, dst, count, scale,
+                                                                             has_scale);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, float scale,
+                       int has_scale, int sms, void *stream)
+{
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dt) {
+    case DT_I8:
+    case DT_U8:
+        return launch_local_dt<DT_U8>(src, dst, count, scale, 0, sms, s);
+    case DT_I16:
+    case DT_U16:
+        return launch_local_dt<DT_U16>(src, dst, count, scale, 0, sms, s);
+    case DT_I32:
+    case DT_U32:
+        return launch_local_dt<DT_U32>(src, dst, count, scale, 0, sms, s);
+    case DT_I64:
+    case DT_U64:
+        return launch_local_dt<DT_U64>(src, dst, count, scale, 0, sms, s);
+    case DT_BF16:
+        return launch_local_dt<DT_BF16>(src, dst, count, scale, has_scale, sms, s);
+    case DT_F16:
+        return launch_local_dt<DT_F16>(src, dst, count, scale, has_scale, sms, s);
+    case DT_F32:
+        return launch_local_dt<DT_F32>(src, dst, count, scale, has_scale, sms, s);
+    case DT_F64:
+        return launch_local_dt<DT_F64>(src, dst, count, scale, has_scale, sms, s);
+    }
+    return -1;
+}
+
 bool nvls_supported(int dt, int op)
 {
     if (dt == DT_F32) { return op == OP_SUM; }

@@ -127,7 +127,9 @@ def test_raw_algorithms_agree(sess):
         torch.cuda.synchronize()
         for r in range(sess.world):
             assert same(dst2[r].cpu(), want), ("twoshot", blocks)
-            assert same(syms[r].cpu(), want), ("twoshot leaves the result in the arena", blocks)
+            if sess.world > 1:  # a single GPU copies straight from src to dst
+                assert same(syms[r].cpu(), want), ("twoshot leaves the result in the arena",
+                                                   blocks)
     sess.check()
     sess.symm_free(sym)
 

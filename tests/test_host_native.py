@@ -1,6 +1,7 @@
 """CPU tests of the native host runtime: builds the C++ test programs and runs
 them (ranks are real processes on TCP loopback, forked by the programs)."""
 import os
+import shutil
 import subprocess
 
 import pytest
@@ -141,3 +142,4 @@ def test_host_runtime_under_address_and_thread_sanitizers():
                                  stderr=subprocess.STDOUT, text=True, timeout=900)
             assert out.returncode == 0, (san, prog, out.stdout[-3000:])
             assert "Sanitizer" not in out.stdout, (san, prog, out.stdout[-3000:])
+        shutil.rmtree(os.path.join(_native.CSRC, "build", f"san-{san}"), ignore_errors=True)
