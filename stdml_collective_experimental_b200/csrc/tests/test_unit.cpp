@@ -11,6 +11,10 @@
 #include <stdml/bits/collective/execution.hpp>
 #include <stdml/bits/collective/http.hpp>
 #include <stdml/bits/collective/json.hpp>
+#include <stdml/bits/collective/net/ioutil.hpp>
+#include <stdml/bits/collective/net/tcp.hpp>
+#include <stdml/bits/collective/patient.hpp>
+#include <stdml/bits/collective/xterm.hpp>
 #include <stdml/bits/collective/waitgroup.hpp>
 #include <stdml/collective>
 
@@ -327,8 +331,64 @@ static void test_misc()
     CHECK(s.all_reduce(x) == 5 && s.broadcast(x) == 5 && s.consistent(x));
 }
 
+static void test_sockets_and_io_tasks()
+{
+    // echo server: u32 length + body in, the same back
+    TcpServer server(0, localhost);
+    server.start();
+    std::thread srv([&] {
+        server.serve([](std::unique_ptr<TcpSocket> s) {
+            uint32_t n = 0;
+            if (s->recv(&n, 4) != 0) { return; }
+            std::vector<char> body(n);
+            if (n > 0 && s->recv(body.data(), n) != 0) { return; }
+            s->send(&n, 4);
+            s->send(body.data(), n);
+        });
+    });
+    {
+        TcpClient client(server.port());
+        client.dial();
+        const std::string msg(100000, 'q');
+        const auto reply = client.Talk(msg.data(), msg.size());
+        CHECK(reply.size() == msg.size() && reply[99999] == 'q');
+    }
+    // the same exchange as polled tasks on non-blocking sockets, one thread
+    {
+        TcpClient client(server.port());
+        client.dial();
+        TcpSocket &sock = client.socket();
+        sock.set_non_blocking(true);
+        using io = basic_ioutil<TcpSocket, true>;
+        std::vector<char> out(300000, 'z'), in(300000, 0);
+        uint32_t n = static_cast<uint32_t>(out.size()), m = 0;
+        task_builder steps;
+        steps << io::new_write_task(sock, &n, 4);
+        steps << io::new_write_task(sock, out.data(), out.size());
+        steps << io::new_read_task(sock, &m, 4);
+        steps << io::new_read_task(sock, in.data(), in.size());
+        std::unique_ptr<task> all(steps.seq());
+        all->finish();
+        CHECK(m == n && in == out);
+    }
+    int code = 0;
+    TcpClient nobody(1);
+    nobody.dial(&code);
+    CHECK(code != 0);
+    server.stop();
+    srv.join();
+
+    patient p(std::chrono::milliseconds(20));
+    CHECK(p.ok() && !p.lost());
+    std::this_thread::sleep_for(std::chrono::milliseconds(30));
+    CHECK(!p.ok() && p.lost() && p.ok());
+    CHECK(xterm::paint("ok", xterm::green) == "\x1b[32mok\x1b[0m");
+    CHECK(xterm::paint("ok", xterm::green, false) == "ok");
+}
+
 int main()
 {
+    test_sockets_and_io_tasks();
     test_dtype();
     test_partition();
     test_topology();
