@@ -3,6 +3,7 @@
 // Counterpart of include/stdml/bits/collective/execution.hpp:55-90.
 #pragma once
 #include <exception>
+#include <mutex>
 #include <thread>
 #include <vector>
 
@@ -28,23 +29,28 @@ template <typename F, typename L>
 void fmap(parallel_policy, const F &f, const L &xs)
 {
     std::vector<std::thread> ths;
+    std::mutex err_mu;
     std::exception_ptr err;
+    auto keep = [&err_mu, &err] {
+        std::lock_guard<std::mutex> lk(err_mu);
+        if (!err) { err = std::current_exception(); }
+    };
     auto it = xs.begin();
     if (it == xs.end()) { return; }
     const auto first = it++;
     for (; it != xs.end(); ++it) {
-        ths.emplace_back([&f, &err, it] {
+        ths.emplace_back([&f, &keep, it] {
             try {
                 f(*it);
             } catch (...) {
-                err = std::current_exception();
+                keep();
             }
         });
     }
     try {
         f(*first);
     } catch (...) {
-        err = std::current_exception();
+        keep();
     }
     for (auto &t : ths) { t.join(); }
     if (err) { std::rethrow_exception(err); }

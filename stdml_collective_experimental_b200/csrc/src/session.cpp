@@ -344,6 +344,7 @@ void session::group_all_reduce(std::vector<std::future<workspace>> fs)
     }
     workers = std::min(workers, n);
     std::atomic<size_t> next{0};
+    std::atomic<bool> failed{false};
     std::mutex err_mu;
     std::exception_ptr err;
     auto work = [&] {
@@ -352,8 +353,9 @@ void session::group_all_reduce(std::vector<std::future<workspace>> fs)
             if (i >= n) { return; }
             try {
                 const workspace w = fs[i].get();
-                if (!err) { all_reduce(w); }
+                if (!failed.load()) { all_reduce(w); }
             } catch (...) {
+                failed.store(true);
                 std::lock_guard<std::mutex> lk(err_mu);
                 if (!err) { err = std::current_exception(); }
             }
