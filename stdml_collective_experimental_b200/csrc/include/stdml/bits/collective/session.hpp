@@ -100,6 +100,14 @@ class session
 
     void all_reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
                     std::string name = "", void *stream = nullptr);
+    // The async interface: starts the operation and returns a task to poll()
+    // (or finish()).  Host buffers: the chunk graph as a polled task tree, no
+    // thread blocks; device buffers: the kernels are enqueued at once and the
+    // task finishes when the GPU has run them.  The buffers must stay alive
+    // until the task has finished.
+    std::unique_ptr<task> async_all_reduce(const void *input, void *output, size_t count,
+                                           dtype dt, reduce_op op, std::string name = "",
+                                           void *stream = nullptr);
     void reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
                 std::string name = "", void *stream = nullptr);
     void all_gather(const void *input, void *output, size_t count, dtype dt,

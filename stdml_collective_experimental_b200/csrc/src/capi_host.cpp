@@ -299,3 +299,37 @@ int stdmlc_trace_write(const char *path)
     return sc::rchan::stat_write_chrome_trace(path) ? 0 : 1;
 }
 }
+
+// ------------------------------------------------------------ async interface
+extern "C" {
+int stdmlc_session_all_reduce_async(void *s, const void *in, void *out, unsigned long long count,
+                                    int dt, int op, const char *name, void *stream, void **task)
+{
+    *task = nullptr;
+    return host_guarded([&] {
+        *task = SS(s)
+                    .async_all_reduce(in, out, count, static_cast<sc::dtype>(dt),
+                                      static_cast<sc::reduce_op>(op), name ? name : "", stream)
+                    .release();
+    });
+}
+
+int stdmlc_task_poll(void *task, int *finished)
+{
+    return host_guarded([&] {
+        auto *t = static_cast<sc::task *>(task);
+        t->poll();
+        *finished = t->finished() ? 1 : 0;
+    });
+}
+
+int stdmlc_task_finish(void *task)
+{
+    return host_guarded([&] { static_cast<sc::task *>(task)->finish(); });
+}
+
+int stdmlc_task_destroy(void *task)
+{
+    return host_guarded([&] { delete static_cast<sc::task *>(task); });
+}
+}

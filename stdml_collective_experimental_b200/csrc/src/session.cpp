@@ -6,6 +6,7 @@
 #include <stdexcept>
 #include <thread>
 
+#include <stdml/bits/collective/device.hpp>
 #include <stdml/bits/collective/execution.hpp>
 #include <stdml/bits/collective/log.hpp>
 #include <stdml/bits/collective/session.hpp>
@@ -291,6 +292,36 @@ void session::all_reduce(const void *input, void *output, size_t count, dtype dt
     w.op = op;
     w.name = std::move(name);
     all_reduce(w, stream);
+}
+
+std::unique_ptr<task> session::async_all_reduce(const void *input, void *output, size_t count,
+                                                dtype dt, reduce_op op, std::string name,
+                                                void *stream)
+{
+    if (!reduce_supported(dt, op)) {
+        throw std::invalid_argument("async_all_reduce: undefined dtype/op pair");
+    }
+    workspace w;
+    w.send = input;
+    w.recv = output;
+    w.count = count;
+    w.dt = dt;
+    w.op = op;
+    w.name = std::move(name);
+    if (count == 0) { return std::make_unique<noop_task>(); }
+    if (on_device(input, output)) {
+        all_reduce(w, stream);  // enqueues and returns
+        return std::make_unique<event_task>(stream);
+    }
+    if (peers_.size() == 1) {
+        w.forward();
+        return std::make_unique<noop_task>();
+    }
+    std::vector<std::unique_ptr<task>> ts;
+    for (const auto &[part, gs] : split_work(w, all_reduce_topo_, chunk_bytes)) {
+        ts.emplace_back(chunk_task(part, gs.first, gs.second));
+    }
+    return std::unique_ptr<task>(task::par(std::move(ts)));
 }
 
 void session::group_all_reduce(const std::vector<workspace> &ws, double scale, void *stream)

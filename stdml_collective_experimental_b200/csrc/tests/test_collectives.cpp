@@ -212,6 +212,17 @@ static void check_others(session &sess)
         t2.join();
         CHECK(threw);
     }
+    // async interface: two operations in flight, polled from this thread
+    {
+        std::vector<float> a(300000, float(r)), b(1000, 1.0f), ra(a.size()), rb(b.size());
+        auto t1 = sess.async_all_reduce(a.data(), ra.data(), a.size(), f32, sum, "async:a");
+        auto t2 = sess.async_all_reduce(b.data(), rb.data(), b.size(), f32, max, "async:b");
+        while (!t1->finished() || !t2->finished()) {
+            t1->poll();
+            t2->poll();
+        }
+        CHECK(ra[0] == float(n * (n - 1) / 2) && ra.back() == ra[0] && rb[0] == 1.0f);
+    }
     sess.barrier();
 }
 

@@ -49,6 +49,11 @@ def _lib():
         lib.stdmlc_peer_resize.argtypes = [vp, vp, c.c_longlong, c.c_char_p, c.POINTER(c.c_int),
                                            c.POINTER(c.c_int)]
         lib.stdmlc_cluster_resize_json.argtypes = [c.c_char_p, u64, c.c_char_p, u64]
+        lib.stdmlc_session_all_reduce_async.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int,
+                                                        c.c_char_p, vp, vpp]
+        lib.stdmlc_task_poll.argtypes = [vp, c.POINTER(c.c_int)]
+        lib.stdmlc_task_finish.argtypes = [vp]
+        lib.stdmlc_task_destroy.argtypes = [vp]
         lib.stdmlc_trace_enable.argtypes = [c.c_int]
         lib.stdmlc_trace_write.argtypes = [c.c_char_p]
         _declared = True
@@ -67,6 +72,44 @@ def _checked(t, what):
     if not t.is_contiguous():
         raise ValueError(f"{what}: contiguous tensor expected")
     return t
+
+
+class Task:
+    """A started operation (the reference's polled `task`): poll() makes progress
+    without blocking, wait() polls to completion.  Keeps its tensors alive."""
+
+    def __init__(self, handle, keep):
+        self._h = handle
+        self._keep = keep
+        self._lib = _lib()
+        self._done = False
+
+    def poll(self):
+        if not self._done:
+            fin = ctypes.c_int()
+            _native.check(self._lib.stdmlc_task_poll(self._h, ctypes.byref(fin)))
+            self._done = bool(fin.value)
+        return self._done
+
+    @property
+    def finished(self):
+        return self.poll()
+
+    def wait(self):
+        if not self._done:
+            _native.check(self._lib.stdmlc_task_finish(self._h))
+            self._done = True
+        return self._keep[-1]
+
+    def __del__(self):
+        try:
+            if self._h is not None:
+                if not self._done:
+                    self._lib.stdmlc_task_finish(self._h)
+                self._lib.stdmlc_task_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
 
 
 class Session:
@@ -123,6 +166,18 @@ class Session:
             self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), op_code(op),
             name.encode(), _stream_of(t)))
         return o
+
+    def all_reduce_async(self, tensor, out=None, op="sum", name=""):
+        """Start an all_reduce and return a Task.  CPU tensors: the chunk graph runs
+        as polled tasks (no thread blocks); CUDA tensors: the kernel is enqueued on
+        the current stream and the task finishes when the GPU has run it."""
+        t = _checked(tensor, "all_reduce_async")
+        o = t if out is None else _checked(out, "all_reduce_async")
+        h = ctypes.c_void_p()
+        _native.check(self._lib.stdmlc_session_all_reduce_async(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), op_code(op),
+            name.encode(), _stream_of(t), ctypes.byref(h)))
+        return Task(h, (t, o))
 
     def reduce(self, tensor, out=None, op="sum", name=""):
         """Result on rank 0 only (the reference's fixed root)."""

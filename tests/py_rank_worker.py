@@ -47,6 +47,13 @@ def main():
             sess.send(torch.tensor([42.0]), 1, name="p2p")
         elif rank == 1:
             assert sess.recv(torch.zeros(1), 0, name="p2p").item() == 42.0
+    # async interface: two operations in flight, polled from this thread
+    a, b = torch.full((300_000,), float(rank)), torch.ones(10)
+    ta = sess.all_reduce_async(a, name="async:a")
+    tb = sess.all_reduce_async(b, op="max", name="async:b")
+    while not (ta.poll() and tb.poll()):
+        pass
+    assert a[0] == n * (n - 1) / 2 and a[-1] == a[0] and b[0] == 1
     sess.barrier()
 
     # elastic: shrink to n - 1 by explicit configuration; the last rank detaches

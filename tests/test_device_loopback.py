@@ -372,3 +372,23 @@ def test_group_with_mixed_dtypes_splits_per_dtype(sess):
         want = reduce_many([host[r][i] for r in range(sess.world)], "sum")
         for r in range(sess.world):
             assert same(dev[r][i].cpu(), want), (r, i)
+
+
+def test_session_async_interface_on_cuda_tensors():
+    """Peer/Session (the C++ session) with device pointers: a single-rank world,
+    the returned task polls a CUDA event."""
+    from stdml_collective_experimental_b200.parallel import Peer
+    peer = Peer.from_list(0, ["127.0.0.1:10990"])
+    sess = peer.join()
+    x = torch.arange(100_000, dtype=torch.float32, device="cuda")
+    y = torch.empty_like(x)
+    task = sess.all_reduce_async(x, out=y, name="dev")
+    task.wait()
+    assert torch.equal(x, y)
+    sess.all_reduce(x, op="max")
+    gathered = torch.empty(100_000, device="cuda")
+    sess.all_gather(x, gathered)
+    torch.cuda.synchronize()
+    assert torch.equal(gathered, x)
+    sess.close()
+    peer.close()
