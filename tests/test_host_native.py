@@ -143,3 +143,7 @@ def test_host_runtime_under_address_and_thread_sanitizers():
             assert out.returncode == 0, (san, prog, out.stdout[-3000:])
             assert "Sanitizer" not in out.stdout, (san, prog, out.stdout[-3000:])
         shutil.rmtree(os.path.join(_native.CSRC, "build", f"san-{san}"), ignore_errors=True)
+
+
+def test_elastic_agreement_with_stale_and_failing_config_providers():
+    assert "test-elastic: OK" in run("test_elastic")
