@@ -3,6 +3,7 @@
 // per (type, target), dialled on first use.  TCP_NODELAY is set on every
 // socket: control messages are latency-bound (the reference leaves Nagle on,
 // src/stdml/collective/platforms/linux/socket_opt.c:41-45).
+#include <algorithm>
 #include <atomic>
 #include <cerrno>
 #include <chrono>
@@ -89,25 +90,60 @@ bool write_iov(int fd, iovec *iov, int cnt)
     return true;
 }
 
+// Per-connection receive buffer: small messages (header, name, short bodies)
+// are served from one recv() of whatever the socket holds, large bodies are
+// read straight into their destination once the buffered part is copied out.
+struct recv_buffer {
+    std::vector<char> data;
+    size_t head = 0, tail = 0;
+
+    recv_buffer() : data(256 << 10) {}
+
+    bool read(int fd, void *dst, size_t n)
+    {
+        char *out = static_cast<char *>(dst);
+        while (n > 0) {
+            if (head < tail) {
+                const size_t take = std::min(n, tail - head);
+                std::memcpy(out, data.data() + head, take);
+                head += take;
+                out += take;
+                n -= take;
+                continue;
+            }
+            head = tail = 0;
+            if (n >= data.size() / 2) { return read_exact(fd, out, n); }
+            const ssize_t got = ::recv(fd, data.data(), data.size(), 0);
+            if (got > 0) {
+                tail = static_cast<size_t>(got);
+            } else if (got == 0 || errno != EINTR) {
+                return false;
+            }
+        }
+        return true;
+    }
+};
+
 class reader_impl final : public message_reader
 {
     int fd_;
+    recv_buffer *buf_;
     uint32_t len_ = 0;
 
   public:
-    explicit reader_impl(int fd) : fd_(fd) {}
+    reader_impl(int fd, recv_buffer *buf) : fd_(fd), buf_(buf) {}
 
     std::optional<received_header> read_header() override
     {
         STDML_COLLECTIVE_PROFILE_RATE("read_header", 0);
         received_header h;
-        if (!read_exact(fd_, &h.name_len, 4)) { return {}; }
+        if (!buf_->read(fd_, &h.name_len, 4)) { return {}; }
         if (h.name_len > (1u << 20)) { return {}; }  // not our protocol
-        std::vector<char> rest(h.name_len + 8);
-        if (!read_exact(fd_, rest.data(), rest.size())) { return {}; }
-        h.name.assign(rest.data(), h.name_len);
-        std::memcpy(&h.flags, rest.data() + h.name_len, 4);
-        std::memcpy(&h.len, rest.data() + h.name_len + 4, 4);
+        h.name.resize(h.name_len);
+        uint32_t tail[2];
+        if (!buf_->read(fd_, h.name.data(), h.name_len) || !buf_->read(fd_, tail, 8)) { return {}; }
+        h.flags = tail[0];
+        h.len = tail[1];
         len_ = h.len;
         return h;
     }
@@ -115,7 +151,7 @@ class reader_impl final : public message_reader
     bool read_body(void *data) override
     {
         STDML_COLLECTIVE_PROFILE_RATE("read_body", len_);
-        return len_ == 0 || read_exact(fd_, data, len_);
+        return len_ == 0 || buf_->read(fd_, data, len_);
     }
 };
 
@@ -125,6 +161,7 @@ class connection_impl final : public connection
     conn_type type_;
     peer_id src_;
     std::mutex send_mu_;
+    recv_buffer rbuf_;  // used by the (single) thread that reads this connection
 
   public:
     connection_impl(int fd, conn_type type, peer_id src) : fd_(fd), type_(type), src_(src) {}
@@ -146,7 +183,7 @@ class connection_impl final : public connection
 
     std::unique_ptr<message_reader> next() override
     {
-        return std::unique_ptr<message_reader>(new reader_impl(fd_));
+        return std::unique_ptr<message_reader>(new reader_impl(fd_, &rbuf_));
     }
 
     void send(const char *name, const void *data, size_t size, uint32_t flags) override
