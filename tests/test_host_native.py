@@ -147,3 +147,28 @@ def test_host_runtime_under_address_and_thread_sanitizers():
 
 def test_elastic_agreement_with_stale_and_failing_config_providers():
     assert "test-elastic: OK" in run("test_elastic")
+
+
+def test_standalone_config_server_get_put():
+    import json
+    import time
+    import urllib.request
+    srv = subprocess.Popen([os.path.join(BIN, "stdml_collective_config_server"), "-port", "19191",
+                            "-ttl", "20"], stdout=subprocess.PIPE, text=True)
+    try:
+        assert "config server on" in srv.stdout.readline()
+        url = "http://127.0.0.1:19191/config"
+        assert json.loads(urllib.request.urlopen(url, timeout=5).read()) == {"Runners": [],
+                                                                             "Workers": []}
+        good = {"Runners": [{"IPv4": 2130706433, "Port": 38080}],
+                "Workers": [{"IPv4": 2130706433, "Port": 10000}]}
+        req = urllib.request.Request(url, data=json.dumps(good).encode(), method="PUT")
+        assert json.loads(urllib.request.urlopen(req, timeout=5).read()) == good
+        assert json.loads(urllib.request.urlopen(url, timeout=5).read()) == good
+        bad = urllib.request.Request(url, data=b"{nope", method="PUT")
+        with pytest.raises(urllib.error.HTTPError):
+            urllib.request.urlopen(bad, timeout=5)
+        time.sleep(0.05)
+    finally:
+        srv.terminate()
+        srv.wait(timeout=10)
