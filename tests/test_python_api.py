@@ -30,3 +30,13 @@ def test_python_elastic_state_under_the_runner(native_lib):
                          timeout=600)
     assert res.returncode == 0, res.stdout[-3000:]
     assert res.stdout.count("weight 36.0 OK") == 2 and res.stdout.count("detached") == 1
+
+
+def test_distributed_optimizer_matches_single_process_training(native_lib):
+    n, base = 3, 12200
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_train_worker.py"), str(r),
+                               str(n), str(base)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(n)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
