@@ -134,11 +134,6 @@ def test_raw_algorithms_agree(sess):
     sess.symm_free(sym)
 
 
-def _grad_set(world, sizes, dtype, seed):
-    return [[t for t in make_inputs(1, n, dtype, seed + 1000 * r + i)] for r in range(world)
-            for i, n in enumerate(sizes)]
-
-
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_group_all_reduce_fused(sess, dtype):
     sizes = [1, 7, 768, 3, 2304, 590_000, 5, 64, 1000, 123_457, 2, 768]
