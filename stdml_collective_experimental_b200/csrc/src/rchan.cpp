@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cerrno>
+#include <cstddef>
 #include <chrono>
 #include <cstring>
 #include <list>
@@ -19,6 +20,7 @@
 #include <poll.h>
 #include <sys/socket.h>
 #include <sys/uio.h>
+#include <sys/un.h>
 #include <unistd.h>
 
 #include <stdml/bits/collective/config.hpp>
@@ -47,6 +49,25 @@ sockaddr_in to_sockaddr(const peer_id &id)
     a.sin_port = htons(id.port);
     a.sin_addr.s_addr = htonl(id.ipv4);
     return a;
+}
+
+// Second back-end: ranks of one host may talk over abstract UNIX-domain stream
+// sockets instead of TCP loopback (STDML_COLLECTIVE_TRANSPORT=unix).  The
+// framing is identical; only dialling and listening differ.  Every server
+// listens on both, so mixed settings still connect.
+bool prefer_unix_sockets()
+{
+    static const bool on = safe_getenv("STDML_COLLECTIVE_TRANSPORT") == "unix";
+    return on;
+}
+
+socklen_t to_unix_addr(const peer_id &id, sockaddr_un &a)
+{
+    std::memset(&a, 0, sizeof(a));
+    a.sun_family = AF_UNIX;
+    const std::string name = "stdml-rchan/" + id.str();  // abstract namespace: leading NUL
+    std::memcpy(a.sun_path + 1, name.data(), name.size());
+    return static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + name.size());
 }
 
 bool read_exact(int fd, void *data, size_t size)
@@ -223,9 +244,20 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
     const sockaddr_in addr = to_sockaddr(remote);
     int wait_ms = 2;
     for (;;) {
-        const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        const bool local_peer = prefer_unix_sockets() &&
+                                (remote.ipv4 == local.ipv4 || local.ipv4 == 0 ||
+                                 (remote.ipv4 >> 24) == 127u);
+        const int fd = ::socket(local_peer ? AF_UNIX : AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         if (fd < 0) { throw std::runtime_error("rchan: socket() failed"); }
-        if (::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr)) == 0) {
+        int rc;
+        if (local_peer) {
+            sockaddr_un ua;
+            const socklen_t ul = to_unix_addr(remote, ua);
+            rc = ::connect(fd, reinterpret_cast<const sockaddr *>(&ua), ul);
+        } else {
+            rc = ::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr));
+        }
+        if (rc == 0) {
             tune_socket(fd);
             conn_header h{static_cast<uint16_t>(type), local.port, local.ipv4};
             connection_ack ack{};
@@ -328,6 +360,7 @@ class server_impl final : public server
     const peer_id self_;
     conn_handler *handler_;
     int listen_fd_ = -1;
+    int unix_fd_ = -1;  // same service on an abstract UNIX socket
     std::atomic<bool> stopping_{false};
     std::thread accept_thread_;
     std::mutex mu_;
@@ -361,6 +394,16 @@ class server_impl final : public server
             throw std::runtime_error("rchan: cannot bind " + self_.str() + ": " + why);
         }
         if (::listen(listen_fd_, 128) != 0) { throw std::runtime_error("rchan: listen() failed"); }
+        unix_fd_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        if (unix_fd_ >= 0) {
+            sockaddr_un ua;
+            const socklen_t ul = to_unix_addr(self_, ua);
+            if (::bind(unix_fd_, reinterpret_cast<sockaddr *>(&ua), ul) != 0 ||
+                ::listen(unix_fd_, 128) != 0) {
+                ::close(unix_fd_);  // TCP alone still serves everybody
+                unix_fd_ = -1;
+            }
+        }
     }
 
     void reap()
@@ -379,10 +422,11 @@ class server_impl final : public server
     void accept_loop()
     {
         while (!stopping_.load()) {
-            pollfd pfd{listen_fd_, POLLIN, 0};
-            const int r = ::poll(&pfd, 1, 100);
+            pollfd pfds[2] = {{listen_fd_, POLLIN, 0}, {unix_fd_, POLLIN, 0}};
+            const int r = ::poll(pfds, unix_fd_ >= 0 ? 2 : 1, 100);
             if (r <= 0) { continue; }
-            const int fd = ::accept4(listen_fd_, nullptr, nullptr, SOCK_CLOEXEC);
+            const int ready = (pfds[0].revents & POLLIN) ? listen_fd_ : unix_fd_;
+            const int fd = ::accept4(ready, nullptr, nullptr, SOCK_CLOEXEC);
             if (fd < 0) { continue; }
             tune_socket(fd);
             conn_header h{};
@@ -447,6 +491,10 @@ class server_impl final : public server
             if (s.wake_fd >= 0) { ::close(s.wake_fd); }
         }
         sessions_.clear();
+        if (unix_fd_ >= 0) {
+            ::close(unix_fd_);
+            unix_fd_ = -1;
+        }
         if (listen_fd_ >= 0) {
             ::close(listen_fd_);
             listen_fd_ = -1;

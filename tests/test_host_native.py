@@ -42,7 +42,10 @@ def test_collectives_star(np_):
     {"KUNGFU_ALLREDUCE_STRATEGY": "RING", "STDML_COLLECTIVE_USE_ASYNC": "1"},
     {"STDML_COLLECTIVE_USE_ASYNC": "1"},
     {"STDML_COLLECTIVE_USE_THREAD_POOL": "1"},
-], ids=["ring", "ring-pool", "ring-async", "star-async", "star-pool"])
+    {"KUNGFU_ALLREDUCE_STRATEGY": "RING", "STDML_COLLECTIVE_TRANSPORT": "unix"},
+    {"STDML_COLLECTIVE_TRANSPORT": "unix", "STDML_COLLECTIVE_USE_ASYNC": "1"},
+], ids=["ring", "ring-pool", "ring-async", "star-async", "star-pool", "ring-unix-sockets",
+        "star-async-unix-sockets"])
 def test_collectives_strategies_and_runtimes(env):
     assert "np=4: OK" in run("test_collectives", 4, env=env)
 
