@@ -109,3 +109,33 @@ def test_device_api_fails_loudly_without_a_gpu():
     assert int(s.all_reduce(torch.tensor([5]))[0]) == 5
     s.close()
     p.close()
+
+
+def test_native_api_reports_misuse_as_exceptions():
+    import pytest
+    from stdml_collective_experimental_b200 import _native
+    from stdml_collective_experimental_b200.parallel import Peer, resized_cluster
+    with pytest.raises(ValueError, match="malformed peer list"):
+        Peer.from_list(0, ["not-an-address"])
+    with pytest.raises(ValueError, match="rank outside"):
+        Peer.from_list(3, ["127.0.0.1:10870"])
+    with pytest.raises(ValueError):
+        resized_cluster({"Runners": "oops"}, 2)
+    grown = resized_cluster({"Runners": [{"IPv4": 2130706433, "Port": 38080}],
+                             "Workers": [{"IPv4": 2130706433, "Port": 10000}]}, 3)
+    assert [w["Port"] for w in grown["Workers"]] == [10000, 10001, 10002]
+    p = Peer.from_list(0, ["127.0.0.1:10871"])
+    s = p.join()
+    with pytest.raises(ValueError, match="contiguous"):
+        s.all_reduce(torch.ones(4, 4).t())
+    with pytest.raises(ValueError, match="not defined"):
+        s.all_reduce(torch.ones(4), op="bit_xor")
+    with pytest.raises(ValueError, match="unknown reduce op"):
+        s.all_reduce(torch.ones(4), op="avg")
+    with pytest.raises(TypeError):
+        s.all_reduce(torch.ones(4, dtype=torch.complex64))
+    with pytest.raises(ValueError, match="must hold"):
+        s.all_gather(torch.ones(4), torch.ones(5))
+    assert _native.lib().stdmlc_dtype_size(8) == 2
+    s.close()
+    p.close()
