@@ -24,7 +24,7 @@ struct Span {
 };
 
 // Sub-range `b` of `nb` of shard `s` of `shards` of [0, nvec).
-__device__ __forceinline__ Span span_of(unsigned long long nvec, int shards, int s, int nb,
+__host__ __device__ __forceinline__ Span span_of(unsigned long long nvec, int shards, int s, int nb,
                                         int b)
 {
     const unsigned long long s_lo = nvec * static_cast<unsigned long long>(s) / shards;
@@ -37,7 +37,7 @@ __device__ __forceinline__ Span span_of(unsigned long long nvec, int shards, int
 }
 
 template <int DT>
-__device__ __forceinline__ unsigned long long entry_nvec(unsigned long long count)
+__host__ __device__ __forceinline__ unsigned long long entry_nvec(unsigned long long count)
 {
     constexpr unsigned long long N = lanes_of<DT>();
     return (count + N - 1) / N;
@@ -138,7 +138,7 @@ __device__ __forceinline__ bool ptr_aligned16(const void *p)
 
 // Index of the last table entry whose first vector is <= v (entries are sorted
 // by voff and entry 0 starts at 0).
-__device__ __forceinline__ int find_entry(const GroupEntry *tab, int n, unsigned long long v)
+__host__ __device__ __forceinline__ int find_entry(const GroupEntry *tab, int n, unsigned long long v)
 {
     int lo = 0, hi = n - 1;
     while (lo < hi) {

@@ -224,7 +224,7 @@ struct Tr<DT_F64> {
 };
 
 template <int DT>
-constexpr int lanes_of()
+__host__ __device__ constexpr int lanes_of()
 {
     return 16 / static_cast<int>(sizeof(typename Tr<DT>::storage));
 }

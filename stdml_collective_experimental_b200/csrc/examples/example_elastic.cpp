@@ -1,5 +1,5 @@
 // Elastic data-parallel loop driven by a resize schedule:
-//   stdml_collective_run -np 4 -w -builtin-config-port 0 \
+//   stdml_collective_run -np 4 -w -builtin-config-port 0
 //       example_elastic --max-step=12 3:2 6:3 9:4
 // "3:2" = after step 3 resize to 2 workers.  Survivors keep running; joiners
 // are started by the runner and catch up: the step counter by a max-all-reduce

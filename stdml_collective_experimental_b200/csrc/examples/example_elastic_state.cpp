@@ -1,7 +1,7 @@
 // The same loop written with elastic_state: progress and resize checks are
 // handled by the state object; membership follows the config server, so a
 // proposal can come from anywhere (here: rank 0 follows a schedule).
-//   stdml_collective_run -np 2 -w -builtin-config-port 0 \
+//   stdml_collective_run -np 2 -w -builtin-config-port 0
 //       example_elastic_state --max-step=9 2:4 5:3
 #include <cstdio>
 #include <map>

@@ -177,3 +177,8 @@ def test_standalone_config_server_get_put():
     finally:
         srv.terminate()
         srv.wait(timeout=10)
+
+
+def test_kernel_index_arithmetic_on_the_cpu():
+    # span partition and descriptor-table search of the device kernels, compiled for the host
+    assert "test-partition: OK" in run("test_partition_cuda")
