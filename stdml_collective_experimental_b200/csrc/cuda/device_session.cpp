@@ -305,6 +305,28 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
     }
 }
 
+std::vector<std::vector<GroupPiece>> plan_group_pieces(size_t n, const size_t *counts,
+                                                       size_t lanes, size_t cap)
+{
+    std::vector<std::vector<GroupPiece>> chunks(1);
+    size_t fill = 0;
+    for (size_t i = 0; i < n; ++i) {
+        size_t done = 0;
+        while (done < counts[i]) {
+            if (fill == cap) {
+                chunks.emplace_back();
+                fill = 0;
+            }
+            const size_t room = (cap - fill) * lanes;
+            const size_t take = std::min(room, counts[i] - done);
+            chunks.back().push_back(GroupPiece{i, done, take, fill});
+            fill += (take + lanes - 1) / lanes;
+            done += take;
+        }
+    }
+    return chunks;
+}
+
 const DeviceSession::GroupPlan &DeviceSession::plan_group(size_t n, const void *const *ins,
                                                           void *const *outs,
                                                           const size_t *counts, int dt,
@@ -331,27 +353,8 @@ const DeviceSession::GroupPlan &DeviceSession::plan_group(size_t n, const void *
     const size_t lanes = 16 / es;
     const size_t cap = world_->staging_bytes() / 16;  // vectors per slot
 
-    // Cut the flat sequence of tensors into slot-sized chunks; a tensor that
-    // does not fit is split at a vector boundary.
-    struct Piece {
-        size_t tensor, first_elem, count, voff;
-    };
-    std::vector<std::vector<Piece>> chunks(1);
-    size_t fill = 0;
-    for (size_t i = 0; i < n; ++i) {
-        size_t done = 0;
-        while (done < counts[i]) {
-            if (fill == cap) {
-                chunks.emplace_back();
-                fill = 0;
-            }
-            const size_t room = (cap - fill) * lanes;
-            const size_t take = std::min(room, counts[i] - done);
-            chunks.back().push_back(Piece{i, done, take, fill});
-            fill += (take + lanes - 1) / lanes;
-            done += take;
-        }
-    }
+    using Piece = GroupPiece;
+    const std::vector<std::vector<Piece>> chunks = plan_group_pieces(n, counts, lanes, cap);
 
     GroupPlan plan;
     for (const auto &pieces : chunks) {

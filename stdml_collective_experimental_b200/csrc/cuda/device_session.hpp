@@ -33,6 +33,19 @@ struct DeviceTimeout : std::runtime_error {
     }
 };
 
+// One tensor (or part of one) placed in a staging slot: elements
+// [first_elem, first_elem + count) of tensor `tensor` at vector offset `voff`.
+struct GroupPiece {
+    size_t tensor, first_elem, count, voff;
+};
+
+// Cuts a sequence of tensors (element counts) into chunks of at most `cap`
+// 16-byte vectors; a tensor that does not fit is split at a vector boundary.
+// Every element appears in exactly one piece; pieces of one chunk are in tensor
+// order and start on vector boundaries.  Pure function (tested on the CPU).
+std::vector<std::vector<GroupPiece>> plan_group_pieces(size_t n, const size_t *counts,
+                                                       size_t lanes, size_t cap);
+
 class DeviceSession
 {
   public:

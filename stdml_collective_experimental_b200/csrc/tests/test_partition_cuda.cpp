@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "../cuda/ar_kernel.cuh"
+#include "../cuda/device_session.hpp"
 
 using namespace stdml::collective::cuda;
 
@@ -69,6 +70,31 @@ int main()
             }
             EXPECT(found);
         }
+    }
+    // group planning: every element lands in exactly one piece, chunks respect
+    // the slot size, pieces start on vector boundaries and keep tensor order
+    for (int trial = 0; trial < 2000; ++trial) {
+        const size_t n = 1 + rng() % 60;
+        const size_t lanes = size_t(1) << (rng() % 5);  // 1, 2, 4, 8, 16 elements per vector
+        const size_t cap = 1 + rng() % 3000;
+        std::vector<size_t> counts(n);
+        for (auto &c : counts) { c = rng() % 7 == 0 ? 0 : 1 + rng() % (cap * lanes * 3); }
+        const auto chunks = plan_group_pieces(n, counts.data(), lanes, cap);
+        std::vector<size_t> covered(n, 0);
+        size_t last_tensor = 0;
+        for (const auto &chunk : chunks) {
+            size_t fill = 0;
+            for (const auto &p : chunk) {
+                EXPECT(p.tensor >= last_tensor && p.count > 0);
+                last_tensor = p.tensor;
+                EXPECT(p.voff == fill && p.first_elem == covered[p.tensor]);
+                covered[p.tensor] += p.count;
+                fill += (p.count + lanes - 1) / lanes;
+                EXPECT(p.first_elem % lanes == 0);  // splits happen at vector boundaries
+            }
+            EXPECT(fill <= cap);
+        }
+        for (size_t i = 0; i < n; ++i) { EXPECT(covered[i] == counts[i]); }
     }
     EXPECT(entry_nvec<DT_BF16>(9) == 2 && entry_nvec<DT_U8>(16) == 1 && entry_nvec<DT_F64>(3) == 2);
     std::printf("test-partition: %s\n", failures == 0 ? "OK" : "FAILED");
