@@ -9,6 +9,7 @@
 
 #include "../cuda/ar_kernel.cuh"
 #include "../cuda/device_session.hpp"
+#include "../cuda/offset_heap.hpp"
 
 using namespace stdml::collective::cuda;
 
@@ -95,6 +96,50 @@ int main()
             EXPECT(fill <= cap);
         }
         for (size_t i = 0; i < n; ++i) { EXPECT(covered[i] == counts[i]); }
+    }
+    // symmetric heap: deterministic first fit, 256-byte granules, coalescing
+    {
+        OffsetHeap h;
+        h.reset(4096, 1 << 20);
+        const size_t a = h.alloc(100), b = h.alloc(300), c = h.alloc(1);
+        EXPECT(a == 4096 && b == 4096 + 256 && c == 4096 + 256 + 512);
+        h.release(b);
+        EXPECT(h.alloc(512) == b);   // exact hole reused
+        h.release(a);
+        h.release(b);
+        EXPECT(h.alloc(700) == a);   // the two holes merged (256 + 512 >= 768)
+        bool threw = false;
+        try {
+            h.alloc(2 << 20);
+        } catch (const std::bad_alloc &) {
+            threw = true;
+        }
+        EXPECT(threw);
+        threw = false;
+        try {
+            h.release(12345);
+        } catch (const std::invalid_argument &) {
+            threw = true;
+        }
+        EXPECT(threw);
+        // two heaps fed the same calls hand out the same offsets (ranks stay symmetric)
+        OffsetHeap x, y;
+        x.reset(0, 1 << 24);
+        y.reset(0, 1 << 24);
+        std::vector<size_t> live;
+        for (int i = 0; i < 2000; ++i) {
+            if (!live.empty() && rng() % 3 == 0) {
+                const size_t k = rng() % live.size();
+                x.release(live[k]);
+                y.release(live[k]);
+                live.erase(live.begin() + k);
+            } else {
+                const size_t bytes = 1 + rng() % 5000;
+                const size_t ox = x.alloc(bytes), oy = y.alloc(bytes);
+                EXPECT(ox == oy && ox % 256 == 0);
+                live.push_back(ox);
+            }
+        }
     }
     EXPECT(entry_nvec<DT_BF16>(9) == 2 && entry_nvec<DT_U8>(16) == 1 && entry_nvec<DT_F64>(3) == 2);
     std::printf("test-partition: %s\n", failures == 0 ? "OK" : "FAILED");
