@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <unistd.h>
 
+#include "algo_table.hpp"
 #include "local_rendezvous.hpp"
 #include "offset_heap.hpp"
 
@@ -262,51 +263,27 @@ class World final : public DeviceWorld
     }
 
     // ------------------------------------------------------- algorithm table
-    // Thresholds below come from device-timed sweeps on 2, 4 and 8 B200s (f32
-    // sum, 4 KB ... 1 GiB, this library's four algorithms against each other).
-    size_t oneshot_limit() const
+    AlgoTuning tuning() const
     {
-        if (oneshot_max_ != 0) { return oneshot_max_; }
-        const size_t w = static_cast<size_t>(opt_.world);
-        return w <= 2 ? (8u << 20) : (16u << 20) / (w * w);
-    }
-
-    size_t nvls_oneshot_limit() const
-    {
-        if (nvls_oneshot_max_ != 0) { return nvls_oneshot_max_; }
-        return 2u << 20;  // only staged / out-of-place calls can take it; beats a
-                          // staged owner algorithm up to a few MB
+        AlgoTuning t;
+        t.world = opt_.world;
+        t.vranks = vranks_;
+        t.num_sms = num_sms_;
+        t.max_blocks = max_blocks_;
+        t.oneshot_max = oneshot_max_;
+        t.nvls_oneshot_max = nvls_oneshot_max_;
+        t.has_nvls = has_nvls();
+        return t;
     }
 
     int pick_algo(size_t bytes, int dt, int op, bool need_owner) const override
     {
-        if (opt_.world == 1) { return need_owner ? kAlgoTwoShot : kAlgoOneShot; }
-        // with two GPUs the switch has nothing to add: peer loads are faster
-        const bool nvls = has_nvls() && nvls_supported(dt, op) && opt_.world > 2;
-        if (nvls) {
-            if (!need_owner && bytes <= nvls_oneshot_limit()) { return kAlgoNvlsOneShot; }
-            return kAlgoNvls;
-        }
-        if (!need_owner && bytes <= oneshot_limit()) { return kAlgoOneShot; }
-        return kAlgoTwoShot;
+        return select_algo(tuning(), bytes, nvls_supported(dt, op), need_owner);
     }
 
     int pick_blocks(size_t nvec, int algo) const override
     {
-        const bool owner = (algo == kAlgoTwoShot || algo == kAlgoNvls);
-        const size_t work = owner ? (nvec + opt_.world - 1) / opt_.world : nvec;
-        const size_t per_block = static_cast<size_t>(kThreads) * 4;
-        size_t b = (work + per_block - 1) / per_block;
-        size_t cap = static_cast<size_t>(max_blocks_);
-        if (algo == kAlgoNvls || algo == kAlgoNvlsOneShot) {
-            // the switch saturates with few CTAs; more only add contention
-            cap = std::min<size_t>(cap, nvec * 16 >= (16u << 20) ? 32 : 64);
-        }
-        // alone on the GPU the kernel is an HBM copy: one resident CTA per SM
-        if (opt_.world == 1) { cap = static_cast<size_t>(num_sms_); }
-        if (vranks_ > 1) { cap = std::min<size_t>(cap, std::max(1, num_sms_ / vranks_)); }
-        b = std::max<size_t>(1, std::min(b, std::min<size_t>(cap, kMaxBlocks)));
-        return static_cast<int>(b);
+        return select_blocks(tuning(), nvec, algo);
     }
 
     // --------------------------------------------------------------- launches

@@ -9,6 +9,7 @@
 
 #include "../cuda/ar_kernel.cuh"
 #include "../cuda/device_session.hpp"
+#include "../cuda/algo_table.hpp"
 #include "../cuda/offset_heap.hpp"
 
 using namespace stdml::collective::cuda;
@@ -138,6 +139,54 @@ int main()
                 const size_t ox = x.alloc(bytes), oy = y.alloc(bytes);
                 EXPECT(ox == oy && ox % 256 == 0);
                 live.push_back(ox);
+            }
+        }
+    }
+    // the measured algorithm table
+    {
+        AlgoTuning t8;
+        t8.world = 8;
+        t8.has_nvls = true;
+        EXPECT(select_algo(t8, 64 << 10, true, false) == kAlgoNvlsOneShot);
+        EXPECT(select_algo(t8, 2 << 20, true, false) == kAlgoNvlsOneShot);
+        EXPECT(select_algo(t8, (2 << 20) + 16, true, false) == kAlgoNvls);
+        EXPECT(select_algo(t8, 4096, true, true) == kAlgoNvls);            // in place
+        EXPECT(select_algo(t8, 256 << 10, false, false) == kAlgoOneShot);  // e.g. prod: no NVLS
+        EXPECT(select_algo(t8, (256 << 10) + 16, false, false) == kAlgoTwoShot);
+        AlgoTuning t2 = t8;
+        t2.world = 2;
+        EXPECT(select_algo(t2, 8 << 20, true, false) == kAlgoOneShot);  // the switch adds nothing at 2
+        EXPECT(select_algo(t2, 1 << 30, true, false) == kAlgoTwoShot);
+        AlgoTuning t4 = t8;
+        t4.world = 4;
+        t4.has_nvls = false;
+        EXPECT(select_algo(t4, 1 << 20, true, false) == kAlgoOneShot);
+        EXPECT(select_algo(t4, (1 << 20) + 16, true, false) == kAlgoTwoShot);
+        AlgoTuning t1;
+        EXPECT(select_algo(t1, 1 << 20, true, false) == kAlgoOneShot);
+        EXPECT(select_algo(t1, 1 << 20, true, true) == kAlgoTwoShot);
+        t8.oneshot_max = 1024;  // overrides
+        EXPECT(select_algo(t8, 2048, false, false) == kAlgoTwoShot);
+        t8.oneshot_max = 0;
+        // grids: one vector ... 1 GiB
+        EXPECT(select_blocks(t8, 1, kAlgoNvls) == 1);
+        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoNvls) == 32);
+        EXPECT(select_blocks(t8, (8ull << 20) / 16, kAlgoNvls) == 32);  // 1 MB per rank / 32 KB per CTA
+        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoTwoShot) == 128);
+        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoOneShot) == 128);
+        EXPECT(select_blocks(t1, (1ull << 30) / 16, kAlgoTwoShot) == 148);
+        AlgoTuning loop = t8;
+        loop.vranks = 8;
+        loop.has_nvls = false;
+        EXPECT(select_blocks(loop, (1ull << 30) / 16, kAlgoTwoShot) == 18);  // 148 SMs / 8 rows
+        for (int w = 1; w <= 16; ++w) {  // never zero, never above the pad size
+            AlgoTuning t;
+            t.world = w;
+            for (unsigned long long nv : {1ull, 7ull, 4096ull, 1ull << 26}) {
+                for (int algo = 0; algo < 4; ++algo) {
+                    const int b = select_blocks(t, nv, algo);
+                    EXPECT(b >= 1 && b <= kMaxBlocks);
+                }
             }
         }
     }
