@@ -18,7 +18,9 @@
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <poll.h>
+#include <sys/mman.h>
 #include <sys/socket.h>
+#include <sys/stat.h>
 #include <sys/uio.h>
 #include <sys/un.h>
 #include <unistd.h>
@@ -27,6 +29,8 @@
 #include <stdml/bits/collective/log.hpp>
 #include <stdml/bits/collective/rchan.hpp>
 #include <stdml/bits/collective/stat.hpp>
+
+#include "shm_ring.hpp"
 
 namespace stdml::collective::rchan
 {
@@ -55,10 +59,72 @@ sockaddr_in to_sockaddr(const peer_id &id)
 // sockets instead of TCP loopback (STDML_COLLECTIVE_TRANSPORT=unix).  The
 // framing is identical; only dialling and listening differ.  Every server
 // listens on both, so mixed settings still connect.
+bool prefer_shared_memory()
+{
+    static const bool on = safe_getenv("STDML_COLLECTIVE_TRANSPORT") == "shm";
+    return on;
+}
+
 bool prefer_unix_sockets()
 {
-    static const bool on = safe_getenv("STDML_COLLECTIVE_TRANSPORT") == "unix";
+    static const bool on =
+        safe_getenv("STDML_COLLECTIVE_TRANSPORT") == "unix" || prefer_shared_memory();
     return on;
+}
+
+// Third back-end (STDML_COLLECTIVE_TRANSPORT=shm): the dialler of a UNIX-domain
+// connection announces a ring with this bit of conn_header::type, creates it
+// and hands its descriptor over the socket; from then on the socket carries no
+// payload and only signals that the other side has gone.
+constexpr uint16_t conn_type_ring_bit = 0x8000;
+
+struct ring_offer {
+    uint64_t capacity;
+};
+
+bool send_fd(int sock, int fd, const ring_offer &offer)
+{
+    msghdr msg{};
+    iovec iov{const_cast<ring_offer *>(&offer), sizeof(offer)};
+    alignas(cmsghdr) char ctl[CMSG_SPACE(sizeof(int))] = {};
+    msg.msg_iov = &iov;
+    msg.msg_iovlen = 1;
+    msg.msg_control = ctl;
+    msg.msg_controllen = sizeof(ctl);
+    cmsghdr *c = CMSG_FIRSTHDR(&msg);
+    c->cmsg_level = SOL_SOCKET;
+    c->cmsg_type = SCM_RIGHTS;
+    c->cmsg_len = CMSG_LEN(sizeof(int));
+    std::memcpy(CMSG_DATA(c), &fd, sizeof(int));
+    ssize_t n;
+    do {
+        n = ::sendmsg(sock, &msg, MSG_NOSIGNAL);
+    } while (n < 0 && errno == EINTR);
+    return n == static_cast<ssize_t>(sizeof(offer));
+}
+
+int recv_fd(int sock, ring_offer &offer)
+{
+    msghdr msg{};
+    iovec iov{&offer, sizeof(offer)};
+    alignas(cmsghdr) char ctl[CMSG_SPACE(sizeof(int))] = {};
+    msg.msg_iov = &iov;
+    msg.msg_iovlen = 1;
+    msg.msg_control = ctl;
+    msg.msg_controllen = sizeof(ctl);
+    ssize_t n;
+    do {
+        n = ::recvmsg(sock, &msg, MSG_CMSG_CLOEXEC | MSG_WAITALL);
+    } while (n < 0 && errno == EINTR);
+    if (n != static_cast<ssize_t>(sizeof(offer))) { return -1; }
+    for (cmsghdr *c = CMSG_FIRSTHDR(&msg); c != nullptr; c = CMSG_NXTHDR(&msg, c)) {
+        if (c->cmsg_level == SOL_SOCKET && c->cmsg_type == SCM_RIGHTS) {
+            int fd;
+            std::memcpy(&fd, CMSG_DATA(c), sizeof(int));
+            return fd;
+        }
+    }
+    return -1;
 }
 
 socklen_t to_unix_addr(const peer_id &id, sockaddr_un &a)
@@ -117,11 +183,13 @@ bool write_iov(int fd, iovec *iov, int cnt)
 struct recv_buffer {
     std::vector<char> data;
     size_t head = 0, tail = 0;
+    shm_ring *ring = nullptr;  // set: the ring is the buffer, the socket carries nothing
 
     recv_buffer() : data(256 << 10) {}
 
     bool read(int fd, void *dst, size_t n)
     {
+        if (ring != nullptr) { return ring->read(dst, n); }
         char *out = static_cast<char *>(dst);
         while (n > 0) {
             if (head < tail) {
@@ -183,12 +251,18 @@ class connection_impl final : public connection
     peer_id src_;
     std::mutex send_mu_;
     recv_buffer rbuf_;  // used by the (single) thread that reads this connection
+    std::unique_ptr<shm_ring> ring_;  // dialler: written by send(); acceptor: read by next()
 
   public:
-    connection_impl(int fd, conn_type type, peer_id src) : fd_(fd), type_(type), src_(src) {}
+    connection_impl(int fd, conn_type type, peer_id src, std::unique_ptr<shm_ring> ring = nullptr)
+        : fd_(fd), type_(type), src_(src), ring_(std::move(ring))
+    {
+        rbuf_.ring = ring_.get();
+    }
 
     ~connection_impl() override
     {
+        if (ring_) { ring_->close(); }
         if (fd_ >= 0) { ::close(fd_); }
     }
 
@@ -220,12 +294,70 @@ class connection_impl final : public connection
         iov[3] = {&const_cast<uint32_t &>(len), 4};
         iov[4] = {const_cast<void *>(data), size};
         std::lock_guard<std::mutex> lk(send_mu_);
+        if (ring_) {
+            // header fields in one piece, so that a short message costs one wake-up
+            char head[256];
+            if (12 + static_cast<size_t>(name_len) <= sizeof(head)) {
+                std::memcpy(head, &name_len, 4);
+                std::memcpy(head + 4, name, name_len);
+                std::memcpy(head + 4 + name_len, &flags, 4);
+                std::memcpy(head + 8 + name_len, &len, 4);
+                if (ring_->write(head, 12 + name_len) && (size == 0 || ring_->write(data, size))) {
+                    return;
+                }
+            } else {
+                bool ok = true;
+                for (int i = 0; ok && i < (size > 0 ? 5 : 4); ++i) {
+                    ok = ring_->write(iov[i].iov_base, iov[i].iov_len);
+                }
+                if (ok) { return; }
+            }
+            throw std::runtime_error("rchan: send to " + src_.str() + " failed: peer has gone");
+        }
         if (!write_iov(fd_, iov, size > 0 ? 5 : 4)) {
             throw std::runtime_error("rchan: send to " + src_.str() + " failed: " +
                                      std::strerror(errno));
         }
     }
 };
+
+size_t ring_capacity()
+{
+    static const size_t v = [] {
+        const auto mb = parse_env_int("STDML_COLLECTIVE_SHM_RING_MB").value_or(8);
+        return static_cast<size_t>(std::min<int64_t>(std::max<int64_t>(mb, 1), 1024)) << 20;
+    }();
+    return v;
+}
+
+// dialler's side: create, map and hand over
+std::unique_ptr<shm_ring> offer_ring(int sock)
+{
+    const size_t cap = ring_capacity();
+    const int mfd = ::memfd_create("stdml-rchan-ring", MFD_CLOEXEC);
+    if (mfd < 0) { return nullptr; }
+    std::unique_ptr<shm_ring> ring(new shm_ring);
+    const bool ok = ::ftruncate(mfd, static_cast<off_t>(shm_ring::bytes_for(cap))) == 0 &&
+                    ring->open(mfd, cap, true, sock) && send_fd(sock, mfd, ring_offer{cap});
+    ::close(mfd);  // the mapping and the receiver's copy keep the memory alive
+    return ok ? std::move(ring) : nullptr;
+}
+
+// acceptor's side
+std::unique_ptr<shm_ring> accept_ring(int sock)
+{
+    ring_offer offer{};
+    const int mfd = recv_fd(sock, offer);
+    if (mfd < 0) { return nullptr; }
+    std::unique_ptr<shm_ring> ring(new shm_ring);
+    struct stat st {};
+    const bool ok = offer.capacity >= 4096 && offer.capacity <= (size_t(1) << 30) &&
+                    ::fstat(mfd, &st) == 0 &&
+                    static_cast<size_t>(st.st_size) >= shm_ring::bytes_for(offer.capacity) &&
+                    ring->open(mfd, offer.capacity, false, sock);
+    ::close(mfd);
+    return ok ? std::move(ring) : nullptr;
+}
 }  // namespace
 
 int64_t connect_timeout_ms()
@@ -259,11 +391,23 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
         }
         if (rc == 0) {
             tune_socket(fd);
-            conn_header h{static_cast<uint16_t>(type), local.port, local.ipv4};
+            const bool want_ring = local_peer && prefer_shared_memory();
+            const uint16_t wire_type =
+                static_cast<uint16_t>(type) | (want_ring ? conn_type_ring_bit : uint16_t(0));
+            conn_header h{wire_type, local.port, local.ipv4};
             connection_ack ack{};
             iovec iov{&h, sizeof(h)};
             if (write_iov(fd, &iov, 1) && read_exact(fd, &ack, sizeof(ack))) {
-                return std::unique_ptr<connection>(new connection_impl(fd, type, remote));
+                if (!want_ring) {
+                    return std::unique_ptr<connection>(new connection_impl(fd, type, remote));
+                }
+                if (auto ring = offer_ring(fd)) {
+                    return std::unique_ptr<connection>(
+                        new connection_impl(fd, type, remote, std::move(ring)));
+                }
+                ::close(fd);
+                throw std::runtime_error("rchan: cannot set up a shared-memory ring to " +
+                                         remote.str());
             }
         }
         ::close(fd);
@@ -436,6 +580,15 @@ class server_impl final : public server
                 ::close(fd);
                 continue;
             }
+            std::unique_ptr<shm_ring> ring;
+            if ((h.type & conn_type_ring_bit) != 0) {
+                ring = accept_ring(fd);
+                if (!ring) {
+                    log(WARN) << "rchan: a peer offered a shared-memory ring that cannot be mapped";
+                    ::close(fd);
+                    continue;
+                }
+            }
             std::lock_guard<std::mutex> lk(mu_);
             if (stopping_.load()) {
                 ::close(fd);
@@ -444,8 +597,9 @@ class server_impl final : public server
             reap();
             sessions_.emplace_back();
             session &s = sessions_.back();
-            auto *conn = new connection_impl(fd, static_cast<conn_type>(h.type),
-                                             peer_id{h.src_ipv4, h.src_port});
+            auto *conn = new connection_impl(
+                fd, static_cast<conn_type>(h.type & ~conn_type_ring_bit),
+                peer_id{h.src_ipv4, h.src_port}, std::move(ring));
             s.wake_fd = ::dup(fd);
             s.th = std::thread([this, conn, &s] {
                 try {

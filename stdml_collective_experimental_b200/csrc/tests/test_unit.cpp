@@ -18,6 +18,7 @@
 #include <stdml/bits/collective/waitgroup.hpp>
 #include <stdml/collective>
 
+#include "../src/shm_ring.hpp"
 #include "testing.hpp"
 
 using namespace stdml::collective;
@@ -386,8 +387,61 @@ static void test_sockets_and_io_tasks()
     CHECK(xterm::paint("ok", xterm::green, false) == "ok");
 }
 
+// The shared-memory ring on its own: a small ring forces many wrap-arounds and
+// both kinds of sleep (full and empty); close() ends a blocked reader.
+static void test_shm_ring()
+{
+    const size_t cap = 4096;
+    const int mfd = ::memfd_create("test-ring", MFD_CLOEXEC);
+    REQUIRE(mfd >= 0);
+    REQUIRE(::ftruncate(mfd, static_cast<off_t>(rchan::shm_ring::bytes_for(cap))) == 0);
+    rchan::shm_ring tx, rx;
+    REQUIRE(tx.open(mfd, cap, true, -1));
+    REQUIRE(rx.open(mfd, cap, false, -1));
+    rchan::shm_ring wrong;
+    CHECK(!wrong.open(mfd, 2 * cap, false, -1));  // capacity in the header does not match
+    ::close(mfd);
+
+    const size_t total = 1 << 20;
+    std::vector<uint8_t> src(total), dst(total, 0);
+    for (size_t i = 0; i < total; ++i) { src[i] = static_cast<uint8_t>((i * 2654435761u) >> 13); }
+    std::thread producer([&] {
+        size_t at = 0, step = 1;
+        while (at < total) {  // pieces from 1 byte to several rings long
+            const size_t k = std::min(step, total - at);
+            CHECK(tx.write(src.data() + at, k));
+            at += k;
+            step = step * 3 + 1;
+            if (step > 3 * cap) { step = 1; }
+        }
+    });
+    size_t at = 0, step = 7;
+    while (at < total) {
+        const size_t k = std::min(step, total - at);
+        CHECK(rx.read(dst.data() + at, k));
+        at += k;
+        step = (step * 5 + 3) % (2 * cap) + 1;
+    }
+    producer.join();
+    CHECK(src == dst);
+
+    // bytes written before close() are still delivered; after them the reader gets end-of-stream
+    CHECK(tx.write("tail", 4));
+    std::thread closer([&] {
+        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        tx.close();
+    });
+    char tail[4];
+    CHECK(rx.read(tail, 4) && std::memcmp(tail, "tail", 4) == 0);
+    char more;
+    CHECK(!rx.read(&more, 1));  // blocks until close() wakes it
+    closer.join();
+    CHECK(!tx.write(src.data(), 2 * cap));  // a writer to a closed ring gives up once it is full
+}
+
 int main()
 {
+    test_shm_ring();
     test_sockets_and_io_tasks();
     test_dtype();
     test_partition();

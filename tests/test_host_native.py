@@ -44,8 +44,13 @@ def test_collectives_star(np_):
     {"STDML_COLLECTIVE_USE_THREAD_POOL": "1"},
     {"KUNGFU_ALLREDUCE_STRATEGY": "RING", "STDML_COLLECTIVE_TRANSPORT": "unix"},
     {"STDML_COLLECTIVE_TRANSPORT": "unix", "STDML_COLLECTIVE_USE_ASYNC": "1"},
+    {"KUNGFU_ALLREDUCE_STRATEGY": "RING", "STDML_COLLECTIVE_TRANSPORT": "shm"},
+    {"STDML_COLLECTIVE_TRANSPORT": "shm", "STDML_COLLECTIVE_USE_ASYNC": "1"},
+    # a ring far smaller than the 1 MB chunks: every body goes through in pieces
+    {"KUNGFU_ALLREDUCE_STRATEGY": "RING", "STDML_COLLECTIVE_TRANSPORT": "shm",
+     "STDML_COLLECTIVE_SHM_RING_MB": "1"},
 ], ids=["ring", "ring-pool", "ring-async", "star-async", "star-pool", "ring-unix-sockets",
-        "star-async-unix-sockets"])
+        "star-async-unix-sockets", "ring-shm", "star-async-shm", "ring-shm-small-ring"])
 def test_collectives_strategies_and_runtimes(env):
     assert "np=4: OK" in run("test_collectives", 4, env=env)
 
@@ -139,8 +144,11 @@ def test_host_runtime_under_address_and_thread_sanitizers():
                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         assert res.returncode == 0, res.stdout[-3000:]
         sdir = os.path.join(_native.CSRC, "build", f"san-{san}", "bin")
-        for prog, args in (("test_unit", []), ("test_collectives", ["3"]), ("test_shutdown", ["3"])):
-            e = dict(os.environ, **opts)
+        for prog, args, extra in (("test_unit", [], {}), ("test_collectives", ["3"], {}),
+                                  ("test_shutdown", ["3"], {}),
+                                  ("test_collectives", ["3"], {"STDML_COLLECTIVE_TRANSPORT": "shm"}),
+                                  ("test_shutdown", ["3"], {"STDML_COLLECTIVE_TRANSPORT": "shm"})):
+            e = dict(os.environ, **opts, **extra)
             for k in ("KUNGFU_SELF_SPEC", "OMPI_COMM_WORLD_SIZE", "RANK", "WORLD_SIZE"):
                 e.pop(k, None)
             out = subprocess.run([os.path.join(sdir, prog), *args], env=e, stdout=subprocess.PIPE,
