@@ -6,11 +6,16 @@ zero-copy: each bucket is a contiguous range of that buffer and one fused kernel
 launch reduces it in place over NVLink with the 1/world scale applied in
 registers.  Buckets are launched from autograd hooks on a side stream as soon as
 their gradients are complete, so communication overlaps the rest of backward.
+Inside `no_sync()` backward only accumulates into the flat buffer; the next
+backward outside it reduces the accumulated sum (gradient accumulation over
+micro-batches with one all-reduce per optimizer step).
 
 This is the PyTorch-side counterpart of the reference's `group_all_reduce`
 (src/stdml/collective/session.cpp:83-97), which its framework bindings call
 with one future per gradient.
 """
+import contextlib
+
 import torch
 
 from ..ops.device import DeviceSession
@@ -69,6 +74,7 @@ class DataParallel(torch.nn.Module):
         self._ready = [0] * self.nbuckets
         self._launched = 0
         self._callback_queued = False
+        self._sync = True
         self._events = [torch.cuda.Event() for _ in range(self.nbuckets)]
         for i, p in enumerate(self.params):
             p.register_post_accumulate_grad_hook(self._make_hook(self.bucket_of[i]))
@@ -78,6 +84,8 @@ class DataParallel(torch.nn.Module):
     # ------------------------------------------------------------------ hooks
     def _make_hook(self, bucket):
         def hook(_param):
+            if not self._sync:
+                return  # accumulating: the reduction waits for a backward outside no_sync()
             if not self._callback_queued:
                 self._callback_queued = True
                 torch.autograd.Variable._execution_engine.queue_callback(self._finish)
@@ -110,6 +118,16 @@ class DataParallel(torch.nn.Module):
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
 
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this context add to the local gradients without
+        communicating; every rank must use it for the same steps."""
+        old, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = old
+
     def zero_grad(self, set_to_none=False):
         """Zeroes the flat gradient buffer (the views must stay in place)."""
         self.flat.zero_()
@@ -119,8 +137,12 @@ class DataParallel(torch.nn.Module):
         with torch.no_grad():
             for t in list(self.module.parameters()) + list(self.module.buffers()):
                 if t.is_floating_point() or t.dtype in (torch.int64, torch.int32):
-                    self.sess.broadcast(t.data if t.is_contiguous() else t.data.contiguous(),
-                                        root=root)
+                    if t.is_contiguous():
+                        self.sess.broadcast(t.data, root=root)
+                    else:  # e.g. channels_last weights: through a dense copy and back
+                        dense = t.data.contiguous()
+                        self.sess.broadcast(dense, root=root)
+                        t.data.copy_(dense)
         torch.cuda.current_stream(self.sess.device).synchronize()
 
     def close(self):

@@ -65,6 +65,23 @@ def main():
     sess.all_reduce(hi, op="max")
     torch.cuda.synchronize()
     assert torch.equal(lo, hi)
+
+    # gradient accumulation: two micro-batches, the first without communication
+    x2, y2 = (t.to(dev) for t in data(rank + 100))
+    ddp.zero_grad()
+    with ddp.no_sync():
+        torch.nn.functional.cross_entropy(ddp(x), y).backward()
+    torch.nn.functional.cross_entropy(ddp(x2), y2).backward()
+    opt.step()
+    torch.cuda.synchronize()
+    sess.check()
+    ropt.zero_grad()
+    batches2 = [tuple(t.to(dev) for t in data(r + 100)) for r in range(world)]
+    loss = sum(torch.nn.functional.cross_entropy(ref(bx), by) for bx, by in batches + batches2) / world
+    loss.backward()
+    ropt.step()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(p, q, rtol=1e-4, atol=1e-5), float((p - q).abs().max())
     ddp.close()
     sess.close()
     print(f"OK rank {rank}", flush=True)

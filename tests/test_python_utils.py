@@ -139,3 +139,100 @@ def test_native_api_reports_misuse_as_exceptions():
     assert _native.lib().stdmlc_dtype_size(8) == 2
     s.close()
     p.close()
+
+
+class _FakeStream:
+    def __init__(self, *a, **k):
+        pass
+
+    def wait_event(self, ev):
+        pass
+
+    def wait_stream(self, s):
+        pass
+
+    def synchronize(self):
+        pass
+
+
+class _FakeEvent:
+    def record(self, stream=None):
+        pass
+
+
+class _FakeSession:
+    """Stands in for a 2-rank device session whose peer holds the same gradients:
+    all_reduce(x, scale) -> x * 2 * scale, recorded call by call."""
+    vranks, world, device = 1, 2, torch.device("cpu")
+
+    def __init__(self):
+        self.calls = []
+
+    def symm_empty(self, n, dtype):
+        return torch.empty(n, dtype=dtype)
+
+    def symm_free(self, t):
+        pass
+
+    def all_reduce(self, t, scale=None, algo=None, stream=None):
+        self.calls.append((t.data_ptr(), t.numel()))
+        t.mul_(2.0 * (scale if scale is not None else 1.0))
+
+    def broadcast(self, t, root=0):
+        pass
+
+
+def test_data_parallel_buckets_and_gradient_accumulation_on_cpu(monkeypatch):
+    """The bucket bookkeeping of DataParallel (readiness order, one launch per
+    bucket per synchronised backward, unused parameters, no_sync) does not
+    depend on the GPU: run it with stand-ins for the streams and the session."""
+    from stdml_collective_experimental_b200.parallel import ddp as ddp_mod
+
+    monkeypatch.setattr(torch.cuda, "Stream", _FakeStream)
+    monkeypatch.setattr(torch.cuda, "Event", _FakeEvent)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a, **k: _FakeStream())
+
+    torch.manual_seed(3)
+    net = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.Tanh(), torch.nn.Linear(7, 3),
+                              torch.nn.Tanh(), torch.nn.Linear(3, 2))
+    unused = torch.nn.Parameter(torch.ones(9))  # never takes part in forward
+    net.register_parameter("unused", unused)
+    ref = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.Tanh(), torch.nn.Linear(7, 3),
+                              torch.nn.Tanh(), torch.nn.Linear(3, 2))
+    ref.load_state_dict({k: v for k, v in net.state_dict().items() if k != "unused"})
+
+    sess = _FakeSession()
+    dp = ddp_mod.DataParallel(net, sess, buckets=3)
+    assert dp.nbuckets == 3
+    # buckets tile the flat buffer, every tensor starts on a 16-byte boundary
+    assert dp.bounds[0][0] == 0 and dp.bounds[-1][1] == dp.flat.numel()
+    assert all(a[1] == b[0] for a, b in zip(dp.bounds, dp.bounds[1:]))
+    assert all(p.grad.data_ptr() % 16 == dp.flat.data_ptr() % 16 for p in dp.params)
+
+    x1, x2 = torch.randn(4, 5), torch.randn(4, 5)
+    dp.zero_grad()
+    dp(x1).square().sum().backward()
+    assert len(sess.calls) == 3  # one launch per bucket, the unused parameter's bucket included
+    assert [c[1] for c in sess.calls] == [hi - lo for lo, hi in dp.bounds]
+    ref(x1).square().sum().backward()
+    for (n, p) in net.named_parameters():
+        if n != "unused":
+            assert torch.allclose(p.grad, dict(ref.named_parameters())[n].grad, atol=1e-6), n
+    assert torch.count_nonzero(unused.grad) == 0
+
+    # accumulation: nothing is launched inside no_sync, the sum is reduced once afterwards
+    sess.calls.clear()
+    dp.zero_grad()
+    ref.zero_grad()
+    with dp.no_sync():
+        dp(x1).square().sum().backward()
+    assert sess.calls == []
+    dp(x2).square().sum().backward()
+    assert len(sess.calls) == 3
+    ref(x1).square().sum().backward()
+    ref(x2).square().sum().backward()
+    for (n, p) in net.named_parameters():
+        if n != "unused":
+            assert torch.allclose(p.grad, dict(ref.named_parameters())[n].grad, atol=1e-6), n
+    dp.close()
+    assert all(p.grad is None for p in dp.params)
