@@ -15,7 +15,7 @@ import subprocess
 import tempfile
 
 from .. import _native
-from ..models.gradsets import GRADSETS, write_sizes_file
+from ..models.gradsets import GRADSETS, SWEEP, write_sizes_file
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 OURS = os.path.join(_native.CSRC, "build", "bin")
@@ -78,6 +78,9 @@ def main():
     ap.add_argument("--workloads", default="1024x100,16384x100,102400x100,262144x10,resnet50,vgg16")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
+    # "sweep" stands for the reference's AxB list (testdata/test-set-1.txt there)
+    args.workloads = ",".join(",".join(SWEEP) if w == "sweep" else w
+                              for w in args.workloads.split(","))
     _native.build()
     lines = ["| workload | strategy | ours all_reduce (threads) | ours all_reduce (pool) | "
              "ours group_all_reduce | ref all_reduce (threads) | ref all_reduce (pool) | "

@@ -6,7 +6,13 @@ The reference benchmarks all-reduce over files of tensor sizes
 32, bert.txt = 599 = BERT-base weights plus two optimizer slots).  Here the
 sets are the TRAINABLE tensors only: ResNet-50 161 tensors / 25,557,032
 elements, VGG16 32 / 138,357,544, BERT-base 199 / ~109.5 M, BERT-large
-391 / ~335 M.
+391 / ~335 M.  Two more sets restate what the reference's own files describe,
+for like-for-like runs against its binaries: `resnet50-214` (the 53
+convolutions carry a bias: 214 tensors / 25,583,592 elements) and `bert-599`
+(BERT-base with its pooler and a 2-way classifier, 201 tensors, followed by two
+optimizer slots for each of the 199 tensors below the pooler: 599 tensors /
+327,270,150 elements).  `SWEEP` is the reference's `AxB` list
+(testdata/test-set-1.txt).
 """
 from functools import reduce
 from operator import mul
@@ -62,7 +68,31 @@ def bert_large_shapes():
     return bert_shapes(24, 1024, 4096)
 
 
+def resnet50_with_conv_bias_shapes(num_classes=1000):
+    shapes = []
+    for sh in resnet50_shapes(num_classes):
+        shapes.append(sh)
+        if len(sh) == 4:
+            shapes.append((sh[0],))
+    return shapes
+
+
+def bert_finetune_with_slots_shapes():
+    body = bert_shapes(12, 768, 3072)[:-2]  # everything below the pooler
+    head = [(2, 768), (2,)]
+    weights = body + [(768, 768), (768,)] + head
+    slots = []
+    for sh in body + head:
+        slots += [sh, sh]  # first and second moment, side by side
+    return weights + slots
+
+
+SWEEP = ["1024x100", "2048x100", "4096x100", "8192x100", "16384x100", "102400x100",
+         "1024000x100", "10240000x10", "262144x10"]
+
 GRADSETS = {
+    "resnet50-214": resnet50_with_conv_bias_shapes,
+    "bert-599": bert_finetune_with_slots_shapes,
     "resnet50": resnet50_shapes,
     "vgg16": vgg16_shapes,
     "bert-base": bert_base_shapes,

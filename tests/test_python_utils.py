@@ -23,6 +23,12 @@ def test_gradient_sets_match_the_named_models(tmp_path):
     assert len(b) == 199 and 109_000_000 < sum(b) < 110_000_000
     assert len(gradsets.gradset_sizes("bert-large")) == 391
     assert gradsets.gradset_sizes("1024x100") == [1024] * 100
+    # the sets the reference's own files describe (testdata/resnet50.txt, bert.txt there)
+    r214 = gradsets.gradset_sizes("resnet50-214")
+    assert (len(r214), sum(r214)) == (214, 25_583_592)
+    b599 = gradsets.gradset_sizes("bert-599")
+    assert (len(b599), sum(b599)) == (599, 327_270_150)
+    assert len(gradsets.SWEEP) == 9 and all("x" in w for w in gradsets.SWEEP)
     path = gradsets.write_sizes_file("resnet50", str(tmp_path / "r.txt"))
     assert [int(x) for x in open(path).read().split()] == r
     model = ResNet50()
