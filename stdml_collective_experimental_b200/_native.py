@@ -58,11 +58,17 @@ class DeviceTimeoutError(NativeError):
     """A device-side bounded wait ran out (a peer never arrived)."""
 
 
+class PeerFailure(NativeError):
+    """Host path: a peer this rank was sending to or waiting for has gone."""
+
+
 def check(rc):
     if rc != 0:
         msg = lib().stdmlc_last_error().decode("utf-8", "replace")
         if rc == 4:
             raise DeviceTimeoutError(rc, msg)
+        if rc == 5:
+            raise PeerFailure(rc, msg)
         if rc == 2:
             raise ValueError(msg)
         if rc == 3:

@@ -15,6 +15,7 @@ enum {
     STDMLC_ERR_ARGS = 2,
     STDMLC_ERR_NOMEM = 3,
     STDMLC_ERR_TIMEOUT = 4,
+    STDMLC_ERR_PEER = 5, /* host path: a peer has gone (its connections closed) */
 };
 
 enum {

@@ -14,6 +14,7 @@
 #include <cstdint>
 #include <optional>
 #include <ostream>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -40,6 +41,14 @@ struct peer_id {
 static_assert(sizeof(peer_id) == 6, "peer_id is a packed 6-byte record");
 
 std::ostream &operator<<(std::ostream &os, const peer_id &id);
+
+// Thrown by sends to and receives from a peer that is known to have gone (its
+// connections closed): see liveness.hpp.  The reference has no such error; a
+// dead peer blocks the others for ever.
+struct peer_failure : std::runtime_error {
+    peer_id who;
+    peer_failure(const peer_id &p, const std::string &what) : std::runtime_error(what), who(p) {}
+};
 
 class peer_list : public std::vector<peer_id>
 {

@@ -100,4 +100,9 @@ class connection
 
 // default 120 s; STDML_COLLECTIVE_CONNECT_TIMEOUT_MS overrides; <= 0 waits forever
 int64_t connect_timeout_ms();
+
+// One conn_ping handshake (connect, header, ack) with a deadline: the round
+// trip in microseconds, or -1 if `remote` does not answer within timeout_ms.
+// The reference defines conn_ping but never uses it (connection.hpp:14 there).
+double ping(const peer_id &remote, const peer_id &local, int timeout_ms);
 }  // namespace stdml::collective::rchan

@@ -101,6 +101,64 @@ class slot
         return t->ok ? 1 : 0;
     }
 
+    // A posted destination.  wait(ms) returns 1 (delivered), 0 (did not fit) or
+    // -1 (not yet; ms <= 0 waits without limit).  A pending that is given up
+    // must be cancel()led, or a late body would be written through a pointer
+    // that its owner no longer holds; cancel() itself waits if a network
+    // thread is filling the destination at that moment.
+    class pending
+    {
+        friend class slot;
+        slot *s_ = nullptr;
+        std::shared_ptr<ticket> t_;
+
+      public:
+        pending() = default;
+        explicit operator bool() const { return s_ != nullptr; }
+
+        int wait(long long ms)
+        {
+            std::unique_lock<std::mutex> lk(s_->mu_);
+            if (ms <= 0) {
+                s_->finished_.wait(lk, [&] { return t_->done; });
+            } else if (!s_->finished_.wait_for(lk, std::chrono::milliseconds(ms),
+                                               [&] { return t_->done; })) {
+                return -1;
+            }
+            return t_->ok ? 1 : 0;
+        }
+
+        // wait() without waiting
+        int ready()
+        {
+            std::lock_guard<std::mutex> lk(s_->mu_);
+            return !t_->done ? -1 : (t_->ok ? 1 : 0);
+        }
+
+        // true: withdrawn, nothing will be written; false: it was (being) delivered
+        bool cancel()
+        {
+            std::unique_lock<std::mutex> lk(s_->mu_);
+            if (t_->done) { return false; }
+            for (auto it = s_->waiting_.begin(); it != s_->waiting_.end(); ++it) {
+                if (*it == t_) {
+                    s_->waiting_.erase(it);
+                    return true;
+                }
+            }
+            s_->finished_.wait(lk, [&] { return t_->done; });
+            return false;
+        }
+    };
+
+    pending post_pending(void *ptr, size_t cap)
+    {
+        pending p;
+        p.s_ = this;
+        p.t_ = post_ticket(ptr, cap);
+        return p;
+    }
+
     // Posts now; the returned function waits for the body.
     std::function<bool()> post(void *ptr, size_t cap)
     {

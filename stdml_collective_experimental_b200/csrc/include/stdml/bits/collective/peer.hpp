@@ -27,6 +27,7 @@ class peer
 
     std::unique_ptr<mailbox> mailbox_;
     std::unique_ptr<slotbox> slotbox_;
+    std::unique_ptr<liveness> liveness_;  // which peers still hold connections to us
     std::unique_ptr<rchan::conn_handler> handler_;
     // the client pool goes away before the server
     std::unique_ptr<rchan::server> server_;
@@ -60,6 +61,10 @@ class peer
     size_t init_version() const { return init_version_; }
     strategy init_strategy() const { return init_strategy_; }
     rchan::client_pool *clients() const { return client_pool_.get(); }
+    liveness *peers_alive() const { return liveness_.get(); }
+    // Round trip of a conn_ping handshake to `target` in microseconds, or a
+    // negative value if it does not answer within timeout_ms.
+    double ping(const peer_id &target, int timeout_ms = 1000) const;
 
     void start();
     void stop();

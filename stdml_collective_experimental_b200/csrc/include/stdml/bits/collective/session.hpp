@@ -16,6 +16,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <atomic>
 #include <future>
 #include <iterator>
 #include <memory>
@@ -27,6 +28,7 @@
 #include <stdml/bits/collective/buffer.hpp>
 #include <stdml/bits/collective/config.hpp>
 #include <stdml/bits/collective/dtype.hpp>
+#include <stdml/bits/collective/liveness.hpp>
 #include <stdml/bits/collective/mailbox.hpp>
 #include <stdml/bits/collective/rchan.hpp>
 #include <stdml/bits/collective/task.hpp>
@@ -61,16 +63,29 @@ class session
     cuda::DeviceSession *device();  // collective on first use
     bool on_device(const void *a, const void *b) const;
 
+    // Every blocking receive of the host path goes through these: they sleep in
+    // slices, throw peer_failure as soon as the source is known to have gone,
+    // and std::runtime_error after config().host_timeout_ms (0: no limit).
+    buffer take_eager(size_t src, const std::string &tag, const char *what);
+    void take_into(size_t src, const std::string &tag, void *dst, size_t cap, const char *what);
+    void finish_pending(slot::pending &p, size_t src, const std::string &tag, const char *what);
+    bool source_gone(size_t src, long long waited_ms) const;
+    // set by the first receive that fails; every other blocked receive of this
+    // session then gives up within one slice (the message streams of a session
+    // that lost a peer no longer line up, so there is nothing to wait for)
+    std::shared_ptr<std::atomic<bool>> broken_ = std::make_shared<std::atomic<bool>>(false);
+
   public:
     static constexpr size_t chunk_bytes = 1u << 20;
 
     mailbox *mailbox_;                 // owned by peer
     slotbox *slotbox_;                 // owned by peer
     rchan::client_pool *client_pool_;  // owned by peer
+    liveness *liveness_;               // owned by peer; may be null (no failure detection)
 
     session(system_config config, size_t version, size_t rank, peer_list peers, peer_list runners,
             mailbox *mailbox, slotbox *slotbox, rchan::client_pool *client_pool,
-            strategy s = star);
+            strategy s = star, liveness *live = nullptr);
     ~session();
 
     session(const session &) = delete;

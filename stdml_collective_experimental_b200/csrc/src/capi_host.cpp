@@ -65,6 +65,9 @@ int host_guarded(F f)
     } catch (const std::invalid_argument &e) {
         sc::cuda::set_last_error(e.what());
         return 2;
+    } catch (const sc::peer_failure &e) {
+        sc::cuda::set_last_error(e.what());
+        return 5;
     } catch (const std::exception &e) {
         sc::cuda::set_last_error(e.what());
         return 1;
@@ -111,6 +114,17 @@ int stdmlc_peer_self(void *p, char *buf, unsigned long long size)
     return host_guarded([&] {
         const std::string s = static_cast<sc::peer *>(p)->self().str();
         std::snprintf(buf, size, "%s", s.c_str());
+    });
+}
+
+// round trip of one conn_ping handshake in microseconds; negative: no answer
+int stdmlc_peer_ping(void *p, const char *target, int timeout_ms, double *us)
+{
+    *us = -1;
+    return host_guarded([&] {
+        const auto id = sc::parse_peer_id(target);
+        if (!id) { throw std::invalid_argument(std::string("ping: bad address ") + target); }
+        *us = static_cast<sc::peer *>(p)->ping(*id, timeout_ms);
     });
 }
 

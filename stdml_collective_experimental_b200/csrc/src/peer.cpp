@@ -60,9 +60,18 @@ class peer_conn_handler final : public rchan::conn_handler
 {
     collective_msg_handler collective_;
     drain_handler drain_;
+    liveness *live_;
+
+    // counts a data connection of a peer for as long as it is served
+    struct presence {
+        liveness *live;
+        peer_id who;
+        presence(liveness *l, const peer_id &p) : live(l), who(p) { live->connected(who); }
+        ~presence() { live->disconnected(who); }
+    };
 
   public:
-    peer_conn_handler(mailbox *mb, slotbox *sb) : collective_(mb, sb) {}
+    peer_conn_handler(mailbox *mb, slotbox *sb, liveness *live) : collective_(mb, sb), live_(live) {}
 
     size_t operator()(std::unique_ptr<rchan::connection> conn) override
     {
@@ -71,9 +80,12 @@ class peer_conn_handler final : public rchan::conn_handler
         case rchan::conn_peer_to_peer:
         case rchan::conn_send:
         case rchan::conn_recv:
-        case rchan::conn_mpi:
+        case rchan::conn_mpi: {
+            // the count drops only after everything read has been handed over
+            presence here(live_, conn->src());
             return handle_to_end(conn.get(), &collective_);
-        default:
+        }
+        default:  // conn_ping, conn_control from runners, user types: no data for a session
             return handle_to_end(conn.get(), &drain_);
         }
     }
@@ -94,7 +106,8 @@ peer::peer(system_config config, size_t init_version, peer_id self, peer_list in
     : config_(std::move(config)), init_version_(init_version), self_(self),
       init_peers_(std::move(init_peers)), init_runners_(std::move(init_runners)),
       init_strategy_(init_strategy), mailbox_(new mailbox), slotbox_(new slotbox),
-      handler_(new peer_conn_handler(mailbox_.get(), slotbox_.get())),
+      liveness_(new liveness),
+      handler_(new peer_conn_handler(mailbox_.get(), slotbox_.get(), liveness_.get())),
       client_pool_(new rchan::client_pool(self))
 {
 }
@@ -192,12 +205,17 @@ void peer::stop()
     }
 }
 
+double peer::ping(const peer_id &target, int timeout_ms) const
+{
+    return rchan::ping(target, self_, timeout_ms);
+}
+
 session peer::join()
 {
     if (!client_pool_) { client_pool_.reset(new rchan::client_pool(self_)); }
     const size_t rank = init_peers_.rank(self_);
     session s(config_, init_version_, rank, init_peers_, init_runners_, mailbox_.get(),
-              slotbox_.get(), client_pool_.get(), init_strategy_);
+              slotbox_.get(), client_pool_.get(), init_strategy_, liveness_.get());
     if (config_.use_affinity) { set_affinity(rank, init_peers_.size()); }
     return s;
 }
@@ -208,7 +226,7 @@ std::unique_ptr<session> peer::join_elastic()
     const size_t rank = init_peers_.rank(self_);
     return std::make_unique<session>(config_, init_version_, rank, init_peers_, init_runners_,
                                      mailbox_.get(), slotbox_.get(), client_pool_.get(),
-                                     init_strategy_);
+                                     init_strategy_, liveness_.get());
 }
 
 resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver &get_config,
@@ -237,10 +255,13 @@ resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver
     init_peers_ = next->workers;
     init_runners_ = next->runners;
     init_version_ = new_version;
+    // a joiner may reuse the address of a member that left earlier: it starts
+    // with a clean record instead of that member's "gone"
+    liveness_->forget(next->workers);
     // the constructor's barrier admits the joiners (they dial until we answer)
     sess = std::make_unique<session>(config_, new_version, next->workers.rank(self_),
                                      next->workers, next->runners, mailbox_.get(),
-                                     slotbox_.get(), client_pool_.get(), s);
+                                     slotbox_.get(), client_pool_.get(), s, liveness_.get());
     return {true, false};
 }
 

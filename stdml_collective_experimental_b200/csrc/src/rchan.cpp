@@ -312,11 +312,11 @@ class connection_impl final : public connection
                 }
                 if (ok) { return; }
             }
-            throw std::runtime_error("rchan: send to " + src_.str() + " failed: peer has gone");
+            throw peer_failure(src_, "rchan: send to " + src_.str() + " failed: peer has gone");
         }
         if (!write_iov(fd_, iov, size > 0 ? 5 : 4)) {
-            throw std::runtime_error("rchan: send to " + src_.str() + " failed: " +
-                                     std::strerror(errno));
+            throw peer_failure(src_, "rchan: send to " + src_.str() + " failed: " +
+                                          std::strerror(errno));
         }
     }
 };
@@ -420,6 +420,45 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
         std::this_thread::sleep_for(std::chrono::milliseconds(wait_ms));
         wait_ms = std::min(wait_ms * 2, 200);  // the peer may simply not be up yet
     }
+}
+
+double ping(const peer_id &remote, const peer_id &local, int timeout_ms)
+{
+    using clock = std::chrono::steady_clock;
+    const auto t0 = clock::now();
+    const auto left = [&] {
+        const auto spent =
+            std::chrono::duration_cast<std::chrono::milliseconds>(clock::now() - t0).count();
+        return static_cast<int>(std::max<int64_t>(0, timeout_ms - spent));
+    };
+    const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
+    if (fd < 0) { return -1; }
+    struct closer {
+        int fd;
+        ~closer() { ::close(fd); }
+    } guard{fd};
+    const sockaddr_in addr = to_sockaddr(remote);
+    if (::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr)) != 0) {
+        if (errno != EINPROGRESS) { return -1; }
+        pollfd p{fd, POLLOUT, 0};
+        if (::poll(&p, 1, left()) <= 0) { return -1; }
+        int err = 0;
+        socklen_t len = sizeof(err);
+        if (::getsockopt(fd, SOL_SOCKET, SO_ERROR, &err, &len) != 0 || err != 0) { return -1; }
+    }
+    tune_socket(fd);
+    const conn_header h{static_cast<uint16_t>(conn_ping), local.port, local.ipv4};
+    if (::send(fd, &h, sizeof(h), MSG_NOSIGNAL) != static_cast<ssize_t>(sizeof(h))) { return -1; }
+    connection_ack ack{};
+    size_t have = 0;
+    while (have < sizeof(ack)) {
+        pollfd p{fd, POLLIN, 0};
+        if (::poll(&p, 1, left()) <= 0) { return -1; }
+        const ssize_t n = ::recv(fd, reinterpret_cast<char *>(&ack) + have, sizeof(ack) - have, 0);
+        if (n <= 0) { return -1; }
+        have += static_cast<size_t>(n);
+    }
+    return std::chrono::duration<double, std::micro>(clock::now() - t0).count();
 }
 
 bool conn_handler::handle_next(connection *conn, msg_handler *h)

@@ -52,11 +52,11 @@ int forced_algo(const system_config &c)
 
 session::session(system_config config, size_t version, size_t rank, peer_list peers,
                  peer_list runners, mailbox *mailbox, slotbox *slotbox,
-                 rchan::client_pool *client_pool, strategy s)
+                 rchan::client_pool *client_pool, strategy s, liveness *live)
     : config_(std::move(config)), version_(version), rank_(rank), peers_(std::move(peers)),
       runners_(std::move(runners)), strategy_(s),
       all_reduce_topo_(make_graph_pair_list(s, peers_.size())), mailbox_(mailbox),
-      slotbox_(slotbox), client_pool_(client_pool)
+      slotbox_(slotbox), client_pool_(client_pool), liveness_(live)
 {
     if (rank_ >= peers_.size()) { throw std::invalid_argument("session: rank outside the peer list"); }
     if (config_.thread_pool_size > 0 &&
@@ -86,6 +86,99 @@ std::string versioned(const session &s, const std::string &name)
 }
 }  // namespace
 
+bool session::source_gone(size_t src, long long waited_ms) const
+{
+    if (liveness_ == nullptr) { return false; }
+    if (liveness_->gone(peers_[src])) { return true; }
+    // never heard of it: after a dialler's patience, ask it about once a second
+    const long long patience = rchan::connect_timeout_ms();
+    if (patience > 0 && waited_ms >= patience &&
+        (waited_ms / liveness::slice_ms) % 10 == 0 && !liveness_->seen(peers_[src])) {
+        return rchan::ping(peers_[src], peers_[rank_], 1000) < 0;
+    }
+    return false;
+}
+
+namespace
+{
+[[noreturn]] void fail_gone(std::atomic<bool> &broken, const peer_id &who, const char *what,
+                            const std::string &tag)
+{
+    broken.store(true);
+    throw peer_failure(who, std::string(what) + " '" + tag + "': peer " + who.str() +
+                                " has gone (its connections closed, or it never connected and does not answer)");
+}
+
+[[noreturn]] void fail_late(std::atomic<bool> &broken, const peer_id &who, const char *what,
+                            const std::string &tag, long long limit)
+{
+    broken.store(true);
+    throw std::runtime_error(std::string(what) + " '" + tag + "': nothing from peer " + who.str() +
+                             " within " + std::to_string(limit) + " ms (peer failed or left?)");
+}
+
+[[noreturn]] void fail_broken(const char *what, const std::string &tag)
+{
+    throw std::runtime_error(std::string(what) + " '" + tag +
+                             "': given up, another receive of this session has failed");
+}
+}  // namespace
+
+buffer session::take_eager(size_t src, const std::string &tag, const char *what)
+{
+    auto *box = mailbox_->require(peers_[src], tag);
+    const long long limit = config_.host_timeout_ms;
+    long long waited = 0;
+    for (;;) {
+        const long long slice =
+            limit > 0 ? std::min(liveness::slice_ms, limit - waited) : liveness::slice_ms;
+        if (auto got = box->get_for(std::chrono::milliseconds(slice))) { return std::move(*got); }
+        waited += slice;
+        if (source_gone(src, waited)) {
+            // what it sent before it went has been handed over by now
+            if (auto got = box->try_get()) { return std::move(*got); }
+            fail_gone(*broken_, peers_[src], what, tag);
+        }
+        if (limit > 0 && waited >= limit) { fail_late(*broken_, peers_[src], what, tag, limit); }
+        if (broken_->load()) { fail_broken(what, tag); }
+    }
+}
+
+void session::finish_pending(slot::pending &p, size_t src, const std::string &tag, const char *what)
+{
+    const long long limit = config_.host_timeout_ms;
+    long long waited = 0;
+    for (;;) {
+        const long long slice =
+            limit > 0 ? std::min(liveness::slice_ms, limit - waited) : liveness::slice_ms;
+        int rc = p.wait(slice);
+        if (rc < 0) {
+            waited += slice;
+            const bool gone = source_gone(src, waited);
+            const bool late = limit > 0 && waited >= limit;
+            if (!gone && !late && !broken_->load()) { continue; }
+            if (p.cancel()) {
+                if (gone) { fail_gone(*broken_, peers_[src], what, tag); }
+                if (late) { fail_late(*broken_, peers_[src], what, tag, limit); }
+                fail_broken(what, tag);
+            }
+            rc = p.wait(0);  // it was delivered while we were giving up
+        }
+        if (rc == 0) {
+            throw std::length_error(std::string(what) + ": the message from peer " +
+                                    peers_[src].str() + " is longer than the posted buffer");
+        }
+        return;
+    }
+}
+
+void session::take_into(size_t src, const std::string &tag, void *dst, size_t cap,
+                        const char *what)
+{
+    slot::pending p = slotbox_->require(peers_[src], tag)->post_pending(dst, cap);
+    finish_pending(p, src, tag, what);
+}
+
 void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
 {
     workspace_state st(&w);
@@ -93,20 +186,8 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
     const size_t bytes = w.bytes();
     rchan::client *out = client_pool_->require(conn_collective);
 
-    const long long limit = config_.host_timeout_ms;
     auto recv_reduce = [&](size_t src) {
-        buffer b;
-        if (limit > 0) {
-            auto got = mailbox_->require(peers_[src], name)->get_for(std::chrono::milliseconds(limit));
-            if (!got) {
-                throw std::runtime_error("all_reduce '" + w.name + "': nothing from peer " +
-                                         peers_[src].str() + " within " + std::to_string(limit) +
-                                         " ms (peer failed or left?)");
-            }
-            b = std::move(*got);
-        } else {
-            b = mailbox_->require(peers_[src], name)->get();
-        }
+        buffer b = take_eager(src, name, "all_reduce");
         if (b.len != bytes) {
             throw std::runtime_error("all_reduce: peer " + peers_[src].str() + " sent " +
                                      std::to_string(b.len) + " bytes for '" + w.name +
@@ -118,15 +199,7 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
         out->send(peers_[dst], name.c_str(), st.effective_data(), bytes, 0);
     };
     auto recv_result = [&](size_t src) {
-        const int rc = slotbox_->require(peers_[src], name)->get_for(w.recv, bytes, limit);
-        if (rc < 0) {
-            throw std::runtime_error("all_reduce '" + w.name + "': no result from peer " +
-                                     peers_[src].str() + " within " + std::to_string(limit) +
-                                     " ms (peer failed or left?)");
-        }
-        if (rc == 0) {
-            throw std::runtime_error("all_reduce: result for '" + w.name + "' did not fit");
-        }
+        take_into(src, name, w.recv, bytes, "all_reduce");
         st.replaced();
     };
     auto send_result = [&](size_t dst) {
@@ -169,13 +242,23 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
     rchan::client *out = client_pool_->require(conn_collective);
 
     task_builder recv1, send1, recv2, send2;
+    liveness *live = liveness_;
+    auto broken = broken_;
     for (size_t src : rg->prevs(rank_)) {
         auto *box = mailbox_->require(peers_[src], sh->name);
         auto got = std::make_shared<buffer>();
+        const peer_id who = peers_[src];
         recv1 << new poll_task(
-            [box, got] {
+            [box, got, live, who, sh, broken] {
                 auto b = box->try_get();
-                if (!b) { return false; }
+                if (!b && live != nullptr && live->gone(who)) {
+                    b = box->try_get();  // sent before it went
+                    if (!b) { fail_gone(*broken, who, "all_reduce", sh->name); }
+                }
+                if (!b) {
+                    if (broken->load()) { fail_broken("all_reduce", sh->name); }
+                    return false;
+                }
                 *got = std::move(*b);
                 return true;
             },
@@ -197,12 +280,24 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
     } else {
         for (size_t src : bg->prevs(rank_)) {
             auto *sl = slotbox_->require(peers_[src], sh->name);
-            auto done = std::make_shared<std::function<bool()>>();
-            recv2 << new poll_task([sl, sh, done, bytes] {
+            auto pend = std::make_shared<slot::pending>();
+            const peer_id who = peers_[src];
+            recv2 << new poll_task([sl, sh, pend, bytes, live, who, broken] {
                 // the destination is posted on the first poll, i.e. after the
                 // reduce phase is over and recv no longer holds partial sums
-                if (!*done) { *done = sl->post_polled(sh->w.recv, bytes); }
-                return (*done)();
+                if (!*pend) { *pend = sl->post_pending(sh->w.recv, bytes); }
+                int rc = pend->ready();
+                if (rc < 0) {
+                    const bool gone = live != nullptr && live->gone(who);
+                    if (!gone && !broken->load()) { return false; }
+                    if (pend->cancel()) {
+                        if (gone) { fail_gone(*broken, who, "all_reduce", sh->name); }
+                        fail_broken("all_reduce", sh->name);
+                    }
+                    rc = pend->wait(0);
+                }
+                if (rc == 0) { throw std::length_error("all_reduce: the result did not fit"); }
+                return true;
             });
         }
     }
@@ -423,7 +518,7 @@ void session::reduce(const void *input, void *output, size_t count, dtype dt, re
     }
     if (output != input) { std::memcpy(output, input, bytes); }
     for (size_t r = 1; r < peers_.size(); ++r) {
-        buffer b = mailbox_->require(peers_[r], tag)->get();
+        buffer b = take_eager(r, tag, "reduce");
         if (b.len != bytes) { throw std::runtime_error("reduce: size mismatch"); }
         stdml::collective::reduce(output, output, b.data.get(), count, dt, op);
     }
@@ -443,10 +538,10 @@ void session::all_gather(const void *input, void *output, size_t count, dtype dt
     const std::string tag = versioned(*this, "stdml::all_gather::" + name);
     char *out = static_cast<char *>(output);
     // post every destination first, then send: the bodies land in place
-    std::vector<std::function<bool()>> waits;
+    std::vector<std::pair<size_t, slot::pending>> waits;
     for (size_t r = 0; r < peers_.size(); ++r) {
         if (r == rank_) { continue; }
-        waits.push_back(slotbox_->require(peers_[r], tag)->post(out + r * bytes, bytes));
+        waits.emplace_back(r, slotbox_->require(peers_[r], tag)->post_pending(out + r * bytes, bytes));
     }
     std::memmove(out + rank_ * bytes, input, bytes);
     std::vector<size_t> others;
@@ -460,9 +555,19 @@ void session::all_gather(const void *input, void *output, size_t count, dtype dt
     } else {
         fmap(par, send_to, others);
     }
-    for (auto &w : waits) {
-        if (!w()) { throw std::runtime_error("all_gather: a block did not fit"); }
+    std::exception_ptr first;
+    for (auto &[r, p] : waits) {
+        if (first) {
+            p.cancel();  // nothing may be written into `output` after we have thrown
+            continue;
+        }
+        try {
+            finish_pending(p, r, tag, "all_gather");
+        } catch (...) {
+            first = std::current_exception();
+        }
     }
+    if (first) { std::rethrow_exception(first); }
 }
 
 void session::gather(const void *input, void *output, size_t count, dtype dt, std::string name)
@@ -478,9 +583,7 @@ void session::gather(const void *input, void *output, size_t count, dtype dt, st
     char *out = static_cast<char *>(output);
     std::memmove(out, input, bytes);
     for (size_t r = 1; r < peers_.size(); ++r) {
-        if (!slotbox_->require(peers_[r], tag)->get(out + r * bytes, bytes)) {
-            throw std::runtime_error("gather: a block did not fit");
-        }
+        take_into(r, tag, out + r * bytes, bytes, "gather");
     }
 }
 
@@ -501,9 +604,7 @@ void session::broadcast(const void *input, void *output, size_t count, dtype dt,
         if (output != input) { std::memcpy(output, input, bytes); }
     } else {
         for (size_t src : g.prevs(rank_)) {
-            if (!slotbox_->require(peers_[src], tag)->get(output, bytes)) {
-                throw std::runtime_error("broadcast: the message did not fit");
-            }
+            take_into(src, tag, output, bytes, "broadcast");
         }
     }
     rchan::client *cl = client_pool_->require(conn_collective);
@@ -526,9 +627,7 @@ void session::recv(void *output, size_t count, dtype dt, size_t target, std::str
 {
     if (target >= peers_.size()) { throw std::out_of_range("recv: no such rank"); }
     const std::string tag = versioned(*this, "stdml::p2p::" + name);
-    if (!slotbox_->require(peers_[target], tag)->get(output, count * dtype_size(dt))) {
-        throw std::length_error("recv: the message is longer than the posted buffer");
-    }
+    take_into(target, tag, output, count * dtype_size(dt), "recv");
 }
 
 bool session::consistent(const void *ptr, size_t size)

@@ -1,3 +1,4 @@
+#include <atomic>
 #include <cstdlib>
 #include <cxxabi.h>
 #include <thread>
@@ -23,25 +24,34 @@ class pool_runtime final : public runtime
         // Each worker owns a strided subset of the tasks and polls them
         // round-robin, so a task that waits for its peer never starves one
         // that could run (there may be far more tasks than workers).
+        // A task that throws ends the whole set: the other workers stop polling
+        // (their tasks may wait for something that will never come) and the
+        // first exception reaches the caller through the pool.
         const size_t workers = std::min(pool_->size() + 1, tasks.size());
+        std::atomic<bool> failed{false};
         std::vector<sync::thread_pool::task> fs;
         for (size_t w = 0; w < workers; ++w) {
-            fs.emplace_back([&tasks, w, workers] {
+            fs.emplace_back([&tasks, &failed, w, workers] {
                 size_t left = 0;
                 for (size_t i = w; i < tasks.size(); i += workers) { ++left; }
                 std::vector<bool> done(tasks.size(), false);
-                while (left > 0) {
-                    bool progressed = false;
-                    for (size_t i = w; i < tasks.size(); i += workers) {
-                        if (done[i]) { continue; }
-                        tasks[i]->poll();
-                        if (tasks[i]->finished()) {
-                            done[i] = true;
-                            --left;
-                            progressed = true;
+                try {
+                    while (left > 0 && !failed.load(std::memory_order_relaxed)) {
+                        bool progressed = false;
+                        for (size_t i = w; i < tasks.size(); i += workers) {
+                            if (done[i]) { continue; }
+                            tasks[i]->poll();
+                            if (tasks[i]->finished()) {
+                                done[i] = true;
+                                --left;
+                                progressed = true;
+                            }
                         }
+                        if (!progressed) { std::this_thread::yield(); }
                     }
-                    if (!progressed) { std::this_thread::yield(); }
+                } catch (...) {
+                    failed.store(true);
+                    throw;
                 }
             });
         }

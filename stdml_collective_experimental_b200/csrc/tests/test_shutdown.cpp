@@ -1,10 +1,14 @@
 // Clean teardown: many collectives, then an explicit stop; and failure
 // detection on the host path: a rank that leaves before a collective makes the
-// others throw (instead of blocking for ever) when
-// STDML_COLLECTIVE_HOST_TIMEOUT_MS is set.
+// others throw peer_failure (no timeout needed), a rank that is alive but
+// silent makes them throw when STDML_COLLECTIVE_HOST_TIMEOUT_MS runs out, a
+// rank that never shows up ends the connect timeout, and conn_ping tells a
+// live address from a dead one.
 //   test_shutdown <np>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <thread>
 #include <vector>
 
 #include <sys/wait.h>
@@ -31,8 +35,61 @@ static int clean_shutdown(int np)
     return 0;
 }
 
-// rank 1 exits without taking part; rank 0 must notice within the timeout
-static int peer_leaves(int np)
+static int reap(const std::vector<pid_t> &kids, const char *what)
+{
+    int bad = 0;
+    for (pid_t pid : kids) {
+        int st = 0;
+        ::waitpid(pid, &st, 0);
+        if (!WIFEXITED(st) || WEXITSTATUS(st) != 0) {
+            std::printf("%s: a rank ended with status %d\n", what, WIFEXITED(st) ? WEXITSTATUS(st) : -1);
+            ++bad;
+        }
+    }
+    if (bad != 0) { std::printf("%s: FAILED (%d ranks)\n", what, bad); }
+    return bad;
+}
+
+// Rank 1 exits between two steps.  No timeout is configured: the others must
+// learn from its closed connections that it has gone (peer_failure, within a
+// few wait slices), directly or because the rank they wait for gave up.
+static int peer_leaves(int np, bool async_runtime)
+{
+    if (async_runtime) { ::setenv("STDML_COLLECTIVE_USE_ASYNC", "1", 1); }
+    std::vector<pid_t> kids;
+    for (int r = 0; r < np; ++r) {
+        const pid_t pid = ::fork();
+        if (pid == 0) {
+            int rc = 3;
+            try {
+                peer p = peer::from_fork(r, np);
+                session sess = p.join();
+                if (r == 1) { ::_exit(0); }  // gone between two steps
+                const auto t0 = std::chrono::steady_clock::now();
+                try {
+                    std::vector<float> x(300000, 1.0f), y(300000);
+                    sess.all_reduce(x.data(), y.data(), x.size(), f32, sum, "after");
+                    rc = 4;  // must not succeed
+                } catch (const peer_failure &e) {
+                    const double s =
+                        std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+                    rc = s < 5.0 ? 0 : 6;
+                }
+            } catch (const std::exception &e) {
+                std::printf("rank %d: %s\n", r, e.what());
+                rc = 5;
+            }
+            ::_exit(rc);
+        }
+        kids.push_back(pid);
+    }
+    const int bad = reap(kids, async_runtime ? "peer leaves (polled tasks)" : "peer leaves");
+    ::unsetenv("STDML_COLLECTIVE_USE_ASYNC");
+    return bad;
+}
+
+// Rank 1 stays alive but silent: only the timeout can end the wait.
+static int peer_stalls(int np)
 {
     ::setenv("STDML_COLLECTIVE_HOST_TIMEOUT_MS", "500", 1);
     std::vector<pid_t> kids;
@@ -43,10 +100,15 @@ static int peer_leaves(int np)
             try {
                 peer p = peer::from_fork(r, np);
                 session sess = p.join();
-                if (r == 1) { ::_exit(0); }  // gone between two steps
+                if (r == 1) {
+                    std::this_thread::sleep_for(std::chrono::seconds(3));
+                    ::_exit(0);
+                }
                 float x = 1, y = 0;
                 sess.all_reduce(&x, &y, 1, f32, sum, "after");
                 rc = 4;  // must not succeed
+            } catch (const peer_failure &) {
+                rc = r == 0 ? 7 : 0;  // rank 0 waits for the silent rank itself; the rest may see rank 0 go
             } catch (const std::runtime_error &e) {
                 rc = std::string(e.what()).find("within 500 ms") != std::string::npos ? 0 : 5;
             }
@@ -54,14 +116,65 @@ static int peer_leaves(int np)
         }
         kids.push_back(pid);
     }
-    int bad = 0;
-    for (pid_t pid : kids) {
-        int st = 0;
-        ::waitpid(pid, &st, 0);
-        if (!WIFEXITED(st) || WEXITSTATUS(st) != 0) { ++bad; }
-    }
+    const int bad = reap(kids, "peer stalls");
     ::unsetenv("STDML_COLLECTIVE_HOST_TIMEOUT_MS");
-    if (bad != 0) { std::printf("peer leaves: FAILED (%d ranks)\n", bad); }
+    return bad;
+}
+
+// Rank 0 dies before it has sent anything: rank 1 has no connection of it to
+// watch, so after a dialler's patience it pings the address and gives up.
+static int peer_dies_before_connecting()
+{
+    ::setenv("STDML_COLLECTIVE_CONNECT_TIMEOUT_MS", "500", 1);
+    std::vector<pid_t> kids;
+    for (int r = 0; r < 2; ++r) {
+        const pid_t pid = ::fork();
+        if (pid == 0) {
+            int rc = 3;
+            try {
+                peer p = peer::from_list(r, *parse_peer_list("127.0.0.1:10460,127.0.0.1:10461"), star);
+                if (r == 0) {
+                    std::this_thread::sleep_for(std::chrono::milliseconds(300));
+                    ::_exit(0);  // listened, never joined
+                }
+                session sess = p.join();
+                rc = 4;  // must not succeed
+            } catch (const peer_failure &) {
+                rc = 0;
+            } catch (const std::runtime_error &e) {
+                // started too late to reach rank 0 at all
+                rc = std::string(e.what()).find("could not reach") != std::string::npos ? 0 : 5;
+            }
+            ::_exit(rc);
+        }
+        kids.push_back(pid);
+    }
+    const int bad = reap(kids, "peer dies before connecting");
+    ::unsetenv("STDML_COLLECTIVE_CONNECT_TIMEOUT_MS");
+    return bad;
+}
+
+// conn_ping: a live peer answers, a dead address does not
+static int ping_peers()
+{
+    int bad = 0;
+    try {
+        prun(2, [&](session &sess) {
+            // prun gives each rank its peer through the session's client pool owner;
+            // the handshake itself needs no session
+            const peer_id other = sess.peers()[1 - sess.rank()];
+            const double us = rchan::ping(other, sess.peers()[sess.rank()], 1000);
+            if (us < 0) { throw std::runtime_error("a live peer did not answer the ping"); }
+            const peer_id nobody{other.ipv4, static_cast<uint16_t>(other.port + 977)};
+            if (rchan::ping(nobody, sess.peers()[sess.rank()], 200) >= 0) {
+                throw std::runtime_error("a dead address answered the ping");
+            }
+            sess.barrier();
+        });
+    } catch (const std::exception &e) {
+        std::printf("ping: FAILED (%s)\n", e.what());
+        bad = 1;
+    }
     return bad;
 }
 
@@ -90,7 +203,9 @@ static int peer_never_joins()
 int main(int argc, char *argv[])
 {
     const int np = argc > 1 ? std::atoi(argv[1]) : 4;
-    const int bad = clean_shutdown(np) + peer_leaves(np) + peer_never_joins();
+    const int bad = clean_shutdown(np) + peer_leaves(np, false) + peer_leaves(np, true) +
+                    peer_stalls(np) + peer_never_joins() + peer_dies_before_connecting() +
+                    ping_peers();
     std::printf("test-shutdown np=%d: %s\n", np, bad == 0 ? "OK" : "FAILED");
     return bad == 0 ? 0 : 1;
 }

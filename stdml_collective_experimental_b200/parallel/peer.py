@@ -30,6 +30,7 @@ def _lib():
         lib.stdmlc_peer_create.argtypes = [vpp, c.c_int, c.c_char_p, c.c_int, u64, c.c_char_p]
         lib.stdmlc_peer_destroy.argtypes = [vp]
         lib.stdmlc_peer_self.argtypes = [vp, c.c_char_p, u64]
+        lib.stdmlc_peer_ping.argtypes = [vp, c.c_char_p, c.c_int, c.POINTER(c.c_double)]
         lib.stdmlc_peer_join.argtypes = [vp, vpp]
         lib.stdmlc_session_destroy.argtypes = [vp]
         lib.stdmlc_session_info.argtypes = [vp, c.c_int, c.POINTER(u64)]
@@ -285,6 +286,14 @@ class Peer:
         buf = ctypes.create_string_buffer(64)
         _native.check(self._lib.stdmlc_peer_self(self._h, buf, len(buf)))
         return buf.value.decode()
+
+    def ping(self, target, timeout_ms=1000):
+        """Round trip of one handshake with `target` ("ip:port") in microseconds,
+        or None if it does not answer in time."""
+        us = ctypes.c_double()
+        _native.check(self._lib.stdmlc_peer_ping(self._h, target.encode(), timeout_ms,
+                                                 ctypes.byref(us)))
+        return us.value if us.value >= 0 else None
 
     def join(self):
         s = ctypes.c_void_p()

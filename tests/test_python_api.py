@@ -19,6 +19,19 @@ def test_python_peer_session(n, strategy, base, native_lib):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
 
 
+@pytest.mark.parametrize("strategy,base", [("star", 12140), ("ring", 12150)])
+def test_python_peer_failure_is_an_exception(strategy, base, native_lib):
+    n = 3
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_fail_worker.py"), str(r),
+                               str(n), str(base), strategy], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(n)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, o[-2000:]
+        if r != 1:
+            assert f"rank {r} OK" in o and "has gone" in o or "failed" in o, o[-2000:]
+
+
 def test_python_elastic_state_under_the_runner(native_lib):
     from stdml_collective_experimental_b200 import _native
     _native.build()
