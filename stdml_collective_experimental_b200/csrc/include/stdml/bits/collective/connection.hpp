@@ -90,6 +90,11 @@ class connection
     // performs the handshake.  Throws std::runtime_error on timeout.
     static std::unique_ptr<connection> dial(const peer_id remote, const conn_type type,
                                             const peer_id local);
+    // One attempt with a deadline (always TCP); null if `remote` does not answer.
+    // dial() is patient because a peer may still be starting; this is for
+    // messages to members that may be dying.
+    static std::unique_ptr<connection> dial_once(const peer_id remote, const conn_type type,
+                                                 const peer_id local, int timeout_ms);
     virtual ~connection() = default;
     virtual conn_type type() const = 0;
     virtual peer_id src() const = 0;

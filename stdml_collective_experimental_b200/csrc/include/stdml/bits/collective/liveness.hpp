@@ -34,8 +34,31 @@ class liveness
     mutable std::mutex mu_;
     std::map<uint64_t, entry> peers_;
     std::atomic<int> gone_{0};
+    std::atomic<uint64_t> aborted_{0};  // 1 + the newest session version a member has given up on
 
   public:
+    // name of the message a member sends to the others when it gives up on the
+    // session of that version (so that ranks which wait for a live member that
+    // will never answer give up too)
+    static std::string abort_tag(size_t version) { return "stdml::abort::v" + std::to_string(version); }
+
+    // handler side: returns true if `name` was an abort message
+    bool note_abort(const std::string &name)
+    {
+        static const std::string prefix = "stdml::abort::v";
+        if (name.compare(0, prefix.size(), prefix) != 0) { return false; }
+        uint64_t v = 0;
+        for (size_t i = prefix.size(); i < name.size(); ++i) {
+            if (name[i] < '0' || name[i] > '9') { return false; }
+            v = v * 10 + static_cast<uint64_t>(name[i] - '0');
+        }
+        uint64_t cur = aborted_.load();
+        while (cur < v + 1 && !aborted_.compare_exchange_weak(cur, v + 1)) {}
+        return true;
+    }
+
+    bool aborted(size_t version) const { return aborted_.load(std::memory_order_acquire) > version; }
+
     // how long a blocked receiver sleeps between two looks at this table
     static constexpr long long slice_ms = 100;
 

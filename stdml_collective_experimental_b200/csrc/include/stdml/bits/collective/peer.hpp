@@ -87,6 +87,17 @@ class peer
     resize_result resize(std::unique_ptr<session> &sess, size_t new_size);
     resize_result resize(std::unique_ptr<session> &sess, const config_prodiver &get_config,
                          const config_committer &commit);
+
+    // Unplanned loss of members (the reference has planned resizes only).
+    // After a peer_failure every surviving member calls recover(): it gives up
+    // on `sess` (telling the others), pings the old members, and replaces
+    // `sess` by a session of those that answer, with the next version.  The
+    // ranks of the survivors keep their order.  Returns the members that were
+    // dropped.  As after a resize, the application re-synchronises its state
+    // (progress by max-all-reduce, parameters by broadcast): a collective that
+    // was in flight when the member died may have finished on some survivors
+    // and not on others.
+    peer_list recover(std::unique_ptr<session> &sess, int ping_timeout_ms = 1000);
 };
 
 // fork n ranks on this host (ports 10000 + i), run g in each, wait for all

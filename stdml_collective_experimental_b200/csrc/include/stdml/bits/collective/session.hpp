@@ -70,6 +70,10 @@ class session
     void take_into(size_t src, const std::string &tag, void *dst, size_t cap, const char *what);
     void finish_pending(slot::pending &p, size_t src, const std::string &tag, const char *what);
     bool source_gone(size_t src, long long waited_ms) const;
+    void ensure_usable(const char *what);
+    enum class failure { gone, late, other };
+    [[noreturn]] void give_up(failure why, const peer_id &who, const char *what,
+                              const std::string &tag);
     // set by the first receive that fails; every other blocked receive of this
     // session then gives up within one slice (the message streams of a session
     // that lost a peer no longer line up, so there is nothing to wait for)
@@ -103,6 +107,12 @@ class session
     const system_config &config() const { return config_; }
 
     void barrier();
+
+    // true once a receive of this session has failed or a member has told us
+    // that it gave up: the session is of no further use (see peer::recover)
+    bool given_up() const;
+    // gives up on this session and tells the other members
+    void abort() noexcept;
 
     void all_reduce(const workspace &w, void *stream = nullptr);
     // Blocks until every tensor is reduced.  Tensors may become ready in any

@@ -287,6 +287,18 @@ int stdmlc_peer_resize(void *p, void *sess, long long new_size, const char *clus
     });
 }
 
+// After STDMLC_ERR_PEER: every survivor calls this; `sess` becomes a session of
+// the members that still answer.  *dropped = how many members were left out.
+int stdmlc_peer_recover(void *p, void *sess, int ping_timeout_ms, int *dropped)
+{
+    *dropped = 0;
+    return host_guarded([&] {
+        auto *box = static_cast<session_box *>(sess);
+        *dropped = static_cast<int>(
+            static_cast<sc::peer *>(p)->recover(box->s, ping_timeout_ms).size());
+    });
+}
+
 int stdmlc_cluster_resize_json(const char *cluster_json, unsigned long long new_size, char *buf,
                                unsigned long long size)
 {

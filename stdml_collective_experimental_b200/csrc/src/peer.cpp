@@ -45,14 +45,24 @@ class collective_msg_handler final : public rchan::msg_handler
     }
 };
 
+// Everything else is read and dropped, except the notice by which a member
+// tells the others that it has given up on a session (liveness::abort_tag).
+// Such notices travel on conn_control connections of their own, which are not
+// counted as a sign of life: they are closed at once.
 class drain_handler final : public rchan::msg_handler
 {
+    liveness *live_;
+
   public:
+    explicit drain_handler(liveness *live) : live_(live) {}
+
     bool operator()(const rchan::received_header &mh, rchan::message_reader *reader,
                     const peer_id &) override
     {
         buffer b = alloc_buffer(mh.len);
-        return reader->read_body(b.data.get());
+        if (!reader->read_body(b.data.get())) { return false; }
+        live_->note_abort(mh.name);
+        return true;
     }
 };
 
@@ -71,7 +81,10 @@ class peer_conn_handler final : public rchan::conn_handler
     };
 
   public:
-    peer_conn_handler(mailbox *mb, slotbox *sb, liveness *live) : collective_(mb, sb), live_(live) {}
+    peer_conn_handler(mailbox *mb, slotbox *sb, liveness *live)
+        : collective_(mb, sb), drain_(live), live_(live)
+    {
+    }
 
     size_t operator()(std::unique_ptr<rchan::connection> conn) override
     {
@@ -263,6 +276,41 @@ resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver
                                      next->workers, next->runners, mailbox_.get(),
                                      slotbox_.get(), client_pool_.get(), s, liveness_.get());
     return {true, false};
+}
+
+peer_list peer::recover(std::unique_ptr<session> &sess, int ping_timeout_ms)
+{
+    sess->abort();
+    const peer_list old = sess->peers();
+    const peer_list runners = sess->runners();
+    const strategy s = sess->get_strategy();
+    const size_t new_version = sess->version() + 1;
+    peer_list alive, dropped;
+    for (const auto &p : old) {
+        // a member that is itself recovering still answers: its server runs
+        if (p == self_ || rchan::ping(p, self_, ping_timeout_ms) >= 0) {
+            alive.push_back(p);
+        } else {
+            dropped.push_back(p);
+        }
+    }
+    sess.reset();
+    client_pool_->reset_peers(dropped);
+    liveness_->forget(old);
+    init_peers_ = alive;
+    init_version_ = new_version;
+    if (!runners.empty() && alive.rank(self_) == 0) {
+        try {
+            commit_cluster_config(cluster_config(runners, alive), new_version);
+        } catch (const std::exception &e) {
+            log(WARN) << "recover: could not tell the runners:" << e.what();
+        }
+    }
+    // the constructor's barrier completes once every survivor has got here
+    sess = std::make_unique<session>(config_, new_version, alive.rank(self_), alive, runners,
+                                     mailbox_.get(), slotbox_.get(), client_pool_.get(), s,
+                                     liveness_.get());
+    return dropped;
 }
 
 resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver &get_config)

@@ -15,6 +15,7 @@
 #include <vector>
 
 #include <arpa/inet.h>
+#include <fcntl.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <poll.h>
@@ -422,7 +423,12 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
     }
 }
 
-double ping(const peer_id &remote, const peer_id &local, int timeout_ms)
+namespace
+{
+// One TCP connect + handshake with a deadline; the socket is blocking again on
+// return.  -1 if `remote` does not accept or acknowledge in time.
+int handshake_with_deadline(const peer_id &remote, const peer_id &local, conn_type type,
+                            int timeout_ms)
 {
     using clock = std::chrono::steady_clock;
     const auto t0 = clock::now();
@@ -433,32 +439,52 @@ double ping(const peer_id &remote, const peer_id &local, int timeout_ms)
     };
     const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
     if (fd < 0) { return -1; }
-    struct closer {
-        int fd;
-        ~closer() { ::close(fd); }
-    } guard{fd};
+    const auto fail = [&] {
+        ::close(fd);
+        return -1;
+    };
     const sockaddr_in addr = to_sockaddr(remote);
     if (::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr)) != 0) {
-        if (errno != EINPROGRESS) { return -1; }
+        if (errno != EINPROGRESS) { return fail(); }
         pollfd p{fd, POLLOUT, 0};
-        if (::poll(&p, 1, left()) <= 0) { return -1; }
+        if (::poll(&p, 1, left()) <= 0) { return fail(); }
         int err = 0;
         socklen_t len = sizeof(err);
-        if (::getsockopt(fd, SOL_SOCKET, SO_ERROR, &err, &len) != 0 || err != 0) { return -1; }
+        if (::getsockopt(fd, SOL_SOCKET, SO_ERROR, &err, &len) != 0 || err != 0) { return fail(); }
     }
     tune_socket(fd);
-    const conn_header h{static_cast<uint16_t>(conn_ping), local.port, local.ipv4};
-    if (::send(fd, &h, sizeof(h), MSG_NOSIGNAL) != static_cast<ssize_t>(sizeof(h))) { return -1; }
+    const conn_header h{static_cast<uint16_t>(type), local.port, local.ipv4};
+    if (::send(fd, &h, sizeof(h), MSG_NOSIGNAL) != static_cast<ssize_t>(sizeof(h))) { return fail(); }
     connection_ack ack{};
     size_t have = 0;
     while (have < sizeof(ack)) {
         pollfd p{fd, POLLIN, 0};
-        if (::poll(&p, 1, left()) <= 0) { return -1; }
+        if (::poll(&p, 1, left()) <= 0) { return fail(); }
         const ssize_t n = ::recv(fd, reinterpret_cast<char *>(&ack) + have, sizeof(ack) - have, 0);
-        if (n <= 0) { return -1; }
+        if (n <= 0) { return fail(); }
         have += static_cast<size_t>(n);
     }
-    return std::chrono::duration<double, std::micro>(clock::now() - t0).count();
+    const int flags = ::fcntl(fd, F_GETFL, 0);
+    if (flags < 0 || ::fcntl(fd, F_SETFL, flags & ~O_NONBLOCK) != 0) { return fail(); }
+    return fd;
+}
+}  // namespace
+
+double ping(const peer_id &remote, const peer_id &local, int timeout_ms)
+{
+    const auto t0 = std::chrono::steady_clock::now();
+    const int fd = handshake_with_deadline(remote, local, conn_ping, timeout_ms);
+    if (fd < 0) { return -1; }
+    ::close(fd);
+    return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+}
+
+std::unique_ptr<connection> connection::dial_once(const peer_id remote, const conn_type type,
+                                                  const peer_id local, int timeout_ms)
+{
+    const int fd = handshake_with_deadline(remote, local, type, timeout_ms);
+    if (fd < 0) { return nullptr; }
+    return std::unique_ptr<connection>(new connection_impl(fd, type, remote));
 }
 
 bool conn_handler::handle_next(connection *conn, msg_handler *h)

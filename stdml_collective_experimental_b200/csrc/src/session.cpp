@@ -99,30 +99,62 @@ bool session::source_gone(size_t src, long long waited_ms) const
     return false;
 }
 
-namespace
+void session::ensure_usable(const char *what)
 {
-[[noreturn]] void fail_gone(std::atomic<bool> &broken, const peer_id &who, const char *what,
-                            const std::string &tag)
-{
-    broken.store(true);
-    throw peer_failure(who, std::string(what) + " '" + tag + "': peer " + who.str() +
-                                " has gone (its connections closed, or it never connected and does not answer)");
+    if (given_up()) { give_up(failure::other, peers_[rank_], what, "(not started)"); }
 }
 
-[[noreturn]] void fail_late(std::atomic<bool> &broken, const peer_id &who, const char *what,
-                            const std::string &tag, long long limit)
+bool session::given_up() const
 {
-    broken.store(true);
-    throw std::runtime_error(std::string(what) + " '" + tag + "': nothing from peer " + who.str() +
-                             " within " + std::to_string(limit) + " ms (peer failed or left?)");
+    return broken_->load() || (liveness_ != nullptr && liveness_->aborted(version_));
 }
 
-[[noreturn]] void fail_broken(const char *what, const std::string &tag)
+// The first failure of a session tells the other members (an empty message
+// named liveness::abort_tag(version)): a member that waits for this rank, which
+// is alive but will never answer, gives up as well.  Members that are known to
+// be dead, or do not accept a connection within half a second, are skipped.
+void session::abort() noexcept
 {
-    throw std::runtime_error(std::string(what) + " '" + tag +
-                             "': given up, another receive of this session has failed");
+    if (broken_->exchange(true) || liveness_ == nullptr) { return; }
+    try {
+        const std::string tag = liveness::abort_tag(version_);
+        for (size_t r = 0; r < peers_.size(); ++r) {
+            if (r == rank_ || liveness_->gone(peers_[r])) { continue; }
+            try {
+                // a connection of its own, made with a deadline: the pooled ones are
+                // dialled with a starter's patience, which a dying member does not deserve
+                auto c = rchan::connection::dial_once(peers_[r], rchan::conn_control, peers_[rank_], 500);
+                if (c) { c->send(tag.c_str(), nullptr, 0, 0); }
+            } catch (const std::exception &) {
+                // that member has gone too
+            }
+        }
+    } catch (const std::exception &) {
+    }
 }
-}  // namespace
+
+void session::give_up(failure why, const peer_id &who, const char *what, const std::string &tag)
+{
+    const long long limit = config_.host_timeout_ms;
+    switch (why) {
+    case failure::gone:
+        abort();
+        throw peer_failure(who, std::string(what) + " '" + tag + "': peer " + who.str() +
+                                    " has gone (its connections closed, or it never connected "
+                                    "and does not answer)");
+    case failure::late:
+        abort();
+        throw std::runtime_error(std::string(what) + " '" + tag + "': nothing from peer " +
+                                 who.str() + " within " + std::to_string(limit) +
+                                 " ms (peer failed or left?)");
+    default:
+        break;
+    }
+    abort();
+    throw peer_failure(who, std::string(what) + " '" + tag +
+                                "': given up, this session has lost a member (another receive "
+                                "failed, or a member told us so)");
+}
 
 buffer session::take_eager(size_t src, const std::string &tag, const char *what)
 {
@@ -137,10 +169,10 @@ buffer session::take_eager(size_t src, const std::string &tag, const char *what)
         if (source_gone(src, waited)) {
             // what it sent before it went has been handed over by now
             if (auto got = box->try_get()) { return std::move(*got); }
-            fail_gone(*broken_, peers_[src], what, tag);
+            give_up(failure::gone, peers_[src], what, tag);
         }
-        if (limit > 0 && waited >= limit) { fail_late(*broken_, peers_[src], what, tag, limit); }
-        if (broken_->load()) { fail_broken(what, tag); }
+        if (limit > 0 && waited >= limit) { give_up(failure::late, peers_[src], what, tag); }
+        if (given_up()) { give_up(failure::other, peers_[src], what, tag); }
     }
 }
 
@@ -156,11 +188,10 @@ void session::finish_pending(slot::pending &p, size_t src, const std::string &ta
             waited += slice;
             const bool gone = source_gone(src, waited);
             const bool late = limit > 0 && waited >= limit;
-            if (!gone && !late && !broken_->load()) { continue; }
+            if (!gone && !late && !given_up()) { continue; }
             if (p.cancel()) {
-                if (gone) { fail_gone(*broken_, peers_[src], what, tag); }
-                if (late) { fail_late(*broken_, peers_[src], what, tag, limit); }
-                fail_broken(what, tag);
+                give_up(gone ? failure::gone : late ? failure::late : failure::other, peers_[src],
+                        what, tag);
             }
             rc = p.wait(0);  // it was delivered while we were giving up
         }
@@ -243,20 +274,19 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
 
     task_builder recv1, send1, recv2, send2;
     liveness *live = liveness_;
-    auto broken = broken_;
     for (size_t src : rg->prevs(rank_)) {
         auto *box = mailbox_->require(peers_[src], sh->name);
         auto got = std::make_shared<buffer>();
         const peer_id who = peers_[src];
         recv1 << new poll_task(
-            [box, got, live, who, sh, broken] {
+            [this, box, got, live, who, sh] {
                 auto b = box->try_get();
                 if (!b && live != nullptr && live->gone(who)) {
                     b = box->try_get();  // sent before it went
-                    if (!b) { fail_gone(*broken, who, "all_reduce", sh->name); }
+                    if (!b) { give_up(failure::gone, who, "all_reduce", sh->name); }
                 }
                 if (!b) {
-                    if (broken->load()) { fail_broken("all_reduce", sh->name); }
+                    if (given_up()) { give_up(failure::other, who, "all_reduce", sh->name); }
                     return false;
                 }
                 *got = std::move(*b);
@@ -282,17 +312,16 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
             auto *sl = slotbox_->require(peers_[src], sh->name);
             auto pend = std::make_shared<slot::pending>();
             const peer_id who = peers_[src];
-            recv2 << new poll_task([sl, sh, pend, bytes, live, who, broken] {
+            recv2 << new poll_task([this, sl, sh, pend, bytes, live, who] {
                 // the destination is posted on the first poll, i.e. after the
                 // reduce phase is over and recv no longer holds partial sums
                 if (!*pend) { *pend = sl->post_pending(sh->w.recv, bytes); }
                 int rc = pend->ready();
                 if (rc < 0) {
                     const bool gone = live != nullptr && live->gone(who);
-                    if (!gone && !broken->load()) { return false; }
+                    if (!gone && !given_up()) { return false; }
                     if (pend->cancel()) {
-                        if (gone) { fail_gone(*broken, who, "all_reduce", sh->name); }
-                        fail_broken("all_reduce", sh->name);
+                        give_up(gone ? failure::gone : failure::other, who, "all_reduce", sh->name);
                     }
                     rc = pend->wait(0);
                 }
@@ -323,6 +352,7 @@ void session::all_reduce(const workspace &w, void *stream)
                                     " is not defined for " + dtype_name(w.dt));
     }
     if (w.count == 0) { return; }
+    ensure_usable("all_reduce");
     if (on_device(w.send, w.recv)) {
         const void *in[1] = {w.send};
         void *out[1] = {w.recv};
@@ -502,6 +532,7 @@ void session::reduce(const void *input, void *output, size_t count, dtype dt, re
 {
     if (count == 0) { return; }
     if (!reduce_supported(dt, op)) { throw std::invalid_argument("reduce: undefined dtype/op"); }
+    ensure_usable("reduce");
     if (on_device(input, output != nullptr ? output : input)) {
         const void *in[1] = {input};
         void *out[1] = {output};
@@ -535,6 +566,7 @@ void session::all_gather(const void *input, void *output, size_t count, dtype dt
         return;
     }
     const size_t bytes = count * dtype_size(dt);
+    ensure_usable("all_gather");
     const std::string tag = versioned(*this, "stdml::all_gather::" + name);
     char *out = static_cast<char *>(output);
     // post every destination first, then send: the bodies land in place
@@ -574,6 +606,7 @@ void session::gather(const void *input, void *output, size_t count, dtype dt, st
 {
     if (count == 0) { return; }
     const size_t bytes = count * dtype_size(dt);
+    ensure_usable("gather");
     const std::string tag = versioned(*this, "stdml::gather::" + name);
     if (rank_ != 0) {
         client_pool_->require(conn_collective)
@@ -598,6 +631,7 @@ void session::broadcast(const void *input, void *output, size_t count, dtype dt,
         return;
     }
     const size_t bytes = count * dtype_size(dt);
+    ensure_usable("broadcast");
     const std::string tag = versioned(*this, "stdml::broadcast::" + name);
     const graph &g = all_reduce_topo_.pairs[0].broadcast_graph;  // rooted at rank 0
     if (g.prevs(rank_).empty()) {
@@ -626,6 +660,7 @@ void session::send(const void *input, size_t count, dtype dt, size_t target, std
 void session::recv(void *output, size_t count, dtype dt, size_t target, std::string name)
 {
     if (target >= peers_.size()) { throw std::out_of_range("recv: no such rank"); }
+    ensure_usable("recv");
     const std::string tag = versioned(*this, "stdml::p2p::" + name);
     take_into(target, tag, output, count * dtype_size(dt), "recv");
 }

@@ -6,8 +6,11 @@
 // live address from a dead one.
 //   test_shutdown <np>
 #include <chrono>
+#include <cstdint>
+#include <memory>
 #include <cstdio>
 #include <cstdlib>
+#include <functional>
 #include <thread>
 #include <vector>
 
@@ -154,6 +157,53 @@ static int peer_dies_before_connecting()
     return bad;
 }
 
+// Unplanned loss: rank 2 dies at step 3 of 8; the others catch peer_failure,
+// call recover() and finish the remaining steps as a world of np - 1.
+static int member_lost_and_recovered(int np, bool async_runtime)
+{
+    if (np < 3) { return 0; }
+    if (async_runtime) { ::setenv("STDML_COLLECTIVE_USE_ASYNC", "1", 1); }
+    std::vector<pid_t> kids;
+    for (int r = 0; r < np; ++r) {
+        const pid_t pid = ::fork();
+        if (pid == 0) {
+            int rc = 3;
+            try {
+                peer p = peer::from_fork(r, np);
+                std::unique_ptr<session> sess = p.join_elastic();
+                int recoveries = 0;
+                int64_t step = 0;
+                while (step < 8) {
+                    if (r == 2 && step == 3) { ::_exit(0); }
+                    try {
+                        std::vector<float> x(50000, 1.0f), y(50000, 0.0f);
+                        sess->all_reduce(x.data(), y.data(), x.size(), f32, sum, "g" + std::to_string(step));
+                        if (y[0] != float(sess->size()) || y.back() != y[0]) { ::_exit(7); }
+                        ++step;
+                    } catch (const peer_failure &) {
+                        const peer_list dropped = p.recover(sess);
+                        ++recoveries;
+                        if (dropped.size() != 1 || sess->size() != size_t(np - 1)) { ::_exit(8); }
+                        // some may have finished the step that failed here: agree on where to go on
+                        step = sess->all_reduce(step, max);
+                    }
+                }
+                rc = (recoveries == 1 && sess->version() == 1) ? 0 : 9;
+            } catch (const std::exception &e) {
+                std::printf("rank %d: %s\n", r, e.what());
+                std::fflush(stdout);
+                rc = 5;
+            }
+            ::_exit(rc);
+        }
+        kids.push_back(pid);
+    }
+    const int bad = reap(kids, async_runtime ? "member lost and recovered (polled tasks)"
+                                             : "member lost and recovered");
+    ::unsetenv("STDML_COLLECTIVE_USE_ASYNC");
+    return bad;
+}
+
 // conn_ping: a live peer answers, a dead address does not
 static int ping_peers()
 {
@@ -203,9 +253,24 @@ static int peer_never_joins()
 int main(int argc, char *argv[])
 {
     const int np = argc > 1 ? std::atoi(argv[1]) : 4;
-    const int bad = clean_shutdown(np) + peer_leaves(np, false) + peer_leaves(np, true) +
-                    peer_stalls(np) + peer_never_joins() + peer_dies_before_connecting() +
-                    ping_peers();
+    const bool verbose = std::getenv("TEST_SHUTDOWN_VERBOSE") != nullptr;
+    int bad = 0;
+    const auto run = [&](const char *name, const std::function<int()> &f) {
+        if (verbose) {
+            std::printf("... %s\n", name);
+            std::fflush(stdout);
+        }
+        bad += f();
+    };
+    run("clean shutdown", [&] { return clean_shutdown(np); });
+    run("peer leaves", [&] { return peer_leaves(np, false); });
+    run("peer leaves (polled tasks)", [&] { return peer_leaves(np, true); });
+    run("peer stalls", [&] { return peer_stalls(np); });
+    run("peer never joins", [&] { return peer_never_joins(); });
+    run("peer dies before connecting", [&] { return peer_dies_before_connecting(); });
+    run("member lost and recovered", [&] { return member_lost_and_recovered(np, false); });
+    run("member lost and recovered (polled tasks)", [&] { return member_lost_and_recovered(np, true); });
+    run("ping", [&] { return ping_peers(); });
     std::printf("test-shutdown np=%d: %s\n", np, bad == 0 ? "OK" : "FAILED");
     return bad == 0 ? 0 : 1;
 }

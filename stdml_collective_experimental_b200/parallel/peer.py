@@ -49,6 +49,7 @@ def _lib():
         lib.stdmlc_session_consistent.argtypes = [vp, vp, u64, c.POINTER(c.c_int)]
         lib.stdmlc_peer_resize.argtypes = [vp, vp, c.c_longlong, c.c_char_p, c.POINTER(c.c_int),
                                            c.POINTER(c.c_int)]
+        lib.stdmlc_peer_recover.argtypes = [vp, vp, c.c_int, c.POINTER(c.c_int)]
         lib.stdmlc_cluster_resize_json.argtypes = [c.c_char_p, u64, c.c_char_p, u64]
         lib.stdmlc_session_all_reduce_async.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int,
                                                         c.c_char_p, vp, vpp]
@@ -312,6 +313,16 @@ class Peer:
             self._h, sess._h, -1 if new_size is None else int(new_size), js,
             ctypes.byref(changed), ctypes.byref(detached)))
         return bool(changed.value), bool(detached.value)
+
+    def recover(self, sess, ping_timeout_ms=1000):
+        """After a PeerFailure: every surviving rank calls this.  `sess` becomes, in
+        place, a session of the members that still answer (ranks keep their order,
+        the version goes up by one).  Returns the number of members dropped.  As
+        after a resize, re-synchronise progress and parameters afterwards."""
+        dropped = ctypes.c_int()
+        _native.check(self._lib.stdmlc_peer_recover(self._h, sess._h, int(ping_timeout_ms),
+                                                    ctypes.byref(dropped)))
+        return dropped.value
 
     def close(self):
         if self._h is not None:

@@ -1,6 +1,7 @@
 """One rank of the Python failure-detection test (spawned by test_python_api.py):
 rank 1 leaves after joining; the others must get PeerFailure from their next
-collective, without any timeout configured."""
+collective, without any timeout configured, and carry on as a smaller world
+after Peer.recover()."""
 import os
 import sys
 import time
@@ -33,9 +34,17 @@ def main():
         sess.all_reduce(torch.ones(100_000), name="after")
     except PeerFailure as e:
         assert time.time() - t0 < 10, "detected too late"
-        print(f"rank {rank} OK: {e}", flush=True)
-        os._exit(0)  # the session is broken; skip its teardown barrier
-    raise SystemExit("all_reduce succeeded without rank 1")
+        why = str(e)
+    else:
+        raise SystemExit("all_reduce succeeded without rank 1")
+    # carry on without it
+    assert peer.recover(sess) == 1
+    assert (sess.size, sess.version) == (n - 1, 1) and sess.rank == (0 if rank == 0 else rank - 1)
+    y = torch.ones(100_000)
+    sess.all_reduce(y, name="after")
+    assert y[0] == n - 1 and y[-1] == n - 1
+    sess.barrier()
+    print(f"rank {rank} OK: {why}", flush=True)
 
 
 if __name__ == "__main__":

@@ -74,6 +74,8 @@ def test_examples_under_the_launcher():
     assert sorted(lines) == ["11", "12", "21", "22"]
     assert lines.index("11") < lines.index("12") and lines.index("21") < lines.index("22")
     assert run("example_rchan").count("hello") == 3
+    out = run("example_recover", 4, 2, 3)
+    assert "example-recover: OK" in out and out.count("done: 3 members, version 1") == 3
 
 
 def test_mpi_env_launch_path():

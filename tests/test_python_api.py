@@ -29,7 +29,7 @@ def test_python_peer_failure_is_an_exception(strategy, base, native_lib):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o[-2000:]
         if r != 1:
-            assert f"rank {r} OK" in o and "has gone" in o or "failed" in o, o[-2000:]
+            assert f"rank {r} OK" in o, o[-2000:]
 
 
 def test_python_elastic_state_under_the_runner(native_lib):
