@@ -30,6 +30,7 @@ class elastic_state
     bool synced_ = false;
     bool detached_ = false;
     bool needs_state_ = false;
+    size_t state_root_ = 0;
     peer::config_prodiver get_config_;
     std::function<void(session &)> on_resize_;
 
@@ -47,9 +48,18 @@ class elastic_state
     bool detached() const { return detached_; }
     session &sess();
     peer &get_peer() { return peer_; }
+    // After a peer_failure in the loop body (or in ++): carry on with the
+    // members that still answer.  Progress becomes the maximum over them and
+    // the resize hook runs, exactly as after a planned resize.  Returns the
+    // members that were dropped.
+    //     try { train(st.sess()); ++st; } catch (const peer_failure &) { st.recover(); }
+    peer_list recover();
     // called on every member of a new session (survivors right after the
     // resize, joiners at their first use of the state), after the progress
     // counter has been synchronised
     void on_resize(std::function<void(session &)> f) { on_resize_ = std::move(f); }
+    // the rank whose state the hook should broadcast: the lowest one that has
+    // made the most progress (0 after a planned resize)
+    size_t state_root() const { return state_root_; }
 };
 }  // namespace stdml::collective

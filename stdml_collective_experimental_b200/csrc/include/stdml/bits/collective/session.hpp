@@ -138,8 +138,11 @@ class session
     void all_gather(const void *input, void *output, size_t count, dtype dt,
                     std::string name = "", void *stream = nullptr);
     void gather(const void *input, void *output, size_t count, dtype dt, std::string name = "");
+    // From rank `root` (the reference fixes root 0: session.cpp:49-62 there).
+    // Root 0 follows the session's broadcast graph; any other root sends to
+    // every member directly.
     void broadcast(const void *input, void *output, size_t count, dtype dt,
-                   std::string name = "", void *stream = nullptr);
+                   std::string name = "", void *stream = nullptr, size_t root = 0);
     void recv(void *output, size_t count, dtype dt, size_t target, std::string name = "");
     void send(const void *input, size_t count, dtype dt, size_t target, std::string name = "");
 

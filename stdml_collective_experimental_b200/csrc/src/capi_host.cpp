@@ -236,6 +236,16 @@ int stdmlc_session_broadcast(void *s, const void *in, void *out, unsigned long l
     });
 }
 
+int stdmlc_session_broadcast_from(void *s, const void *in, void *out, unsigned long long count,
+                                  int dt, int root, const char *name, void *stream)
+{
+    return host_guarded([&] {
+        if (root < 0) { throw std::invalid_argument("broadcast: negative root"); }
+        SS(s).broadcast(in, out, count, static_cast<sc::dtype>(dt), name ? name : "", stream,
+                        static_cast<size_t>(root));
+    });
+}
+
 int stdmlc_session_send(void *s, const void *in, unsigned long long count, int dt, int target,
                         const char *name)
 {

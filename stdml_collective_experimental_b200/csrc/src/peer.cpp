@@ -9,6 +9,7 @@
 #include <unistd.h>
 
 #include <stdml/bits/collective/affinity.hpp>
+#include <stdml/bits/collective/config.hpp>
 #include <stdml/bits/collective/log.hpp>
 #include <stdml/bits/collective/peer.hpp>
 #include <stdml/bits/collective/stat.hpp>
@@ -299,11 +300,19 @@ peer_list peer::recover(std::unique_ptr<session> &sess, int ping_timeout_ms)
     liveness_->forget(old);
     init_peers_ = alive;
     init_version_ = new_version;
-    if (!runners.empty() && alive.rank(self_) == 0) {
+    if (alive.rank(self_) == 0) {
+        // the wanted membership is now the surviving one: tell the config server
+        // (else the next resize check would ask for the dead member again) and
+        // the runners (which start and stop worker processes)
+        const cluster_config next(runners, alive);
         try {
-            commit_cluster_config(cluster_config(runners, alive), new_version);
+            const std::string url = safe_getenv("KUNGFU_CONFIG_SERVER");
+            if (!url.empty() && !propose_cluster(url, next)) {
+                log(WARN) << "recover: the config server at" << url << "refused the new membership";
+            }
+            commit_cluster_config(next, new_version);
         } catch (const std::exception &e) {
-            log(WARN) << "recover: could not tell the runners:" << e.what();
+            log(WARN) << "recover: could not publish the new membership:" << e.what();
         }
     }
     // the constructor's barrier completes once every survivor has got here

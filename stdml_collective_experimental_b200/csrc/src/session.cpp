@@ -621,13 +621,34 @@ void session::gather(const void *input, void *output, size_t count, dtype dt, st
 }
 
 void session::broadcast(const void *input, void *output, size_t count, dtype dt,
-                        std::string name, void *stream)
+                        std::string name, void *stream, size_t root)
 {
     if (count == 0) { return; }
+    if (root >= peers_.size()) { throw std::out_of_range("broadcast: no such root"); }
     if (on_device(input, output)) {
         const void *in[1] = {input};
         void *out[1] = {output};
-        device()->broadcast(in, out, count, dt, 0, stream);
+        device()->broadcast(in, out, count, dt, static_cast<int>(root), stream);
+        return;
+    }
+    if (root != 0) {
+        ensure_usable("broadcast");
+        const size_t nbytes = count * dtype_size(dt);
+        const std::string rtag =
+            versioned(*this, "stdml::broadcast::r" + std::to_string(root) + "::" + name);
+        if (rank_ != root) {
+            take_into(root, rtag, output, nbytes, "broadcast");
+            return;
+        }
+        if (output != input) { std::memcpy(output, input, nbytes); }
+        std::vector<size_t> others;
+        for (size_t r = 0; r < peers_.size(); ++r) {
+            if (r != root) { others.push_back(r); }
+        }
+        rchan::client *cl = client_pool_->require(conn_collective);
+        fmap(par, [&](size_t r) {
+            cl->send(peers_[r], rtag.c_str(), output, nbytes, message_header::wait_recv_buf);
+        }, others);
         return;
     }
     const size_t bytes = count * dtype_size(dt);

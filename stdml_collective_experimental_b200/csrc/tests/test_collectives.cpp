@@ -169,6 +169,11 @@ static void check_others(session &sess)
         std::vector<int> b(count, -5);
         sess.broadcast(x.data(), b.data(), count, i32, "bc" + std::to_string(count));
         for (size_t i = 0; i < count; ++i) { CHECK(b[i] == int(i)); }
+        // any root (the last rank here), in place on the root
+        const size_t root = n - 1;
+        std::vector<int> br = x;
+        sess.broadcast(br.data(), br.data(), count, i32, "bcr" + std::to_string(count), nullptr, root);
+        for (size_t i = 0; i < count; ++i) { CHECK(br[i] == int(root * 1000 + i)); }
         std::vector<int> red(count, -7);
         sess.reduce(x.data(), red.data(), count, i32, sum, "rd" + std::to_string(count));
         if (r == 0) {

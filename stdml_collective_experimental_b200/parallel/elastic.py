@@ -3,7 +3,7 @@ changes, the counterpart of the reference's C++ `elastic_state`
 (include/stdml/bits/collective/elastic_state.hpp:8-38):
 
     state = ElasticState(max_progress=1000)
-    state.on_resize(lambda sess: sess.broadcast(weights))   # state from rank 0
+    state.on_resize(lambda sess: sess.broadcast(weights, root=state.state_root))
     while not state.should_stop():
         train_step(state.sess)
         state.advance()                                     # checks for a resize
@@ -12,7 +12,8 @@ changes, the counterpart of the reference's C++ `elastic_state`
 the membership changed, survivors get a new session in place, the progress
 counter becomes the maximum over the new members and the resize hook runs
 (joiners run it at their first use of the state).  A removed rank sees
-`should_stop()` become true.
+`should_stop()` become true.  An unplanned loss surfaces as `PeerFailure`;
+`state.recover()` then rebuilds the session from the members that still answer.
 """
 import torch
 
@@ -32,17 +33,25 @@ class ElasticState:
         self._needs_state = self.sess.version > 0  # joined a running job
         self._hook = None
         self._get_cluster = get_cluster
+        self.state_root = 0  # the rank whose state the resize hook should broadcast
 
     def on_resize(self, fn):
         self._hook = fn
 
     def _sync(self):
         if not self._synced:
-            t = torch.tensor([self.progress], dtype=torch.int64)
+            mine = torch.tensor([self.progress], dtype=torch.int64)
+            t = mine.clone()
             self.progress = int(self.sess.all_reduce(t, op="max", name="stdml::progress").item())
             self._synced = True
             if self._needs_state:
                 self._needs_state = False
+                # the lowest rank that is as far as anyone holds the state to copy: rank 0
+                # after a planned resize, possibly another one after a loss (the step in
+                # flight may have finished on some members only)
+                everyone = torch.empty(self.sess.size, dtype=torch.int64)
+                self.sess.all_gather(mine, everyone, name="stdml::progress")
+                self.state_root = int((everyone == self.progress).nonzero()[0].item())
                 if self._hook is not None:
                     self._hook(self.sess)
 
@@ -66,6 +75,16 @@ class ElasticState:
             self._synced = False
             self._needs_state = True
             self._sync()
+
+    def recover(self):
+        """After a PeerFailure in the loop body (or in advance()): carry on with the
+        members that still answer.  Progress becomes the maximum over them and the
+        resize hook runs, as after a planned resize.  Returns how many were dropped."""
+        dropped = self.peer.recover(self.sess)
+        self._synced = False
+        self._needs_state = True
+        self._sync()
+        return dropped
 
     def should_stop(self):
         if self.detached:

@@ -43,6 +43,8 @@ def _lib():
         lib.stdmlc_session_all_gather.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p, vp]
         lib.stdmlc_session_gather.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p]
         lib.stdmlc_session_broadcast.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p, vp]
+        lib.stdmlc_session_broadcast_from.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p,
+                                                      vp]
         lib.stdmlc_session_send.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_recv.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_barrier.argtypes = [vp]
@@ -224,13 +226,13 @@ class Session:
             self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), name.encode()))
         return o
 
-    def broadcast(self, tensor, out=None, name=""):
-        """From rank 0 to everyone."""
+    def broadcast(self, tensor, out=None, name="", root=0):
+        """From rank `root` to everyone."""
         t = _checked(tensor, "broadcast")
         o = t if out is None else _checked(out, "broadcast")
-        _native.check(self._lib.stdmlc_session_broadcast(
-            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), name.encode(),
-            _stream_of(t)))
+        _native.check(self._lib.stdmlc_session_broadcast_from(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), int(root),
+            name.encode(), _stream_of(t)))
         return o
 
     def send(self, tensor, target, name=""):

@@ -7,6 +7,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
+from stdml_collective_experimental_b200 import PeerFailure  # noqa: E402
 from stdml_collective_experimental_b200.parallel.elastic import ElasticState  # noqa: E402
 from stdml_collective_experimental_b200.parallel.peer import resized_cluster  # noqa: E402
 import json  # noqa: E402
@@ -21,18 +22,27 @@ def propose(sess, new_size):
 
 def main():
     max_step = int(sys.argv[1])
-    schedule = dict(tuple(map(int, a.split(":"))) for a in sys.argv[2:])
+    args = sys.argv[2:]
+    die = [a[len("--die="):].split(":") for a in args if a.startswith("--die=")]
+    die_port, die_step = (int(die[0][0]), int(die[0][1])) if die else (-1, -1)
+    schedule = dict(tuple(map(int, a.split(":"))) for a in args if not a.startswith("--"))
     weights = torch.zeros(256)
     state = ElasticState(max_progress=max_step)
-    state.on_resize(lambda s: s.broadcast(weights, name="state"))
+    state.on_resize(lambda s: s.broadcast(weights, name="state", root=state.state_root))
+    my_port = int(state.peer.self_id.split(":")[1])
     while not state.should_stop():
-        step = int(state)
-        g = torch.full((256,), float(step + 1))
-        state.sess.all_reduce(g, name="grad")
-        weights += g / state.sess.size
-        if state.sess.rank == 0 and step in schedule:
-            propose(state.sess, schedule[step])
-        state.advance()
+        try:
+            step = int(state)
+            if step == die_step and my_port == die_port:
+                os._exit(3)  # an unplanned loss
+            g = torch.full((256,), float(step + 1))
+            state.sess.all_reduce(g, name="grad")
+            weights += g / state.sess.size
+            if state.sess.rank == 0 and step in schedule:
+                propose(state.sess, schedule[step])
+            state.advance()
+        except PeerFailure:
+            print(f"lost {state.recover()} member(s)", flush=True)
     if state.detached:
         print("detached", flush=True)
         return

@@ -16,14 +16,14 @@ def built():
     _native.build()
 
 
-def run(prog, *args, env=None, timeout=600):
+def run(prog, *args, env=None, timeout=600, want_rc=0):
     e = dict(os.environ)
     for k in ("KUNGFU_SELF_SPEC", "OMPI_COMM_WORLD_SIZE", "RANK", "WORLD_SIZE"):
         e.pop(k, None)
     e.update(env or {})
     res = subprocess.run([os.path.join(BIN, prog), *map(str, args)], env=e, timeout=timeout,
                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    assert res.returncode == 0, res.stdout[-3000:]
+    assert res.returncode == want_rc, res.stdout[-3000:]
     return res.stdout
 
 
@@ -115,6 +115,19 @@ def test_elastic_state_follows_config_server():
               os.path.join(BIN, "example_elastic_state"), "--max-step=9", "2:4", "5:3",
               timeout=300)
     assert out.count("weight 45.0 (want 45.0) OK") == 3 and out.count("detached") == 1
+
+
+def test_elastic_state_survives_a_crash_and_grows_back():
+    # the worker on port 10601 dies at step 3; the others recover (version 1, two
+    # members), rank 0 asks for three again at step 6 and the runner starts a
+    # replacement, which receives progress and state.  The runner reports the
+    # crashed worker in its exit status.
+    out = run("stdml_collective_run", "-np", 3, "-w", "-builtin-config-port", 0, "-runner-port", 38383,
+              "-port-range", 10600, os.path.join(BIN, "example_elastic_state"), "--max-step=9",
+              "--die=10601:3", "6:3", timeout=300, want_rc=1)
+    assert out.count("weight 45.0 (want 45.0) OK") == 3, out
+    assert out.count("lost 127.0.0.1:10601, carrying on with 2 members") == 2
+    assert "[runner] version 1 : 3 -> 2 workers" in out and "[runner] version 2 : 2 -> 3 workers" in out
 
 
 def test_shutdown_and_host_side_failure_detection():

@@ -45,6 +45,18 @@ def test_python_elastic_state_under_the_runner(native_lib):
     assert res.stdout.count("weight 36.0 OK") == 2 and res.stdout.count("detached") == 1
 
 
+def test_python_elastic_state_recovers_from_a_crash(native_lib):
+    from stdml_collective_experimental_b200 import _native
+    runner = os.path.join(_native.CSRC, "build", "bin", "stdml_collective_run")
+    cmd = [runner, "-q", "-np", "3", "-w", "-builtin-config-port", "0", "-runner-port", "38284",
+           "-port-range", "10540", sys.executable, os.path.join(HERE, "py_elastic_worker.py"),
+           "8", "--die=10541:3"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         timeout=600)
+    assert res.returncode == 1, res.stdout[-3000:]  # the runner counts the crashed worker
+    assert res.stdout.count("weight 36.0 OK") == 2 and res.stdout.count("lost 1 member(s)") == 2
+
+
 def test_distributed_optimizer_matches_single_process_training(native_lib):
     n, base = 3, 12200
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_train_worker.py"), str(r),
