@@ -81,6 +81,7 @@ class session
 
   public:
     static constexpr size_t chunk_bytes = 1u << 20;
+    static constexpr size_t tiny_chunk_bytes = 32u << 10;  // handled without helper threads
 
     mailbox *mailbox_;                 // owned by peer
     slotbox *slotbox_;                 // owned by peer

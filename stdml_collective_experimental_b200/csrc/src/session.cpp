@@ -237,8 +237,15 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
         out->send(peers_[dst], name.c_str(), w.recv, bytes, message_header::wait_recv_buf);
     };
 
+    // A small chunk is latency-bound: its messages fit the socket buffers, so
+    // sends do not block, and starting a thread per neighbour costs more than
+    // the work; everything runs on the calling thread, in order.
+    const bool tiny = bytes <= tiny_chunk_bytes;
     // reduce graph: accumulate what the predecessors send, pass the partial on
-    if (pool_) {
+    if (tiny) {
+        fmap(seq, recv_reduce, rg->prevs(rank_));
+        fmap(seq, send_partial, rg->nexts(rank_));
+    } else if (pool_) {
         fmap(pool_.get(), recv_reduce, rg->prevs(rank_));
         fmap(pool_.get(), send_partial, rg->nexts(rank_));
     } else {
@@ -251,7 +258,9 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
     } else {
         fmap(seq, recv_result, bg->prevs(rank_));
     }
-    if (pool_) {
+    if (tiny) {
+        fmap(seq, send_result, bg->nexts(rank_));
+    } else if (pool_) {
         fmap(pool_.get(), send_result, bg->nexts(rank_));
     } else {
         fmap(par, send_result, bg->nexts(rank_));
