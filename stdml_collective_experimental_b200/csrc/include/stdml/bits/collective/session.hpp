@@ -48,6 +48,7 @@ class session
     std::unique_ptr<runtime> async_runtime_;
     std::unique_ptr<cuda::DeviceSession> device_;
     bool device_tried_ = false;
+    int spin_polls_ = 0;  // looks at a mailbox before a receiver sleeps (see session.cpp)
 
     const system_config config_;
     const size_t version_;

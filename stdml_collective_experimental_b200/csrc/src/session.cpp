@@ -6,6 +6,8 @@
 #include <stdexcept>
 #include <thread>
 
+#include <sched.h>
+
 #include <stdml/bits/collective/device.hpp>
 #include <stdml/bits/collective/execution.hpp>
 #include <stdml/bits/collective/log.hpp>
@@ -39,6 +41,8 @@ split_work(const workspace &w, const graph_pair_list &gps, size_t chunk_size)
 
 namespace
 {
+int default_spin_polls(const peer_list &peers, const peer_id &self);
+
 // STDML_COLLECTIVE_ALGO: auto | oneshot | twoshot | nvls | nvls_oneshot
 int forced_algo(const system_config &c)
 {
@@ -64,6 +68,7 @@ session::session(system_config config, size_t version, size_t rank, peer_list pe
         pool_ = sync::thread_pool::make(config_.thread_pool_size);
     }
     async_runtime_.reset(runtime::New(8));
+    spin_polls_ = default_spin_polls(peers_, peers_[rank_]);
     barrier();
 }
 
@@ -83,6 +88,52 @@ std::string versioned(const session &s, const std::string &name)
 {
     // keeps messages of an old membership from matching operations of a new one
     return s.version() == 0 ? name : name + "@v" + std::to_string(s.version());
+}
+}  // namespace
+
+namespace
+{
+// How many times a receiver looks for its message before it goes to sleep.
+// Meeting a message awake saves a wake-up per hop (measured on 4 ranks, 4 KB
+// tensors: ring +35 %, star +30 %), but only while every rank has cores to
+// spare: on 8 ranks sharing 8 cores the same spin cost a factor of three.  So
+// the default spins only when this process may run on at least two cores per
+// rank of this host.  STDML_COLLECTIVE_SPIN_POLLS overrides (0: never spin).
+int default_spin_polls(const peer_list &peers, const peer_id &self)
+{
+    if (const auto v = parse_env_int("STDML_COLLECTIVE_SPIN_POLLS"); v && *v >= 0) {
+        return static_cast<int>(*v);
+    }
+    size_t local = 0;
+    for (const auto &p : peers) { local += p.ipv4 == self.ipv4 ? 1 : 0; }
+    cpu_set_t set;
+    CPU_ZERO(&set);
+    const size_t cores = ::sched_getaffinity(0, sizeof(set), &set) == 0
+                             ? static_cast<size_t>(CPU_COUNT(&set))
+                             : std::thread::hardware_concurrency();
+    return cores >= 2 * std::max<size_t>(local, 1) ? 10000 : 0;
+}
+
+// Spinning is for a thread that is the only receiver of its process: a single
+// small operation on the calling thread.  Lanes of a chunked tensor and the
+// workers of a fused group keep several receivers waiting at once (all of them
+// spinning costs more than it saves: measured), so they sleep at once.
+thread_local int tl_spin_polls = 0;
+thread_local bool tl_in_group = false;
+
+struct spin_scope {
+    int saved;
+    explicit spin_scope(int polls) : saved(tl_spin_polls) { tl_spin_polls = tl_in_group ? 0 : polls; }
+    ~spin_scope() { tl_spin_polls = saved; }
+};
+
+inline void cpu_relax()
+{
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#else
+    std::this_thread::yield();
+#endif
 }
 }  // namespace
 
@@ -159,6 +210,11 @@ void session::give_up(failure why, const peer_id &who, const char *what, const s
 buffer session::take_eager(size_t src, const std::string &tag, const char *what)
 {
     auto *box = mailbox_->require(peers_[src], tag);
+    // a message that is about to arrive is cheaper to meet spinning than asleep
+    for (int spin = 0; spin < tl_spin_polls; ++spin) {
+        if (auto got = box->try_get()) { return std::move(*got); }
+        cpu_relax();
+    }
     const long long limit = config_.host_timeout_ms;
     long long waited = 0;
     for (;;) {
@@ -178,6 +234,7 @@ buffer session::take_eager(size_t src, const std::string &tag, const char *what)
 
 void session::finish_pending(slot::pending &p, size_t src, const std::string &tag, const char *what)
 {
+    for (int spin = 0; spin < tl_spin_polls && p.ready() < 0; ++spin) { cpu_relax(); }
     const long long limit = config_.host_timeout_ms;
     long long waited = 0;
     for (;;) {
@@ -393,6 +450,7 @@ void session::all_reduce(const workspace &w, void *stream)
     }
     lanes = std::min(lanes, work.size());
     if (lanes <= 1) {
+        spin_scope spin(spin_polls_);
         for (const auto &[part, gs] : work) { run_chunk(part, gs.first, gs.second); }
         return;
     }
@@ -516,6 +574,11 @@ void session::group_all_reduce(std::vector<std::future<workspace>> fs)
     std::mutex err_mu;
     std::exception_ptr err;
     auto work = [&] {
+        struct in_group {
+            bool saved = tl_in_group;
+            in_group() { tl_in_group = true; }
+            ~in_group() { tl_in_group = saved; }
+        } mark;
         for (;;) {
             const size_t i = next.fetch_add(1);
             if (i >= n) { return; }
