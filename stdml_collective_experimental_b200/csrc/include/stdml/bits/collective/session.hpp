@@ -82,7 +82,7 @@ class session
 
   public:
     static constexpr size_t chunk_bytes = 1u << 20;
-    static constexpr size_t tiny_chunk_bytes = 32u << 10;  // handled without helper threads
+    static constexpr size_t tiny_chunk_bytes = 512u << 10;  // handled without helper threads (measured: star, 4 ranks, 64 KB +80 %, 400 KB +45 %; 1 MB chunks -15 %)
 
     mailbox *mailbox_;                 // owned by peer
     slotbox *slotbox_;                 // owned by peer

@@ -294,9 +294,9 @@ void session::run_chunk(const workspace &w, const graph *rg, const graph *bg)
         out->send(peers_[dst], name.c_str(), w.recv, bytes, message_header::wait_recv_buf);
     };
 
-    // A small chunk is latency-bound: its messages fit the socket buffers, so
-    // sends do not block, and starting a thread per neighbour costs more than
-    // the work; everything runs on the calling thread, in order.
+    // Below a full chunk the messages fit the socket buffers, so sends do not
+    // block, and starting a thread per neighbour costs more than copying in
+    // turn; everything runs on the calling thread, in order.
     const bool tiny = bytes <= tiny_chunk_bytes;
     // reduce graph: accumulate what the predecessors send, pass the partial on
     if (tiny) {
