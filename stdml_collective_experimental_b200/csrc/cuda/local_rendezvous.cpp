@@ -78,6 +78,27 @@ LocalRendezvous::LocalRendezvous(const std::string &key, int rank, int world, in
     : rank_(rank), world_(world), listen_fd_(-1), conn_(world, -1)
 {
     if (world <= 1) { return; }
+    try {
+        connect_mesh(key, timeout_ms);
+    } catch (...) {
+        close_all();  // no destructor runs for an object whose constructor threw
+        throw;
+    }
+}
+
+void LocalRendezvous::close_all()
+{
+    for (int &fd : conn_) {
+        if (fd >= 0) { ::close(fd); }
+        fd = -1;
+    }
+    if (listen_fd_ >= 0) { ::close(listen_fd_); }
+    listen_fd_ = -1;
+}
+
+void LocalRendezvous::connect_mesh(const std::string &key, int timeout_ms)
+{
+    const int rank = rank_, world = world_;
     const auto deadline = clock_type::now() + std::chrono::milliseconds(timeout_ms);
 
     listen_fd_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
@@ -97,9 +118,9 @@ LocalRendezvous::LocalRendezvous(const std::string &key, int rank, int world, in
             if (fd < 0) { fail("socket"); }
             if (::connect(fd, reinterpret_cast<sockaddr *>(&pa), pl) == 0) {
                 set_timeouts(fd, timeout_ms);
+                conn_[peer] = fd;  // owned from here on (closed by close_all on failure)
                 const int32_t hello = rank;
                 write_all(fd, &hello, sizeof(hello));
-                conn_[peer] = fd;
                 break;
             }
             ::close(fd);
@@ -115,7 +136,12 @@ LocalRendezvous::LocalRendezvous(const std::string &key, int rank, int world, in
         if (fd < 0) { fail("accept"); }
         set_timeouts(fd, timeout_ms);
         int32_t hello = -1;
-        read_all(fd, &hello, sizeof(hello));
+        try {
+            read_all(fd, &hello, sizeof(hello));
+        } catch (...) {
+            ::close(fd);
+            throw;
+        }
         if (hello <= rank || hello >= world || conn_[hello] != -1) {
             ::close(fd);
             throw std::runtime_error("local rendezvous: unexpected hello");
@@ -124,13 +150,7 @@ LocalRendezvous::LocalRendezvous(const std::string &key, int rank, int world, in
     }
 }
 
-LocalRendezvous::~LocalRendezvous()
-{
-    for (int fd : conn_) {
-        if (fd >= 0) { ::close(fd); }
-    }
-    if (listen_fd_ >= 0) { ::close(listen_fd_); }
-}
+LocalRendezvous::~LocalRendezvous() { close_all(); }
 
 void LocalRendezvous::send_bytes(int peer, const void *data, size_t size)
 {

@@ -7,6 +7,7 @@
 // (src/stdml/collective/net/old/rchan.cpp).  File descriptors cannot travel
 // over TCP, hence this side channel.
 #pragma once
+#include <cstddef>
 #include <string>
 #include <vector>
 
@@ -42,6 +43,9 @@ class LocalRendezvous
     void barrier() { (void)all_agree(true); }
 
   private:
+    void connect_mesh(const std::string &key, int timeout_ms);
+    void close_all();
+
     int rank_;
     int world_;
     int listen_fd_;

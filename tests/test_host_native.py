@@ -136,6 +136,11 @@ def test_shutdown_and_host_side_failure_detection():
     assert "test-shutdown np=3: OK" in run("test_shutdown", 3)
 
 
+def test_local_rendezvous_mesh_descriptor_passing_and_timeouts():
+    # the side channel of the device world set-up (UNIX sockets, SCM_RIGHTS) needs no GPU
+    assert "test-rendezvous: OK" in run("test_rendezvous", 4)
+
+
 def test_public_headers_compile_as_cxx17():
     run("test_cxx17")
 
@@ -160,7 +165,7 @@ def test_host_runtime_under_address_and_thread_sanitizers():
         assert res.returncode == 0, res.stdout[-3000:]
         sdir = os.path.join(_native.CSRC, "build", f"san-{san}", "bin")
         for prog, args, extra in (("test_unit", [], {}), ("test_collectives", ["3"], {}),
-                                  ("test_shutdown", ["3"], {}),
+                                  ("test_shutdown", ["3"], {}), ("test_rendezvous", ["3"], {}),
                                   ("test_collectives", ["3"], {"STDML_COLLECTIVE_TRANSPORT": "shm"}),
                                   ("test_shutdown", ["3"], {"STDML_COLLECTIVE_TRANSPORT": "shm"})):
             e = dict(os.environ, **opts, **extra)
