@@ -3,6 +3,7 @@
 // stdmlc_last_error() then holds the message (thread-local).
 #include <cstring>
 #include <memory>
+#include <stdexcept>
 #include <string>
 
 #include "capi_cuda.h"
@@ -32,10 +33,17 @@ int guarded(F f)
     } catch (const std::exception &e) {
         g_error = e.what();
         return STDMLC_ERR_RUNTIME;
+    } catch (...) {  // nothing may unwind through the C boundary
+        g_error = "unknown C++ exception";
+        return STDMLC_ERR_RUNTIME;
     }
 }
 
-DeviceSession *S(void *h) { return static_cast<DeviceSession *>(h); }
+DeviceSession *S(void *h)
+{
+    if (h == nullptr) { throw std::invalid_argument("null device session handle"); }
+    return static_cast<DeviceSession *>(h);
+}
 }  // namespace
 
 namespace stdml::collective::cuda
@@ -75,7 +83,7 @@ int stdmlc_dw_create(void **out, int rank, int world, int device, int loopback,
 
 int stdmlc_dw_destroy(void *h)
 {
-    return guarded([&] { delete S(h); });
+    return guarded([&] { delete static_cast<DeviceSession *>(h); });  // null is a no-op, as for free()
 }
 
 int stdmlc_dw_info(void *h, int what, unsigned long long *out)

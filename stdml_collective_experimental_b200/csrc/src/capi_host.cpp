@@ -71,6 +71,9 @@ int host_guarded(F f)
     } catch (const std::exception &e) {
         sc::cuda::set_last_error(e.what());
         return 1;
+    } catch (...) {  // nothing may unwind through the C boundary
+        sc::cuda::set_last_error("unknown C++ exception");
+        return 1;
     }
 }
 
@@ -78,7 +81,18 @@ struct session_box {
     std::unique_ptr<sc::session> s;
 };
 
-sc::session &SS(void *h) { return *static_cast<session_box *>(h)->s; }
+sc::peer *PP(void *h)
+{
+    if (h == nullptr) { throw std::invalid_argument("null peer handle"); }
+    return static_cast<sc::peer *>(h);
+}
+
+sc::session &SS(void *h)
+{
+    auto *box = static_cast<session_box *>(h);
+    if (box == nullptr || !box->s) { throw std::invalid_argument("null or closed session handle"); }
+    return *box->s;
+}
 }  // namespace
 
 extern "C" {
@@ -106,13 +120,13 @@ int stdmlc_peer_create(void **out, int rank, const char *peers_csv, int strategy
 
 int stdmlc_peer_destroy(void *p)
 {
-    return host_guarded([&] { delete static_cast<sc::peer *>(p); });
+    return host_guarded([&] { delete static_cast<sc::peer *>(p); });  // null is a no-op
 }
 
 int stdmlc_peer_self(void *p, char *buf, unsigned long long size)
 {
     return host_guarded([&] {
-        const std::string s = static_cast<sc::peer *>(p)->self().str();
+        const std::string s = PP(p)->self().str();
         std::snprintf(buf, size, "%s", s.c_str());
     });
 }
@@ -124,7 +138,7 @@ int stdmlc_peer_ping(void *p, const char *target, int timeout_ms, double *us)
     return host_guarded([&] {
         const auto id = sc::parse_peer_id(target);
         if (!id) { throw std::invalid_argument(std::string("ping: bad address ") + target); }
-        *us = static_cast<sc::peer *>(p)->ping(*id, timeout_ms);
+        *us = PP(p)->ping(*id, timeout_ms);
     });
 }
 
@@ -133,7 +147,7 @@ int stdmlc_peer_join(void *p, void **sess)
     *sess = nullptr;
     return host_guarded([&] {
         auto box = std::make_unique<session_box>();
-        box->s = static_cast<sc::peer *>(p)->join_elastic();
+        box->s = PP(p)->join_elastic();
         *sess = box.release();
     });
 }
@@ -280,7 +294,7 @@ int stdmlc_peer_resize(void *p, void *sess, long long new_size, const char *clus
                        int *changed, int *detached)
 {
     return host_guarded([&] {
-        auto *peer = static_cast<sc::peer *>(p);
+        auto *peer = PP(p);
         auto *box = static_cast<session_box *>(sess);
         sc::resize_result r{false, false};
         if (cluster_json != nullptr) {
@@ -305,7 +319,7 @@ int stdmlc_peer_recover(void *p, void *sess, int ping_timeout_ms, int *dropped)
     return host_guarded([&] {
         auto *box = static_cast<session_box *>(sess);
         *dropped = static_cast<int>(
-            static_cast<sc::peer *>(p)->recover(box->s, ping_timeout_ms).size());
+            PP(p)->recover(box->s, ping_timeout_ms).size());
     });
 }
 

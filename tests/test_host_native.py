@@ -122,7 +122,7 @@ def test_elastic_state_survives_a_crash_and_grows_back():
     # members), rank 0 asks for three again at step 6 and the runner starts a
     # replacement, which receives progress and state.  The runner reports the
     # crashed worker in its exit status.
-    out = run("stdml_collective_run", "-np", 3, "-w", "-builtin-config-port", 0, "-runner-port", 38383,
+    out = run("stdml_collective_run", "-np", 3, "-w", "-builtin-config-port", 0, "-runner-port", 38385,
               "-port-range", 10600, os.path.join(BIN, "example_elastic_state"), "--max-step=9",
               "--die=10601:3", "6:3", timeout=300, want_rc=1)
     assert out.count("weight 45.0 (want 45.0) OK") == 3, out

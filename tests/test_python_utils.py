@@ -94,7 +94,9 @@ def test_launcher_module_runs_a_job():
                           "from stdml_collective_experimental_b200.parallel import Peer\n"
                           "import torch\n"
                           "p = Peer.from_env(); s = p.join()\n"
-                          "print('sum', int(s.all_reduce(torch.tensor([s.rank + 1]))[0]))\n"
+                          "import os\n"
+                          "v = int(s.all_reduce(torch.tensor([s.rank + 1]))[0])\n"
+                          "os.write(1, ('sum %d\\n' % v).encode())\n"  # one write: ranks share the pipe
                           "s.close(); p.close()"],
                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
                          cwd=os.path.dirname(HERE))
@@ -145,6 +147,17 @@ def test_native_api_reports_misuse_as_exceptions():
     assert _native.lib().stdmlc_dtype_size(8) == 2
     s.close()
     p.close()
+    # null handles are errors with a message, never a crash; destroying null is a no-op
+    import ctypes
+    lib = _native.lib()
+    v = ctypes.c_ulonglong()
+    assert lib.stdmlc_session_info(None, 0, ctypes.byref(v)) == 2
+    assert b"session handle" in lib.stdmlc_last_error()
+    assert lib.stdmlc_session_barrier(None) == 2
+    buf = ctypes.create_string_buffer(64)
+    assert lib.stdmlc_peer_self(None, buf, 64) == 2 and b"peer handle" in lib.stdmlc_last_error()
+    assert lib.stdmlc_dw_info(None, 0, ctypes.byref(v)) == 2
+    assert lib.stdmlc_dw_destroy(None) == 0 and lib.stdmlc_peer_destroy(None) == 0
 
 
 class _FakeStream:
