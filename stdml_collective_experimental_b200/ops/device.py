@@ -262,15 +262,16 @@ class DeviceSession:
 
         `wire_dtype` (bf16/f16) sends f32 tensors as 16-bit floats (cast fused into
         the pack/unpack phases).  Loopback: `tensors[rank][i]`."""
-        # The same list object is usually passed every step (a model's gradients):
-        # its prepared pointer tables are kept, keyed by the list's identity and
-        # guarded by a few data pointers, so a step costs one native call.
+        # The same tensors are usually passed every step (a model's gradients):
+        # the prepared pointer table is kept, keyed by every data pointer and
+        # element count of the call, so a step costs one pass over the list and
+        # one native call instead of the checks and conversions below.
         cache = getattr(self, "_group_cache", None)
         if cache is None:
             cache = self._group_cache = {}
         if outs is None and self.vranks == 1 and isinstance(tensors, list) and tensors:
-            key = (id(tensors), len(tensors), tensors[0].data_ptr(), tensors[-1].data_ptr(),
-                   tensors[len(tensors) // 2].data_ptr(), wire_dtype)
+            key = (tuple([t.data_ptr() for t in tensors]), tuple([t.numel() for t in tensors]),
+                   tensors[0].dtype, wire_dtype)
             hit = cache.get(key)
             if hit is not None:
                 n, arr, counts, wire, user, nbytes = hit
