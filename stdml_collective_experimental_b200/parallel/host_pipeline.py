@@ -39,6 +39,13 @@ class HostAllReduce:
     def run(self, host_in, host_out, op="sum", scale=None):
         """host_out = scale * all_reduce(host_in); both pinned, flat, `numel` long.
         Returns when host_out is complete."""
+        for name, t in (("host_in", host_in), ("host_out", host_out)):
+            if t.is_cuda or t.dtype != self.dtype or t.numel() != self.numel or not t.is_contiguous():
+                raise ValueError(f"HostAllReduce.run: {name} must be a contiguous host tensor of "
+                                 f"{self.numel} x {self.dtype}")
+            if not t.is_pinned():
+                raise ValueError(f"HostAllReduce.run: {name} must be pinned (a pageable buffer "
+                                 "makes every copy synchronous and ends the overlap)")
         cur = torch.cuda.current_stream(self.sess.device)
         for s in (self.h2d, self.comm, self.d2h):
             s.wait_stream(cur)
