@@ -33,6 +33,28 @@ def test_gradient_sets_match_the_named_models(tmp_path):
     assert [int(x) for x in open(path).read().split()] == r
     model = ResNet50()
     assert sorted(p.numel() for p in model.parameters()) == sorted(r)
+    # the other benchmark models carry exactly their gradient sets too
+    from stdml_collective_experimental_b200.models.bert import Bert, bert_base, bert_large
+    from stdml_collective_experimental_b200.models.vgg import VGG16
+    with torch.device("meta"):
+        assert sorted(p.numel() for p in VGG16().parameters()) == sorted(v)
+        assert sorted(p.numel() for p in bert_base().parameters()) == sorted(b)
+        assert sorted(p.numel() for p in bert_large().parameters()) == \
+            sorted(gradsets.gradset_sizes("bert-large"))
+    # a small BERT runs, every parameter gets a gradient, padding does not leak
+    torch.manual_seed(0)
+    tiny = Bert(2, 64, 4, 128, vocab=100, max_pos=32, dropout=0.0)
+    ids = torch.randint(0, 100, (3, 16))
+    mask = torch.ones(3, 16)
+    mask[:, 10:] = 0
+    seq, pooled = tiny(ids, mask=mask)
+    (seq.sum() + pooled.sum()).backward()
+    assert seq.shape == (3, 16, 64) and pooled.shape == (3, 64)
+    assert all(p.grad is not None for p in tiny.parameters())
+    other = ids.clone()
+    other[:, 10:] = 7
+    assert torch.allclose(tiny(other, mask=mask)[0][:, :10], seq[:, :10], atol=1e-5)
+    assert VGG16(num_classes=10)(torch.randn(1, 3, 32, 32)).shape == (1, 10)
 
 
 def test_trace_lines_round_trip_through_the_native_runtime(tmp_path):
