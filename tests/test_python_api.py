@@ -57,6 +57,18 @@ def test_python_elastic_state_recovers_from_a_crash(native_lib):
     assert res.stdout.count("weight 36.0 OK") == 2 and res.stdout.count("lost 1 member(s)") == 2
 
 
+@pytest.mark.parametrize("strategy,port", [("STAR", 29871), ("RING", 29873)])
+def test_torch_distributed_backend_and_ddp(strategy, port, native_lib):
+    n = 3
+    env = dict(os.environ, KUNGFU_ALLREDUCE_STRATEGY=strategy)
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "pg_worker.py"), str(r), str(n),
+                               str(port)], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(n)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
+
+
 def test_distributed_optimizer_matches_single_process_training(native_lib):
     n, base = 3, 12200
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_train_worker.py"), str(r),
