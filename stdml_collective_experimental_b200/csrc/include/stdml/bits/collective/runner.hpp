@@ -27,6 +27,10 @@ namespace stdml::collective
 struct runner_options {
     size_t np = 1;
     peer_id self{(127u << 24) | 1u, 38080};  // this runner
+    // -H ip:slots,ip:slots: the hosts of the job in rank order.  One runner per
+    // host (same command line, its own -self ip) starts that host's workers; the
+    // first np slots are used.  Empty: everything on `self`.
+    std::vector<std::pair<uint32_t, size_t>> hosts;
     uint16_t worker_base_port = 10000;
     strategy strat = star;
     bool watch = false;              // elastic: keep serving updates

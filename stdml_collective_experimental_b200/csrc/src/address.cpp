@@ -81,7 +81,11 @@ cluster_config cluster_config::resize(size_t new_size) const
     }
     if (runners.empty()) { return next; }
     std::map<uint32_t, std::set<uint16_t>> ports;  // host -> worker ports in use
-    for (const auto &w : workers) { ports[w.ipv4].insert(w.port); }
+    uint16_t base = workers.empty() ? 10000 : workers.front().port;
+    for (const auto &w : workers) {
+        ports[w.ipv4].insert(w.port);
+        base = std::min(base, w.port);
+    }
     while (next.workers.size() < new_size) {
         // least loaded runner host; the first such runner wins ties
         const peer_id *host = &runners.front();
@@ -89,7 +93,8 @@ cluster_config cluster_config::resize(size_t new_size) const
             if (ports[r.ipv4].size() < ports[host->ipv4].size()) { host = &r; }
         }
         auto &used = ports[host->ipv4];
-        uint16_t port = used.empty() ? 10000 : static_cast<uint16_t>(*used.begin() + 1);
+        // a host without workers starts at the lowest port of the job (its port range)
+        uint16_t port = used.empty() ? base : static_cast<uint16_t>(*used.begin() + 1);
         while (used.count(port) != 0) { ++port; }
         used.insert(port);
         next.workers.push_back(peer_id{host->ipv4, port});

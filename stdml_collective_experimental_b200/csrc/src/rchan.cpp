@@ -588,6 +588,12 @@ class server_impl final : public server
         setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
         sockaddr_in a = to_sockaddr(self_);
         a.sin_addr.s_addr = htonl(INADDR_ANY);
+        // a loopback alias (127.0.0.x, x > 1) stands for a host of its own when
+        // several hosts are emulated on one machine: bind the alias itself so
+        // that the same port can be used by each of them
+        if ((self_.ipv4 >> 24) == 127u && self_.ipv4 != ((127u << 24) | 1u)) {
+            a.sin_addr.s_addr = htonl(self_.ipv4);
+        }
         // a predecessor on the same port (a rank that was removed and is being
         // replaced, a previous job) may still be closing: give it a moment
         int rc = -1;

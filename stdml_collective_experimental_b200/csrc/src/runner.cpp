@@ -57,11 +57,32 @@ class control_conn_handler final : public rchan::conn_handler
 
 runner::runner(runner_options opt) : opt_(std::move(opt))
 {
-    peer_list workers;
-    for (size_t i = 0; i < opt_.np; ++i) {
-        workers.push_back(peer_id{opt_.self.ipv4, static_cast<uint16_t>(opt_.worker_base_port + i)});
+    peer_list workers, runners;
+    if (opt_.hosts.empty()) {
+        for (size_t i = 0; i < opt_.np; ++i) {
+            workers.push_back(
+                peer_id{opt_.self.ipv4, static_cast<uint16_t>(opt_.worker_base_port + i)});
+        }
+        runners.push_back(opt_.self);
+    } else {
+        bool mine = false;
+        size_t slots = 0;
+        for (const auto &[ip, n] : opt_.hosts) {
+            runners.push_back(peer_id{ip, opt_.self.port});
+            for (size_t j = 0; j < n && workers.size() < opt_.np; ++j) {
+                workers.push_back(peer_id{ip, static_cast<uint16_t>(opt_.worker_base_port + j)});
+            }
+            mine = mine || ip == opt_.self.ipv4;
+            slots += n;
+        }
+        if (slots < opt_.np) { throw std::invalid_argument("runner: -H offers fewer slots than -np"); }
+        if (!mine) { throw std::invalid_argument("runner: -self is not one of the hosts of -H"); }
+        if (opt_.config_port == 0) {
+            throw std::invalid_argument(
+                "runner: with several hosts the config server needs a fixed -builtin-config-port");
+        }
     }
-    cluster_ = cluster_config(peer_list{opt_.self}, workers);
+    cluster_ = cluster_config(runners, workers);
     stored_config_ = cluster_.json();
 }
 
@@ -75,6 +96,11 @@ std::string runner::config_url() const
 {
     if (!opt_.config_server_url.empty()) { return opt_.config_server_url; }
     if (http_) { return "http://127.0.0.1:" + std::to_string(http_->port()) + "/config"; }
+    if (!opt_.hosts.empty() && opt_.config_port > 0) {
+        // served by the first host's runner
+        return "http://" + peer_id{opt_.hosts[0].first, 0}.hostname() + ":" +
+               std::to_string(opt_.config_port) + "/config";
+    }
     return "";
 }
 
@@ -180,7 +206,8 @@ void runner::on_update(size_t version, const cluster_config &next)
 int runner::run()
 {
     if (opt_.command.empty()) { throw std::invalid_argument("runner: no program given"); }
-    if (opt_.config_port >= 0) {
+    const bool first_host = opt_.hosts.empty() || opt_.hosts[0].first == opt_.self.ipv4;
+    if (opt_.config_port >= 0 && first_host) {
         http_ = std::make_unique<http_server>(
             static_cast<uint16_t>(opt_.config_port), [this](const http_server::request &rq) {
                 http_response rs;
@@ -206,15 +233,41 @@ int runner::run()
     }
     {
         std::lock_guard<std::mutex> lk(mu_);
-        for (const auto &w : cluster_.workers) { spawn(w, cluster_, 0); }
+        for (const auto &w : cluster_.workers) {
+            if (w.ipv4 == opt_.self.ipv4) { spawn(w, cluster_, 0); }  // other hosts' runners start theirs
+        }
     }
+    // A runner of a several-host elastic job may have no worker of its own for a
+    // while (its host was shrunk away) and must still be there when the job
+    // grows back: it stays for as long as some worker of the current
+    // configuration, on any host, answers a ping.
+    const bool lingers = opt_.watch && !opt_.hosts.empty();
+    int silent_checks = 0;
     for (;;) {
         reap(false);
+        bool idle;
+        peer_list workers;
         {
             std::lock_guard<std::mutex> lk(mu_);
-            if (pids_.empty()) { break; }
+            idle = pids_.empty();
+            workers = cluster_.workers;
         }
-        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        if (!idle) {
+            silent_checks = 0;
+            std::this_thread::sleep_for(std::chrono::milliseconds(20));
+            continue;
+        }
+        if (!lingers) { break; }
+        bool alive = false;
+        for (const auto &w : workers) {
+            if (rchan::ping(w, opt_.self, 300) >= 0) {
+                alive = true;
+                break;
+            }
+        }
+        silent_checks = alive ? 0 : silent_checks + 1;
+        if (silent_checks >= 3) { break; }
+        std::this_thread::sleep_for(std::chrono::milliseconds(500));
     }
     if (server_) { server_->stop(); }
     if (http_) { http_->stop(); }
@@ -237,8 +290,34 @@ bool parse_runner_args(int argc, char *argv[], runner_options &o, std::string &e
             const char *v = need("-np");
             if (!v) { return false; }
             o.np = static_cast<size_t>(std::atoi(v));
-        } else if (a == "-H") {  // accepted for kungfu-run compatibility: ip:slots
-            if (!need("-H")) { return false; }
+        } else if (a == "-H") {  // ip:slots,ip:slots (kungfu-run's host list)
+            const char *v = need("-H");
+            if (!v) { return false; }
+            std::string list = v;
+            size_t at = 0;
+            while (at <= list.size()) {
+                const size_t comma = std::min(list.find(',', at), list.size());
+                const std::string item = list.substr(at, comma - at);
+                at = comma + 1;
+                if (item.empty()) { continue; }
+                const size_t colon = item.find(':');
+                const auto ip = parse_peer_id(item.substr(0, colon) + ":1");
+                const int slots = colon == std::string::npos ? 1 : std::atoi(item.c_str() + colon + 1);
+                if (!ip || slots <= 0) {
+                    error = "-H wants ip:slots[,ip:slots...]";
+                    return false;
+                }
+                o.hosts.emplace_back(ip->ipv4, static_cast<size_t>(slots));
+            }
+        } else if (a == "-self") {
+            const char *v = need("-self");
+            if (!v) { return false; }
+            const auto ip = parse_peer_id(std::string(v) + ":1");
+            if (!ip) {
+                error = "-self wants an IPv4 address";
+                return false;
+            }
+            o.self.ipv4 = ip->ipv4;
         } else if (a == "-strategy") {
             const char *v = need("-strategy");
             if (!v) { return false; }
@@ -288,6 +367,7 @@ bool parse_runner_args(int argc, char *argv[], runner_options &o, std::string &e
         }
     }
     for (; i < argc; ++i) { o.command.push_back(argv[i]); }
+    if (o.hosts.size() == 1 && o.hosts[0].first == o.self.ipv4) { o.hosts.clear(); }
     if (o.np == 0) {
         error = "-np must be positive";
         return false;

@@ -110,6 +110,26 @@ def test_elastic_resize_schedule_with_state_broadcast():
         assert f"[runner] version {v}" in out
 
 
+def test_elastic_job_over_two_emulated_hosts():
+    # two "hosts" (loopback aliases), one runner each, same command line except -self:
+    # 4 -> 2 workers empties the second host (its runner stays), 3 and 4 grow back onto it
+    common = ["-H", "127.0.0.2:2,127.0.0.3:2", "-np", "4", "-w", "-builtin-config-port", "38393",
+              "-port-range", "10820", "-runner-port", "38392"]
+    prog = [os.path.join(BIN, "example_elastic"), "--max-step=12", "3:2", "6:3", "9:4"]
+    e = dict(os.environ)
+    for k in ("KUNGFU_SELF_SPEC", "OMPI_COMM_WORLD_SIZE", "RANK", "WORLD_SIZE"):
+        e.pop(k, None)
+    procs = [subprocess.Popen([os.path.join(BIN, "stdml_collective_run"), *common, "-self", ip,
+                               *prog], env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True) for ip in ("127.0.0.2", "127.0.0.3")]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert outs[0].count("weight 78.0 (want 78.0) OK") == 2, outs[0]
+    assert outs[1].count("weight 78.0 (want 78.0) OK") == 2, outs[1]
+    assert outs[1].count("detached after step 3") == 2
+    assert "[runner] started worker 127.0.0.3:10820" in outs[1]  # grown back, same port range
+
+
 def test_elastic_state_follows_config_server():
     out = run("stdml_collective_run", "-q", "-np", 2, "-w", "-builtin-config-port", 0,
               os.path.join(BIN, "example_elastic_state"), "--max-step=9", "2:4", "5:3",
