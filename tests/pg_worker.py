@@ -85,6 +85,15 @@ def main():
     assert [int(o.item()) for o in a2a_out] == [r * 10 + rank for r in range(n)]
     dist.barrier()
 
+    # a sub-group is a process group of its own (its members build their own session)
+    if n >= 3:
+        sub = dist.new_group([0, n - 1])
+        if rank in (0, n - 1):
+            v = torch.tensor([float(rank + 1)])
+            dist.all_reduce(v, group=sub)
+            assert v.item() == 1 + n
+        dist.barrier()
+
     # DistributedDataParallel over the backend == one process on the joint batch
     model = make_model()
     ddp = torch.nn.parallel.DistributedDataParallel(model)
