@@ -39,6 +39,16 @@ typedef enum mpi_op_t MPI_Op;
 
 #define MPI_SUCCESS 0
 #define MPI_ERR_OTHER 15
+/* sendbuf of MPI_Allreduce / MPI_Reduce: the operand is already in recvbuf */
+#define MPI_IN_PLACE ((void *)1)
+#define MPI_MAX_PROCESSOR_NAME 64
+
+typedef struct mpi_status_t {
+    int MPI_SOURCE;
+    int MPI_TAG;
+    int MPI_ERROR;
+} MPI_Status;
+#define MPI_STATUS_IGNORE ((MPI_Status *)0)
 
 extern int MPI_Init(int *argc, char ***argv);
 extern int MPI_Finalize(void);
@@ -55,6 +65,19 @@ extern int MPI_Allgather(const void *sendbuf, int sendcount, MPI_Datatype sendty
                          int recvcount, MPI_Datatype recvtype, MPI_Comm comm);
 extern int MPI_Reduce(const void *sendbuf, void *recvbuf, int count, MPI_Datatype datatype,
                       MPI_Op op, int root, MPI_Comm comm);
+/* recvbuf matters on root only; root must be 0 for MPI_Reduce and MPI_Gather */
+extern int MPI_Gather(const void *sendbuf, int sendcount, MPI_Datatype sendtype, void *recvbuf,
+                      int recvcount, MPI_Datatype recvtype, int root, MPI_Comm comm);
+/* a message is matched by (source, tag); a send does not wait for its receive */
+extern int MPI_Send(const void *buf, int count, MPI_Datatype datatype, int dest, int tag,
+                    MPI_Comm comm);
+extern int MPI_Recv(void *buf, int count, MPI_Datatype datatype, int source, int tag,
+                    MPI_Comm comm, MPI_Status *status);
+extern int MPI_Initialized(int *flag);
+extern int MPI_Finalized(int *flag);
+extern int MPI_Abort(MPI_Comm comm, int errorcode);
+extern int MPI_Get_processor_name(char *name, int *resultlen);
+extern double MPI_Wtime(void);
 #ifdef __cplusplus
 }
 #endif

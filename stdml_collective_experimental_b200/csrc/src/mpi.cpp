@@ -1,4 +1,10 @@
+#include <chrono>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+#include <unistd.h>
 #include <exception>
 #include <memory>
 
@@ -11,6 +17,7 @@ namespace
 {
 std::unique_ptr<sc::peer> g_peer;
 std::unique_ptr<sc::session> g_sess;
+bool g_finalized = false;
 
 bool to_dtype(MPI_Datatype t, sc::dtype &out)
 {
@@ -100,7 +107,40 @@ int MPI_Finalize(void)
 {
     g_sess.reset();
     g_peer.reset();
+    g_finalized = true;
     return MPI_SUCCESS;
+}
+
+int MPI_Initialized(int *flag)
+{
+    *flag = (g_sess || g_finalized) ? 1 : 0;
+    return MPI_SUCCESS;
+}
+
+int MPI_Finalized(int *flag)
+{
+    *flag = g_finalized ? 1 : 0;
+    return MPI_SUCCESS;
+}
+
+int MPI_Abort(MPI_Comm, int errorcode)
+{
+    // the other ranks learn from the closed connections (peer_failure)
+    std::fflush(nullptr);
+    std::_Exit(errorcode);
+}
+
+int MPI_Get_processor_name(char *name, int *resultlen)
+{
+    if (::gethostname(name, MPI_MAX_PROCESSOR_NAME) != 0) { std::snprintf(name, MPI_MAX_PROCESSOR_NAME, "localhost"); }
+    name[MPI_MAX_PROCESSOR_NAME - 1] = 0;
+    *resultlen = static_cast<int>(std::strlen(name));
+    return MPI_SUCCESS;
+}
+
+double MPI_Wtime(void)
+{
+    return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
 int MPI_Comm_rank(MPI_Comm, int *p)
@@ -123,6 +163,7 @@ int MPI_Allreduce(const void *sendbuf, void *recvbuf, int count, MPI_Datatype da
     sc::dtype dt;
     sc::reduce_op rop;
     if (count < 0 || !to_dtype(datatype, dt) || !to_op(op, rop)) { return MPI_ERR_OTHER; }
+    if (sendbuf == MPI_IN_PLACE) { sendbuf = recvbuf; }
     return guarded([&] { g_sess->all_reduce(sendbuf, recvbuf, static_cast<size_t>(count), dt, rop); });
 }
 
@@ -134,8 +175,11 @@ int MPI_Barrier(MPI_Comm)
 int MPI_Bcast(void *buffer, int count, MPI_Datatype datatype, int root, MPI_Comm)
 {
     sc::dtype dt;
-    if (count < 0 || !to_dtype(datatype, dt) || root != 0) { return MPI_ERR_OTHER; }
-    return guarded([&] { g_sess->broadcast(buffer, buffer, static_cast<size_t>(count), dt); });
+    if (count < 0 || !to_dtype(datatype, dt) || root < 0) { return MPI_ERR_OTHER; }
+    return guarded([&] {
+        g_sess->broadcast(buffer, buffer, static_cast<size_t>(count), dt, "", nullptr,
+                          static_cast<size_t>(root));
+    });
 }
 
 int MPI_Allgather(const void *sendbuf, int sendcount, MPI_Datatype sendtype, void *recvbuf,
@@ -157,6 +201,45 @@ int MPI_Reduce(const void *sendbuf, void *recvbuf, int count, MPI_Datatype datat
     if (count < 0 || !to_dtype(datatype, dt) || !to_op(op, rop) || root != 0) {
         return MPI_ERR_OTHER;
     }
+    if (sendbuf == MPI_IN_PLACE) { sendbuf = recvbuf; }
     return guarded([&] { g_sess->reduce(sendbuf, recvbuf, static_cast<size_t>(count), dt, rop); });
+}
+
+int MPI_Gather(const void *sendbuf, int sendcount, MPI_Datatype sendtype, void *recvbuf,
+               int recvcount, MPI_Datatype recvtype, int root, MPI_Comm)
+{
+    sc::dtype dt;
+    if (sendcount < 0 || root != 0 || !to_dtype(sendtype, dt)) { return MPI_ERR_OTHER; }
+    if (g_sess && g_sess->rank() == 0 && (sendcount != recvcount || sendtype != recvtype)) {
+        return MPI_ERR_OTHER;
+    }
+    return guarded([&] { g_sess->gather(sendbuf, recvbuf, static_cast<size_t>(sendcount), dt); });
+}
+
+int MPI_Send(const void *buf, int count, MPI_Datatype datatype, int dest, int tag, MPI_Comm)
+{
+    sc::dtype dt;
+    if (count < 0 || dest < 0 || !to_dtype(datatype, dt)) { return MPI_ERR_OTHER; }
+    return guarded([&] {
+        g_sess->send(buf, static_cast<size_t>(count), dt, static_cast<size_t>(dest),
+                     "mpi/tag/" + std::to_string(tag));
+    });
+}
+
+int MPI_Recv(void *buf, int count, MPI_Datatype datatype, int source, int tag, MPI_Comm,
+             MPI_Status *status)
+{
+    sc::dtype dt;
+    if (count < 0 || source < 0 || !to_dtype(datatype, dt)) { return MPI_ERR_OTHER; }
+    const int rc = guarded([&] {
+        g_sess->recv(buf, static_cast<size_t>(count), dt, static_cast<size_t>(source),
+                     "mpi/tag/" + std::to_string(tag));
+    });
+    if (status != MPI_STATUS_IGNORE) {
+        status->MPI_SOURCE = source;
+        status->MPI_TAG = tag;
+        status->MPI_ERROR = rc;
+    }
+    return rc;
 }
 }
