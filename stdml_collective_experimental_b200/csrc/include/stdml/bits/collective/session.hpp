@@ -135,11 +135,13 @@ class session
     std::unique_ptr<task> async_all_reduce(const void *input, void *output, size_t count,
                                            dtype dt, reduce_op op, std::string name = "",
                                            void *stream = nullptr);
+    // only `root` receives the result (output may be null elsewhere)
     void reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
-                std::string name = "", void *stream = nullptr);
+                std::string name = "", void *stream = nullptr, size_t root = 0);
     void all_gather(const void *input, void *output, size_t count, dtype dt,
                     std::string name = "", void *stream = nullptr);
-    void gather(const void *input, void *output, size_t count, dtype dt, std::string name = "");
+    void gather(const void *input, void *output, size_t count, dtype dt, std::string name = "",
+                size_t root = 0);
     // From rank `root` (the reference fixes root 0: session.cpp:49-62 there).
     // Root 0 follows the session's broadcast graph; any other root sends to
     // every member directly.

@@ -65,7 +65,7 @@ extern int MPI_Allgather(const void *sendbuf, int sendcount, MPI_Datatype sendty
                          int recvcount, MPI_Datatype recvtype, MPI_Comm comm);
 extern int MPI_Reduce(const void *sendbuf, void *recvbuf, int count, MPI_Datatype datatype,
                       MPI_Op op, int root, MPI_Comm comm);
-/* recvbuf matters on root only; root must be 0 for MPI_Reduce and MPI_Gather */
+/* recvbuf matters on root only */
 extern int MPI_Gather(const void *sendbuf, int sendcount, MPI_Datatype sendtype, void *recvbuf,
                       int recvcount, MPI_Datatype recvtype, int root, MPI_Comm comm);
 /* a message is matched by (source, tag); a send does not wait for its receive */

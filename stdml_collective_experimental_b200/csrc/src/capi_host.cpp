@@ -235,6 +235,26 @@ int stdmlc_session_all_gather(void *s, const void *in, void *out, unsigned long 
     });
 }
 
+int stdmlc_session_reduce_to(void *s, const void *in, void *out, unsigned long long count, int dt,
+                             int op, int root, const char *name, void *stream)
+{
+    return host_guarded([&] {
+        if (root < 0) { throw std::invalid_argument("reduce: negative root"); }
+        SS(s).reduce(in, out, count, static_cast<sc::dtype>(dt), static_cast<sc::reduce_op>(op),
+                     name ? name : "", stream, static_cast<size_t>(root));
+    });
+}
+
+int stdmlc_session_gather_to(void *s, const void *in, void *out, unsigned long long count, int dt,
+                             int root, const char *name)
+{
+    return host_guarded([&] {
+        if (root < 0) { throw std::invalid_argument("gather: negative root"); }
+        SS(s).gather(in, out, count, static_cast<sc::dtype>(dt), name ? name : "",
+                     static_cast<size_t>(root));
+    });
+}
+
 int stdmlc_session_gather(void *s, const void *in, void *out, unsigned long long count, int dt,
                           const char *name)
 {

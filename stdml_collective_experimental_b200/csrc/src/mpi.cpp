@@ -198,22 +198,29 @@ int MPI_Reduce(const void *sendbuf, void *recvbuf, int count, MPI_Datatype datat
 {
     sc::dtype dt;
     sc::reduce_op rop;
-    if (count < 0 || !to_dtype(datatype, dt) || !to_op(op, rop) || root != 0) {
+    if (count < 0 || !to_dtype(datatype, dt) || !to_op(op, rop) || root < 0) {
         return MPI_ERR_OTHER;
     }
     if (sendbuf == MPI_IN_PLACE) { sendbuf = recvbuf; }
-    return guarded([&] { g_sess->reduce(sendbuf, recvbuf, static_cast<size_t>(count), dt, rop); });
+    return guarded([&] {
+        g_sess->reduce(sendbuf, recvbuf, static_cast<size_t>(count), dt, rop, "", nullptr,
+                       static_cast<size_t>(root));
+    });
 }
 
 int MPI_Gather(const void *sendbuf, int sendcount, MPI_Datatype sendtype, void *recvbuf,
                int recvcount, MPI_Datatype recvtype, int root, MPI_Comm)
 {
     sc::dtype dt;
-    if (sendcount < 0 || root != 0 || !to_dtype(sendtype, dt)) { return MPI_ERR_OTHER; }
-    if (g_sess && g_sess->rank() == 0 && (sendcount != recvcount || sendtype != recvtype)) {
+    if (sendcount < 0 || root < 0 || !to_dtype(sendtype, dt)) { return MPI_ERR_OTHER; }
+    if (g_sess && g_sess->rank() == static_cast<size_t>(root) &&
+        (sendcount != recvcount || sendtype != recvtype)) {
         return MPI_ERR_OTHER;
     }
-    return guarded([&] { g_sess->gather(sendbuf, recvbuf, static_cast<size_t>(sendcount), dt); });
+    return guarded([&] {
+        g_sess->gather(sendbuf, recvbuf, static_cast<size_t>(sendcount), dt, "",
+                       static_cast<size_t>(root));
+    });
 }
 
 int MPI_Send(const void *buf, int count, MPI_Datatype datatype, int dest, int tag, MPI_Comm)

@@ -600,30 +600,47 @@ void session::group_all_reduce(std::vector<std::future<workspace>> fs)
 }
 
 void session::reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
-                     std::string name, void *stream)
+                     std::string name, void *stream, size_t root)
 {
     if (count == 0) { return; }
     if (!reduce_supported(dt, op)) { throw std::invalid_argument("reduce: undefined dtype/op"); }
+    if (root >= peers_.size()) { throw std::out_of_range("reduce: no such root"); }
     ensure_usable("reduce");
     if (on_device(input, output != nullptr ? output : input)) {
         const void *in[1] = {input};
         void *out[1] = {output};
-        device()->reduce(in, out, count, dt, op, 0, 1.0, stream);
+        device()->reduce(in, out, count, dt, op, static_cast<int>(root), 1.0, stream);
         return;
     }
-    // root 0 gathers the operands in rank order and folds them left to right
+    // the root gathers the operands and folds them in rank order, left to right
     const size_t bytes = count * dtype_size(dt);
     const std::string tag = versioned(*this, "stdml::reduce::" + name);
-    if (rank_ != 0) {
-        client_pool_->require(conn_collective)
-            ->send(peers_[0], tag.c_str(), input, bytes, 0);
+    if (rank_ != root) {
+        client_pool_->require(conn_collective)->send(peers_[root], tag.c_str(), input, bytes, 0);
         return;
     }
-    if (output != input) { std::memcpy(output, input, bytes); }
-    for (size_t r = 1; r < peers_.size(); ++r) {
-        buffer b = take_eager(r, tag, "reduce");
-        if (b.len != bytes) { throw std::runtime_error("reduce: size mismatch"); }
-        stdml::collective::reduce(output, output, b.data.get(), count, dt, op);
+    bool started = false;  // output holds the fold of the ranks before r
+    std::vector<char> mine;
+    if (output == input && root != 0) {
+        // in place on a root that is not first: keep the own operand aside
+        mine.assign(static_cast<const char *>(input), static_cast<const char *>(input) + bytes);
+    }
+    for (size_t r = 0; r < peers_.size(); ++r) {
+        const void *operand;
+        buffer b;
+        if (r == root) {
+            operand = mine.empty() ? input : mine.data();
+        } else {
+            b = take_eager(r, tag, "reduce");
+            if (b.len != bytes) { throw std::runtime_error("reduce: size mismatch"); }
+            operand = b.data.get();
+        }
+        if (!started) {
+            if (output != operand) { std::memcpy(output, operand, bytes); }
+            started = true;
+        } else {
+            stdml::collective::reduce(output, output, operand, count, dt, op);
+        }
     }
 }
 
@@ -674,21 +691,23 @@ void session::all_gather(const void *input, void *output, size_t count, dtype dt
     if (first) { std::rethrow_exception(first); }
 }
 
-void session::gather(const void *input, void *output, size_t count, dtype dt, std::string name)
+void session::gather(const void *input, void *output, size_t count, dtype dt, std::string name,
+                     size_t root)
 {
     if (count == 0) { return; }
-    const size_t bytes = count * dtype_size(dt);
+    if (root >= peers_.size()) { throw std::out_of_range("gather: no such root"); }
     ensure_usable("gather");
+    const size_t bytes = count * dtype_size(dt);
     const std::string tag = versioned(*this, "stdml::gather::" + name);
-    if (rank_ != 0) {
+    if (rank_ != root) {
         client_pool_->require(conn_collective)
-            ->send(peers_[0], tag.c_str(), input, bytes, message_header::wait_recv_buf);
+            ->send(peers_[root], tag.c_str(), input, bytes, message_header::wait_recv_buf);
         return;
     }
     char *out = static_cast<char *>(output);
-    std::memmove(out, input, bytes);
-    for (size_t r = 1; r < peers_.size(); ++r) {
-        take_into(r, tag, out + r * bytes, bytes, "gather");
+    std::memmove(out + root * bytes, input, bytes);
+    for (size_t r = 0; r < peers_.size(); ++r) {
+        if (r != root) { take_into(r, tag, out + r * bytes, bytes, "gather"); }
     }
 }
 

@@ -174,6 +174,17 @@ static void check_others(session &sess)
         std::vector<int> br = x;
         sess.broadcast(br.data(), br.data(), count, i32, "bcr" + std::to_string(count), nullptr, root);
         for (size_t i = 0; i < count; ++i) { CHECK(br[i] == int(root * 1000 + i)); }
+        // reduce and gather to the last rank, reduce in place
+        std::vector<int> rr = x;
+        sess.reduce(rr.data(), rr.data(), count, i32, sum, "rdr" + std::to_string(count), nullptr, root);
+        if (r == root) {
+            for (size_t i = 0; i < count; ++i) { CHECK(rr[i] == int(1000 * n * (n - 1) / 2 + n * i)); }
+        } else {
+            CHECK(rr == x);
+        }
+        std::vector<int> gr(count * n, -1);
+        sess.gather(x.data(), gr.data(), count, i32, "gr" + std::to_string(count), root);
+        if (r == root) { CHECK(gr == y); }
         std::vector<int> red(count, -7);
         sess.reduce(x.data(), red.data(), count, i32, sum, "rd" + std::to_string(count));
         if (r == 0) {

@@ -45,6 +45,9 @@ def _lib():
         lib.stdmlc_session_broadcast.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p, vp]
         lib.stdmlc_session_broadcast_from.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p,
                                                       vp]
+        lib.stdmlc_session_reduce_to.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_int,
+                                                 c.c_char_p, vp]
+        lib.stdmlc_session_gather_to.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_send.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_recv.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_barrier.argtypes = [vp]
@@ -183,13 +186,13 @@ class Session:
             name.encode(), _stream_of(t), ctypes.byref(h)))
         return Task(h, (t, o))
 
-    def reduce(self, tensor, out=None, op="sum", name=""):
-        """Result on rank 0 only (the reference's fixed root)."""
+    def reduce(self, tensor, out=None, op="sum", name="", root=0):
+        """Result on rank `root` only; `out` of the other ranks is left alone."""
         t = _checked(tensor, "reduce")
         o = t if out is None else _checked(out, "reduce")
-        _native.check(self._lib.stdmlc_session_reduce(
+        _native.check(self._lib.stdmlc_session_reduce_to(
             self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), op_code(op),
-            name.encode(), _stream_of(t)))
+            int(root), name.encode(), _stream_of(t)))
         return o
 
     def group_all_reduce(self, tensors, outs=None, op="sum", scale=None, names=None):
@@ -220,10 +223,12 @@ class Session:
             _stream_of(t)))
         return o
 
-    def gather(self, tensor, out, name=""):
+    def gather(self, tensor, out, name="", root=0):
+        """Rank-major blocks on rank `root` (host tensors); `out` matters there only."""
         t, o = _checked(tensor, "gather"), _checked(out, "gather")
-        _native.check(self._lib.stdmlc_session_gather(
-            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), name.encode()))
+        _native.check(self._lib.stdmlc_session_gather_to(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), int(root),
+            name.encode()))
         return o
 
     def broadcast(self, tensor, out=None, name="", root=0):

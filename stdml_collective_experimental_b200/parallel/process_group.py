@@ -153,10 +153,11 @@ class StdmlProcessGroup(dist.ProcessGroup):
         op, average = _op_of(opts)
         root = getattr(opts, "rootRank", 0)
         for t in tensors:
-            tmp = self._dense(t).clone()
-            self.sess.all_reduce(tmp, op=op, name=self._name("rd"))
+            src = self._dense(t)
+            out = torch.empty_like(src) if self._rank == root else src  # others keep their tensor
+            self.sess.reduce(src, out=out, op=op, root=root, name=self._name("rd"))
             if self._rank == root:
-                t.copy_(tmp.div_(self._size) if average else tmp)
+                t.copy_(out.div_(self._size) if average else out)
         return _DoneWork(tensors)
 
     def _allgather_base(self, output, input, opts=None):

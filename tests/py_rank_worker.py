@@ -41,6 +41,14 @@ def main():
     ro = torch.full((4,), -1.0)
     sess.reduce(r, out=ro)
     assert torch.all(ro == (n * (n - 1) / 2 if rank == 0 else -1))
+    # any root: reduce and gather to the last rank
+    rl = torch.full((4,), -1.0)
+    sess.reduce(r, out=rl, root=n - 1, name="to-last")
+    assert torch.all(rl == (n * (n - 1) / 2 if rank == n - 1 else -1))
+    gl = torch.full((n * 2,), -1.0)
+    sess.gather(torch.full((2,), float(rank)), gl, root=n - 1, name="g-last")
+    if rank == n - 1:
+        assert gl.tolist() == [float(q) for q in range(n) for _ in range(2)]
     assert sess.consistent(b) and (n == 1 or not sess.consistent(torch.tensor([rank])))
     if n > 1:
         if rank == 0:
