@@ -17,6 +17,7 @@
 #include <sys/wait.h>
 #include <unistd.h>
 
+#include <stdml/bits/collective/net/tcp.hpp>
 #include <stdml/collective>
 
 using namespace stdml::collective;
@@ -204,6 +205,39 @@ static int member_lost_and_recovered(int np, bool async_runtime)
     return bad;
 }
 
+// Bytes that are not this protocol (a port scanner, an HTTP client, a half-sent
+// header) must neither crash a peer nor disturb its collectives.
+static int stray_connections()
+{
+    int bad = 0;
+    try {
+        prun(2, [&](session &sess) {
+            const peer_id other = sess.peers()[1 - sess.rank()];
+            const auto knock = [&](const std::string &bytes) {
+                TcpClient c(other.port, other.ipv4);
+                int code = 0;
+                c.dial(&code);
+                if (code == 0 && !bytes.empty()) { c.write(bytes.data(), bytes.size()); }
+            };  // closed here
+            knock("");                                   // connects and leaves
+            knock("GET / HTTP/1.1\r\nHost: x\r\n\r\n");  // another protocol altogether
+            knock(std::string("\x02\x00\x10\x27\x01\x00\x00\x7f", 8) +  // a valid handshake ...
+                  std::string("\xff\xff\xff\x7f", 4));                    // ... then an absurd name length
+            knock(std::string("\x02\x00\x10\x27\x01\x00\x00\x7f", 8) +
+                  std::string("\x03\x00\x00\x00" "abc", 7));  // a header that stops half way
+            for (int i = 0; i < 20; ++i) {
+                std::vector<int> x(1000, int(sess.rank()) + i), y(1000);
+                sess.all_reduce(x.data(), y.data(), x.size(), i32, sum, "after-strays");
+                if (y[0] != 2 * i + 1 || y[999] != y[0]) { throw std::runtime_error("wrong sum"); }
+            }
+        });
+    } catch (const std::exception &e) {
+        std::printf("stray connections: FAILED (%s)\n", e.what());
+        bad = 1;
+    }
+    return bad;
+}
+
 // conn_ping: a live peer answers, a dead address does not
 static int ping_peers()
 {
@@ -270,6 +304,7 @@ int main(int argc, char *argv[])
     run("peer dies before connecting", [&] { return peer_dies_before_connecting(); });
     run("member lost and recovered", [&] { return member_lost_and_recovered(np, false); });
     run("member lost and recovered (polled tasks)", [&] { return member_lost_and_recovered(np, true); });
+    run("stray connections", [&] { return stray_connections(); });
     run("ping", [&] { return ping_peers(); });
     std::printf("test-shutdown np=%d: %s\n", np, bad == 0 ? "OK" : "FAILED");
     return bad == 0 ? 0 : 1;
