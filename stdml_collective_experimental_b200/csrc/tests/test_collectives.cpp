@@ -10,6 +10,7 @@
 // than one 1 MiB chunk, send/recv, reduce, gather, consistent, and a
 // 300-tensor group whose futures resolve in a different order on every rank.
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <cmath>
 #include <future>
@@ -202,6 +203,31 @@ static void check_others(session &sess)
     };
     const pod p = sess.broadcast(pod{r + 0.25, int(r) - 3});
     CHECK(p.a == 0.25 && p.b == -3);
+
+    // one session used from several threads at once: operations with distinct
+    // names do not disturb each other, whatever order the threads run in
+    {
+        std::atomic<int> wrong{0};
+        std::vector<std::thread> ths;
+        for (int t = 0; t < 4; ++t) {
+            ths.emplace_back([&, t] {
+                for (int i = 0; i < 10; ++i) {
+                    const size_t count = 1000 * (t + 1) + i;
+                    std::vector<int64_t> x(count, int64_t(r) * (t + 1) + i), y(count, -1);
+                    sess.all_reduce(x.data(), y.data(), count, i64, sum, "mt" + std::to_string(t));
+                    const int64_t want = int64_t(n * (n - 1) / 2) * (t + 1) + int64_t(n) * i;
+                    if (y.front() != want || y.back() != want) { ++wrong; }
+                    std::vector<int> g(3 * n, -1), mine(3, int(r) + 10 * t);
+                    sess.all_gather(mine.data(), g.data(), 3, "mtg" + std::to_string(t));
+                    for (size_t q = 0; q < n; ++q) {
+                        if (g[3 * q] != int(q) + 10 * t) { ++wrong; }
+                    }
+                }
+            });
+        }
+        for (auto &th : ths) { th.join(); }
+        CHECK(wrong.load() == 0);
+    }
 
     // consistent: same bytes everywhere / one rank differs / lengths differ
     int same = 42;
