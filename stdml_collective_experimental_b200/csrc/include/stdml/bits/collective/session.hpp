@@ -50,6 +50,7 @@ class session
     bool device_tried_ = false;
     int spin_polls_ = 0;  // looks at a mailbox before a receiver sleeps (see session.cpp)
 
+    const std::string scope_;  // names the sub-group among its parent's messages ("" = the whole group)
     const system_config config_;
     const size_t version_;
     const size_t rank_;
@@ -91,7 +92,7 @@ class session
 
     session(system_config config, size_t version, size_t rank, peer_list peers, peer_list runners,
             mailbox *mailbox, slotbox *slotbox, rchan::client_pool *client_pool,
-            strategy s = star, liveness *live = nullptr);
+            strategy s = star, liveness *live = nullptr, std::string scope = "");
     ~session();
 
     session(const session &) = delete;
@@ -105,6 +106,14 @@ class session
     runtime *async_rt() const { return async_runtime_.get(); }
     cluster_config cluster() const { return cluster_config(runners_, peers_); }
     size_t version() const { return version_; }
+    const std::string &scope() const { return scope_; }
+    // A session of a subset of the members, in the order given (the counterpart of
+    // a communicator split; the reference has one group only).  Collective among
+    // the listed ranks, which all pass the same list and the same `scope`, a name
+    // that is unique among the sub-groups alive at the same time; other ranks
+    // need not call it and get null.  It shares this session's connections and
+    // must not outlive the peer.
+    std::unique_ptr<session> subgroup(const std::vector<size_t> &ranks, const std::string &scope);
     strategy get_strategy() const { return strategy_; }
     const system_config &config() const { return config_; }
 

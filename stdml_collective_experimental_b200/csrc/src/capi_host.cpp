@@ -152,6 +152,23 @@ int stdmlc_peer_join(void *p, void **sess)
     });
 }
 
+// *out = a session of the listed ranks (null handle if this rank is not listed);
+// it shares the parent's connections and must be destroyed before the peer
+int stdmlc_session_subgroup(void *s, const unsigned long long *ranks, unsigned long long n,
+                            const char *scope, void **out)
+{
+    *out = nullptr;
+    return host_guarded([&] {
+        std::vector<size_t> rs(ranks, ranks + n);
+        auto sub = SS(s).subgroup(rs, scope ? scope : "");
+        if (sub) {
+            auto box = std::make_unique<session_box>();
+            box->s = std::move(sub);
+            *out = box.release();
+        }
+    });
+}
+
 int stdmlc_session_destroy(void *s)
 {
     return host_guarded([&] { delete static_cast<session_box *>(s); });

@@ -56,8 +56,8 @@ int forced_algo(const system_config &c)
 
 session::session(system_config config, size_t version, size_t rank, peer_list peers,
                  peer_list runners, mailbox *mailbox, slotbox *slotbox,
-                 rchan::client_pool *client_pool, strategy s, liveness *live)
-    : config_(std::move(config)), version_(version), rank_(rank), peers_(std::move(peers)),
+                 rchan::client_pool *client_pool, strategy s, liveness *live, std::string scope)
+    : scope_(std::move(scope)), config_(std::move(config)), version_(version), rank_(rank), peers_(std::move(peers)),
       runners_(std::move(runners)), strategy_(s),
       all_reduce_topo_(make_graph_pair_list(s, peers_.size())), mailbox_(mailbox),
       slotbox_(slotbox), client_pool_(client_pool), liveness_(live)
@@ -75,6 +75,26 @@ session::session(system_config config, size_t version, size_t rank, peer_list pe
 session::~session() = default;
 session::session(session &&) noexcept = default;
 
+std::unique_ptr<session> session::subgroup(const std::vector<size_t> &ranks,
+                                           const std::string &scope)
+{
+    if (scope.empty()) { throw std::invalid_argument("subgroup: a scope name is needed"); }
+    peer_list members;
+    size_t me = ranks.size();
+    for (size_t i = 0; i < ranks.size(); ++i) {
+        if (ranks[i] >= peers_.size()) { throw std::out_of_range("subgroup: no such rank"); }
+        for (size_t j = 0; j < i; ++j) {
+            if (ranks[j] == ranks[i]) { throw std::invalid_argument("subgroup: rank listed twice"); }
+        }
+        if (ranks[i] == rank_) { me = i; }
+        members.push_back(peers_[ranks[i]]);
+    }
+    if (me == ranks.size()) { return nullptr; }  // not a member: nothing to take part in
+    const std::string full = scope_.empty() ? scope : scope_ + "/" + scope;
+    return std::make_unique<session>(config_, version_, me, members, runners_, mailbox_, slotbox_,
+                                     client_pool_, strategy_, liveness_, full);
+}
+
 void session::barrier()
 {
     uint32_t one = 1, all = 0;
@@ -86,8 +106,11 @@ namespace
 {
 std::string versioned(const session &s, const std::string &name)
 {
-    // keeps messages of an old membership from matching operations of a new one
-    return s.version() == 0 ? name : name + "@v" + std::to_string(s.version());
+    // keeps messages of an old membership from matching operations of a new one,
+    // and those of a sub-group from matching the whole group's
+    std::string out = s.version() == 0 ? name : name + "@v" + std::to_string(s.version());
+    if (!s.scope().empty()) { out += "#" + s.scope(); }
+    return out;
 }
 }  // namespace
 
@@ -833,7 +856,7 @@ cuda::DeviceSession *session::device()
                 "device collectives need all ranks on one box (one NVLink domain)");
         }
     }
-    o.key = peers_[0].str() + ".v" + std::to_string(version_);
+    o.key = peers_[0].str() + ".v" + std::to_string(version_) + (scope_.empty() ? "" : "#" + scope_);
     if (const auto v = parse_env_int("STDML_COLLECTIVE_HEAP_MB")) {
         o.heap_bytes = static_cast<size_t>(*v) << 20;
     }

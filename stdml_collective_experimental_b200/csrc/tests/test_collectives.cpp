@@ -229,6 +229,37 @@ static void check_others(session &sess)
         CHECK(wrong.load() == 0);
     }
 
+    // sub-groups: evens and odds reduce among themselves while the whole group
+    // goes on working; a sub-group of a sub-group; ranks in a chosen order
+    if (n >= 2) {
+        std::vector<size_t> mine_group;
+        for (size_t q = r % 2; q < n; q += 2) { mine_group.push_back(q); }
+        auto half = sess.subgroup(mine_group, r % 2 == 0 ? "evens" : "odds");
+        REQUIRE(half != nullptr);
+        CHECK(half->size() == mine_group.size() && half->rank() == r / 2);
+        int64_t got = half->all_reduce(int64_t(r), sum);
+        int64_t want = 0;
+        for (size_t q : mine_group) { want += int64_t(q); }
+        CHECK(got == want);
+        CHECK(sess.all_reduce(int64_t(1), sum) == int64_t(n));  // the parent is undisturbed
+        std::vector<int> blocks(half->size(), -1);
+        const int me = int(r);
+        half->all_gather(&me, blocks.data(), 1, "who");
+        for (size_t i = 0; i < mine_group.size(); ++i) { CHECK(blocks[i] == int(mine_group[i])); }
+        if (half->size() >= 2) {
+            auto pair = half->subgroup({1, 0}, "first-two-swapped");
+            if (half->rank() < 2) {
+                REQUIRE(pair != nullptr);
+                CHECK(pair->rank() == 1 - half->rank());
+                CHECK(pair->broadcast(int(r)) == int(mine_group[1]));  // its rank 0 is the half's rank 1
+            } else {
+                CHECK(pair == nullptr);
+            }
+        }
+        CHECK(sess.subgroup({(r + 1) % n}, "not-me") == nullptr || n == 1);
+        sess.barrier();
+    }
+
     // consistent: same bytes everywhere / one rank differs / lengths differ
     int same = 42;
     CHECK(sess.consistent(same));

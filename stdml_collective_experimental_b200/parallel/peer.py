@@ -33,6 +33,7 @@ def _lib():
         lib.stdmlc_peer_ping.argtypes = [vp, c.c_char_p, c.c_int, c.POINTER(c.c_double)]
         lib.stdmlc_peer_join.argtypes = [vp, vpp]
         lib.stdmlc_session_destroy.argtypes = [vp]
+        lib.stdmlc_session_subgroup.argtypes = [vp, c.POINTER(u64), u64, c.c_char_p, vpp]
         lib.stdmlc_session_info.argtypes = [vp, c.c_int, c.POINTER(u64)]
         lib.stdmlc_session_cluster_json.argtypes = [vp, c.c_char_p, u64]
         lib.stdmlc_session_all_reduce.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p, vp]
@@ -153,6 +154,17 @@ class Session:
         buf = ctypes.create_string_buffer(1 << 16)
         _native.check(self._lib.stdmlc_session_cluster_json(self._h, buf, len(buf)))
         return json.loads(buf.value.decode())
+
+    def subgroup(self, ranks, scope):
+        """A Session of the listed ranks, in that order (like a communicator split).
+        Collective among them: all pass the same list and the same `scope`, a name
+        unique among the sub-groups alive at one time.  Ranks that are not listed
+        get None.  Close it before the parent."""
+        arr = (ctypes.c_ulonglong * len(ranks))(*[int(r) for r in ranks])
+        h = ctypes.c_void_p()
+        _native.check(self._lib.stdmlc_session_subgroup(self._h, arr, len(ranks), scope.encode(),
+                                                        ctypes.byref(h)))
+        return Session(h) if h.value else None
 
     def close(self):
         if self._h is not None:

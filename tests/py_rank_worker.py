@@ -55,6 +55,16 @@ def main():
             sess.send(torch.tensor([42.0]), 1, name="p2p")
         elif rank == 1:
             assert sess.recv(torch.zeros(1), 0, name="p2p").item() == 42.0
+    # sub-group: all but the last rank
+    if n > 2:
+        sub = sess.subgroup(list(range(n - 1)), "head")
+        if rank < n - 1:
+            v = torch.tensor([float(rank)])
+            sub.all_reduce(v, name="sub")
+            assert (sub.size, sub.rank) == (n - 1, rank) and v.item() == (n - 1) * (n - 2) / 2
+            sub.close()
+        else:
+            assert sub is None
     # async interface: two operations in flight, polled from this thread
     a, b = torch.full((300_000,), float(rank)), torch.ones(10)
     ta = sess.all_reduce_async(a, name="async:a")
