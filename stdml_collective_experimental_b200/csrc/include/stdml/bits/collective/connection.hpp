@@ -86,10 +86,11 @@ class msg_handler
 class connection
 {
   public:
-    // Connects (retrying until the peer is up or the connect timeout runs out),
-    // performs the handshake.  Throws std::runtime_error on timeout.
+    // Connects (retrying until the peer is up or `patience_ms` runs out; negative:
+    // the connect timeout of the configuration), performs the handshake.  Throws
+    // peer_failure (a std::runtime_error) when the patience runs out.
     static std::unique_ptr<connection> dial(const peer_id remote, const conn_type type,
-                                            const peer_id local);
+                                            const peer_id local, int64_t patience_ms = -1);
     // One attempt with a deadline (always TCP); null if `remote` does not answer.
     // dial() is patient because a peer may still be starting; this is for
     // messages to members that may be dying.

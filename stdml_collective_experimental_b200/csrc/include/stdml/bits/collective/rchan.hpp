@@ -37,6 +37,10 @@ class client
     virtual std::unique_ptr<connection> dial(peer_id target, conn_type type) = 0;
     // drop the connections to these peers
     virtual void reset_peers(const peer_list &ids) = 0;
+    // how long a first connection to a peer is retried (negative: the configured
+    // connect timeout).  Long while members may still be starting, short once
+    // all of them have been seen alive: then a refused connection means a dead peer.
+    virtual void set_dial_patience_ms(int64_t ms) = 0;
     static std::unique_ptr<client> New(peer_id self, conn_type type);
 };
 
@@ -45,11 +49,13 @@ class client_pool
     const peer_id self_;
     std::mutex mu_;
     std::map<conn_type, std::unique_ptr<client>> clients_;
+    int64_t patience_ms_ = -1;
 
   public:
     explicit client_pool(const peer_id self) : self_(self) {}
     client *require(conn_type type);
     void reset_peers(const peer_list &ids);
+    void set_dial_patience_ms(int64_t ms);
 };
 
 class server

@@ -17,6 +17,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <atomic>
+#include <chrono>
 #include <future>
 #include <iterator>
 #include <memory>
@@ -49,6 +50,9 @@ class session
     std::unique_ptr<cuda::DeviceSession> device_;
     bool device_tried_ = false;
     int spin_polls_ = 0;  // looks at a mailbox before a receiver sleeps (see session.cpp)
+    bool established_ = false;  // the constructor's barrier has completed
+    // how long a first connection is retried once the session is established
+    static constexpr long long established_patience_ms = 1000;
 
     const std::string scope_;  // names the sub-group among its parent's messages ("" = the whole group)
     const system_config config_;
@@ -72,6 +76,11 @@ class session
     void take_into(size_t src, const std::string &tag, void *dst, size_t cap, const char *what);
     void finish_pending(slot::pending &p, size_t src, const std::string &tag, const char *what);
     bool source_gone(size_t src, long long waited_ms) const;
+    struct poll_watch {
+        std::chrono::steady_clock::time_point start{}, asked{};
+        unsigned polls = 0;
+    };
+    bool polled_source_gone(const peer_id &who, poll_watch &w) const;
     void ensure_usable(const char *what);
     enum class failure { gone, late, other };
     [[noreturn]] void give_up(failure why, const peer_id &who, const char *what,

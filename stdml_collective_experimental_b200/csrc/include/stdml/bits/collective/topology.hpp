@@ -70,6 +70,7 @@ struct graph_pair_list {
 enum strategy {
     star,
     ring,
+    binary_tree,  // the reference lists it and leaves it commented out (topology.hpp:85-89 there)
 };
 
 // star rooted at `root`: edges root -> i
@@ -77,6 +78,10 @@ graph_builder start_broadcast_graph_builder(size_t n, size_t root);
 
 // star: one pair rooted at 0.  ring: n pairs; pair r reduces along
 // (r+1) -> (r+2) -> ... -> r and broadcasts along r -> r+1 -> ... -> r+n-1.
+// binary_tree: n pairs; pair r is a complete binary tree over the ranks renumbered
+// from r (rank (r + k) % n is node k, whose parent is node (k - 1) / 2): log2(n)
+// hops instead of the ring's n - 1, two children per node instead of the star's
+// n - 1 at the root.
 graph_pair_list make_graph_pair_list(strategy s, size_t n);
 
 const char *strategy_name(strategy s);

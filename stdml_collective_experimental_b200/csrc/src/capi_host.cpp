@@ -113,7 +113,7 @@ int stdmlc_peer_create(void **out, int rank, const char *peers_csv, int strategy
             throw std::invalid_argument("peer: malformed peer list");
         }
         *out = new sc::peer(sc::peer::from_list(static_cast<size_t>(rank), *peers,
-                                                strategy == 1 ? sc::ring : sc::star, version,
+                                                strategy == 1 ? sc::ring : strategy == 2 ? sc::binary_tree : sc::star, version,
                                                 *runners));
     });
 }
@@ -174,7 +174,7 @@ int stdmlc_session_destroy(void *s)
     return host_guarded([&] { delete static_cast<session_box *>(s); });
 }
 
-// what: 0 rank, 1 size, 2 version, 3 strategy (0 star, 1 ring)
+// what: 0 rank, 1 size, 2 version, 3 strategy (0 star, 1 ring, 2 binary tree)
 int stdmlc_session_info(void *s, int what, unsigned long long *out)
 {
     return host_guarded([&] {
@@ -190,7 +190,7 @@ int stdmlc_session_info(void *s, int what, unsigned long long *out)
             *out = ss.version();
             break;
         case 3:
-            *out = ss.get_strategy() == sc::ring ? 1 : 0;
+            *out = ss.get_strategy() == sc::ring ? 1 : ss.get_strategy() == sc::binary_tree ? 2 : 0;
             break;
         default:
             throw std::invalid_argument("session_info: unknown item");

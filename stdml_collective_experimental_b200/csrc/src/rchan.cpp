@@ -369,11 +369,11 @@ int64_t connect_timeout_ms()
 }
 
 std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_type type,
-                                             const peer_id local)
+                                             const peer_id local, int64_t patience_ms)
 {
     using clock = std::chrono::steady_clock;
     const auto t0 = clock::now();
-    const int64_t limit = connect_timeout_ms();
+    const int64_t limit = patience_ms >= 0 ? std::max<int64_t>(patience_ms, 1) : connect_timeout_ms();
     const sockaddr_in addr = to_sockaddr(remote);
     int wait_ms = 2;
     for (;;) {
@@ -415,8 +415,8 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
         const auto waited =
             std::chrono::duration_cast<std::chrono::milliseconds>(clock::now() - t0).count();
         if (limit > 0 && waited > limit) {
-            throw std::runtime_error("rchan: could not reach " + remote.str() + " within " +
-                                     std::to_string(limit) + " ms");
+            throw peer_failure(remote, "rchan: could not reach " + remote.str() + " within " +
+                                           std::to_string(limit) + " ms");
         }
         std::this_thread::sleep_for(std::chrono::milliseconds(wait_ms));
         wait_ms = std::min(wait_ms * 2, 200);  // the peer may simply not be up yet
@@ -511,13 +511,17 @@ class client_impl final : public client
     const conn_type type_;
     std::mutex mu_;
     std::map<uint64_t, std::shared_ptr<connection>> conns_;
+    std::atomic<int64_t> patience_ms_{-1};
 
     std::shared_ptr<connection> require(const peer_id &target)
     {
         std::lock_guard<std::mutex> lk(mu_);
-        auto &c = conns_[target.hash()];
-        if (!c) { c = connection::dial(target, type_, self_); }
-        return c;
+        auto it = conns_.find(target.hash());
+        if (it == conns_.end()) {
+            // (nothing is stored when dial throws)
+            it = conns_.emplace(target.hash(), connection::dial(target, type_, self_, patience_ms_.load())).first;
+        }
+        return it->second;
     }
 
   public:
@@ -539,6 +543,8 @@ class client_impl final : public client
         std::lock_guard<std::mutex> lk(mu_);
         for (const auto &id : ids) { conns_.erase(id.hash()); }
     }
+
+    void set_dial_patience_ms(int64_t ms) override { patience_ms_.store(ms); }
 };
 }  // namespace
 
@@ -551,8 +557,18 @@ client *client_pool::require(conn_type type)
 {
     std::lock_guard<std::mutex> lk(mu_);
     auto &c = clients_[type];
-    if (!c) { c = client::New(self_, type); }
+    if (!c) {
+        c = client::New(self_, type);
+        c->set_dial_patience_ms(patience_ms_);
+    }
     return c.get();
+}
+
+void client_pool::set_dial_patience_ms(int64_t ms)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    patience_ms_ = ms;
+    for (auto &kv : clients_) { kv.second->set_dial_patience_ms(ms); }
 }
 
 void client_pool::reset_peers(const peer_list &ids)

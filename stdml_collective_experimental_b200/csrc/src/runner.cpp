@@ -12,6 +12,7 @@
 
 #include <stdml/bits/collective/json.hpp>
 #include <stdml/bits/collective/log.hpp>
+#include <stdml/bits/collective/peer.hpp>
 #include <stdml/bits/collective/runner.hpp>
 
 namespace stdml::collective
@@ -321,7 +322,7 @@ bool parse_runner_args(int argc, char *argv[], runner_options &o, std::string &e
         } else if (a == "-strategy") {
             const char *v = need("-strategy");
             if (!v) { return false; }
-            o.strat = std::string(v) == "RING" || std::string(v) == "ring" ? ring : star;
+            o.strat = parse_kungfu_startegy(v);
         } else if (a == "-w") {
             o.watch = true;
         } else if (a == "-q") {

@@ -1,5 +1,6 @@
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <numeric>
@@ -69,7 +70,13 @@ session::session(system_config config, size_t version, size_t rank, peer_list pe
     }
     async_runtime_.reset(runtime::New(8));
     spin_polls_ = default_spin_polls(peers_, peers_[rank_]);
+    // members may still be starting: first connections are retried patiently
+    client_pool_->set_dial_patience_ms(-1);
     barrier();
+    // every member has answered, so each has a listening server from now on: a
+    // connection that is refused means a dead peer, not a late one
+    established_ = true;
+    client_pool_->set_dial_patience_ms(established_patience_ms);
 }
 
 session::~session() = default;
@@ -113,6 +120,31 @@ std::string versioned(const session &s, const std::string &name)
     return out;
 }
 }  // namespace
+
+// The polled tasks' form of source_gone(): looks at the clock once in a while.
+bool session::polled_source_gone(const peer_id &who, poll_watch &w) const
+{
+    using clock = std::chrono::steady_clock;
+    if (liveness_ == nullptr) { return false; }
+    if (liveness_->gone(who)) { return true; }
+    if ((++w.polls & 1023u) != 0) { return false; }
+    const auto now = clock::now();
+    if (w.start == clock::time_point()) {
+        w.start = w.asked = now;
+        return false;
+    }
+    const auto ms = [](clock::duration d) {
+        return std::chrono::duration_cast<std::chrono::milliseconds>(d).count();
+    };
+    const long long patience =
+        established_ ? established_patience_ms / 2 : rchan::connect_timeout_ms();
+    if (patience > 0 && ms(now - w.start) >= patience && ms(now - w.asked) >= 1000 &&
+        !liveness_->seen(who)) {
+        w.asked = now;
+        return rchan::ping(who, peers_[rank_], 1000) < 0;
+    }
+    return false;
+}
 
 namespace
 {
@@ -164,8 +196,11 @@ bool session::source_gone(size_t src, long long waited_ms) const
 {
     if (liveness_ == nullptr) { return false; }
     if (liveness_->gone(peers_[src])) { return true; }
-    // never heard of it: after a dialler's patience, ask it about once a second
-    const long long patience = rchan::connect_timeout_ms();
+    // never heard of it (no message of it has come our way yet): ask it about once
+    // a second, at once in a session whose members have all been seen alive, after
+    // a dialler's patience while they may still be starting
+    const long long patience =
+        established_ ? established_patience_ms / 2 : rchan::connect_timeout_ms();
     if (patience > 0 && waited_ms >= patience &&
         (waited_ms / liveness::slice_ms) % 10 == 0 && !liveness_->seen(peers_[src])) {
         return rchan::ping(peers_[src], peers_[rank_], 1000) < 0;
@@ -362,15 +397,15 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
     rchan::client *out = client_pool_->require(conn_collective);
 
     task_builder recv1, send1, recv2, send2;
-    liveness *live = liveness_;
     for (size_t src : rg->prevs(rank_)) {
         auto *box = mailbox_->require(peers_[src], sh->name);
         auto got = std::make_shared<buffer>();
+        auto watch = std::make_shared<poll_watch>();
         const peer_id who = peers_[src];
         recv1 << new poll_task(
-            [this, box, got, live, who, sh] {
+            [this, box, got, watch, who, sh] {
                 auto b = box->try_get();
-                if (!b && live != nullptr && live->gone(who)) {
+                if (!b && polled_source_gone(who, *watch)) {
                     b = box->try_get();  // sent before it went
                     if (!b) { give_up(failure::gone, who, "all_reduce", sh->name); }
                 }
@@ -400,14 +435,15 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
         for (size_t src : bg->prevs(rank_)) {
             auto *sl = slotbox_->require(peers_[src], sh->name);
             auto pend = std::make_shared<slot::pending>();
+            auto watch = std::make_shared<poll_watch>();
             const peer_id who = peers_[src];
-            recv2 << new poll_task([this, sl, sh, pend, bytes, live, who] {
+            recv2 << new poll_task([this, sl, sh, pend, bytes, watch, who] {
                 // the destination is posted on the first poll, i.e. after the
                 // reduce phase is over and recv no longer holds partial sums
                 if (!*pend) { *pend = sl->post_pending(sh->w.recv, bytes); }
                 int rc = pend->ready();
                 if (rc < 0) {
-                    const bool gone = live != nullptr && live->gone(who);
+                    const bool gone = polled_source_gone(who, *watch);
                     if (!gone && !given_up()) { return false; }
                     if (pend->cancel()) {
                         give_up(gone ? failure::gone : failure::other, who, "all_reduce", sh->name);
@@ -467,7 +503,8 @@ void session::all_reduce(const workspace &w, void *stream)
     // which keeps the pipeline free of deadlocks (see group_all_reduce).  The
     // reference runs the chunks of one tensor strictly one after another
     // (src/stdml/collective/run_graph_pair_list_multi_thread.cpp:93-95).
-    size_t lanes = strategy_ == ring ? 8 : 2;  // measured on 4 ranks: ring 4 -> 8 +8 %, star 1 -> 2 +33 %
+    // measured on 4 ranks: ring 4 -> 8 +8 %, star 1 -> 2 +33 %; the tree spreads its roots like the ring
+    size_t lanes = strategy_ == star ? 2 : 8;
     if (const auto v = parse_env_int("STDML_COLLECTIVE_CHUNK_LANES"); v && *v > 0) {
         lanes = static_cast<size_t>(*v);
     }

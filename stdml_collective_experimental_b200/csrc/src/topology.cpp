@@ -57,6 +57,12 @@ graph_pair ring_pair(size_t n, size_t root)
     }
     return graph_pair{reduce.build(false, true), bcast.build(false, false)};
 }
+graph_pair tree_pair(size_t n, size_t root)
+{
+    graph_builder bcast(n);
+    for (size_t k = 1; k < n; ++k) { bcast.add_edge((root + (k - 1) / 2) % n, (root + k) % n); }
+    return graph_pair{bcast.build(true, true), bcast.build(false, false)};
+}
 }  // namespace
 
 graph_pair_list make_graph_pair_list(strategy s, size_t n)
@@ -64,11 +70,16 @@ graph_pair_list make_graph_pair_list(strategy s, size_t n)
     graph_pair_list l;
     if (s == ring && n > 1) {
         for (size_t r = 0; r < n; ++r) { l.pairs.push_back(ring_pair(n, r)); }
+    } else if (s == binary_tree && n > 1) {
+        for (size_t r = 0; r < n; ++r) { l.pairs.push_back(tree_pair(n, r)); }
     } else {
         l.pairs.push_back(star_pair(n, 0));
     }
     return l;
 }
 
-const char *strategy_name(strategy s) { return s == ring ? "RING" : "STAR"; }
+const char *strategy_name(strategy s)
+{
+    return s == ring ? "RING" : s == binary_tree ? "BINARY_TREE" : "STAR";
+}
 }  // namespace stdml::collective

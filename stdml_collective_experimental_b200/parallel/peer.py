@@ -146,7 +146,7 @@ class Session:
 
     @property
     def strategy(self):
-        return "ring" if self._info(3) == 1 else "star"
+        return {1: "ring", 2: "binary_tree"}.get(self._info(3), "star")
 
     @property
     def cluster(self):
@@ -297,7 +297,8 @@ class Peer:
         """peers / runners: 'ip:port' strings."""
         h = ctypes.c_void_p()
         _native.check(_lib().stdmlc_peer_create(
-            ctypes.byref(h), rank, ",".join(peers).encode(), 1 if strategy == "ring" else 0,
+            ctypes.byref(h), rank, ",".join(peers).encode(),
+            {"ring": 1, "binary_tree": 2, "tree": 2}.get(strategy.lower(), 0),
             version, ",".join(runners).encode()))
         return cls(h)
 

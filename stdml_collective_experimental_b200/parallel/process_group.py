@@ -96,7 +96,7 @@ class StdmlProcessGroup(dist.ProcessGroup):
         store.set(f"stdml/addr/{rank}", f"{ip}:{port}")
         peers = [store.get(f"stdml/addr/{r}").decode() for r in range(size)]
         strategy = os.environ.get("KUNGFU_ALLREDUCE_STRATEGY", "STAR").lower()
-        self.peer = Peer.from_list(rank, peers, strategy="ring" if strategy == "ring" else "star")
+        self.peer = Peer.from_list(rank, peers, strategy=strategy)
         self.sess = self.peer.join()
         self._seq = 0
 

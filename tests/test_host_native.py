@@ -150,6 +150,12 @@ def test_elastic_state_survives_a_crash_and_grows_back():
     assert "[runner] version 1 : 3 -> 2 workers" in out and "[runner] version 2 : 2 -> 3 workers" in out
 
 
+def test_failure_detection_with_the_tree_strategy():
+    # chunks of one tensor use trees with different roots, so a rank may wait for a
+    # peer that has never sent it anything: the established-session ping covers that
+    assert "np=5: OK" in run("test_shutdown", 5, env={"KUNGFU_ALLREDUCE_STRATEGY": "BINARY_TREE"})
+
+
 def test_shutdown_and_host_side_failure_detection():
     # clean teardown after 100 collectives; a rank that leaves between steps and a rank
     # that never joins both end in exceptions on the others, not in a hang
@@ -165,7 +171,9 @@ def test_public_headers_compile_as_cxx17():
     run("test_cxx17")
 
 
-@pytest.mark.parametrize("np_,strategy", [(16, "STAR"), (16, "RING"), (7, "RING")])
+@pytest.mark.parametrize("np_,strategy", [(16, "STAR"), (16, "RING"), (7, "RING"),
+                                          (4, "BINARY_TREE"), (7, "BINARY_TREE"),
+                                          (16, "BINARY_TREE")])
 def test_collectives_many_ranks(np_, strategy):
     # the reference's CI sweeps np = 1..16 (t:37-57 there)
     assert f"np={np_}: OK" in run("test_collectives", np_,
