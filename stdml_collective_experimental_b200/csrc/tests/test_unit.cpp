@@ -94,6 +94,31 @@ static void test_topology()
         CHECK(b.prevs(r).empty() && b.nexts(r)[0] == (r + 1) % 4 && b.nexts((r + 3) % 4).empty());
     }
     CHECK(make_graph_pair_list(ring, 1).pairs.size() == 1);
+    // binary tree: n rotated trees; every non-root has one parent, at most two
+    // children, the reduce graph is the broadcast graph reversed, depth <= log2
+    for (size_t n : {2u, 5u, 8u, 13u}) {
+        const auto tl = make_graph_pair_list(binary_tree, n);
+        CHECK(tl.pairs.size() == n);
+        for (size_t r = 0; r < n; ++r) {
+            const graph &g = tl.pairs[r].reduce_graph, &b = tl.pairs[r].broadcast_graph;
+            CHECK(b.prevs(r).empty() && g.nexts(r).empty() && g.self_loop(r) && !b.self_loop(r));
+            for (size_t v = 0; v < n; ++v) {
+                CHECK(b.nexts(v).size() <= 2 && b.nexts(v) == g.prevs(v));
+                if (v != r) { CHECK(b.prevs(v).size() == 1 && g.nexts(v) == b.prevs(v)); }
+                size_t hops = 0, at = v;
+                while (at != r && hops <= n) {
+                    at = b.prevs(at)[0];
+                    ++hops;
+                }
+                size_t depth_bound = 0;
+                while ((size_t(1) << depth_bound) <= n) { ++depth_bound; }
+                CHECK(at == r && hops < depth_bound);
+            }
+        }
+    }
+    CHECK(std::string(strategy_name(binary_tree)) == "BINARY_TREE" &&
+          parse_kungfu_startegy("tree") == binary_tree && parse_kungfu_startegy("Ring") == ring &&
+          parse_kungfu_startegy(nullptr) == star);
     CHECK(rl.choose(6).first == &rl.pairs[2].reduce_graph);
     graph_builder gb(3);
     CHECK(gb.add_edge(0, 1) && !gb.add_edge(0, 1) && !gb.add_edge(1, 1) && !gb.add_edge(0, 9));
