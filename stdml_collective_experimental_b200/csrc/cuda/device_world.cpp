@@ -861,6 +861,20 @@ int cuda_device_count()
 
 bool cuda_available() { return cuda_device_count() > 0; }
 
+void copy_device_to_host(void *host, const void *device, size_t bytes, void *stream)
+{
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rt_check(cudaMemcpyAsync(host, device, bytes, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync(D2H)");
+    rt_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+}
+
+void copy_host_to_device(void *device, const void *host, size_t bytes, void *stream)
+{
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rt_check(cudaMemcpyAsync(device, host, bytes, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync(H2D)");
+    rt_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+}
+
 int pointer_kind(const void *p)
 {
     if (p == nullptr || !cuda_available()) { return 0; }

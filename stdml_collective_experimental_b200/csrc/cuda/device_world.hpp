@@ -134,4 +134,8 @@ bool cuda_available();
 int cuda_device_count();
 // memory kind of a pointer: 0 host/unknown, 1 device
 int pointer_kind(const void *p);
+// Blocking copy between host and device memory in stream order: enqueues after
+// what `stream` holds and returns when the copy is complete.
+void copy_device_to_host(void *host, const void *device, size_t bytes, void *stream);
+void copy_host_to_device(void *device, const void *host, size_t bytes, void *stream);
 }  // namespace stdml::collective::cuda

@@ -30,6 +30,9 @@ struct system_config {
     // ---- failure detection on the host path: how long a collective waits for a
     // peer's message before it throws (0 = for ever, as the reference does)
     int64_t host_timeout_ms = 0;       // STDML_COLLECTIVE_HOST_TIMEOUT_MS
+    // ---- members on several hosts: reduce inside each host, all-reduce among one
+    // leader per host, broadcast inside each host (always for device buffers)
+    bool hierarchical = false;         // STDML_COLLECTIVE_HIERARCHICAL
 };
 
 std::ostream &operator<<(std::ostream &os, const system_config &c);

@@ -51,6 +51,16 @@ class session
     bool device_tried_ = false;
     int spin_polls_ = 0;  // looks at a mailbox before a receiver sleeps (see session.cpp)
     bool established_ = false;  // the constructor's barrier has completed
+    // Two-level execution for members on several hosts (built on first use,
+    // collectively): the ranks of this host, and one leader per host.
+    struct levels {
+        std::unique_ptr<session> local;    // same address, in rank order; its rank 0 leads
+        std::unique_ptr<session> leaders;  // null on ranks that do not lead
+    };
+    std::unique_ptr<levels> levels_;
+    bool spans_hosts() const;
+    levels &two_levels();
+    void all_reduce_two_level(const workspace &w, bool device, void *stream, double scale = 1.0);
     // how long a first connection is retried once the session is established
     static constexpr long long established_patience_ms = 1000;
 

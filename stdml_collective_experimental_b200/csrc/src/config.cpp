@@ -81,6 +81,7 @@ system_config parse_system_config_from_env()
     if (const auto t = parse_env_int("STDML_COLLECTIVE_HOST_TIMEOUT_MS"); t && *t > 0) {
         c.host_timeout_ms = *t;
     }
+    c.hierarchical = parse_env_bool("STDML_COLLECTIVE_HIERARCHICAL");
     const std::string nvls = safe_getenv("STDML_COLLECTIVE_NVLS");
     if (nvls == "0" || nvls == "off" || nvls == "false") { c.use_nvls = false; }
     return c;

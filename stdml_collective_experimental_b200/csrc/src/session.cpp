@@ -77,6 +77,8 @@ session::session(system_config config, size_t version, size_t rank, peer_list pe
     // connection that is refused means a dead peer, not a late one
     established_ = true;
     client_pool_->set_dial_patience_ms(established_patience_ms);
+    // built now, by one thread, rather than by whichever worker gets there first
+    if (scope_.empty() && peers_.size() > 1 && spans_hosts()) { two_levels(); }
 }
 
 session::~session() = default;
@@ -478,7 +480,12 @@ void session::all_reduce(const workspace &w, void *stream)
     }
     if (w.count == 0) { return; }
     ensure_usable("all_reduce");
-    if (on_device(w.send, w.recv)) {
+    const bool dev = on_device(w.send, w.recv);
+    if (scope_.empty() && peers_.size() > 1 && (dev || config_.hierarchical) && spans_hosts()) {
+        all_reduce_two_level(w, dev, stream);
+        return;
+    }
+    if (dev) {
         const void *in[1] = {w.send};
         void *out[1] = {w.recv};
         device()->all_reduce(in, out, w.count, w.dt, w.op, 1.0, forced_algo(config_), stream);
@@ -536,6 +543,58 @@ void session::all_reduce(const workspace &w, void *stream)
     if (err) { std::rethrow_exception(err); }
 }
 
+bool session::spans_hosts() const
+{
+    for (const auto &p : peers_) {
+        if (p.ipv4 != peers_[0].ipv4) { return true; }
+    }
+    return false;
+}
+
+session::levels &session::two_levels()
+{
+    if (levels_) { return *levels_; }
+    auto lv = std::make_unique<levels>();
+    std::vector<size_t> local, leaders;
+    for (size_t r = 0; r < peers_.size(); ++r) {
+        if (peers_[r].ipv4 == peers_[rank_].ipv4) { local.push_back(r); }
+        bool first_of_host = true;
+        for (size_t q = 0; q < r; ++q) { first_of_host = first_of_host && peers_[q].ipv4 != peers_[r].ipv4; }
+        if (first_of_host) { leaders.push_back(r); }
+    }
+    lv->local = subgroup(local, "host-" + peers_[rank_].hostname());
+    lv->leaders = subgroup(leaders, "leaders");  // null unless this rank leads its host
+    log() << "two-level all_reduce:" << local.size() << "ranks on this host," << leaders.size()
+          << "hosts" << (lv->leaders ? "(leader)" : "");
+    levels_ = std::move(lv);
+    return *levels_;
+}
+
+// Reduce inside each host, all-reduce among one leader per host, broadcast
+// inside each host: the links between hosts carry one flow per host instead of
+// one per rank.  Device buffers take this path whenever the members span hosts:
+// the two inner stages run on the host's GPUs over NVLink, the leaders' stage
+// goes through host memory and the network.
+void session::all_reduce_two_level(const workspace &w, bool device, void *stream, double scale)
+{
+    levels &lv = two_levels();
+    const std::string name = "2l::" + w.name;
+    lv.local->reduce(w.send, w.recv, w.count, w.dt, w.op, name, stream, 0);
+    if (lv.leaders) {
+        if (device) {
+            std::vector<char> host(w.bytes());
+            cuda::copy_device_to_host(host.data(), w.recv, host.size(), stream);
+            lv.leaders->all_reduce(host.data(), host.data(), w.count, w.dt, w.op, name);
+            if (scale != 1.0) { scale_in_place(host.data(), w.count, w.dt, scale); }
+            cuda::copy_host_to_device(w.recv, host.data(), host.size(), stream);
+        } else {
+            lv.leaders->all_reduce(w.recv, w.recv, w.count, w.dt, w.op, name);
+            if (scale != 1.0) { scale_in_place(w.recv, w.count, w.dt, scale); }
+        }
+    }
+    lv.local->broadcast(w.recv, w.recv, w.count, w.dt, name, stream, 0);
+}
+
 void session::all_reduce(const void *input, void *output, size_t count, dtype dt, reduce_op op,
                          std::string name, void *stream)
 {
@@ -586,6 +645,17 @@ void session::group_all_reduce(const std::vector<workspace> &ws, double scale, v
     for (const auto &w : ws) {
         dev = dev && on_device(w.send, w.recv);
         same = same && w.dt == ws[0].dt && w.op == ws[0].op;
+    }
+    if (dev && scope_.empty() && peers_.size() > 1 && spans_hosts()) {
+        // members on several hosts: tensor by tensor through the two-level path
+        // (the fused kernel needs one NVLink domain)
+        for (const auto &w : ws) {
+            if (w.count == 0) { continue; }
+            if (!reduce_supported(w.dt, w.op)) { throw std::invalid_argument("group_all_reduce: undefined dtype/op"); }
+            ensure_usable("group_all_reduce");
+            all_reduce_two_level(w, true, stream, scale);
+        }
+        return;
     }
     if (dev && same) {
         std::vector<const void *> ins;

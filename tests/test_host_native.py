@@ -130,6 +130,23 @@ def test_elastic_job_over_two_emulated_hosts():
     assert "[runner] started worker 127.0.0.3:10820" in outs[1]  # grown back, same port range
 
 
+def test_two_level_all_reduce_over_uneven_emulated_hosts():
+    # 3 ranks on one "host", 2 on the other: reduce inside each host, all-reduce
+    # among the two leaders, broadcast inside each host
+    common = ["-q", "-H", "127.0.0.2:3,127.0.0.3:2", "-np", "5", "-port-range", "10840",
+              "-runner-port", "38394", "-env", "STDML_COLLECTIVE_HIERARCHICAL=1"]
+    e = dict(os.environ)
+    for k in ("KUNGFU_SELF_SPEC", "OMPI_COMM_WORLD_SIZE", "RANK", "WORLD_SIZE"):
+        e.pop(k, None)
+    procs = [subprocess.Popen([os.path.join(BIN, "stdml_collective_run"), *common, "-self", ip,
+                               os.path.join(BIN, "test_two_level")], env=e,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for ip in ("127.0.0.2", "127.0.0.3")]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert outs[0].count("/5: OK") == 3 and outs[1].count("/5: OK") == 2, outs
+
+
 def test_elastic_state_follows_config_server():
     out = run("stdml_collective_run", "-q", "-np", 2, "-w", "-builtin-config-port", 0,
               os.path.join(BIN, "example_elastic_state"), "--max-step=9", "2:4", "5:3",
