@@ -737,6 +737,16 @@ void session::reduce(const void *input, void *output, size_t count, dtype dt, re
     if (root >= peers_.size()) { throw std::out_of_range("reduce: no such root"); }
     ensure_usable("reduce");
     if (on_device(input, output != nullptr ? output : input)) {
+        if (scope_.empty() && spans_hosts()) {
+            // members on several hosts: through host memory and the network
+            const size_t nbytes = count * dtype_size(dt);
+            std::vector<char> a(nbytes), b(rank_ == root ? nbytes : 0);
+            cuda::copy_device_to_host(a.data(), input, nbytes, stream);
+            reduce(a.data(), rank_ == root ? b.data() : nullptr, count, dt, op, "dev::" + name,
+                   nullptr, root);
+            if (rank_ == root) { cuda::copy_host_to_device(output, b.data(), nbytes, stream); }
+            return;
+        }
         const void *in[1] = {input};
         void *out[1] = {output};
         device()->reduce(in, out, count, dt, op, static_cast<int>(root), 1.0, stream);
@@ -779,6 +789,15 @@ void session::all_gather(const void *input, void *output, size_t count, dtype dt
 {
     if (count == 0) { return; }
     if (on_device(input, output)) {
+        if (scope_.empty() && spans_hosts()) {
+            // members on several hosts: through host memory and the network
+            const size_t nbytes = count * dtype_size(dt);
+            std::vector<char> a(nbytes), all(nbytes * peers_.size());
+            cuda::copy_device_to_host(a.data(), input, nbytes, stream);
+            all_gather(a.data(), all.data(), count, dt, "dev::" + name, nullptr);
+            cuda::copy_host_to_device(output, all.data(), all.size(), stream);
+            return;
+        }
         const void *in[1] = {input};
         void *out[1] = {output};
         device()->all_gather(in, out, count, dt, stream);
@@ -847,6 +866,15 @@ void session::broadcast(const void *input, void *output, size_t count, dtype dt,
     if (count == 0) { return; }
     if (root >= peers_.size()) { throw std::out_of_range("broadcast: no such root"); }
     if (on_device(input, output)) {
+        if (scope_.empty() && spans_hosts()) {
+            // members on several hosts: through host memory and the network
+            const size_t nbytes = count * dtype_size(dt);
+            std::vector<char> a(nbytes);
+            if (rank_ == root) { cuda::copy_device_to_host(a.data(), input, nbytes, stream); }
+            broadcast(a.data(), a.data(), count, dt, "dev::" + name, nullptr, root);
+            cuda::copy_host_to_device(output, a.data(), nbytes, stream);
+            return;
+        }
         const void *in[1] = {input};
         void *out[1] = {output};
         device()->broadcast(in, out, count, dt, static_cast<int>(root), stream);
