@@ -74,6 +74,7 @@ class runner
 
     void spawn(const peer_id &worker, const cluster_config &cluster, size_t version);
     void reap(bool block);
+    void stop_workers();
 };
 
 // parses the command line of the stdml-collective-run program

@@ -5,7 +5,10 @@
 #include <stdexcept>
 #include <thread>
 
+#include <csignal>
+
 #include <fcntl.h>
+#include <sys/prctl.h>
 #include <sys/stat.h>
 #include <sys/wait.h>
 #include <unistd.h>
@@ -19,6 +22,11 @@ namespace stdml::collective
 {
 namespace
 {
+// set by SIGINT / SIGTERM: the run loop then stops the workers and leaves
+volatile std::sig_atomic_t g_stop_signal = 0;
+
+void on_stop_signal(int sig) { g_stop_signal = sig; }
+
 class control_msg_handler final : public rchan::msg_handler
 {
     runner *runner_;
@@ -119,6 +127,10 @@ void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t 
     const pid_t pid = ::fork();
     if (pid < 0) { throw std::runtime_error("runner: fork failed"); }
     if (pid == 0) {
+        // a worker does not outlive its runner, however the runner ends
+        ::prctl(PR_SET_PDEATHSIG, SIGTERM);
+        std::signal(SIGINT, SIG_DFL);
+        std::signal(SIGTERM, SIG_DFL);
         ::setenv("KUNGFU_SELF_SPEC", worker.str().c_str(), 1);
         ::setenv("KUNGFU_INIT_PEERS", peers.c_str(), 1);
         ::setenv("KUNGFU_INIT_RUNNERS", runners.c_str(), 1);
@@ -171,6 +183,34 @@ void runner::reap(bool block)
         }
         if (block) { return; }
     }
+}
+
+// SIGTERM to every worker, a grace period, SIGKILL to what is left.
+void runner::stop_workers()
+{
+    std::vector<int> pids;
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        for (const auto &kv : pids_) { pids.push_back(kv.second); }
+    }
+    if (!opt_.quiet) { log(PRINT) << "[runner] signal" << int(g_stop_signal) << ": stopping" << pids.size() << "workers"; }
+    for (int pid : pids) { ::kill(pid, SIGTERM); }
+    for (int waited_ms = 0; waited_ms < 5000; waited_ms += 50) {
+        reap(false);
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            if (pids_.empty()) { break; }
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(50));
+    }
+    std::lock_guard<std::mutex> lk(mu_);
+    for (const auto &kv : pids_) {
+        ::kill(kv.second, SIGKILL);
+        ::waitpid(kv.second, nullptr, 0);
+        ++failed_;
+    }
+    pids_.clear();
+    if (failed_ == 0) { failed_ = 1; }  // a job that was stopped did not succeed
 }
 
 void runner::on_update(size_t version, const cluster_config &next)
@@ -244,7 +284,13 @@ int runner::run()
     // configuration, on any host, answers a ping.
     const bool lingers = opt_.watch && !opt_.hosts.empty();
     int silent_checks = 0;
+    std::signal(SIGINT, on_stop_signal);
+    std::signal(SIGTERM, on_stop_signal);
     for (;;) {
+        if (g_stop_signal != 0) {
+            stop_workers();
+            break;
+        }
         reap(false);
         bool idle;
         peer_list workers;

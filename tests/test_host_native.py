@@ -147,6 +147,28 @@ def test_two_level_all_reduce_over_uneven_emulated_hosts():
     assert outs[0].count("/5: OK") == 3 and outs[1].count("/5: OK") == 2, outs
 
 
+def test_launcher_stops_its_workers_when_it_is_told_to_stop():
+    import signal
+    import time
+    p = subprocess.Popen([os.path.join(BIN, "stdml_collective_run"), "-np", "3", "-port-range",
+                          "10860", "-runner-port", "38396", "sleep", "300"],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    kids = []
+    for _ in range(100):  # wait for the three workers
+        out = subprocess.run(["pgrep", "-P", str(p.pid)], stdout=subprocess.PIPE, text=True).stdout
+        kids = [int(x) for x in out.split()]
+        if len(kids) == 3:
+            break
+        time.sleep(0.05)
+    assert len(kids) == 3
+    p.send_signal(signal.SIGTERM)
+    out = p.communicate(timeout=30)[0]
+    assert p.returncode == 1 and "stopping 3 workers" in out, out
+    for k in kids:  # reaped: no such process any more
+        with pytest.raises(ProcessLookupError):
+            os.kill(k, 0)
+
+
 def test_elastic_state_follows_config_server():
     out = run("stdml_collective_run", "-q", "-np", 2, "-w", "-builtin-config-port", 0,
               os.path.join(BIN, "example_elastic_state"), "--max-step=9", "2:4", "5:3",
