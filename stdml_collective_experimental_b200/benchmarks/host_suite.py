@@ -77,6 +77,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--workloads", default="1024x100,16384x100,102400x100,262144x10,resnet50,vgg16")
     ap.add_argument("--out", default="")
+    ap.add_argument("--strategies", default="RING,STAR",
+                    help="comma list of RING, STAR, BINARY_TREE (the reference knows the first two)")
     args = ap.parse_args()
     # "sweep" stands for the reference's AxB list (testdata/test-set-1.txt there)
     args.workloads = ",".join(",".join(SWEEP) if w == "sweep" else w
@@ -89,12 +91,15 @@ def main():
     with tempfile.TemporaryDirectory() as tmp:
         for w in args.workloads.split(","):
             path = write_sizes_file(w, os.path.join(tmp, w + ".txt")) if w in GRADSETS else w
-            for strategy in ("RING", "STAR"):
+            for strategy in args.strategies.split(","):
                 a = (args.np, strategy, path, args.steps, args.warmup)
                 row = [run_ours("bench_all_reduce", *a), run_ours("bench_all_reduce", *a, env=pool),
-                       run_ours("bench_group_all_reduce", *a),
-                       run_ref("bench-all-reduce", *a), run_ref("bench-all-reduce", *a, env=pool),
-                       run_ref("bench-group-all-reduce", *a, timeout=60)]
+                       run_ours("bench_group_all_reduce", *a)]
+                if strategy in ("RING", "STAR"):
+                    row += [run_ref("bench-all-reduce", *a), run_ref("bench-all-reduce", *a, env=pool),
+                            run_ref("bench-group-all-reduce", *a, timeout=60)]
+                else:
+                    row += [None, None, None]
                 line = f"| {w} | {strategy} | " + " | ".join(fmt(x) for x in row) + " |"
                 print(line, flush=True)
                 lines.append(line)
