@@ -8,7 +8,6 @@
 #include <csignal>
 
 #include <fcntl.h>
-#include <sys/prctl.h>
 #include <sys/stat.h>
 #include <sys/wait.h>
 #include <unistd.h>
@@ -127,8 +126,8 @@ void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t 
     const pid_t pid = ::fork();
     if (pid < 0) { throw std::runtime_error("runner: fork failed"); }
     if (pid == 0) {
-        // a worker does not outlive its runner, however the runner ends
-        ::prctl(PR_SET_PDEATHSIG, SIGTERM);
+        // (no PR_SET_PDEATHSIG here: it fires when the forking THREAD ends, and
+        // joiners are started from a short-lived connection thread)
         std::signal(SIGINT, SIG_DFL);
         std::signal(SIGTERM, SIG_DFL);
         ::setenv("KUNGFU_SELF_SPEC", worker.str().c_str(), 1);
