@@ -175,6 +175,14 @@ class session
     // every member directly.
     void broadcast(const void *input, void *output, size_t count, dtype dt,
                    std::string name = "", void *stream = nullptr, size_t root = 0);
+    // Beyond the reference.  reduce_scatter: input holds size() blocks of `count`
+    // elements; rank r receives block r reduced over all ranks (folded in rank
+    // order).  all_to_all: block q of the input goes to rank q, block q of the
+    // output comes from rank q.  Device buffers are staged through host memory.
+    void reduce_scatter(const void *input, void *output, size_t count, dtype dt, reduce_op op,
+                        std::string name = "", void *stream = nullptr);
+    void all_to_all(const void *input, void *output, size_t count, dtype dt,
+                    std::string name = "", void *stream = nullptr);
     void recv(void *output, size_t count, dtype dt, size_t target, std::string name = "");
     void send(const void *input, size_t count, dtype dt, size_t target, std::string name = "");
 

@@ -297,6 +297,23 @@ int stdmlc_session_broadcast_from(void *s, const void *in, void *out, unsigned l
     });
 }
 
+int stdmlc_session_reduce_scatter(void *s, const void *in, void *out, unsigned long long count,
+                                  int dt, int op, const char *name, void *stream)
+{
+    return host_guarded([&] {
+        SS(s).reduce_scatter(in, out, count, static_cast<sc::dtype>(dt),
+                             static_cast<sc::reduce_op>(op), name ? name : "", stream);
+    });
+}
+
+int stdmlc_session_all_to_all(void *s, const void *in, void *out, unsigned long long count, int dt,
+                              const char *name, void *stream)
+{
+    return host_guarded([&] {
+        SS(s).all_to_all(in, out, count, static_cast<sc::dtype>(dt), name ? name : "", stream);
+    });
+}
+
 int stdmlc_session_send(void *s, const void *in, unsigned long long count, int dt, int target,
                         const char *name)
 {

@@ -820,12 +820,16 @@ void session::all_gather(const void *input, void *output, size_t count, dtype dt
     auto send_to = [&](size_t r) {
         cl->send(peers_[r], tag.c_str(), input, bytes, message_header::wait_recv_buf);
     };
-    if (pool_) {
-        fmap(pool_.get(), send_to, others);
-    } else {
-        fmap(par, send_to, others);
-    }
     std::exception_ptr first;
+    try {
+        if (pool_) {
+            fmap(pool_.get(), send_to, others);
+        } else {
+            fmap(par, send_to, others);
+        }
+    } catch (...) {
+        first = std::current_exception();  // the posted destinations are withdrawn below
+    }
     for (auto &[r, p] : waits) {
         if (first) {
             p.cancel();  // nothing may be written into `output` after we have thrown
@@ -916,6 +920,84 @@ void session::broadcast(const void *input, void *output, size_t count, dtype dt,
         cl->send(peers_[r], tag.c_str(), output, bytes, message_header::wait_recv_buf);
     };
     fmap(par, send_to, g.nexts(rank_));
+}
+
+void session::reduce_scatter(const void *input, void *output, size_t count, dtype dt,
+                             reduce_op op, std::string name, void *stream)
+{
+    if (count == 0) { return; }
+    if (!reduce_supported(dt, op)) { throw std::invalid_argument("reduce_scatter: undefined dtype/op"); }
+    ensure_usable("reduce_scatter");
+    const size_t bytes = count * dtype_size(dt), n = peers_.size();
+    if (on_device(input, output)) {
+        std::vector<char> a(bytes * n), b(bytes);
+        cuda::copy_device_to_host(a.data(), input, a.size(), stream);
+        reduce_scatter(a.data(), b.data(), count, dt, op, "dev::" + name, nullptr);
+        cuda::copy_host_to_device(output, b.data(), bytes, stream);
+        return;
+    }
+    // one rooted reduce per block; a rank only sends (eagerly) for the blocks of
+    // others, so going through the blocks in order cannot deadlock
+    const char *in = static_cast<const char *>(input);
+    std::vector<char> own;
+    if (output == static_cast<const void *>(in + rank_ * bytes) || output == input) {
+        own.assign(in + rank_ * bytes, in + (rank_ + 1) * bytes);  // output overlaps the input
+    }
+    for (size_t q = 0; q < n; ++q) {
+        const void *block = (q == rank_ && !own.empty()) ? own.data() : in + q * bytes;
+        reduce(block, q == rank_ ? output : nullptr, count, dt, op,
+               "rs" + std::to_string(q) + "::" + name, nullptr, q);
+    }
+}
+
+void session::all_to_all(const void *input, void *output, size_t count, dtype dt,
+                         std::string name, void *stream)
+{
+    if (count == 0) { return; }
+    ensure_usable("all_to_all");
+    const size_t bytes = count * dtype_size(dt), n = peers_.size();
+    if (on_device(input, output)) {
+        std::vector<char> a(bytes * n), b(bytes * n);
+        cuda::copy_device_to_host(a.data(), input, a.size(), stream);
+        all_to_all(a.data(), b.data(), count, dt, "dev::" + name, nullptr);
+        cuda::copy_host_to_device(output, b.data(), b.size(), stream);
+        return;
+    }
+    if (input == output) { throw std::invalid_argument("all_to_all: in place is not supported"); }
+    const std::string tag = versioned(*this, "stdml::all_to_all::" + name);
+    const char *in = static_cast<const char *>(input);
+    char *out = static_cast<char *>(output);
+    // post every destination first, then send: the bodies land in place
+    std::vector<std::pair<size_t, slot::pending>> waits;
+    for (size_t r = 0; r < n; ++r) {
+        if (r != rank_) {
+            waits.emplace_back(r, slotbox_->require(peers_[r], tag)->post_pending(out + r * bytes, bytes));
+        }
+    }
+    std::memcpy(out + rank_ * bytes, in + rank_ * bytes, bytes);
+    std::vector<size_t> others;
+    for (size_t k = 1; k < n; ++k) { others.push_back((rank_ + k) % n); }
+    rchan::client *cl = client_pool_->require(conn_collective);
+    std::exception_ptr first;
+    try {
+        fmap(par, [&](size_t r) {
+            cl->send(peers_[r], tag.c_str(), in + r * bytes, bytes, message_header::wait_recv_buf);
+        }, others);
+    } catch (...) {
+        first = std::current_exception();
+    }
+    for (auto &[r, p] : waits) {
+        if (first) {
+            p.cancel();  // nothing may be written into `output` after we have thrown
+            continue;
+        }
+        try {
+            finish_pending(p, r, tag, "all_to_all");
+        } catch (...) {
+            first = std::current_exception();
+        }
+    }
+    if (first) { std::rethrow_exception(first); }
 }
 
 void session::send(const void *input, size_t count, dtype dt, size_t target, std::string name)

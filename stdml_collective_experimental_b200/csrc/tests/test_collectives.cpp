@@ -186,6 +186,23 @@ static void check_others(session &sess)
         std::vector<int> gr(count * n, -1);
         sess.gather(x.data(), gr.data(), count, i32, "gr" + std::to_string(count), root);
         if (r == root) { CHECK(gr == y); }
+        // reduce_scatter and all_to_all
+        std::vector<int> rsin(count * n), rsout(count, -1);
+        for (size_t i = 0; i < rsin.size(); ++i) { rsin[i] = int(i) + int(r); }
+        sess.reduce_scatter(rsin.data(), rsout.data(), count, i32, sum, "rs" + std::to_string(count));
+        for (size_t i = 0; i < count; ++i) {
+            CHECK(rsout[i] == int(n) * int(r * count + i) + int(n * (n - 1) / 2));
+        }
+        std::vector<int> a2in(count * n), a2out(count * n, -1);
+        for (size_t q = 0; q < n; ++q) {
+            for (size_t i = 0; i < count; ++i) { a2in[q * count + i] = int(r * 100000 + q * 1000 + i % 1000); }
+        }
+        sess.all_to_all(a2in.data(), a2out.data(), count, i32, "a2a" + std::to_string(count));
+        for (size_t q = 0; q < n; ++q) {
+            for (size_t i = 0; i < count; i += 1 + count / 7) {
+                CHECK(a2out[q * count + i] == int(q * 100000 + r * 1000 + i % 1000));
+            }
+        }
         std::vector<int> red(count, -7);
         sess.reduce(x.data(), red.data(), count, i32, sum, "rd" + std::to_string(count));
         if (r == 0) {

@@ -49,6 +49,8 @@ def _lib():
         lib.stdmlc_session_reduce_to.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_int,
                                                  c.c_char_p, vp]
         lib.stdmlc_session_gather_to.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
+        lib.stdmlc_session_reduce_scatter.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int, c.c_char_p, vp]
+        lib.stdmlc_session_all_to_all.argtypes = [vp, vp, vp, u64, c.c_int, c.c_char_p, vp]
         lib.stdmlc_session_send.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_recv.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_barrier.argtypes = [vp]
@@ -241,6 +243,27 @@ class Session:
         _native.check(self._lib.stdmlc_session_gather_to(
             self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), int(root),
             name.encode()))
+        return o
+
+    def reduce_scatter(self, tensor, out, op="sum", name=""):
+        """`tensor` holds size blocks of out.numel() elements; `out` = block `rank`
+        reduced over all ranks."""
+        t, o = _checked(tensor, "reduce_scatter"), _checked(out, "reduce_scatter")
+        if t.numel() != o.numel() * self.size:
+            raise ValueError("reduce_scatter: tensor must hold size * out.numel() elements")
+        _native.check(self._lib.stdmlc_session_reduce_scatter(
+            self._h, t.data_ptr(), o.data_ptr(), o.numel(), dtype_code(t.dtype), op_code(op),
+            name.encode(), _stream_of(t)))
+        return o
+
+    def all_to_all(self, tensor, out, name=""):
+        """Block q of `tensor` goes to rank q; block q of `out` comes from rank q."""
+        t, o = _checked(tensor, "all_to_all"), _checked(out, "all_to_all")
+        if t.numel() != o.numel() or t.numel() % self.size != 0:
+            raise ValueError("all_to_all: both tensors must hold size equal blocks")
+        _native.check(self._lib.stdmlc_session_all_to_all(
+            self._h, t.data_ptr(), o.data_ptr(), t.numel() // self.size, dtype_code(t.dtype),
+            name.encode(), _stream_of(t)))
         return o
 
     def broadcast(self, tensor, out=None, name="", root=0):

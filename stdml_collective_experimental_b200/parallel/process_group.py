@@ -183,11 +183,14 @@ class StdmlProcessGroup(dist.ProcessGroup):
 
     def _reduce_scatter_base(self, output, input, opts=None):
         op, average = _op_of(opts)
-        tmp = self._dense(input).clone().view(-1)
-        self.sess.all_reduce(tmp, op=op, name=self._name("rs"))
-        n = output.numel()
-        mine = tmp[self._rank * n:(self._rank + 1) * n].view_as(output)
-        output.copy_(mine.div_(self._size) if average else mine)
+        out = output if output.is_contiguous() else torch.empty_like(
+            output, memory_format=torch.contiguous_format)
+        self.sess.reduce_scatter(self._dense(input).view(-1), out.view(-1), op=op,
+                                 name=self._name("rs"))
+        if average:
+            out.div_(self._size)
+        if out is not output:
+            output.copy_(out)
         return _DoneWork(output)
 
     def reduce_scatter(self, output_tensors, input_tensors, opts=None):
@@ -269,6 +272,10 @@ class StdmlProcessGroup(dist.ProcessGroup):
 
     def alltoall_base(self, output, input, output_split_sizes, input_split_sizes, opts=None):
         n = self._size
+        if not input_split_sizes and not output_split_sizes and input.is_contiguous() and \
+                output.is_contiguous() and input.numel() == output.numel():
+            self.sess.all_to_all(input.view(-1), output.view(-1), name=self._name("a2ab"))
+            return _DoneWork(output)
         ins = list(input.split(input_split_sizes if input_split_sizes else input.shape[0] // n))
         outs = list(output.split(output_split_sizes if output_split_sizes else output.shape[0] // n))
         tmp = [torch.empty_like(o, memory_format=torch.contiguous_format) for o in outs]

@@ -83,6 +83,10 @@ def main():
     a2a_out = [torch.empty(1) for _ in range(n)]
     dist.all_to_all(a2a_out, [torch.tensor([float(rank * 10 + r)]) for r in range(n)])
     assert [int(o.item()) for o in a2a_out] == [r * 10 + rank for r in range(n)]
+    single_in = torch.arange(n * 2, dtype=torch.float32) + 100 * rank
+    single_out = torch.empty(n * 2)
+    dist.all_to_all_single(single_out, single_in)
+    assert single_out.tolist() == [100.0 * q + 2 * rank + j for q in range(n) for j in range(2)]
     dist.barrier()
 
     # a sub-group is a process group of its own (its members build their own session)

@@ -55,6 +55,13 @@ def main():
             sess.send(torch.tensor([42.0]), 1, name="p2p")
         elif rank == 1:
             assert sess.recv(torch.zeros(1), 0, name="p2p").item() == 42.0
+    # reduce_scatter / all_to_all
+    rs = torch.empty(3)
+    sess.reduce_scatter(torch.arange(3 * n, dtype=torch.float32) + rank, rs, name="rs")
+    assert torch.equal(rs, (torch.arange(3 * n, dtype=torch.float32) * n + n * (n - 1) / 2)[3 * rank:3 * rank + 3])
+    a2 = torch.empty(n, dtype=torch.int64)
+    sess.all_to_all(torch.arange(n, dtype=torch.int64) + 10 * rank, a2, name="a2a")
+    assert a2.tolist() == [10 * q + rank for q in range(n)]
     # sub-group: all but the last rank
     if n > 2:
         sub = sess.subgroup(list(range(n - 1)), "head")
