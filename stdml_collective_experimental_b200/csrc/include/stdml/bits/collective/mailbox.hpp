@@ -41,6 +41,7 @@ class slot
         size_t cap = 0;
         bool done = false;
         bool ok = false;
+        bool withdrawn = false;  // cancelled before any body was matched to it
     };
     std::mutex mu_;
     std::condition_variable finished_;
@@ -140,9 +141,11 @@ class slot
         {
             std::unique_lock<std::mutex> lk(s_->mu_);
             if (t_->done) { return false; }
+            if (t_->withdrawn) { return true; }  // cancelled before: still nothing will be written
             for (auto it = s_->waiting_.begin(); it != s_->waiting_.end(); ++it) {
                 if (*it == t_) {
                     s_->waiting_.erase(it);
+                    t_->withdrawn = true;
                     return true;
                 }
             }

@@ -436,21 +436,30 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
     } else {
         for (size_t src : bg->prevs(rank_)) {
             auto *sl = slotbox_->require(peers_[src], sh->name);
-            auto pend = std::make_shared<slot::pending>();
+            // withdrawn with the task if the tree is abandoned (another task threw):
+            // nothing may be written into the user's buffer after all_reduce has returned
+            struct posted {
+                slot::pending p;
+                ~posted()
+                {
+                    if (p) { p.cancel(); }
+                }
+            };
+            auto pend = std::make_shared<posted>();
             auto watch = std::make_shared<poll_watch>();
             const peer_id who = peers_[src];
             recv2 << new poll_task([this, sl, sh, pend, bytes, watch, who] {
                 // the destination is posted on the first poll, i.e. after the
                 // reduce phase is over and recv no longer holds partial sums
-                if (!*pend) { *pend = sl->post_pending(sh->w.recv, bytes); }
-                int rc = pend->ready();
+                if (!pend->p) { pend->p = sl->post_pending(sh->w.recv, bytes); }
+                int rc = pend->p.ready();
                 if (rc < 0) {
                     const bool gone = polled_source_gone(who, *watch);
                     if (!gone && !given_up()) { return false; }
-                    if (pend->cancel()) {
+                    if (pend->p.cancel()) {
                         give_up(gone ? failure::gone : failure::other, who, "all_reduce", sh->name);
                     }
-                    rc = pend->wait(0);
+                    rc = pend->p.wait(0);
                 }
                 if (rc == 0) { throw std::length_error("all_reduce: the result did not fit"); }
                 return true;

@@ -247,6 +247,25 @@ static void test_sync_primitives()
         return true;
     });
     CHECK(polled() && dst[0] == 'o');
+    // a pending post: not ready, withdrawn (twice: the second time must not wait),
+    // and a body that comes afterwards goes to the next receiver, not to the old buffer
+    char old_buf[4] = {'-', '-', '-', '-'};
+    slot::pending pd = s.post_pending(old_buf, 4);
+    CHECK(pd.ready() == -1 && pd.wait(5) == -1);
+    CHECK(pd.cancel() && pd.cancel());
+    s.put(2, [](void *p) {
+        std::memcpy(p, "zz", 2);
+        return true;
+    });
+    CHECK(old_buf[0] == '-');
+    CHECK(s.get(dst, 8) && dst[0] == 'z');
+    // delivered before the cancel: cancel reports it and the data is there
+    slot::pending pd2 = s.post_pending(old_buf, 4);
+    s.put(2, [](void *p) {
+        std::memcpy(p, "in", 2);
+        return true;
+    });
+    CHECK(!pd2.cancel() && pd2.ready() == 1 && old_buf[0] == 'i');
 
     auto pool = stdml::sync::thread_pool::make(3);
     std::atomic<int> sum{0};
