@@ -10,6 +10,7 @@
 // messages (the head-of-line blocking that deadlocks the reference's
 // group_all_reduce when ranks submit tensors in different orders).
 #pragma once
+#include <atomic>
 #include <chrono>
 #include <condition_variable>
 #include <cstring>
@@ -39,9 +40,12 @@ class slot
     struct ticket {
         void *ptr = nullptr;
         size_t cap = 0;
-        bool done = false;
+        // written under the slot's mutex; atomic so that the holder of a pending can
+        // ask "is there anything left to withdraw?" without touching the slot, which
+        // may be gone by the time a finished operation's handle is destroyed
+        std::atomic<bool> done{false};
         bool ok = false;
-        bool withdrawn = false;  // cancelled before any body was matched to it
+        std::atomic<bool> withdrawn{false};  // cancelled before any body was matched to it
     };
     std::mutex mu_;
     std::condition_variable finished_;
@@ -77,7 +81,7 @@ class slot
     {
         auto t = post_ticket(ptr, cap);
         std::unique_lock<std::mutex> lk(mu_);
-        finished_.wait(lk, [&] { return t->done; });
+        finished_.wait(lk, [&] { return t->done.load(); });
         return t->ok;
     }
 
@@ -89,7 +93,7 @@ class slot
         if (ms <= 0) { return get(ptr, cap) ? 1 : 0; }
         auto t = post_ticket(ptr, cap);
         std::unique_lock<std::mutex> lk(mu_);
-        if (!finished_.wait_for(lk, std::chrono::milliseconds(ms), [&] { return t->done; })) {
+        if (!finished_.wait_for(lk, std::chrono::milliseconds(ms), [&] { return t->done.load(); })) {
             for (auto it = waiting_.begin(); it != waiting_.end(); ++it) {
                 if (*it == t) {
                     waiting_.erase(it);
@@ -97,7 +101,7 @@ class slot
                 }
             }
             // a network thread has taken the ticket and is filling it right now
-            finished_.wait(lk, [&] { return t->done; });
+            finished_.wait(lk, [&] { return t->done.load(); });
         }
         return t->ok ? 1 : 0;
     }
@@ -121,13 +125,17 @@ class slot
         {
             std::unique_lock<std::mutex> lk(s_->mu_);
             if (ms <= 0) {
-                s_->finished_.wait(lk, [&] { return t_->done; });
+                s_->finished_.wait(lk, [&] { return t_->done.load(); });
             } else if (!s_->finished_.wait_for(lk, std::chrono::milliseconds(ms),
-                                               [&] { return t_->done; })) {
+                                               [&] { return t_->done.load(); })) {
                 return -1;
             }
             return t_->ok ? 1 : 0;
         }
+
+        // true when nothing can be written through this post any more (delivered or
+        // withdrawn); does not touch the slot
+        bool settled() const { return !t_ || t_->done.load() || t_->withdrawn.load(); }
 
         // wait() without waiting
         int ready()
@@ -149,7 +157,7 @@ class slot
                     return true;
                 }
             }
-            s_->finished_.wait(lk, [&] { return t_->done; });
+            s_->finished_.wait(lk, [&] { return t_->done.load(); });
             return false;
         }
     };
@@ -168,7 +176,7 @@ class slot
         auto t = post_ticket(ptr, cap);
         return [this, t] {
             std::unique_lock<std::mutex> lk(mu_);
-            finished_.wait(lk, [&] { return t->done; });
+            finished_.wait(lk, [&] { return t->done.load(); });
             return t->ok;
         };
     }
@@ -180,7 +188,7 @@ class slot
         auto t = post_ticket(ptr, cap);
         return [this, t] {
             std::lock_guard<std::mutex> lk(mu_);
-            return t->done;
+            return t->done.load();
         };
     }
 

@@ -442,7 +442,7 @@ task *session::chunk_task(const workspace &w, const graph *rg, const graph *bg)
                 slot::pending p;
                 ~posted()
                 {
-                    if (p) { p.cancel(); }
+                    if (p && !p.settled()) { p.cancel(); }
                 }
             };
             auto pend = std::make_shared<posted>();
