@@ -11,6 +11,18 @@ from stdml_collective_experimental_b200 import _native
 BIN = os.path.join(_native.CSRC, "build", "bin")
 
 
+def collect(procs, timeout):
+    """Outputs of all processes; none of them is left behind if one hangs."""
+    try:
+        return [p.communicate(timeout=timeout)[0] for p in procs]
+    except subprocess.TimeoutExpired:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        raise
+
+
+
 @pytest.fixture(scope="module", autouse=True)
 def built():
     _native.build()
@@ -122,7 +134,7 @@ def test_elastic_job_over_two_emulated_hosts():
     procs = [subprocess.Popen([os.path.join(BIN, "stdml_collective_run"), *common, "-self", ip,
                                *prog], env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                               text=True) for ip in ("127.0.0.2", "127.0.0.3")]
-    outs = [p.communicate(timeout=300)[0] for p in procs]
+    outs = collect(procs, 300)
     assert all(p.returncode == 0 for p in procs), outs
     assert outs[0].count("weight 78.0 (want 78.0) OK") == 2, outs[0]
     assert outs[1].count("weight 78.0 (want 78.0) OK") == 2, outs[1]
@@ -142,7 +154,7 @@ def test_two_level_all_reduce_over_uneven_emulated_hosts():
                                os.path.join(BIN, "test_two_level")], env=e,
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
              for ip in ("127.0.0.2", "127.0.0.3")]
-    outs = [p.communicate(timeout=300)[0] for p in procs]
+    outs = collect(procs, 300)
     assert all(p.returncode == 0 for p in procs), outs
     assert outs[0].count("/5: OK") == 3 and outs[1].count("/5: OK") == 2, outs
 

@@ -8,13 +8,25 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def collect(procs, timeout):
+    """Outputs of all processes; none of them is left behind if one hangs."""
+    try:
+        return [p.communicate(timeout=timeout)[0] for p in procs]
+    except subprocess.TimeoutExpired:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        raise
+
+
+
 @pytest.mark.parametrize("n,strategy,base", [(1, "star", 12100), (3, "star", 12110),
                                              (4, "ring", 12120)])
 def test_python_peer_session(n, strategy, base, native_lib):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_rank_worker.py"), str(r),
                                str(n), str(base), strategy], stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(n)]
-    outs = [p.communicate(timeout=300)[0] for p in procs]
+    outs = collect(procs, 300)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
 
@@ -25,7 +37,7 @@ def test_python_peer_failure_is_an_exception(strategy, base, native_lib):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_fail_worker.py"), str(r),
                                str(n), str(base), strategy], stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(n)]
-    outs = [p.communicate(timeout=300)[0] for p in procs]
+    outs = collect(procs, 300)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o[-2000:]
         if r != 1:
@@ -64,7 +76,7 @@ def test_torch_distributed_backend_and_ddp(strategy, port, native_lib):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "pg_worker.py"), str(r), str(n),
                                str(port)], env=env, stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(n)]
-    outs = [p.communicate(timeout=300)[0] for p in procs]
+    outs = collect(procs, 300)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
 
@@ -74,6 +86,6 @@ def test_distributed_optimizer_matches_single_process_training(native_lib):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_train_worker.py"), str(r),
                                str(n), str(base)], stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(n)]
-    outs = [p.communicate(timeout=300)[0] for p in procs]
+    outs = collect(procs, 300)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
