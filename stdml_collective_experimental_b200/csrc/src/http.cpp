@@ -155,6 +155,10 @@ std::optional<http_response> roundtrip(const std::string &method, const std::str
         return {};
     }
     const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+    {
+        int one = 1;  // see rchan.cpp: keeps this client's TIME_WAIT entry from blocking a later bind
+        setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+    }
     if (fd < 0) {
         freeaddrinfo(res);
         return {};

@@ -46,6 +46,15 @@ void tune_socket(int fd)
     setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &buf, sizeof(buf));
 }
 
+// An outgoing connection takes an ephemeral local port, which can be the very
+// port a peer or runner of a later job wants to listen on; its TIME_WAIT entry
+// blocks that bind for a minute unless BOTH sockets were marked reusable.
+void mark_reusable(int fd)
+{
+    int one = 1;
+    setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+}
+
 sockaddr_in to_sockaddr(const peer_id &id)
 {
     sockaddr_in a;
@@ -382,6 +391,7 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
                                  (remote.ipv4 >> 24) == 127u);
         const int fd = ::socket(local_peer ? AF_UNIX : AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         if (fd < 0) { throw std::runtime_error("rchan: socket() failed"); }
+        mark_reusable(fd);
         int rc;
         if (local_peer) {
             sockaddr_un ua;
@@ -439,6 +449,7 @@ int handshake_with_deadline(const peer_id &remote, const peer_id &local, conn_ty
     };
     const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
     if (fd < 0) { return -1; }
+    mark_reusable(fd);
     const auto fail = [&] {
         ::close(fd);
         return -1;

@@ -26,6 +26,8 @@ int InetAddr::connect(int sock) const { return ::connect(sock, get(), sizeof(add
 TcpSocket::TcpSocket() : fd_(::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0))
 {
     if (fd_ < 0) { throw std::system_error(errno, std::generic_category(), "socket"); }
+    int one = 1;  // keeps a client's TIME_WAIT entry from blocking a later bind of its local port
+    setsockopt(fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
 }
 
 TcpSocket::TcpSocket(int fd) : fd_(fd) {}
