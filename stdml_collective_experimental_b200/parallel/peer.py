@@ -11,6 +11,7 @@ reduce / gather / send / recv / consistent / barrier and the elastic
 """
 import ctypes
 import json
+import weakref
 
 import torch
 
@@ -111,13 +112,18 @@ class Task:
             self._done = True
         return self._keep[-1]
 
+    def release(self):
+        """Finish the operation if it is still running and free the native task."""
+        if self._h is not None:
+            if not self._done:
+                self._lib.stdmlc_task_finish(self._h)
+                self._done = True
+            self._lib.stdmlc_task_destroy(self._h)
+            self._h = None
+
     def __del__(self):
         try:
-            if self._h is not None:
-                if not self._done:
-                    self._lib.stdmlc_task_finish(self._h)
-                self._lib.stdmlc_task_destroy(self._h)
-                self._h = None
+            self.release()
         except Exception:
             pass
 
@@ -128,6 +134,7 @@ class Session:
     def __init__(self, handle):
         self._h = handle
         self._lib = _lib()
+        self._tasks = weakref.WeakSet()  # started operations: finished before the session goes
 
     def _info(self, what):
         v = ctypes.c_ulonglong()
@@ -170,6 +177,12 @@ class Session:
 
     def close(self):
         if self._h is not None:
+            # a task must not outlive the native session it polls
+            for task in list(getattr(self, "_tasks", ())):
+                try:
+                    task.release()
+                except Exception:
+                    pass
             h, self._h = self._h, None
             _native.check(self._lib.stdmlc_session_destroy(h))
 
@@ -198,7 +211,9 @@ class Session:
         _native.check(self._lib.stdmlc_session_all_reduce_async(
             self._h, t.data_ptr(), o.data_ptr(), t.numel(), dtype_code(t.dtype), op_code(op),
             name.encode(), _stream_of(t), ctypes.byref(h)))
-        return Task(h, (t, o))
+        task = Task(h, (t, o))
+        self._tasks.add(task)
+        return task
 
     def reduce(self, tensor, out=None, op="sum", name="", root=0):
         """Result on rank `root` only; `out` of the other ranks is left alone."""
