@@ -46,7 +46,40 @@ def main():
 
     peer = Peer.from_env()
     sess = peer.join()
+    try:
+        run(args, peer, sess, schedule, use_cuda, dev)
+    finally:
+        # orderly on every path (detached, finished, error): the device world is
+        # torn down (barrier -> unbind -> release) before the process goes
+        sess.close()
+        peer.close()
+
+
+def shrinks(size_now, schedule, from_step=0):
+    """True if following `schedule` ({step: size}) from `size_now` ever drops members."""
+    cur = size_now
+    for k in sorted(schedule):
+        if k < from_step:
+            continue
+        if schedule[k] < cur:
+            return True
+        cur = schedule[k]
+    return False
+
+
+def nvls_requested():
+    return os.environ.get("STDML_COLLECTIVE_NVLS", "1") not in ("0", "off", "false")
+
+
+def run(args, peer, sess, schedule, use_cuda, dev):
     me = peer.self_id
+    if use_cuda and shrinks(sess.size, schedule) and nvls_requested():
+        # A rank that leaves while its arena is bound to an NVLink multicast
+        # object can fault the GPUs of the ranks that stay.  Runs in which the
+        # membership shrinks therefore use plain peer loads (two-shot); the
+        # NVLS figures belong to fixed-membership runs.
+        raise SystemExit("elastic: this schedule drops members; set STDML_COLLECTIVE_NVLS=0 "
+                         "(and NCCL_NVLS_ENABLE=0) for runs in which a rank leaves")
     sizes = gradset_sizes(args.model)
     set_bytes = 4 * sum(sizes)
     grads = [torch.full((n,), 1.0, device=dev) for n in sizes]
@@ -119,8 +152,6 @@ def main():
              "allreduce_ms_median": med,
              "bus_gb_s": None if not med else 2 * (n - 1) / n * set_bytes / (med * 1e-3) / 1e9,
              "weights_ok": bool(abs(float(weights[0]) - args.max_step) < 1e-3)})
-    sess.close()
-    peer.close()
 
 
 if __name__ == "__main__":

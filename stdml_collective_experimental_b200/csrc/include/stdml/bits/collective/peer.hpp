@@ -97,7 +97,20 @@ class peer
     // (progress by max-all-reduce, parameters by broadcast): a collective that
     // was in flight when the member died may have finished on some survivors
     // and not on others.
+    // The survivors agree on one member list before any of them builds the new
+    // session (their pings may have seen different things); a member that the
+    // others could not reach gets peer_failure from its own recover().
     peer_list recover(std::unique_ptr<session> &sess, int ping_timeout_ms = 1000);
+    // Same with the liveness probe supplied by the caller (`answers(p)`: does
+    // old member p still answer?), for tests that make one rank's probe fail.
+    peer_list recover(std::unique_ptr<session> &sess, int ping_timeout_ms,
+                      const std::function<bool(const peer_id &)> &answers);
+
+  private:
+    peer_list agree_on_survivors(const peer_list &old, peer_list alive, size_t new_version,
+                                 int ping_timeout_ms);
+
+  public:
 };
 
 // fork n ranks on this host (ports 10000 + i), run g in each, wait for all

@@ -282,23 +282,120 @@ resize_result peer::resize(std::unique_ptr<session> &sess, const config_prodiver
 
 peer_list peer::recover(std::unique_ptr<session> &sess, int ping_timeout_ms)
 {
+    return recover(sess, ping_timeout_ms, [this, ping_timeout_ms](const peer_id &p) {
+        return rchan::ping(p, self_, ping_timeout_ms) >= 0;
+    });
+}
+
+// Survivors must build the new session from ONE member list.  Each starts from
+// its own pings, which can differ (a member that is slow, a ping that races
+// with a death), so the views are intersected until they stop changing: in
+// round k every member sends its view (one byte per old member) to the members
+// of that view and waits for theirs; a member whose view does not come in time
+// is dropped; the next view is the intersection of everything received.  The
+// exchange ends when a round changes nothing and every view received equalled
+// one's own.  A member that finds itself outside a view it received leaves with
+// peer_failure (the others go on without it).
+peer_list peer::agree_on_survivors(const peer_list &old, peer_list alive, size_t new_version,
+                                   int ping_timeout_ms)
+{
+    using namespace std::chrono;
+    const size_t n = old.size();
+    // members enter recover() at different times: the one that saw the failure
+    // first, the others after its notice and their own pings of the dead
+    const long long patience_ms =
+        std::max<long long>(5000, 3ll * std::max(ping_timeout_ms, 1) * static_cast<long long>(n));
+    auto *out = client_pool_->require(rchan::conn_collective);
+    out->set_dial_patience_ms(std::max<long long>(1000, ping_timeout_ms));
+    peer_list told;  // everyone a view has gone to: they also hear of being dropped
+    for (int round = 0; round < static_cast<int>(n) + 2; ++round) {
+        const std::string name = "stdml::recover::v" + std::to_string(new_version) +
+                                 "::view" + std::to_string(round);
+        std::vector<uint8_t> mine(n, 0);
+        for (size_t i = 0; i < n; ++i) { mine[i] = alive.contains(old[i]) ? 1 : 0; }
+        peer_list reachable;
+        for (const auto &p : alive) {
+            if (p == self_) {
+                reachable.push_back(p);
+                continue;
+            }
+            try {
+                out->send(p, name.c_str(), mine.data(), mine.size(), 0);
+                reachable.push_back(p);
+            } catch (const std::exception &) {
+                // it went between the ping and now
+            }
+            if (!told.contains(p)) { told.push_back(p); }
+        }
+        for (const auto &p : told) {
+            if (alive.contains(p)) { continue; }
+            try {  // best effort: lets a member that is alive but was dropped give up at once
+                out->send(p, name.c_str(), mine.data(), mine.size(), 0);
+            } catch (const std::exception &) {
+            }
+        }
+        bool all_equal = reachable.size() == alive.size();
+        std::vector<uint8_t> next = mine;
+        peer_list heard;
+        const auto deadline = steady_clock::now() + milliseconds(patience_ms);
+        for (const auto &p : reachable) {
+            if (p == self_) {
+                heard.push_back(p);
+                continue;
+            }
+            auto *box = mailbox_->require(p, name);
+            std::optional<buffer> got;
+            for (;;) {
+                got = box->get_for(milliseconds(liveness::slice_ms));
+                if (got || steady_clock::now() >= deadline) { break; }
+            }
+            if (!got || got->len != n) {
+                all_equal = false;  // silent (or not speaking this protocol): not a member
+                continue;
+            }
+            const auto *theirs = reinterpret_cast<const uint8_t *>(got->data.get());
+            const size_t me = old.rank(self_);
+            if (theirs[me] == 0) {
+                throw peer_failure(p, "recover: member " + p.str() +
+                                          " could not reach this rank and the survivors go on "
+                                          "without it");
+            }
+            heard.push_back(p);
+            for (size_t i = 0; i < n; ++i) {
+                if (theirs[i] != mine[i]) { all_equal = false; }
+                next[i] = next[i] && theirs[i];
+            }
+        }
+        peer_list agreed;
+        for (size_t i = 0; i < n; ++i) {
+            if (next[i] && heard.contains(old[i])) { agreed.push_back(old[i]); }
+        }
+        const bool stable = all_equal && agreed.size() == alive.size();
+        alive = agreed;
+        if (stable) { break; }
+    }
+    out->set_dial_patience_ms(-1);
+    return alive;
+}
+
+peer_list peer::recover(std::unique_ptr<session> &sess, int ping_timeout_ms,
+                        const std::function<bool(const peer_id &)> &answers)
+{
     sess->abort();
     const peer_list old = sess->peers();
     const peer_list runners = sess->runners();
     const strategy s = sess->get_strategy();
     const size_t new_version = sess->version() + 1;
-    peer_list alive, dropped;
+    peer_list alive;
     for (const auto &p : old) {
         // a member that is itself recovering still answers: its server runs
-        if (p == self_ || rchan::ping(p, self_, ping_timeout_ms) >= 0) {
-            alive.push_back(p);
-        } else {
-            dropped.push_back(p);
-        }
+        if (p == self_ || answers(p)) { alive.push_back(p); }
     }
     sess.reset();
-    client_pool_->reset_peers(dropped);
     liveness_->forget(old);
+    alive = agree_on_survivors(old, alive, new_version, ping_timeout_ms);
+    const peer_list dropped = old - alive;
+    client_pool_->reset_peers(dropped);
     init_peers_ = alive;
     init_version_ = new_version;
     if (alive.rank(self_) == 0) {
@@ -320,6 +417,12 @@ peer_list peer::recover(std::unique_ptr<session> &sess, int ping_timeout_ms)
     sess = std::make_unique<session>(config_, new_version, alive.rank(self_), alive, runners,
                                      mailbox_.get(), slotbox_.get(), client_pool_.get(), s,
                                      liveness_.get());
+    // belt and braces: every member of the new session was built from the same list
+    const std::vector<std::byte> view = cluster_config(runners, alive).bytes();
+    if (!sess->consistent(view.data(), view.size())) {
+        throw std::runtime_error("recover: the survivors built sessions from different member "
+                                 "lists (version " + std::to_string(new_version) + ")");
+    }
     return dropped;
 }
 

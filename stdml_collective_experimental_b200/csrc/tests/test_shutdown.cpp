@@ -205,6 +205,65 @@ static int member_lost_and_recovered(int np, bool async_runtime)
     return bad;
 }
 
+// Survivors whose probes disagree: rank 3 dies; rank 0's probe of rank 2, which
+// is alive, is made to fail.  Ranks 0 and 1 must end up in ONE session of two
+// members and finish; rank 2 must be told that it was left out (peer_failure
+// from its own recover()), not form a session of its own.
+static int survivors_disagree()
+{
+    const int np = 4;
+    std::vector<pid_t> kids;
+    for (int r = 0; r < np; ++r) {
+        const pid_t pid = ::fork();
+        if (pid == 0) {
+            int rc = 3;
+            try {
+                peer p = peer::from_fork(r, np);
+                std::unique_ptr<session> sess = p.join_elastic();
+                const peer_list members = sess->peers();
+                int64_t step = 0;
+                bool left_out = false;
+                while (step < 6 && !left_out) {
+                    if (r == 3 && step == 2) { ::_exit(0); }
+                    try {
+                        std::vector<float> x(20000, 1.0f), y(20000, 0.0f);
+                        sess->all_reduce(x.data(), y.data(), x.size(), f32, sum, "d" + std::to_string(step));
+                        if (y[0] != float(sess->size())) { ::_exit(7); }
+                        ++step;
+                    } catch (const peer_failure &) {
+                        try {
+                            p.recover(sess, 300, [&](const peer_id &q) {
+                                if (r == 0 && q == members[2]) { return false; }  // the injected miss
+                                return p.ping(q, 300) >= 0;
+                            });
+                        } catch (const peer_failure &) {
+                            left_out = true;
+                            break;
+                        }
+                        if (sess->size() != 2 || sess->peers()[0] != members[0] ||
+                            sess->peers()[1] != members[1]) {
+                            ::_exit(8);
+                        }
+                        step = sess->all_reduce(step, max);
+                    }
+                }
+                if (r == 2) {
+                    rc = left_out ? 0 : 9;
+                } else {
+                    rc = (!left_out && sess->version() == 1) ? 0 : 10;
+                }
+            } catch (const std::exception &e) {
+                std::printf("rank %d: %s\n", r, e.what());
+                std::fflush(stdout);
+                rc = 5;
+            }
+            ::_exit(rc);
+        }
+        kids.push_back(pid);
+    }
+    return reap(kids, "survivors disagree");
+}
+
 // Bytes that are not this protocol (a port scanner, an HTTP client, a half-sent
 // header) must neither crash a peer nor disturb its collectives.
 static int stray_connections()
@@ -304,6 +363,7 @@ int main(int argc, char *argv[])
     run("peer dies before connecting", [&] { return peer_dies_before_connecting(); });
     run("member lost and recovered", [&] { return member_lost_and_recovered(np, false); });
     run("member lost and recovered (polled tasks)", [&] { return member_lost_and_recovered(np, true); });
+    run("survivors disagree", [&] { return survivors_disagree(); });
     run("stray connections", [&] { return stray_connections(); });
     run("ping", [&] { return ping_peers(); });
     std::printf("test-shutdown np=%d: %s\n", np, bad == 0 ? "OK" : "FAILED");

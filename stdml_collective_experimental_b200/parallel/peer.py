@@ -175,14 +175,19 @@ class Session:
                                                         ctypes.byref(h)))
         return Session(h) if h.value else None
 
+    def _release_tasks(self):
+        """Finish and free every operation started on this session.  A task polls
+        the native session it was started on, so none may outlive it: not when the
+        session is closed, and not when resize()/recover() replace it in place."""
+        for task in list(getattr(self, "_tasks", ())):
+            try:
+                task.release()
+            except Exception:
+                pass
+
     def close(self):
         if self._h is not None:
-            # a task must not outlive the native session it polls
-            for task in list(getattr(self, "_tasks", ())):
-                try:
-                    task.release()
-                except Exception:
-                    pass
+            self._release_tasks()
             h, self._h = self._h, None
             _native.check(self._lib.stdmlc_session_destroy(h))
 
@@ -365,6 +370,7 @@ class Peer:
         new_size: propose that many workers to the config server, then follow it;
         cluster: an explicit {"Runners": [...], "Workers": [...]} dict (no server);
         neither: follow the config server.  Returns (changed, detached)."""
+        sess._release_tasks()  # the native session is replaced: its tasks go first
         changed, detached = ctypes.c_int(), ctypes.c_int()
         js = None if cluster is None else json.dumps(cluster).encode()
         _native.check(self._lib.stdmlc_peer_resize(
@@ -377,6 +383,9 @@ class Peer:
         place, a session of the members that still answer (ranks keep their order,
         the version goes up by one).  Returns the number of members dropped.  As
         after a resize, re-synchronise progress and parameters afterwards."""
+        # unfinished operations of the broken session end here (with its failure);
+        # afterwards nothing refers to the native session that recover() destroys
+        sess._release_tasks()
         dropped = ctypes.c_int()
         _native.check(self._lib.stdmlc_peer_recover(self._h, sess._h, int(ping_timeout_ms),
                                                     ctypes.byref(dropped)))

@@ -83,9 +83,16 @@ def main():
 
     # elastic: shrink to n - 1 by explicit configuration; the last rank detaches
     if n > 2:
+        # an operation that is still unfinished when the session is replaced: resize
+        # must finish and free it first (its native task polls the old session), and
+        # dropping the handle afterwards must touch nothing that is gone
+        pending_in = torch.full((400_000,), float(rank + 1))
+        pending = sess.all_reduce_async(pending_in, name="async:across-resize")
         smaller = resized_cluster(sess.cluster, n - 1)
         changed, detached = peer.resize(sess, cluster=smaller)
         assert changed
+        assert pending._h is None and pending_in[0] == n * (n + 1) / 2
+        del pending
         if rank == n - 1:
             assert detached
         else:

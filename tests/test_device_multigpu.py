@@ -59,7 +59,9 @@ def test_elastic_resize_on_gpus():
     if not os.path.exists(runner):
         from stdml_collective_experimental_b200 import _native
         _native.build()
-    env = dict(os.environ, PYTHONPATH=root, NCCL_NVLS_ENABLE="0")
+    # a rank leaves between steps: no multicast binding may be live then, neither
+    # NCCL's nor the library's own
+    env = dict(os.environ, PYTHONPATH=root, NCCL_NVLS_ENABLE="0", STDML_COLLECTIVE_NVLS="0")
     cmd = [runner, "-q", "-np", "2", "-w", "-builtin-config-port", "0", "-runner-port", "38181",
            "-port-range", "10300", sys.executable, "-m",
            "stdml_collective_experimental_b200.benchmarks.elastic", "--model", "resnet50",
