@@ -37,8 +37,20 @@ def parse_args():
     p.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     p.add_argument("--algo", default="auto")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-extras", action="store_true",
+                   help="skip the blocks beside the headline (other dtype, loopback kernel)")
+    p.add_argument("--e2e-chunks", type=int, default=8)
     p.add_argument("--strategy", default="RING", help="reference arm: RING or STAR")
     return p.parse_args()
+
+
+def workload_config(workload, sizes, n, dtype):
+    """The workload, in the same words for both arms; what differs between the
+    implementations goes under `impl_detail`."""
+    esize = 4 if dtype == "f32" else 2
+    return {"model": workload, "tensors": len(sizes), "elements": sum(sizes),
+            "set_bytes": esize * sum(sizes), "global_batch": None, "seq_len": None,
+            "parallelism": f"dp{n}", "dtype": dtype, "op": "sum"}
 
 
 def env_rank():
@@ -120,10 +132,14 @@ def run_reference(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "timing": "host wall clock of the reference's own benchmark loop (it has no device path)",
         "reference_metric_gib_s": float(final.group(1)) if final else None,
-        "config": {"model": args.workload, "tensors": len(sizes), "elements": sum(sizes),
-                   "set_bytes": total_bytes, "parallelism": f"dp{n}", "memory": "host",
-                   "transport": "tcp-loopback", "strategy": args.strategy,
-                   "runtime": "rt_thread_pool"},
+        # the reference reduces host buffers in place: its figure already is end to end
+        # (host memory in, host memory out), with no device copies to count
+        "e2e": {"value": value, "unit": "GB/s", "ms_per_step": ms, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0,
+                "path": "host buffers -> TCP loopback ring -> host buffers (no GPU involved)"},
+        "config": workload_config(args.workload, sizes, n, "f32"),
+        "impl_detail": {"memory": "host", "transport": "tcp-loopback", "strategy": args.strategy,
+                        "runtime": "rt_thread_pool", "scale": "not applied (the reference has none)"},
     })
     return 0
 
@@ -167,110 +183,207 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     sizes = gradset_sizes(args.workload)
-    esize = 4 if args.dtype == "f32" else 2
-    padded = [-(-s * esize // 16) * 16 // esize for s in sizes]
-    total = sum(padded)
-    set_bytes = sum(sizes) * esize
-    heap = (2 * total * esize + (64 << 20))
-    sess = DeviceSession.from_env(heap_bytes=heap, rank=rank, world=n, device=local)
-
-    # gradients live in the symmetric heap, one flat region, tensors as views
-    flat = sess.symm_empty(total, dtype)
-    views, off = [], 0
-    for s, p in zip(sizes, padded):
-        views.append(flat[off:off + s])
-        off += p
-    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
-    host_in = torch.empty(total, dtype=dtype).pin_memory()
-    host_in.copy_((torch.randn(total, generator=g) * 1e-3).to(dtype))
-    host_out = torch.empty(total, dtype=dtype).pin_memory()
-    flat.copy_(host_in, non_blocking=True)
-    torch.cuda.synchronize()
     scale = 1.0 / n
     algo = None if args.algo == "auto" else args.algo
+    steps, warmup = args.steps, max(args.warmup, 3)
 
-    # correctness of the exact call that is timed (against NCCL when N > 1)
-    check = flat.clone()
-    sess.group_all_reduce(views, scale=scale, algo=algo)
-    torch.cuda.synchronize()
-    sess.check()
-    if n > 1:
-        dist.all_reduce(check)
-        check.mul_(scale)
-    err = float((flat.float() - check.float()).abs().max())
-    ref_mag = float(check.float().abs().max())
-    tol = 1e-6 if dtype == torch.float32 else 2e-2
-    if not err <= tol * max(ref_mag, 1e-30) + 1e-12:
-        raise SystemExit(f"rank {rank}: fused group_all_reduce mismatch: max err {err}")
+    def layout(esize):
+        padded = [-(-s * esize // 16) * 16 // esize for s in sizes]
+        return padded, sum(padded)
 
-    def step():
+    max_total_bytes = layout(4)[1] * 4
+    heap = 2 * max_total_bytes + layout(2)[1] * 2 + (96 << 20)
+    sess = DeviceSession.from_env(heap_bytes=heap, rank=rank, world=n, device=local)
+
+    def gradient_set(dtype_name, seed):
+        """The set as one flat region of the symmetric heap, tensors as views of it,
+        plus its pinned host twin (N(0, 1e-3), seeded per rank)."""
+        dtype = torch.float32 if dtype_name == "f32" else torch.bfloat16
+        esize = 4 if dtype_name == "f32" else 2
+        padded, total = layout(esize)
+        flat = sess.symm_empty(total, dtype)
+        views, off = [], 0
+        for s_, p_ in zip(sizes, padded):
+            views.append(flat[off:off + s_])
+            off += p_
+        g = torch.Generator(device="cpu").manual_seed(seed + rank)
+        host_in = torch.empty(total, dtype=dtype).pin_memory()
+        host_in.copy_((torch.randn(total, generator=g) * 1e-3).to(dtype))
+        flat.copy_(host_in, non_blocking=True)
+        torch.cuda.synchronize()
+        return dtype, esize, total, flat, views, host_in
+
+    def check_against_nccl(flat, views, dtype):
+        """Correctness of the exact call that is timed (against NCCL when N > 1,
+        against the input itself when alone)."""
+        check = flat.clone()
         sess.group_all_reduce(views, scale=scale, algo=algo)
+        torch.cuda.synchronize()
+        sess.check()
+        if n > 1:
+            dist.all_reduce(check)
+            check.mul_(scale)
+        err = float((flat.float() - check.float()).abs().max())
+        ref_mag = float(check.float().abs().max())
+        tol = 1e-6 if dtype == torch.float32 else 2e-2
+        if not err <= tol * max(ref_mag, 1e-30) + 1e-12:
+            raise SystemExit(f"rank {rank}: fused group_all_reduce mismatch: max err {err}")
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    sampler.start()
-    torch.cuda.synchronize()
-    host_barrier()
-    sess.barrier()  # ranks leave the host barrier at different times: line them up on the device
-    launches0 = sess.launches
-    ev[0].record()
-    for i in range(args.steps):
-        step()
-        ev[i + 1].record()
-    torch.cuda.synchronize()
-    host_barrier()
-    launches = sess.launches - launches0
-    total_ms = ev[0].elapsed_time(ev[-1])
-    ms = max_over_ranks(total_ms / args.steps)
-    clocks = sampler.stop()
-    sess.check()
+    def timed_device_steps(views, with_sampler):
+        def step():
+            sess.group_all_reduce(views, scale=scale, algo=algo)
+
+        if with_sampler:
+            sampler.start()  # runs through the warm-up too: short regions still get samples
+        for _ in range(warmup):
+            step()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        torch.cuda.synchronize()
+        host_barrier()
+        sess.barrier()  # ranks leave the host barrier at different times: line them up on the device
+        launches0 = sess.launches
+        if with_sampler:
+            sampler.mark_begin()
+        ev[0].record()
+        for i in range(steps):
+            step()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        if with_sampler:
+            sampler.mark_end()
+        host_barrier()
+        launches = sess.launches - launches0
+        ms = max_over_ranks(ev[0].elapsed_time(ev[-1]) / steps)
+        clocks = sampler.stop() if with_sampler else None
+        sess.check()
+        return ms, launches, clocks
+
+    # ---- the headline: the set in the dtype asked for (f32 is what the reference can do)
+    dtype, esize, total, flat, views, host_in = gradient_set(args.dtype, 1234)
+    set_bytes = sum(sizes) * esize
+    check_against_nccl(flat, views, dtype)
+    ms, launches, clocks = timed_device_steps(views, True)
     value = n * set_bytes / (ms * 1e-3) / 1e9
 
     e2e = None
     if not args.no_e2e:
-        pipe = HostAllReduce(sess, total, dtype, chunks=8)
+        host_out = torch.empty(total, dtype=dtype).pin_memory()
+        pipe = HostAllReduce(sess, total, dtype, chunks=args.e2e_chunks)
         for _ in range(3):
             pipe.run(host_in, host_out, scale=scale)
         torch.cuda.synchronize()
         host_barrier()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
+        for _ in range(steps):
             pipe.run(host_in, host_out, scale=scale)
         torch.cuda.synchronize()
-        dt_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        dt_ms = (time.perf_counter() - t0) * 1e3 / steps
         host_barrier()
         e2e_ms = max_over_ranks(dt_ms)
         e2e = {"value": n * set_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                "ms_per_step": e2e_ms, "h2d_bytes_per_step": pipe.h2d_bytes,
                "d2h_bytes_per_step": pipe.d2h_bytes,
                "path": "pinned host set -> H2D -> fused all-reduce in the symmetric heap -> D2H "
-                       "(HostAllReduce, 8 chunks pipelined on 3 streams)"}
+                       f"(HostAllReduce, {args.e2e_chunks} chunks pipelined on 3 streams)"}
         sess.check()
+        pipe.close()
+        del host_out
+
+    # ---- the same set in the other float width (bf16 when the headline is f32): the
+    # reference has no 16-bit reducers, so this block has no counterpart in its arm
+    other = None
+    other_name = "bf16" if args.dtype == "f32" else "f32"
+    if not args.no_extras:
+        try:
+            o_dtype, o_esize, _, o_flat, o_views, _ = gradient_set(other_name, 4321)
+            check_against_nccl(o_flat, o_views, o_dtype)
+            o_ms, o_launches, _ = timed_device_steps(o_views, False)
+            o_bytes = sum(sizes) * o_esize
+            other = {"dtype": other_name, "set_bytes": o_bytes, "ms_per_step": o_ms,
+                     "value": n * o_bytes / (o_ms * 1e-3) / 1e9, "unit": "GB/s",
+                     "bus_bandwidth_gb_s": 2 * (n - 1) / n * o_bytes / (o_ms * 1e-3) / 1e9,
+                     "gpu_launches": o_launches}
+            sess.symm_free(o_flat)
+        except Exception as e:  # an extra must never cost the headline
+            other = {"dtype": other_name, "error": str(e)[:200]}
 
     bus = 2 * (n - 1) / n * set_bytes / (ms * 1e-3) / 1e9
     out = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": n, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": n, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
         "impl": "ours", "bus_bandwidth_gb_s": bus, "gpu_launches": launches, "clocks": clocks,
-        "e2e": e2e,
-        "config": {"model": args.workload, "tensors": len(sizes), "elements": sum(sizes),
-                   "set_bytes": set_bytes, "global_batch": None, "seq_len": None,
-                   "parallelism": f"dp{n}", "op": "sum, scale 1/N fused",
-                   "memory": "symmetric heap (zero-copy)", "nvls": sess.has_nvls,
-                   "backend": sess.backend, "numa_node": numa_node,
-                   "l2": "inputs (438 MB per rank) are larger than the 126 MB L2; no flush"},
+        "e2e": e2e, "also_" + other_name: other,
+        "config": workload_config(args.workload, sizes, n, args.dtype),
+        "impl_detail": {"memory": "symmetric heap (zero-copy)", "nvls": sess.has_nvls,
+                        "backend": sess.backend, "numa_node": numa_node, "scale": "fused, 1/N",
+                        "l2": f"inputs ({set_bytes >> 20} MB per rank) are larger than the 126 MB "
+                              "L2; no flush"},
     }
-    if rank == 0:
-        print(json.dumps(out), flush=True)
     host_barrier()
     sess.close()
+    if n == 1 and not args.no_extras:
+        # Alone on a GPU an all-reduce is a scaled copy: no barrier, no peer.  So that
+        # a one-GPU run still exercises the collective kernel itself, the same set is
+        # also reduced among 8 ranks emulated on this GPU (one cooperative launch,
+        # every "peer" access an HBM access).  Reported beside the headline, not in it.
+        try:
+            out["kernel_loopback8"] = loopback_kernel_block(args, sizes, steps, warmup)
+        except Exception as e:
+            out["kernel_loopback8"] = {"error": str(e)[:200]}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
     if n > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def loopback_kernel_block(args, sizes, steps, warmup, world=8):
+    import torch
+
+    from stdml_collective_experimental_b200 import DeviceSession
+    esize = 4 if args.dtype == "f32" else 2
+    dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    padded = [-(-s * esize // 16) * 16 // esize for s in sizes]
+    total = sum(padded)
+    with DeviceSession.loopback(world, heap_bytes=total * esize + (32 << 20),
+                                staging_bytes=1 << 20) as sess:
+        flats = sess.symm_empty(total, dtype)
+        for r, f in enumerate(flats):
+            f.normal_(0, 1e-3, generator=torch.Generator(device="cuda").manual_seed(r))
+        views = []
+        for f in flats:
+            off, vs = 0, []
+            for s_, p_ in zip(sizes, padded):
+                vs.append(f[off:off + s_])
+                off += p_
+            views.append(vs)
+        want = torch.stack([f.double() for f in flats]).sum(0) / world
+        sess.group_all_reduce(views, scale=1.0 / world)
+        torch.cuda.synchronize()
+        sess.check()
+        err = float((flats[3].double() - want).abs().max())
+        if not err <= (1e-6 if esize == 4 else 2e-2) * float(want.abs().max()) + 1e-12:
+            raise RuntimeError(f"loopback all-reduce mismatch: {err}")
+        del want
+        for _ in range(warmup):
+            sess.group_all_reduce(views, scale=1.0 / world)
+        l0 = sess.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            sess.group_all_reduce(views, scale=1.0 / world)
+        e1.record()
+        torch.cuda.synchronize()
+        sess.check()
+        ms = e0.elapsed_time(e1) / steps
+        hbm = 2 * world * total * esize  # every rank's set is read once and written once
+        return {"ranks_emulated": world, "ms_per_step": ms, "gpu_launches": sess.launches - l0,
+                "hbm_bytes_per_step": hbm, "hbm_gb_s": hbm / (ms * 1e-3) / 1e9,
+                "kernel": "owner_kernel (bulk-copy two-shot), one cooperative launch per step"}
 
 
 def main():

@@ -92,6 +92,7 @@ def _declare(l):
     l.stdmlc_dw_ptr.argtypes = [vp, c.c_int, u64, vpp]
     l.stdmlc_dw_mc_ptr.argtypes = [vp, u64, vpp]
     l.stdmlc_dw_set_tuning.argtypes = [vp, c.c_int, c.c_longlong, c.c_longlong, c.c_longlong]
+    l.stdmlc_dw_set_knob.argtypes = [vp, c.c_char_p, c.c_longlong]
     l.stdmlc_dw_all_reduce.argtypes = [vp, vpp, vpp, u64, c.c_int, c.c_int, c.c_double, c.c_int, vp]
     l.stdmlc_dw_reduce.argtypes = [vp, vpp, vpp, u64, c.c_int, c.c_int, c.c_int, c.c_double, vp]
     l.stdmlc_dw_group_all_reduce.argtypes = [vp, u64, vpp, vpp, c.POINTER(u64), c.c_int, c.c_int,
@@ -100,7 +101,7 @@ def _declare(l):
     l.stdmlc_dw_broadcast.argtypes = [vp, vpp, vpp, u64, c.c_int, c.c_int, vp]
     l.stdmlc_dw_barrier.argtypes = [vp, vp]
     l.stdmlc_dw_raw_all_reduce.argtypes = [vp, u64, vpp, vpp, u64, c.c_int, c.c_int, c.c_int,
-                                           c.c_int, c.c_int, c.c_int, c.c_int, c.c_float, vp]
+                                           c.c_int, c.c_int, c.c_int, c.c_int, c.c_double, vp]
     l.stdmlc_dw_status.argtypes = [vp, c.POINTER(c.c_int)]
     l.stdmlc_dw_check.argtypes = [vp]
     l.stdmlc_dw_recover.argtypes = [vp]

@@ -43,6 +43,10 @@ def main():
     ap.add_argument("--algos", default="oneshot,twoshot,nvls,nvls_oneshot,auto")
     ap.add_argument("--out", default="")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--configs", default="",
+                    help="extra columns, ';'-separated: ALGO@knob=value,knob=value (knobs of "
+                         "DeviceSession.set_knob), e.g. 'nvls@nvls_variant=2,nvls_blocks=48;"
+                         "twoshot_tma@tma_blocks=64'; run zero-copy on the symmetric buffer")
     args = ap.parse_args()
     rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
     torch.cuda.set_device(local)
@@ -86,6 +90,20 @@ def main():
                 except ValueError:
                     continue
                 row[key] = {"us": ms * 1e3, "busbw": bus(ms)}
+        for cfg in filter(None, args.configs.split(";")):
+            algo, _, knobs = cfg.partition("@")
+            if algo.startswith("nvls") and not sess.has_nvls:
+                continue
+            pairs = [kv.split("=") for kv in filter(None, knobs.split(","))]
+            for k, v in pairs:
+                sess.set_knob(k, int(v))
+            try:
+                ms = timed(lambda: sess.all_reduce(sym[:n], algo=algo), iters, 5, dev)
+                row[cfg] = {"us": ms * 1e3, "busbw": bus(ms)}
+            except ValueError:
+                pass
+            for k, _ in pairs:
+                sess.set_knob(k, {"nvls_variant": 1}.get(k, 0))
         sess.check()
         rows.append(row)
         if rank == 0:

@@ -19,6 +19,15 @@ struct AlgoTuning {
     size_t oneshot_max = 0;       // 0: measured default
     size_t nvls_oneshot_max = 0;  // 0: measured default
     bool has_nvls = false;
+    // two-shot calls of at least this many bytes pull with bulk async copies
+    // (kAlgoTwoShotTma); SIZE_MAX: never
+    size_t tma_min = 1u << 20;
+    // NVLS worlds: owner calls of at least this many bytes prefer the bulk-copy
+    // two-shot over the in-switch reduction (fewer bytes per link direction:
+    // (n-1)/n x S instead of (n+1)/n x S); SIZE_MAX: never
+    size_t tma_over_nvls_min = SIZE_MAX;
+    int nvls_blocks = 0;  // > 0: grid of large NVLS calls
+    int tma_blocks = 0;   // > 0: grid of bulk-copy two-shot calls
 };
 
 inline size_t oneshot_limit(const AlgoTuning &t)
@@ -46,15 +55,16 @@ inline int select_algo(const AlgoTuning &t, size_t bytes, bool nvls_defined_for_
     const bool nvls = t.has_nvls && nvls_defined_for_op && t.world > 2;
     if (nvls) {
         if (!need_owner && bytes <= nvls_oneshot_limit(t)) { return kAlgoNvlsOneShot; }
+        if (bytes >= t.tma_over_nvls_min) { return kAlgoTwoShotTma; }
         return kAlgoNvls;
     }
     if (!need_owner && bytes <= oneshot_limit(t)) { return kAlgoOneShot; }
-    return kAlgoTwoShot;
+    return bytes >= t.tma_min ? kAlgoTwoShotTma : kAlgoTwoShot;
 }
 
 inline int select_blocks(const AlgoTuning &t, size_t nvec, int algo)
 {
-    const bool owner = (algo == kAlgoTwoShot || algo == kAlgoNvls);
+    const bool owner = is_owner_algo(algo);
     const size_t work = owner ? (nvec + t.world - 1) / t.world : nvec;
     const size_t per_block = static_cast<size_t>(kThreads) * 4;
     size_t b = (work + per_block - 1) / per_block;
@@ -62,6 +72,12 @@ inline int select_blocks(const AlgoTuning &t, size_t nvec, int algo)
     if (algo == kAlgoNvls || algo == kAlgoNvlsOneShot) {
         // the switch saturates with few CTAs; more only add contention
         cap = std::min<size_t>(cap, nvec * 16 >= (16u << 20) ? 32 : 64);
+        if (t.nvls_blocks > 0 && nvec * 16 >= (16u << 20)) { cap = static_cast<size_t>(t.nvls_blocks); }
+    }
+    if (algo == kAlgoTwoShotTma) {
+        // one CTA per SM at most (the ring takes the SM's shared memory)
+        cap = static_cast<size_t>(t.tma_blocks > 0 ? t.tma_blocks : t.num_sms);
+        cap = std::min<size_t>(cap, static_cast<size_t>(t.num_sms));
     }
     // alone on the GPU the kernel is an HBM copy: one resident CTA per SM
     if (t.world == 1) { cap = static_cast<size_t>(t.num_sms); }

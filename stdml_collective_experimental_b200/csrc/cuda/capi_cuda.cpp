@@ -156,6 +156,11 @@ int stdmlc_dw_set_tuning(void *h, int max_blocks, long long oneshot_max_bytes,
     });
 }
 
+int stdmlc_dw_set_knob(void *h, const char *name, long long value)
+{
+    return guarded([&] { S(h)->world().set_knob(name != nullptr ? name : "", value); });
+}
+
 int stdmlc_dw_all_reduce(void *h, const void *const *in, void *const *out,
                          unsigned long long count, int dt, int op, double scale, int algo,
                          void *stream)
@@ -207,7 +212,7 @@ int stdmlc_dw_barrier_rows(void *h, int rows, void *stream)
 
 int stdmlc_dw_raw_all_reduce(void *h, unsigned long long off, const void *const *src,
                              void *const *dst, unsigned long long count, int dt, int op, int algo,
-                             int blocks, int root, int end_barrier, int has_scale, float scale,
+                             int blocks, int root, int end_barrier, int has_scale, double scale,
                              void *stream)
 {
     return guarded([&] {

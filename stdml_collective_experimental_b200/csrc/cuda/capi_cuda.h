@@ -46,6 +46,10 @@ int stdmlc_dw_mc_ptr(void *h, unsigned long long off, void **out);
 int stdmlc_dw_set_tuning(void *h, int max_blocks, long long oneshot_max_bytes,
                          long long nvls_oneshot_max_bytes, long long wait_timeout_ms);
 
+/* Named knobs (same value on every rank): nvls_variant, nvls_blocks, tma_blocks,
+ * tma_tile_vec, tma_min_bytes, tma_over_nvls_min_bytes, debug_checks. */
+int stdmlc_dw_set_knob(void *h, const char *name, long long value);
+
 int stdmlc_dw_all_reduce(void *h, const void *const *in, void *const *out,
                          unsigned long long count, int dt, int op, double scale, int algo,
                          void *stream);
@@ -65,7 +69,7 @@ int stdmlc_dw_barrier_rows(void *h, int rows, void *stream);
 /* Launches the kernel as given (no staging, no chunking): for tests and tuning. */
 int stdmlc_dw_raw_all_reduce(void *h, unsigned long long off, const void *const *src,
                              void *const *dst, unsigned long long count, int dt, int op, int algo,
-                             int blocks, int root, int end_barrier, int has_scale, float scale,
+                             int blocks, int root, int end_barrier, int has_scale, double scale,
                              void *stream);
 int stdmlc_dw_status(void *h, int *out7);
 int stdmlc_dw_check(void *h);

@@ -12,6 +12,12 @@
 #include <cstddef>
 #include <cstdint>
 
+#if defined(__CUDACC__)
+#define STDML_HD __host__ __device__
+#else
+#define STDML_HD
+#endif
+
 namespace stdml::collective::cuda
 {
 constexpr int kMaxRanks = 16;     // ranks addressable from one kernel
@@ -66,7 +72,40 @@ enum : int {
     kAlgoTwoShot = 1,      // owner reduces its shard, stores it to all peers
     kAlgoNvls = 2,         // owner multimem.ld_reduce -> multimem.st
     kAlgoNvlsOneShot = 3,  // every rank multimem.ld_reduce of everything
+    kAlgoTwoShotTma = 4,   // two-shot whose pulls are bulk async copies (TMA) of every
+                           // rank's tile into a shared-memory ring; results leave as
+                           // plain 16-byte stores
+    kAlgoCount = 5,
 };
+
+// Owner algorithms: rank r reduces shard r and writes the result into every
+// rank's symmetric buffer, so they can run in place.
+STDML_HD inline bool is_owner_algo(int algo)
+{
+    return algo == kAlgoTwoShot || algo == kAlgoNvls || algo == kAlgoTwoShotTma;
+}
+
+// Shared-memory ring of the bulk-copy two-shot kernel: `stages` slots, each
+// holding one tile of `tile_vec` 16-byte vectors from every rank.
+constexpr int kTmaMaxStages = 16;
+constexpr unsigned int kTmaSmemBudget = 192u << 10;  // bytes of the 227 KB an SM offers
+
+// Ring geometry for a world: the wanted tile (default: one vector per thread),
+// halved until two slots fit the budget, then as many slots as fit.
+inline void tma_geometry(int world, unsigned int want_tile_vec, int *stages,
+                         unsigned int *tile_vec, unsigned int *smem_bytes)
+{
+    unsigned int tv = want_tile_vec > 0 ? want_tile_vec : static_cast<unsigned int>(kThreads);
+    tv = (tv + 31u) / 32u * 32u;
+    while (tv > 32u && 2ull * world * tv * 16ull > kTmaSmemBudget) { tv /= 2; }
+    unsigned int st = static_cast<unsigned int>(
+        kTmaSmemBudget / (static_cast<unsigned long long>(world) * tv * 16ull));
+    if (st > static_cast<unsigned int>(kTmaMaxStages)) { st = kTmaMaxStages; }
+    if (st < 1u) { st = 1u; }
+    *stages = static_cast<int>(st);
+    *tile_vec = tv;
+    *smem_bytes = st * static_cast<unsigned int>(world) * tv * 16u;
+}
 
 // One tensor of a fused group: `count` elements that live at vector offset
 // `voff` (16-byte units) of the flat symmetric region.
@@ -92,8 +131,22 @@ struct AllReduceArgs {
     int end_barrier;  // one-shot: protect an arena-resident input from reuse
     int root;         // >= 0: reduce-to-root (only `root` computes and stores)
     int has_scale;
-    float scale;
+    double scale;     // applied as f64 to f64 buffers, as its f32 value otherwise
     int phases;       // bit 0 pack, bit 1 reduce (with its barriers), bit 2 unpack
+    int nvls_variant; // inner loop of the NVLS reduce: see kNvls* below
+    int tma_stages;   // kAlgoTwoShotTma: slots of the shared-memory ring
+    unsigned int tma_tile_vec;  // kAlgoTwoShotTma: vectors per rank per tile
+    int debug_checks; // != 0: validate offsets / table / alignment in the kernel and
+                      // report kStatusBadArgs instead of touching memory
+};
+
+// NVLS inner loops (all produce the same values; measured against each other).
+enum : int {
+    kNvlsPlain4 = 0,  // 4 loads, then 4 stores per thread and iteration
+    kNvlsPipe4 = 1,   // the loads of iteration i+1 are issued before the stores of i
+    kNvlsPipe8 = 2,   // same with 8 vectors per thread
+    kNvlsPlain8 = 3,
+    kNvlsVariants = 4,
 };
 
 enum : int { kPhasePack = 1, kPhaseReduce = 2, kPhaseUnpack = 4, kPhaseAll = 7 };
@@ -124,6 +177,6 @@ int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op
                       int blocks, int vranks, void *stream);
 bool nvls_supported(int dt, int op);
 // world of one GPU: dst = scale * src (integers: copy), no arena involved
-int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, float scale,
+int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, double scale,
                        int has_scale, int sms, void *stream);
 }  // namespace stdml::collective::cuda

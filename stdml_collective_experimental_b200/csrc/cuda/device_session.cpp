@@ -79,7 +79,14 @@ DeviceSession::~DeviceSession()
 
 void DeviceSession::check()
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     const DeviceStatus s = world_->poll_status();
+    if (s.code == kStatusBadArgs) {
+        throw std::invalid_argument("device collective refused its launch arguments (in-kernel "
+                                    "debug checks): rank " + std::to_string(s.rank) + " block " +
+                                    std::to_string(s.block) + "; nothing was read or written; "
+                                    "call recover() on every rank");
+    }
     if (s.code != 0) {
         throw DeviceTimeout("device collective gave up: rank " + std::to_string(s.rank) +
                                 " block " + std::to_string(s.block) + " waited for rank " +
@@ -166,6 +173,7 @@ void DeviceSession::run_pipelined(std::vector<AllReduceCall> &calls, void *strea
 void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t count, int dt,
                                int op, double scale, int algo, void *stream)
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
     if (count == 0) { return; }
     const size_t es = elem_size(dt);
@@ -175,7 +183,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
     c.op = op;
     c.algo = algo;
     c.has_scale = scale != 1.0;
-    c.scale = static_cast<float>(scale);
+    c.scale = scale;
 
     // zero-copy: the buffer lives at the same arena offset on every rank
     size_t off = world_->offset_of(in[0], 0);
@@ -214,7 +222,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
     size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
     const size_t total_bytes = count * es;
     if (world_->world() > 1 && total_bytes >= pipeline_min_bytes_ && !in_capture &&
-        (algo < 0 || algo == kAlgoTwoShot || algo == kAlgoNvls)) {
+        (algo < 0 || is_owner_algo(algo))) {
         // large message: chunks of about 1/8 of it (8 MB at least, a slot at most)
         const size_t lanes = 16 / es;
         size_t chunk = std::max<size_t>(pipeline_chunk_bytes_ / es,
@@ -264,6 +272,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
 void DeviceSession::reduce(const void *const *in, void *const *out, size_t count, int dt, int op,
                            int root, double scale, void *stream)
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
     if (count == 0) { return; }
     if (root < 0 || root >= world_->world()) { throw std::invalid_argument("reduce: bad root"); }
@@ -285,7 +294,7 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         k.op = op;
         k.root = root;
         k.has_scale = scale != 1.0;
-        k.scale = static_cast<float>(scale);
+        k.scale = scale;
         k.off = world_->next_staging_slot();
         k.src = src.data();
         k.dst = dst.data();
@@ -392,6 +401,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
                                      const size_t *counts, int dt, int op, int user_dt,
                                      double scale, int algo, void *stream)
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
     if (n == 0) { return; }
     const size_t es = elem_size(dt);
@@ -423,7 +433,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
         c.off = first;
         c.count = total / es;
         c.has_scale = scale != 1.0;
-        c.scale = static_cast<float>(scale);
+        c.scale = scale;
         c.algo = algo;
         if (c.algo == kAlgoOneShot || c.algo == kAlgoNvlsOneShot) { c.algo = -1; }
         if (c.algo < 0) { c.algo = world_->pick_algo(total, dt, op, true); }
@@ -435,7 +445,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
     size_t plan_bytes = 0;
     for (const auto &chunk : plan.chunks) { plan_bytes += chunk[0].nvec * 16; }
     if (world_->world() > 1 && plan.chunks.size() >= 2 && plan_bytes >= pipeline_min_bytes_ &&
-        !capturing(stream) && (algo < 0 || algo == kAlgoTwoShot || algo == kAlgoNvls)) {
+        !capturing(stream) && (algo < 0 || is_owner_algo(algo))) {
         std::vector<std::vector<const GroupEntry *>> all_tabs;
         std::vector<AllReduceCall> calls;
         for (const auto &chunk : plan.chunks) {
@@ -448,7 +458,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
             c.ntable = chunk[0].n;
             c.count = chunk[0].nvec * (16 / es);
             c.has_scale = scale != 1.0;
-            c.scale = static_cast<float>(scale);
+            c.scale = scale;
             c.algo = algo >= 0 ? algo : world_->pick_algo(chunk[0].nvec * 16, dt, op, true);
             calls.push_back(c);
         }
@@ -468,7 +478,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
         c.ntable = chunk[0].n;
         c.count = chunk[0].nvec * (16 / es);
         c.has_scale = scale != 1.0;
-        c.scale = static_cast<float>(scale);
+        c.scale = scale;
         c.algo = algo;
         c.end_barrier = capturing(stream);
         launch_ar(c, stream);
@@ -478,6 +488,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
 void DeviceSession::all_gather(const void *const *in, void *const *out, size_t count, int dt,
                                void *stream)
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
     const size_t bytes = count * elem_size(dt);
     if (bytes == 0) { return; }
@@ -506,6 +517,7 @@ void DeviceSession::all_gather(const void *const *in, void *const *out, size_t c
 void DeviceSession::broadcast(const void *const *in, void *const *out, size_t count, int dt,
                               int root, void *stream)
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
     if (root < 0 || root >= world_->world()) { throw std::invalid_argument("broadcast: bad root"); }
     const size_t bytes = count * elem_size(dt);
@@ -535,6 +547,7 @@ void DeviceSession::broadcast(const void *const *in, void *const *out, size_t co
 
 void DeviceSession::barrier(void *stream)
 {
+    std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
     launch_check(world_->barrier(stream), "barrier");
     ++launches_;

@@ -17,6 +17,7 @@
 #include <cstddef>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -98,6 +99,11 @@ class DeviceSession
     const GroupPlan &plan_group(size_t n, const void *const *ins, void *const *outs,
                                 const size_t *counts, int dt, int user_dt);
 
+    // Every public call holds this from its first look at the session's state
+    // to its last launch: calls from several threads of one rank are serialised
+    // (the order in which they reach the stream must still be the same on every
+    // rank: that is the callers' business).
+    std::recursive_mutex mu_;
     std::unique_ptr<DeviceWorld> world_;
     std::map<std::string, GroupPlan> plans_;
     std::vector<void *> table_mem_;

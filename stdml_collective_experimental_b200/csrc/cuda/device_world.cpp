@@ -151,6 +151,16 @@ class World final : public DeviceWorld
     int max_blocks_ = 128;
     size_t oneshot_max_ = 0;       // 0: measured default for this world size
     size_t nvls_oneshot_max_ = 0;  // 0: measured default for this world size
+    size_t tma_min_ = 1u << 20;            // STDML_COLLECTIVE_TMA_MIN_BYTES (-1: never)
+    size_t tma_over_nvls_min_ = SIZE_MAX;  // STDML_COLLECTIVE_TMA_OVER_NVLS_MIN_BYTES
+    int nvls_blocks_ = 0;                  // STDML_COLLECTIVE_NVLS_BLOCKS
+    int tma_blocks_ = 0;                   // STDML_COLLECTIVE_TMA_BLOCKS
+    unsigned int tma_tile_vec_ = 0;        // STDML_COLLECTIVE_TMA_TILE_VEC (0: one vector per thread)
+    int nvls_variant_ = kNvlsPipe4;        // STDML_COLLECTIVE_NVLS_VARIANT
+    bool debug_checks_ = false;            // STDML_COLLECTIVE_DEBUG
+    int debug_inject_ = 0;  // tests: hand the next all_reduce kernel arguments that its
+                            // own checks must refuse (1: misaligned offset, 2: offset
+                            // inside the signal pad); implies debug_checks for that launch
     unsigned long long wait_timeout_ns_;
 
   public:
@@ -178,6 +188,25 @@ class World final : public DeviceWorld
         }
         if (const char *e = std::getenv("STDML_COLLECTIVE_NVLS_ONESHOT_MAX_BYTES")) {
             nvls_oneshot_max_ = static_cast<size_t>(std::atoll(e));
+        }
+        auto env_bytes = [](const char *name, size_t &out) {
+            if (const char *e = std::getenv(name)) {
+                const long long v = std::atoll(e);
+                out = v < 0 ? SIZE_MAX : static_cast<size_t>(v);
+            }
+        };
+        env_bytes("STDML_COLLECTIVE_TMA_MIN_BYTES", tma_min_);
+        env_bytes("STDML_COLLECTIVE_TMA_OVER_NVLS_MIN_BYTES", tma_over_nvls_min_);
+        if (const char *e = std::getenv("STDML_COLLECTIVE_NVLS_BLOCKS")) { nvls_blocks_ = std::atoi(e); }
+        if (const char *e = std::getenv("STDML_COLLECTIVE_TMA_BLOCKS")) { tma_blocks_ = std::atoi(e); }
+        if (const char *e = std::getenv("STDML_COLLECTIVE_TMA_TILE_VEC")) {
+            tma_tile_vec_ = static_cast<unsigned int>(std::max(0, std::atoi(e)));
+        }
+        if (const char *e = std::getenv("STDML_COLLECTIVE_NVLS_VARIANT")) {
+            nvls_variant_ = std::max(0, std::min(kNvlsVariants - 1, std::atoi(e)));
+        }
+        if (const char *e = std::getenv("STDML_COLLECTIVE_DEBUG")) {
+            debug_checks_ = std::atoi(e) != 0;
         }
 
         const size_t staging = round_up(std::max<size_t>(o.staging_bytes, 4096), 4096);
@@ -262,6 +291,29 @@ class World final : public DeviceWorld
         if (nvls_oneshot_max_bytes != SIZE_MAX) { nvls_oneshot_max_ = nvls_oneshot_max_bytes; }
     }
 
+    void set_knob(const std::string &name, long long value) override
+    {
+        if (name == "nvls_variant") {
+            nvls_variant_ = static_cast<int>(std::max<long long>(0, std::min<long long>(kNvlsVariants - 1, value)));
+        } else if (name == "nvls_blocks") {
+            nvls_blocks_ = static_cast<int>(std::max<long long>(0, std::min<long long>(kMaxBlocks, value)));
+        } else if (name == "tma_blocks") {
+            tma_blocks_ = static_cast<int>(std::max<long long>(0, std::min<long long>(kMaxBlocks, value)));
+        } else if (name == "tma_tile_vec") {
+            tma_tile_vec_ = static_cast<unsigned int>(std::max<long long>(0, value));
+        } else if (name == "tma_min_bytes") {
+            tma_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "tma_over_nvls_min_bytes") {
+            tma_over_nvls_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "debug_checks") {
+            debug_checks_ = value != 0;
+        } else if (name == "debug_inject") {
+            debug_inject_ = static_cast<int>(value);
+        } else {
+            throw std::invalid_argument("device world: unknown knob '" + name + "'");
+        }
+    }
+
     // ------------------------------------------------------- algorithm table
     AlgoTuning tuning() const
     {
@@ -273,6 +325,10 @@ class World final : public DeviceWorld
         t.oneshot_max = oneshot_max_;
         t.nvls_oneshot_max = nvls_oneshot_max_;
         t.has_nvls = has_nvls();
+        t.tma_min = tma_min_;
+        t.tma_over_nvls_min = tma_over_nvls_min_;
+        t.nvls_blocks = nvls_blocks_;
+        t.tma_blocks = tma_blocks_;
         return t;
     }
 
@@ -339,7 +395,8 @@ class World final : public DeviceWorld
         }
         int algo = c.algo;
         if (algo < 0) { algo = pick_algo(bytes, c.dt, c.op, any_dst_null); }
-        const bool owner = (algo == kAlgoTwoShot || algo == kAlgoNvls);
+        if (algo >= kAlgoCount) { throw std::invalid_argument("all_reduce: unknown algorithm"); }
+        const bool owner = is_owner_algo(algo);
         const bool nvls = (algo == kAlgoNvls || algo == kAlgoNvlsOneShot);
         if (!owner && any_dst_null && c.table == nullptr && c.root < 0) {
             throw std::invalid_argument("all_reduce: one-shot algorithms need a destination");
@@ -360,6 +417,7 @@ class World final : public DeviceWorld
             blocks = std::max(blocks, pick_blocks(nvec, algo == kAlgoNvls ? kAlgoTwoShot
                                                                           : kAlgoOneShot));
         }
+        if (algo == kAlgoTwoShotTma) { blocks = std::min(blocks, num_sms_); }
         if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
         blocks = std::min(blocks, kMaxBlocks);
 
@@ -381,6 +439,20 @@ class World final : public DeviceWorld
         a.has_scale = c.has_scale ? 1 : 0;
         a.scale = c.scale;
         a.phases = c.phases;
+        a.nvls_variant = nvls_variant_;
+        a.debug_checks = debug_checks_ ? 1 : 0;
+        if (debug_inject_ != 0) {
+            // after the host-side validation, on purpose: this is what the kernel's
+            // self-check exists to catch.  The kernel returns before any access.
+            a.debug_checks = 1;
+            if (debug_inject_ == 1) { a.off += 8; }
+            if (debug_inject_ == 2) { a.off = 64; }
+            debug_inject_ = 0;
+        }
+        if (algo == kAlgoTwoShotTma) {
+            unsigned int smem = 0;
+            tma_geometry(opt_.world, tma_tile_vec_, &a.tma_stages, &a.tma_tile_vec, &smem);
+        }
         if ((c.phases & kPhaseReduce) == 0) {
             // a local copy phase: no peer waits, any grid will do
             blocks = static_cast<int>(std::min<size_t>(

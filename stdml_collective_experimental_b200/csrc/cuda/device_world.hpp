@@ -61,7 +61,7 @@ struct AllReduceCall {
     int root = -1;
     bool end_barrier = false;
     bool has_scale = false;
-    float scale = 1.0f;
+    double scale = 1.0;  // f64 buffers use all of it; other float types its f32 value
     int phases = 7;  // kPhasePack | kPhaseReduce | kPhaseUnpack
 };
 
@@ -127,6 +127,11 @@ class DeviceWorld
     virtual void set_wait_timeout_ms(unsigned long long ms) = 0;
     virtual void set_tuning(int max_blocks, size_t oneshot_max_bytes,
                             size_t nvls_oneshot_max_bytes) = 0;
+    // Named tuning knobs (each also has an environment variable, read at
+    // creation): nvls_variant, nvls_blocks, tma_blocks, tma_tile_vec,
+    // tma_min_bytes, tma_over_nvls_min_bytes (negative: never), debug_checks.
+    // Every rank must set the same values.
+    virtual void set_knob(const std::string &name, long long value) = 0;
 };
 
 // true when a usable CUDA device is present (never throws)

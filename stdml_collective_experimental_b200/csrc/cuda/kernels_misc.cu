@@ -33,7 +33,7 @@ int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op
 template <int DT>
 __global__ void __launch_bounds__(256)
     local_scale_kernel(const void *src, void *dst,
-                       unsigned long long count, float scale, int has_scale)
+                       unsigned long long count, double scale, int has_scale)
 {
     constexpr unsigned long long N = lanes_of<DT>();
     const unsigned long long nvec = (count + N - 1) / N;
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256)
 }
 
 template <int DT>
-static int launch_local_dt(const void *src, void *dst, unsigned long long count, float scale,
+static int launch_local_dt(const void *src, void *dst, unsigned long long count, double scale,
                            int has_scale, int sms, cudaStream_t s)
 {
     constexpr unsigned long long N = lanes_of<DT>();
@@ -79,7 +79,7 @@ static int launch_local_dt(const void *src, void *dst, unsigned long long count,
     return static_cast<int>(cudaGetLastError());
 }
 
-int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, float scale,
+int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, double scale,
                        int has_scale, int sms, void *stream)
 {
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -142,7 +142,7 @@ extern "C" int stdmlc_all_reduce_noalloc(const void *const *in, void *const *out
     a.user_dtype = dt;
     a.root = -1;
     a.has_scale = scale != 1.0 ? 1 : 0;
-    a.scale = static_cast<float>(scale);
+    a.scale = scale;
     a.phases = kPhaseAll;
 
     // all rows of the grid wait on one another: they must be resident together

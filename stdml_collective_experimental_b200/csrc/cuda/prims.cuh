@@ -290,7 +290,9 @@ struct Accum {
         for (int i = 0; i < N; ++i) { a[i] = combine<OP>(a[i], Tr<DT>::widen(u.e[i])); }
     }
 
-    __device__ __forceinline__ uint4 finish(float scale, bool has_scale) const
+    // `scale` is used in the accumulator's type: all 53 bits for f64, its f32
+    // value for f32 and the 16-bit floats (as the host reducers do)
+    __device__ __forceinline__ uint4 finish(double scale, bool has_scale) const
     {
         VecU<DT> u;
 #pragma unroll
@@ -306,7 +308,7 @@ struct Accum {
 };
 
 template <int DT>
-__device__ __forceinline__ uint4 scale_vec(const uint4 &x, float scale)
+__device__ __forceinline__ uint4 scale_vec(const uint4 &x, double scale)
 {
     Accum<DT> a;
     a.init(x);

@@ -21,6 +21,7 @@
 #include <future>
 #include <iterator>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <utility>
 #include <vector>
@@ -49,6 +50,7 @@ class session
     std::unique_ptr<runtime> async_runtime_;
     std::unique_ptr<cuda::DeviceSession> device_;
     bool device_tried_ = false;
+    std::shared_ptr<std::mutex> device_mu_ = std::make_shared<std::mutex>();  // guards device_'s creation
     int spin_polls_ = 0;  // looks at a mailbox before a receiver sleeps (see session.cpp)
     bool established_ = false;  // the constructor's barrier has completed
     // Two-level execution for members on several hosts (built on first use,
@@ -102,6 +104,8 @@ class session
 
   public:
     static constexpr size_t chunk_bytes = 1u << 20;
+    // group_all_reduce(futures): device tensors are fused in buckets of about this size
+    static constexpr size_t group_bucket_bytes = 64u << 20;
     static constexpr size_t tiny_chunk_bytes = 512u << 10;  // handled without helper threads (measured: star, 4 ranks, 64 KB +80 %, 400 KB +45 %; 1 MB chunks -15 %)
 
     mailbox *mailbox_;                 // owned by peer
@@ -138,6 +142,10 @@ class session
 
     void barrier();
 
+    // Kernels this session has launched on the device so far (0 before its first
+    // device call): lets callers and tests see how many launches a call cost.
+    unsigned long long device_launches() const;
+
     // true once a receive of this session has failed or a member has told us
     // that it gave up: the session is of no further use (see peer::recover)
     bool given_up() const;
@@ -145,8 +153,12 @@ class session
     void abort() noexcept;
 
     void all_reduce(const workspace &w, void *stream = nullptr);
-    // Blocks until every tensor is reduced.  Tensors may become ready in any
-    // order and in different orders on different ranks.
+    // Blocks until every tensor is reduced (device tensors: until every launch
+    // is enqueued on the default stream).  Tensors may become ready in any order
+    // and in different orders on different ranks.  Device tensors are reduced by
+    // fused launches over buckets of consecutive tensors (same dtype and
+    // operator, about group_bucket_bytes each), issued from the calling thread in
+    // list order; host tensors run on worker threads in list order.
     void group_all_reduce(std::vector<std::future<workspace>> ws);
     // Same for tensors that are ready now; on device pointers this is ONE fused
     // launch per staging slot, with `scale` applied in the kernel.

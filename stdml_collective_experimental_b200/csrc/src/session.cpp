@@ -1,6 +1,8 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <condition_variable>
+#include <deque>
 #include <cstdlib>
 #include <cstring>
 #include <numeric>
@@ -693,13 +695,20 @@ void session::group_all_reduce(const std::vector<workspace> &ws, double scale, v
 
 void session::group_all_reduce(std::vector<std::future<workspace>> fs)
 {
-    // Tensors are handed to a small set of workers strictly in submission
-    // order, which is the same on every rank (futures are positional).  The
-    // earliest unfinished tensor is therefore always being worked on by every
-    // rank, whatever order the futures resolve in, so the group cannot
-    // deadlock (the reference runs each tensor on an ad-hoc pool of 76 threads
-    // as it becomes ready, which deadlocks for larger sets:
-    // src/stdml/collective/session.cpp:83-97).
+    // ONE thread (the caller's) takes the futures in submission order, which is
+    // the same on every rank (futures are positional), whatever order they
+    // resolve in.
+    //   * Host tensors go, in that order, to a small set of workers.  The
+    //     earliest unfinished tensor is therefore always being worked on by every
+    //     rank, so the group cannot deadlock (the reference runs each tensor on
+    //     an ad-hoc pool of 76 threads as it becomes ready, which deadlocks for
+    //     larger sets: src/stdml/collective/session.cpp:83-97).
+    //   * Device tensors are collected into buckets and every bucket is ONE
+    //     fused launch, issued by this thread only.  A bucket ends where the
+    //     dtype or the operator changes, where a host tensor comes in between,
+    //     and once it holds group_bucket_bytes: all of these depend on the list
+    //     alone, never on when a future resolved, so every rank cuts the same
+    //     buckets and the kernels of different ranks pair up.
     const size_t n = fs.size();
     if (n == 0) { return; }
     size_t workers = 8;
@@ -708,10 +717,18 @@ void session::group_all_reduce(std::vector<std::future<workspace>> fs)
         workers = std::max<size_t>(1, std::min<size_t>(8, pool_->size() / fan));
     }
     workers = std::min(workers, n);
-    std::atomic<size_t> next{0};
+
+    std::mutex mu;
+    std::condition_variable cv;
+    std::deque<workspace> host_q;
+    bool closed = false;
     std::atomic<bool> failed{false};
-    std::mutex err_mu;
     std::exception_ptr err;
+    auto note_error = [&] {
+        failed.store(true);
+        std::lock_guard<std::mutex> lk(mu);
+        if (!err) { err = std::current_exception(); }
+    };
     auto work = [&] {
         struct in_group {
             bool saved = tl_in_group;
@@ -719,21 +736,66 @@ void session::group_all_reduce(std::vector<std::future<workspace>> fs)
             ~in_group() { tl_in_group = saved; }
         } mark;
         for (;;) {
-            const size_t i = next.fetch_add(1);
-            if (i >= n) { return; }
+            workspace w;
+            {
+                std::unique_lock<std::mutex> lk(mu);
+                cv.wait(lk, [&] { return closed || !host_q.empty(); });
+                if (host_q.empty()) { return; }
+                w = host_q.front();
+                host_q.pop_front();
+            }
             try {
-                const workspace w = fs[i].get();
                 if (!failed.load()) { all_reduce(w); }
             } catch (...) {
-                failed.store(true);
-                std::lock_guard<std::mutex> lk(err_mu);
-                if (!err) { err = std::current_exception(); }
+                note_error();
             }
         }
     };
-    std::vector<std::thread> ths;
-    for (size_t t = 1; t < workers; ++t) { ths.emplace_back(work); }
-    work();
+    std::vector<std::thread> ths;  // started when the first host tensor shows up
+
+    std::vector<workspace> bucket;
+    size_t bucket_bytes = 0;
+    auto flush = [&] {
+        if (bucket.empty()) { return; }
+        std::vector<workspace> b;
+        b.swap(bucket);
+        bucket_bytes = 0;
+        if (!failed.load()) { group_all_reduce(b, 1.0, nullptr); }
+    };
+    for (size_t i = 0; i < n; ++i) {
+        try {
+            const workspace w = fs[i].get();
+            if (failed.load() || w.count == 0) { continue; }
+            if (on_device(w.send, w.recv)) {
+                if (!bucket.empty() && (bucket[0].dt != w.dt || bucket[0].op != w.op)) { flush(); }
+                bucket.push_back(w);
+                bucket_bytes += w.count * dtype_size(w.dt);
+                if (bucket_bytes >= group_bucket_bytes) { flush(); }
+            } else {
+                flush();
+                if (ths.empty()) {
+                    for (size_t t = 0; t < workers; ++t) { ths.emplace_back(work); }
+                }
+                {
+                    std::lock_guard<std::mutex> lk(mu);
+                    host_q.push_back(w);
+                }
+                cv.notify_one();
+            }
+        } catch (...) {
+            note_error();
+        }
+    }
+    try {
+        flush();
+    } catch (...) {
+        note_error();
+    }
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        closed = true;
+    }
+    cv.notify_all();
     for (auto &t : ths) { t.join(); }
     if (err) { std::rethrow_exception(err); }
 }
@@ -1054,8 +1116,16 @@ bool session::on_device(const void *a, const void *b) const
     return ka == 1;
 }
 
+unsigned long long session::device_launches() const
+{
+    std::lock_guard<std::mutex> lk(*device_mu_);
+    return device_ ? device_->launches() : 0ull;
+}
+
 cuda::DeviceSession *session::device()
 {
+    // several threads of one rank may reach their first device call together
+    std::lock_guard<std::mutex> lk(*device_mu_);
     if (device_) { return device_.get(); }
     if (device_tried_) { throw std::runtime_error("device collectives are unavailable"); }
     device_tried_ = true;

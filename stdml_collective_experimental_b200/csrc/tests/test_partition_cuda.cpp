@@ -26,7 +26,8 @@ static int failures = 0;
 int main()
 {
     std::mt19937_64 rng(7);
-    // spans: contiguous, ordered, exact cover, balanced within one vector
+    // spans: contiguous, ordered, exact cover, every boundary but the buffer's end on a
+    // 512-byte granule, balanced within one granule
     for (int trial = 0; trial < 20000; ++trial) {
         const unsigned long long nvec = rng() % (trial % 3 == 0 ? 50 : 5000000) ;
         const int shards = 1 + static_cast<int>(rng() % 16);
@@ -37,13 +38,15 @@ int main()
             for (int b = 0; b < nb; ++b) {
                 const Span sp = span_of(nvec, shards, s, nb, b);
                 EXPECT(sp.lo == expect && sp.hi >= sp.lo && sp.hi <= nvec);
+                EXPECT(sp.lo % kSpanGranule == 0 || sp.lo == nvec);
+                EXPECT(sp.hi % kSpanGranule == 0 || sp.hi == nvec);
                 expect = sp.hi;
                 lo_min = sp.lo < lo_min ? sp.lo : lo_min;
                 const unsigned long long len = sp.hi - sp.lo;
                 len_min = len < len_min ? len : len_min;
                 len_max = len > len_max ? len : len_max;
             }
-            EXPECT(len_max - len_min <= 1);
+            EXPECT(len_max - len_min <= 2 * kSpanGranule);
         }
         EXPECT(expect == nvec);
     }
@@ -156,12 +159,21 @@ int main()
         AlgoTuning t2 = t8;
         t2.world = 2;
         EXPECT(select_algo(t2, 8 << 20, true, false) == kAlgoOneShot);  // the switch adds nothing at 2
+        EXPECT(select_algo(t2, 1 << 30, true, false) == kAlgoTwoShotTma);  // large: bulk-copy pulls
+        t2.tma_min = SIZE_MAX;
         EXPECT(select_algo(t2, 1 << 30, true, false) == kAlgoTwoShot);
         AlgoTuning t4 = t8;
         t4.world = 4;
         t4.has_nvls = false;
         EXPECT(select_algo(t4, 1 << 20, true, false) == kAlgoOneShot);
+        EXPECT(select_algo(t4, (1 << 20) + 16, true, false) == kAlgoTwoShotTma);
+        t4.tma_min = 64u << 20;
         EXPECT(select_algo(t4, (1 << 20) + 16, true, false) == kAlgoTwoShot);
+        EXPECT(select_algo(t4, 64u << 20, true, true) == kAlgoTwoShotTma);
+        t8.tma_over_nvls_min = 32u << 20;  // NVLS worlds may prefer it from some size up
+        EXPECT(select_algo(t8, 16u << 20, true, true) == kAlgoNvls);
+        EXPECT(select_algo(t8, 32u << 20, true, true) == kAlgoTwoShotTma);
+        t8.tma_over_nvls_min = SIZE_MAX;
         AlgoTuning t1;
         EXPECT(select_algo(t1, 1 << 20, true, false) == kAlgoOneShot);
         EXPECT(select_algo(t1, 1 << 20, true, true) == kAlgoTwoShot);
@@ -175,6 +187,22 @@ int main()
         EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoTwoShot) == 128);
         EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoOneShot) == 128);
         EXPECT(select_blocks(t1, (1ull << 30) / 16, kAlgoTwoShot) == 148);
+        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoTwoShotTma) == 148);  // one CTA per SM
+        t8.tma_blocks = 64;
+        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoTwoShotTma) == 64);
+        t8.tma_blocks = 0;
+        {   // ring geometry: at least two slots, inside the budget, whole granules
+            for (int w = 1; w <= kMaxRanks; ++w) {
+                for (unsigned int want : {0u, 64u, 256u, 512u, 1000u, 4096u}) {
+                    int st = 0;
+                    unsigned int tv = 0, bytes = 0;
+                    tma_geometry(w, want, &st, &tv, &bytes);
+                    EXPECT(st >= 2 && st <= kTmaMaxStages && tv >= 32 && tv % 32 == 0);
+                    EXPECT(bytes == st * w * tv * 16u && bytes <= kTmaSmemBudget);
+                    EXPECT(w * tv * 16u < (1u << 20));  // one slot's bytes fit an mbarrier's count
+                }
+            }
+        }
         AlgoTuning loop = t8;
         loop.vranks = 8;
         loop.has_nvls = false;
@@ -183,7 +211,7 @@ int main()
             AlgoTuning t;
             t.world = w;
             for (unsigned long long nv : {1ull, 7ull, 4096ull, 1ull << 26}) {
-                for (int algo = 0; algo < 4; ++algo) {
+                for (int algo = 0; algo < kAlgoCount; ++algo) {
                     const int b = select_blocks(t, nv, algo);
                     EXPECT(b >= 1 && b <= kMaxBlocks);
                 }

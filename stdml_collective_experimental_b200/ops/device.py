@@ -17,8 +17,9 @@ import torch
 
 from .. import _native
 
-ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_NVLS_ONESHOT = 0, 1, 2, 3
-_ALGOS = {None: -1, "auto": -1, "oneshot": 0, "twoshot": 1, "nvls": 2, "nvls_oneshot": 3}
+ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_NVLS_ONESHOT, ALGO_TWOSHOT_TMA = 0, 1, 2, 3, 4
+_ALGOS = {None: -1, "auto": -1, "oneshot": 0, "twoshot": 1, "nvls": 2, "nvls_oneshot": 3,
+          "twoshot_tma": 4}
 
 _DTYPES = {
     torch.int8: 0, torch.int16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4,
@@ -174,6 +175,12 @@ class DeviceSession:
                    wait_timeout_ms=-1):
         _native.check(self._lib.stdmlc_dw_set_tuning(self._h, max_blocks, oneshot_max_bytes,
                                                      nvls_oneshot_max_bytes, wait_timeout_ms))
+
+    def set_knob(self, name, value):
+        """Named tuning knob, same value on every rank: nvls_variant (0..3),
+        nvls_blocks, tma_blocks, tma_tile_vec, tma_min_bytes,
+        tma_over_nvls_min_bytes (negative: never), debug_checks."""
+        _native.check(self._lib.stdmlc_dw_set_knob(self._h, name.encode(), int(value)))
 
     # ---------------------------------------------------------- symmetric heap
     def symm_empty(self, shape, dtype=torch.float32):

@@ -14,10 +14,12 @@ _REASONS = {
 
 
 class ClockSampler:
-    def __init__(self, device_index=0, period_s=0.01):
+    def __init__(self, device_index=0, period_s=0.002):
         self.device_index = device_index
         self.period_s = period_s
         self.samples = []
+        self.stamps = []      # perf_counter() of every sample
+        self.window = [None, None]  # the timed region, see mark_begin / mark_end
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
@@ -40,6 +42,7 @@ class ClockSampler:
         if True:
             try:
                 self.samples.append(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
+                self.stamps.append(time.perf_counter())
                 mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle) if hasattr(
                     n, "nvmlDeviceGetCurrentClocksEventReasons") else \
                     n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
@@ -61,6 +64,14 @@ class ClockSampler:
             self._thread.start()
         return self
 
+    def mark_begin(self):
+        """The timed region starts now (the sampler may have been running through
+        the warm-up already, so that short regions still see the GPU under load)."""
+        self.window[0] = time.perf_counter()
+
+    def mark_end(self):
+        self.window[1] = time.perf_counter()
+
     def stop(self):
         if self._thread is not None:
             self._sample()  # one more while the GPU is still busy or just done
@@ -73,5 +84,12 @@ class ClockSampler:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
                     "samples": 0}
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        lo, hi = self.window
+        inside = [c for c, t in zip(self.samples, self.stamps)
+                  if lo is not None and hi is not None and lo <= t <= hi]
+        # a region of a few milliseconds holds few samples: then the median is taken
+        # over everything since start(), which is warm-up plus region, all under load
+        used = inside if len(inside) >= 3 else self.samples
+        return {"sm_mhz": statistics.median(used), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "samples_in_timed_region": len(inside)}

@@ -41,7 +41,7 @@ def main():
                                   wait_timeout_ms=20000)
     assert sess.rank == rank and sess.world == world
     info = f"backend={sess.backend} nvls={sess.has_nvls}"
-    algos = ["oneshot", "twoshot"] + (["nvls", "nvls_oneshot"] if sess.has_nvls else [])
+    algos = ["oneshot", "twoshot", "twoshot_tma"] + (["nvls", "nvls_oneshot"] if sess.has_nvls else [])
 
     # ---- all_reduce: dtype x op x size, default algorithm choice (staged path)
     for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int32,
@@ -81,7 +81,7 @@ def main():
                     assert bits_equal(got, want), (algo, dtype, n)
 
     # ---- zero-copy symmetric buffers, every owner algorithm
-    for algo in [a for a in algos if a in ("twoshot", "nvls")]:
+    for algo in [a for a in algos if a in ("twoshot", "twoshot_tma", "nvls")]:
         n = 1_000_003
         host = inputs(world, n, torch.float32, seed=99, exact=True)
         want = reduce_many(host, "sum")
@@ -94,6 +94,28 @@ def main():
         assert sess.launches == before + 1
         assert bits_equal(sym.cpu(), want), algo
         sess.symm_free(sym)
+
+    # ---- every inner loop of the NVLS reduce and several ring geometries of the
+    # bulk-copy two-shot give the same values
+    n = 3_000_017
+    host = inputs(world, n, torch.float32, seed=5, exact=True)
+    want = reduce_many(host, "sum")
+    sym = sess.symm_empty(n, torch.float32)
+    cases = [("twoshot_tma", "tma_tile_vec", v) for v in (32, 256, 512)]
+    cases += [("twoshot_tma", "tma_blocks", v) for v in (1, 7, 148)]
+    if sess.has_nvls:
+        cases += [("nvls", "nvls_variant", v) for v in (0, 1, 2, 3)]
+        cases += [("nvls", "nvls_blocks", v) for v in (16, 64)]
+    for algo, knob, value in cases:
+        sess.set_knob(knob, value)
+        sym.copy_(host[rank])
+        sess.all_reduce(sym, algo=algo)
+        torch.cuda.synchronize()
+        sess.check()
+        assert bits_equal(sym.cpu(), want), (algo, knob, value)
+    for knob, value in (("tma_tile_vec", 0), ("tma_blocks", 0), ("nvls_variant", 1), ("nvls_blocks", 0)):
+        sess.set_knob(knob, value)
+    sess.symm_free(sym)
 
     # ---- fused group, f32 and bf16-wire
     sizes = [1, 7, 768, 3, 2304, 590_000, 5, 64, 1000, 1_234_567, 2, 768]

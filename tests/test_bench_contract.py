@@ -35,7 +35,15 @@ def test_reference_arm_prints_the_agreed_json_line():
                 "higher_is_better", "scaling", "dtype", "data", "config"):
         assert key in line, key
     assert line["n_gpus"] == 2 and line["steps"] == 2 and line["value"] > 0
-    assert line["config"]["tensors"] == 161 and line["config"]["transport"] == "tcp-loopback"
+    assert line["config"]["tensors"] == 161 and line["impl_detail"]["transport"] == "tcp-loopback"
+    # end to end on host memory is what the reference measures: it says so itself
+    assert line["e2e"]["value"] == line["value"] and line["e2e"]["unit"] == "GB/s"
+    assert line["e2e"]["h2d_bytes_per_step"] == 0
+    # both arms describe the workload with the same keys and values
+    sys.path.insert(0, ROOT)
+    import bench
+    from stdml_collective_experimental_b200.models.gradsets import gradset_sizes
+    assert line["config"] == bench.workload_config("resnet50", gradset_sizes("resnet50"), 2, "f32")
 
 
 def test_reference_arm_reports_unsupported_dtype():

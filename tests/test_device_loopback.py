@@ -8,7 +8,7 @@ pytestmark = pytest.mark.gpu
 
 from stdml_collective_experimental_b200 import DeviceSession, DeviceTimeoutError  # noqa: E402
 from stdml_collective_experimental_b200.ops.device import (ALGO_ONESHOT,  # noqa: E402
-                                                           ALGO_TWOSHOT)
+                                                           ALGO_TWOSHOT, ALGO_TWOSHOT_TMA)
 from stdml_collective_experimental_b200.utils.oracle import reduce_many  # noqa: E402
 
 FLOATS = [torch.float32, torch.float64, torch.bfloat16, torch.float16]
@@ -132,6 +132,101 @@ def test_raw_algorithms_agree(sess):
                                                    blocks)
     sess.check()
     sess.symm_free(sym)
+
+
+@pytest.mark.parametrize("dtype,op", [(torch.float32, "sum"), (torch.bfloat16, "sum"),
+                                      (torch.float64, "prod"), (torch.int32, "max"),
+                                      (torch.uint8, "bit_xor"), (torch.float16, "min")])
+def test_bulk_copy_two_shot_matches_the_oracle(sess, dtype, op):
+    """The two-shot whose owner pulls tiles with bulk async copies into a shared
+    memory ring: every dtype path, grids of 1..16 CTAs per rank, tiles small enough
+    that each ring slot is reused many times (both mbarrier parities), ragged
+    sizes (partial last tile, partial last vector)."""
+    if sess.world == 1:
+        pytest.skip("a world of one has no peers to pull from")
+    for tile_vec, n, blocks in [(0, 1, 1), (0, 33, 3), (64, 4099, 1), (32, 70_001, 2),
+                                (128, 1_000_003, 1), (0, 1_000_003, 16), (64, 262_144, 16)]:
+        sess.set_knob("tma_tile_vec", tile_vec)
+        host = make_inputs(sess.world, n, dtype, seed=n + blocks, small=(op == "prod"))
+        scale = 0.5 if dtype.is_floating_point else None
+        want = reduce_many(host, op, 1.0 if scale is None else scale)
+        sym = sess.symm_empty(n, dtype)
+        src = [h.cuda() for h in host]
+        dst = [torch.empty_like(x) for x in src]
+        sess.raw_all_reduce(sym, src=src, dst=dst, op=op, algo=ALGO_TWOSHOT_TMA, blocks=blocks,
+                            scale=scale)
+        torch.cuda.synchronize()
+        sess.check()
+        for r in range(sess.world):
+            assert same(dst[r].cpu(), want), (dtype, op, n, blocks, tile_vec, r)
+            assert same(sym[r][:n].cpu(), want), "the result also stays in the symmetric buffer"
+        sess.symm_free(sym)
+    sess.set_knob("tma_tile_vec", 0)
+
+
+def test_bulk_copy_two_shot_through_the_public_calls(sess):
+    """Staged (several 1 MiB slots, pack and unpack fused) and zero-copy in place."""
+    n = (3 << 20) // 4 + 13
+    host = make_inputs(sess.world, n, torch.float32, seed=21)
+    want = reduce_many(host, "sum", 1.0 / sess.world)
+    dev = [h.cuda() for h in host]
+    sess.all_reduce(dev if sess.vranks > 1 else dev[0], scale=1.0 / sess.world, algo="twoshot_tma")
+    sym = sess.symm_empty(n, torch.float32)
+    syms = sym if sess.vranks > 1 else [sym]
+    for r in range(sess.world):
+        syms[r].copy_(host[r])
+    sess.all_reduce(sym, scale=1.0 / sess.world, algo="twoshot_tma")
+    torch.cuda.synchronize()
+    sess.check()
+    for r in range(sess.world):
+        assert same(dev[r].cpu(), want) and same(syms[r].cpu(), want)
+    sess.symm_free(sym)
+
+
+def test_f64_scale_keeps_all_its_bits(sess):
+    """1/3 is not a float: f64 buffers must be scaled in double, like the host reducer."""
+    n = 10_007
+    host = make_inputs(sess.world, n, torch.float64, seed=9)
+    want = reduce_many(host, "sum", 1.0 / 3.0)
+    assert torch.allclose(want, torch.stack(host).sum(0) / 3.0, rtol=1e-15, atol=0)
+    for algo in ("oneshot", "twoshot", "twoshot_tma"):
+        if sess.world == 1 and algo == "twoshot_tma":
+            continue
+        dev = [h.cuda() for h in host]
+        sess.all_reduce(dev if sess.vranks > 1 else dev[0], scale=1.0 / 3.0, algo=algo)
+        torch.cuda.synchronize()
+        sess.check()
+        for r in range(sess.world):
+            assert same(dev[r].cpu(), want), algo
+
+
+def test_kernel_refuses_arguments_that_fail_its_own_checks():
+    """With debug checks on, a kernel handed a misaligned offset (or one inside the
+    signal pad) reports kStatusBadArgs and touches nothing; recover() clears it."""
+    with DeviceSession.loopback(2, heap_bytes=8 << 20, staging_bytes=1 << 20) as s:
+        for inject, algo in [(1, ALGO_TWOSHOT), (2, ALGO_TWOSHOT_TMA), (1, ALGO_ONESHOT)]:
+            sym = s.symm_empty(4096, torch.float32)
+            src = [torch.ones(4096, device="cuda") for _ in range(2)]
+            dst = [torch.full((4096,), -7.0, device="cuda") for _ in range(2)]
+            for t in sym:
+                t.fill_(3.0)
+            s.set_knob("debug_inject", inject)
+            s.raw_all_reduce(sym, src=src, dst=dst, algo=algo, blocks=2)
+            torch.cuda.synchronize()
+            assert s.status()[0] == 2  # kStatusBadArgs
+            with pytest.raises(ValueError):
+                s.check()
+            assert all(bool((d == -7.0).all()) for d in dst) and all(bool((t == 3.0).all()) for t in sym)
+            s.recover()
+            assert s.status()[0] == 0
+            # and the same call runs normally afterwards, with the checks on
+            s.set_knob("debug_checks", 1)
+            s.raw_all_reduce(sym, src=src, dst=dst, algo=algo, blocks=2)
+            torch.cuda.synchronize()
+            s.check()
+            assert bool((dst[0] == 2.0).all()) and bool((dst[1] == 2.0).all())
+            s.set_knob("debug_checks", 0)
+            s.symm_free(sym)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
