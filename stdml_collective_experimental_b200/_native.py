@@ -93,6 +93,7 @@ def _declare(l):
     l.stdmlc_dw_mc_ptr.argtypes = [vp, u64, vpp]
     l.stdmlc_dw_set_tuning.argtypes = [vp, c.c_int, c.c_longlong, c.c_longlong, c.c_longlong]
     l.stdmlc_dw_set_knob.argtypes = [vp, c.c_char_p, c.c_longlong]
+    l.stdmlc_dw_drop_registrations.argtypes = [vp]
     l.stdmlc_dw_all_reduce.argtypes = [vp, vpp, vpp, u64, c.c_int, c.c_int, c.c_double, c.c_int, vp]
     l.stdmlc_dw_reduce.argtypes = [vp, vpp, vpp, u64, c.c_int, c.c_int, c.c_int, c.c_double, vp]
     l.stdmlc_dw_group_all_reduce.argtypes = [vp, u64, vpp, vpp, c.POINTER(u64), c.c_int, c.c_int,

@@ -85,6 +85,13 @@ def main():
                         ms = timed(lambda: sess.all_reduce(plain[:n], algo=algo), iters, 5, dev)
                     elif algo == "auto":
                         ms = timed(lambda: sess.all_reduce(plain[:n]), iters, 5, dev)
+                    elif algo == "auto_registered":
+                        # ordinary tensor, its allocation mapped on every peer (no staging)
+                        sess.set_knob("register_min_bytes", 0)
+                        try:
+                            ms = timed(lambda: sess.all_reduce(plain[:n]), iters, 5, dev)
+                        finally:
+                            sess.set_knob("register_min_bytes", -1)
                     else:
                         ms = timed(lambda: sess.all_reduce(sym[:n], algo=algo), iters, 5, dev)
                 except ValueError:

@@ -5,6 +5,10 @@
 
 Sizes are bytes per rank (all_gather: per-rank block).  Device-timed, max over
 ranks.  GB/s figures: all_gather (n-1)/n * n*bytes / t; broadcast and reduce bytes / t.
+Three forms of each call: ordinary tensors staged through the arena, ordinary
+tensors registered (their allocations mapped on every peer, no staging), and
+tensors that live in the symmetric heap (zero-copy, through the switch where
+there is one).
 """
 import argparse
 import json
@@ -26,10 +30,11 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    sess = DeviceSession.from_env(heap_bytes=64 << 20, staging_bytes=128 << 20, rank=rank,
-                                  world=world, device=local)
+    sizes = [int(s) for s in args.sizes.split(",")]
+    sess = DeviceSession.from_env(heap_bytes=(world + 2) * max(sizes) + (64 << 20),
+                                  staging_bytes=128 << 20, rank=rank, world=world, device=local)
     rows = []
-    for nbytes in [int(s) for s in args.sizes.split(",")]:
+    for nbytes in sizes:
         n = nbytes // 4
         iters = 100 if nbytes <= (1 << 20) else 20
         x = torch.full((n,), float(rank), device=dev)
@@ -53,6 +58,43 @@ def main():
                          "ok": rank != 0 or float(r_out[0]) == world}
         ms = timed(lambda: dist.reduce(r_in.clone(), 0), iters, 5, dev)
         row["nccl_reduce_incl_clone"] = {"us": ms * 1e3}
+        # registered: the same ordinary tensors, no staging
+        sess.set_knob("register_min_bytes", 0)
+        out.zero_()
+        ms = timed(lambda: sess.all_gather(x, out), iters, 5, dev)
+        ok = all(float(out[r * n]) == r and float(out[(r + 1) * n - 1]) == r for r in range(world))
+        row["all_gather_registered"] = {"us": ms * 1e3, "gb_s": (world - 1) * nbytes / (ms * 1e-3) / 1e9, "ok": ok}
+        b.fill_(float(rank))
+        ms = timed(lambda: sess.broadcast(b, root=0), iters, 5, dev)
+        row["broadcast_registered"] = {"us": ms * 1e3, "gb_s": nbytes / (ms * 1e-3) / 1e9,
+                                       "ok": float(b[0]) == 0.0 and float(b[-1]) == 0.0}
+        r_out.zero_()
+        ms = timed(lambda: sess.reduce(r_in, out=r_out, root=0), iters, 5, dev)
+        row["reduce_registered"] = {"us": ms * 1e3, "gb_s": nbytes / (ms * 1e-3) / 1e9,
+                                    "ok": rank != 0 or float(r_out[0]) == world}
+        sess.set_knob("register_min_bytes", -1)
+        # symmetric heap: zero-copy
+        s_out = sess.symm_empty(n * world, torch.float32)
+        s_out.zero_()
+        ms = timed(lambda: sess.all_gather(x, s_out), iters, 5, dev)
+        ok = all(float(s_out[r * n]) == r and float(s_out[(r + 1) * n - 1]) == r for r in range(world))
+        row["all_gather_symmetric"] = {"us": ms * 1e3, "gb_s": (world - 1) * nbytes / (ms * 1e-3) / 1e9, "ok": ok}
+        sess.set_knob("gather_mc", 0)
+        ms = timed(lambda: sess.all_gather(x, s_out), iters, 5, dev)
+        row["all_gather_symmetric_plain_stores"] = {"us": ms * 1e3, "gb_s": (world - 1) * nbytes / (ms * 1e-3) / 1e9}
+        sess.set_knob("gather_mc", 1)
+        sess.symm_free(s_out)
+        s_b = sess.symm_empty(n, torch.float32)
+        s_b.fill_(float(rank))
+        ms = timed(lambda: sess.broadcast(s_b, root=0), iters, 5, dev)
+        row["broadcast_symmetric"] = {"us": ms * 1e3, "gb_s": nbytes / (ms * 1e-3) / 1e9,
+                                      "ok": float(s_b[0]) == 0.0 and float(s_b[-1]) == 0.0}
+        s_b.fill_(1.0)
+        r_out.zero_()
+        ms = timed(lambda: sess.reduce(s_b, out=r_out, root=0), iters, 5, dev)
+        row["reduce_symmetric"] = {"us": ms * 1e3, "gb_s": nbytes / (ms * 1e-3) / 1e9,
+                                   "ok": rank != 0 or float(r_out[0]) == world}
+        sess.symm_free(s_b)
         ms = timed(lambda: sess.barrier(), 200, 10, dev)
         row["barrier_us"] = ms * 1e3
         sess.check()

@@ -21,7 +21,7 @@ struct AlgoTuning {
     bool has_nvls = false;
     // two-shot calls of at least this many bytes pull with bulk async copies
     // (kAlgoTwoShotTma); SIZE_MAX: never
-    size_t tma_min = 1u << 20;
+    size_t tma_min = 64u << 20;  // measured at 2 GPUs: ahead of the register path from 64 MB
     // NVLS worlds: owner calls of at least this many bytes prefer the bulk-copy
     // two-shot over the in-switch reduction (fewer bytes per link direction:
     // (n-1)/n x S instead of (n+1)/n x S); SIZE_MAX: never

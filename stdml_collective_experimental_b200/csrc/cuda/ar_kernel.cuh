@@ -193,11 +193,11 @@ __device__ __forceinline__ void for_each_entry(const GroupEntry *tab, int n,
     }
 }
 
-// Reduce vectors [lo, hi) of the symmetric buffer at arena offset `off` over
-// all ranks with peer loads (rank-ascending) and hand each result to
+// Reduce vectors [lo, hi) of the buffers data[0..world) (rank r's buffer as
+// mapped here) with peer loads (rank-ascending) and hand each result to
 // store(v, value).
 template <int DT, int OP, typename Store>
-__device__ __forceinline__ void reduce_span(const CommCtx &ctx, unsigned long long off,
+__device__ __forceinline__ void reduce_span(const CommCtx &ctx, char *const *data,
                                             unsigned long long lo, unsigned long long hi,
                                             double scale, bool has_scale, Store store)
 {
@@ -213,7 +213,7 @@ __device__ __forceinline__ void reduce_span(const CommCtx &ctx, unsigned long lo
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (r0 + j < world && vu < hi) {
-                        x[u][j] = ld_arena_v4(ctx.base[r0 + j] + off + vu * 16ull);
+                        x[u][j] = ld_arena_v4(data[r0 + j] + vu * 16ull);
                     }
                 }
             }
@@ -391,9 +391,16 @@ template <int DT>
 __device__ __forceinline__ bool args_look_sane(const CommCtx &ctx, const AllReduceArgs &a,
                                                const GroupEntry *tab, unsigned int dyn_smem)
 {
-    bool ok = (a.off % 16ull == 0ull) && a.off >= kDataOffset && ctx.world >= 1 &&
-              ctx.world <= kMaxRanks && a.algo >= 0 && a.algo < kAlgoCount &&
+    bool ok = (a.off % 16ull == 0ull) && (a.off >= kDataOffset || a.off == 0ull) &&
+              ctx.world >= 1 && ctx.world <= kMaxRanks && a.algo >= 0 && a.algo < kAlgoCount &&
               a.root < ctx.world && a.nvec > 0;
+    for (int r = 0; ok && r < ctx.world; ++r) {
+        // every rank's buffer: mapped, 16-byte aligned, and (arena buffers) past the pad
+        const unsigned long long p = reinterpret_cast<unsigned long long>(a.data[r]);
+        const unsigned long long q = reinterpret_cast<unsigned long long>(a.push[r]);
+        ok = p != 0ull && (p & 15ull) == 0ull && (q & 15ull) == 0ull &&
+             (a.off == 0ull || a.data[r] == ctx.base[r] + a.off);
+    }
     if (ok && tab != nullptr) {
         ok = a.ntable > 0 && tab[0].voff == 0;
         for (int i = threadIdx.x; ok && i < a.ntable; i += kThreads) {
@@ -456,7 +463,7 @@ __global__ void __launch_bounds__(kThreads)
     const bool do_reduce = (phases & kPhaseReduce) != 0;
     if (do_reduce) { sync_begin(ctx, rank, &sync); }
 
-    char *mine = ctx.base[rank] + a.off;
+    char *mine = a.data[rank];
     GroupEntry single;
     single.src = a.src[vr];
     single.dst = a.dst[vr];
@@ -478,14 +485,14 @@ __global__ void __launch_bounds__(kThreads)
         const Span sp = span_of(a.nvec, shards, rank, nb, b);
         auto push = [&](unsigned long long v, const uint4 &x) {
             if (a.root >= 0) {
-                st_arena_v4(ctx.base[a.root] + a.off + v * 16ull, x);
+                st_arena_v4(a.push[a.root] + v * 16ull, x);
             } else {
                 for (int r = 0; r < world; ++r) {
-                    st_arena_v4(ctx.base[r] + a.off + v * 16ull, x);
+                    st_arena_v4(a.push[r] + v * 16ull, x);
                 }
             }
         };
-        reduce_span<DT, OP>(ctx, a.off, sp.lo, sp.hi, a.scale, a.has_scale != 0, push);
+        reduce_span<DT, OP>(ctx, a.data, sp.lo, sp.hi, a.scale, a.has_scale != 0, push);
     } else if (computes) {
         const Span sp = span_of(a.nvec, 1, 0, nb, b);
         for_each_entry<DT>(
@@ -500,7 +507,7 @@ __global__ void __launch_bounds__(kThreads)
                     nvls_span<DT, OP, kNvlsPlain4>(ctx, a.off, lo, hi, a.scale, a.has_scale != 0,
                                                    put);
                 } else {
-                    reduce_span<DT, OP>(ctx, a.off, lo, hi, a.scale, a.has_scale != 0, put);
+                    reduce_span<DT, OP>(ctx, a.data, lo, hi, a.scale, a.has_scale != 0, put);
                 }
             });
     }
@@ -511,7 +518,7 @@ __global__ void __launch_bounds__(kThreads)
 
     if ((phases & kPhaseUnpack) != 0 && owner_algo && computes &&
         (tab != nullptr || single.dst != nullptr)) {
-        unpack_phase<DT>(a, tab, single, mine, shards, nb, b, user_f32);
+        unpack_phase<DT>(a, tab, single, a.push[rank], shards, nb, b, user_f32);
     }
 
     if (do_reduce) { sync_end(ctx, rank, &sync); }
@@ -625,7 +632,7 @@ __device__ __forceinline__ bool tma_reduce_span(const CommCtx &ctx, const AllRed
             // the same GPU at the same moment
             const int r = (rank + 1 + i) % world;
             bulk_load(ring_s + (static_cast<uint32_t>(s) * world + r) * tile_bytes,
-                      ctx.base[r] + a.off + v0 * 16ull, bytes, bar);
+                      a.data[r] + v0 * 16ull, bytes, bar);
         }
     };
     if (threadIdx.x == 0) {
@@ -730,7 +737,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool do_reduce = (phases & kPhaseReduce) != 0;
     if (do_reduce) { sync_begin(ctx, rank, &sync); }
 
-    char *mine = ctx.base[rank] + a.off;
+    char *mine = a.data[rank];
     GroupEntry single;
     single.src = a.src[vr];
     single.dst = a.dst[vr];
@@ -749,11 +756,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         if constexpr (MODE == kOwnerTma) {
             auto push = [&](unsigned long long v, const uint4 &x) {
                 if (a.root >= 0) {
-                    st_arena_v4(ctx.base[a.root] + a.off + v * 16ull, x);
+                    st_arena_v4(a.push[a.root] + v * 16ull, x);
                 } else {
                     for (int i = 0; i < world; ++i) {
                         const int r = (rank + i) % world;
-                        st_arena_v4(ctx.base[r] + a.off + v * 16ull, x);
+                        st_arena_v4(a.push[r] + v * 16ull, x);
                     }
                 }
             };
@@ -763,7 +770,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else {
             auto push = [&](unsigned long long v, const uint4 &x) {
                 if (a.root >= 0) {
-                    st_arena_v4(ctx.base[a.root] + a.off + v * 16ull, x);
+                    st_arena_v4(a.push[a.root] + v * 16ull, x);
                 } else {
                     mm_st_v4(ctx.mc_base + a.off + v * 16ull, x);
                 }
@@ -774,7 +781,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     if ((phases & kPhaseUnpack) != 0 && computes && (tab != nullptr || single.dst != nullptr)) {
-        unpack_phase<DT>(a, tab, single, mine, world, nb, b, user_f32);
+        unpack_phase<DT>(a, tab, single, a.push[rank], world, nb, b, user_f32);
     }
 
     if (do_reduce) { sync_end(ctx, rank, &sync); }

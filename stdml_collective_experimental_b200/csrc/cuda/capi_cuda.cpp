@@ -158,7 +158,12 @@ int stdmlc_dw_set_tuning(void *h, int max_blocks, long long oneshot_max_bytes,
 
 int stdmlc_dw_set_knob(void *h, const char *name, long long value)
 {
-    return guarded([&] { S(h)->world().set_knob(name != nullptr ? name : "", value); });
+    return guarded([&] { S(h)->set_knob(name != nullptr ? name : "", value); });
+}
+
+int stdmlc_dw_drop_registrations(void *h)
+{
+    return guarded([&] { S(h)->drop_registrations(); });
 }
 
 int stdmlc_dw_all_reduce(void *h, const void *const *in, void *const *out,

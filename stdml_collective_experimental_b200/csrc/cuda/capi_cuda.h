@@ -49,6 +49,9 @@ int stdmlc_dw_set_tuning(void *h, int max_blocks, long long oneshot_max_bytes,
 /* Named knobs (same value on every rank): nvls_variant, nvls_blocks, tma_blocks,
  * tma_tile_vec, tma_min_bytes, tma_over_nvls_min_bytes, debug_checks. */
 int stdmlc_dw_set_knob(void *h, const char *name, long long value);
+/* Collective: unmap every peer buffer that registered calls have mapped
+ * (register_min_bytes knob); call it before such memory is freed. */
+int stdmlc_dw_drop_registrations(void *h);
 
 int stdmlc_dw_all_reduce(void *h, const void *const *in, void *const *out,
                          unsigned long long count, int dt, int op, double scale, int algo,

@@ -90,12 +90,13 @@ STDML_HD inline bool is_owner_algo(int algo)
 constexpr int kTmaMaxStages = 16;
 constexpr unsigned int kTmaSmemBudget = 192u << 10;  // bytes of the 227 KB an SM offers
 
-// Ring geometry for a world: the wanted tile (default: one vector per thread),
-// halved until two slots fit the budget, then as many slots as fit.
+// Ring geometry for a world: the wanted tile (default: 1024 vectors, 16 KB per
+// rank and copy; measured at 2 GPUs: 1024 > 512 > 256), halved until two slots
+// fit the budget, then as many slots as fit.
 inline void tma_geometry(int world, unsigned int want_tile_vec, int *stages,
                          unsigned int *tile_vec, unsigned int *smem_bytes)
 {
-    unsigned int tv = want_tile_vec > 0 ? want_tile_vec : static_cast<unsigned int>(kThreads);
+    unsigned int tv = want_tile_vec > 0 ? want_tile_vec : 1024u;
     tv = (tv + 31u) / 32u * 32u;
     while (tv > 32u && 2ull * world * tv * 16ull > kTmaSmemBudget) { tv /= 2; }
     unsigned int st = static_cast<unsigned int>(
@@ -121,6 +122,15 @@ struct AllReduceArgs {
     const void *src[kMaxRanks];  // nullptr: input already at arena offset `off`
     void *dst[kMaxRanks];        // nullptr: result stays in the arena (two-shot/nvls)
     const GroupEntry *table[kMaxRanks];  // non-null: fused group, src/dst unused
+    // Rank r's buffer as mapped in this process: arena base + `off` for symmetric
+    // and staged buffers, the peer mapping of a registered user buffer otherwise
+    // (then `off` is 0 and the NVLS algorithms, which need the arena's multicast
+    // mapping, are not available).
+    char *data[kMaxRanks];
+    // Where the owner algorithms store results: the same buffers, except for
+    // registered out-of-place calls (operands pulled from the peers' inputs,
+    // results stored into their outputs; reduce-to-root: only [root] is used).
+    char *push[kMaxRanks];
     unsigned long long off;    // byte offset of the symmetric buffer in the arena
     unsigned long long count;  // elements (single buffer) or padded elements (group)
     unsigned long long nvec;   // 16-byte vectors of the symmetric buffer
@@ -152,26 +162,41 @@ enum : int {
 enum : int { kPhasePack = 1, kPhaseReduce = 2, kPhaseUnpack = 4, kPhaseAll = 7 };
 
 struct GatherArgs {
-    const void *src[kMaxRanks];  // nullptr: block already at arena offset `off`
-    void *dst[kMaxRanks];
-    unsigned long long off;     // arena slot (one block per rank)
-    unsigned long long bytes;   // bytes per rank block
-    unsigned long long stride;  // distance between rank blocks in dst (all_gather)
-    int root;                   // < 0: all_gather; >= 0: broadcast from `root`
-    int end_barrier;
-    int algo;                   // broadcast only: see kBcast*
+    const void *src[kMaxRanks];  // per virtual rank; nullptr: the rank's block is already in
+                                 // place in its own symmetric region
+    void *dst[kMaxRanks];        // per virtual rank; nullptr: the result stays in the region
+    // Rank r's symmetric region as mapped here (an arena slot, a symmetric-heap
+    // tensor, or a registered user buffer).  all_gather: world blocks, block p at
+    // p * sym_stride; broadcast: one block.
+    char *data[kMaxRanks];
+    unsigned long long off;         // arena offset of the region (multimem), 0 if not in the arena
+    unsigned long long bytes;       // bytes per rank block
+    unsigned long long sym_stride;  // all_gather: distance between blocks in the region
+    unsigned long long stride;      // all_gather: distance between blocks in dst
+    int root;                       // < 0: all_gather; >= 0: broadcast from `root`
+    int start_barrier;  // the region is memory its owner may still be using (zero-copy)
+    int end_barrier;    // the region is reused by the next call (captured staged calls)
+    int algo;           // see kGather* / kBcast*
+    int use_mc;         // push through the switch (multimem.st) instead of one store per peer
 };
 
 enum : int {
-    kBcastPull = 0,     // everybody reads root's slot (small messages)
-    kBcastNvls = 1,     // root multimem.st once, everybody copies its own slot
-    kBcastScatter = 2,  // rank r pulls slice r from root, then all ranks exchange slices
+    kBcastPull = 0,     // root packs, everybody reads root's region (small messages);
+                        // all_gather: everybody packs, then reads every peer's region
+    kBcastNvls = 1,     // root multimem.st once, everybody copies its own region
+    kBcastScatter = 2,  // root stores slice r to rank r, then every rank stores its slice
+                        // to all others (root's links carry ~2 copies, not n-1)
+    kGatherPush = 3,    // every rank stores its block into every rank's region; broadcast:
+                        // root stores the block into every rank's region
 };
 
 // kernels_misc.cu
 void launch_barrier(const CommCtx &ctx, int vranks, void *stream);
 int launch_gather(const CommCtx &ctx, const GatherArgs &a, int blocks, int vranks,
                   void *stream);
+int launch_unpack_blocks(const void *region, void *dst, unsigned long long bytes,
+                         unsigned long long sym_stride, unsigned long long stride, int blocks_n,
+                         int grid, void *stream);
 // kernels_ar_*.cu: returns cudaError_t as int; -1 if (dtype, op, algo) is not built
 int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op,
                       int blocks, int vranks, void *stream);

@@ -54,6 +54,10 @@ DeviceSession::DeviceSession(std::unique_ptr<DeviceWorld> world) : world_(std::m
     if (const char *e = std::getenv("STDML_COLLECTIVE_PIPELINE_MIN_BYTES")) {
         pipeline_min_bytes_ = static_cast<size_t>(std::atoll(e));
     }
+    if (const char *e = std::getenv("STDML_COLLECTIVE_REGISTER_MIN_BYTES")) {
+        const long long v = std::atoll(e);
+        register_min_bytes_ = v < 0 ? SIZE_MAX : static_cast<size_t>(v);
+    }
     if (const char *e = std::getenv("STDML_COLLECTIVE_PIPELINE_CHUNK_BYTES")) {
         pipeline_chunk_bytes_ = std::max<size_t>(1u << 16, static_cast<size_t>(std::atoll(e)));
     }
@@ -76,6 +80,47 @@ DeviceSession::~DeviceSession()
     table_mem_.clear();
     (void)cudaGetLastError();
 }
+
+void DeviceSession::set_knob(const std::string &name, long long value)
+{
+    std::lock_guard<std::recursive_mutex> lk(mu_);
+    if (name == "register_min_bytes") {
+        register_min_bytes_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        return;
+    }
+    if (name == "pipeline_min_bytes") {
+        pipeline_min_bytes_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        return;
+    }
+    world_->set_knob(name, value);
+}
+
+void DeviceSession::drop_registrations()
+{
+    std::lock_guard<std::recursive_mutex> lk(mu_);
+    world_->drop_registrations();
+}
+
+// Registered (zero-copy on user memory) execution applies to real multi-GPU
+// worlds, outside stream capture (the handle exchange is host work), from the
+// configured size up.
+bool DeviceSession::registered_path(size_t bytes, void *stream) const
+{
+    return world_->world() > 1 && world_->vranks() == 1 && bytes >= register_min_bytes_ &&
+           !capturing(stream);
+}
+
+namespace
+{
+bool all_aligned16(void *const *p, int n, bool allow_null = false)
+{
+    for (int i = 0; i < n; ++i) {
+        if (p[i] == nullptr && allow_null) { continue; }
+        if (p[i] == nullptr || reinterpret_cast<uintptr_t>(p[i]) % 16 != 0) { return false; }
+    }
+    return true;
+}
+}  // namespace
 
 void DeviceSession::check()
 {
@@ -168,6 +213,11 @@ void DeviceSession::run_pipelined(std::vector<AllReduceCall> &calls, void *strea
             rt_check(cudaStreamWaitEvent(main_s, ev(unpacked_ev_[i]), 0), "cudaStreamWaitEvent");
         }
     }
+    // The unpack ran outside the kernels that carry the barriers, so "a peer has
+    // passed the barrier of my next call" no longer implies "it is done with its
+    // slots": line the ranks up once, after which the slots are free everywhere.
+    launch_check(world_->barrier(stream), "barrier (end of pipeline)");
+    ++launches_;
 }
 
 void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t count, int dt,
@@ -215,6 +265,30 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
         c.algo = zc_algo;
         launch_ar(c, stream);
         return;
+    }
+
+    // registered: ordinary device buffers whose allocations every peer has mapped;
+    // the owners pull the operands from the inputs and store the results into the
+    // outputs, nothing is packed or unpacked
+    if (!symmetric && registered_path(count * es, stream) && (algo < 0 || is_owner_algo(algo))) {
+        const int world = world_->world();
+        void *p_out[kMaxRanks], *p_in[kMaxRanks];
+        const bool same = in[0] == out[0];
+        bool ok = world_->resolve_peers(out, count * es, p_out) && all_aligned16(p_out, world);
+        if (ok && !same) {
+            ok = world_->resolve_peers(in, count * es, p_in) && all_aligned16(p_in, world);
+        }
+        if (ok) {
+            c.peer_data = same ? p_out : p_in;
+            c.peer_push = same ? nullptr : p_out;
+            c.count = count;
+            c.algo = algo >= 0 ? algo : world_->pick_algo(count * es, dt, op, true);
+            if (c.algo == kAlgoNvls) {  // the multicast mapping covers the arena only
+                c.algo = count * es >= (64u << 20) ? kAlgoTwoShotTma : kAlgoTwoShot;
+            }
+            launch_ar(c, stream);
+            return;
+        }
     }
 
     // staged: pack into a staging slot inside the launch, one slot per chunk
@@ -278,6 +352,62 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
     if (root < 0 || root >= world_->world()) { throw std::invalid_argument("reduce: bad root"); }
     const size_t es = elem_size(dt);
     const int vr = world_->vranks();
+    // zero-copy: the inputs live in the symmetric heap; root alone reads them (the
+    // switch reduces on the way when it can, else root loads every peer), nothing
+    // is packed.  Without the switch only small messages go this way: root's
+    // links would carry n-1 copies.
+    const size_t in_off = symmetric_offset(in);
+    const bool by_switch = world_->has_nvls() && nvls_supported(dt, op) && world_->world() > 2;
+    if (in_off != SIZE_MAX && world_->world() > 1 && (by_switch || count * es <= (1u << 20))) {
+        std::vector<void *> dsts(vr);
+        for (int v = 0; v < vr; ++v) {
+            dsts[v] = (out != nullptr && out[v] != nullptr) ? out[v] : nullptr;
+        }
+        AllReduceCall k;
+        k.dt = dt;
+        k.op = op;
+        k.root = root;
+        k.has_scale = scale != 1.0;
+        k.scale = scale;
+        k.off = in_off;
+        k.dst = dsts.data();
+        k.count = count;
+        k.end_barrier = true;  // the inputs stay untouched until root has read them
+        k.algo = by_switch ? kAlgoNvlsOneShot : kAlgoOneShot;
+        launch_ar(k, stream);
+        return;
+    }
+    if (registered_path(count * es, stream)) {
+        // owners pull their shard from every rank's input and store the result
+        // into root's output: root's links carry one copy of the message
+        const int world = world_->world();
+        void *p_in[kMaxRanks], *p_out[kMaxRanks];
+        const void *mine_out[1] = {(world_->rank() == root && out != nullptr) ? out[0] : nullptr};
+        if (world_->rank() == root && mine_out[0] == nullptr) {
+            throw std::invalid_argument("reduce: root needs an output buffer");
+        }
+        const bool ok = world_->resolve_peers(in, count * es, p_in) && all_aligned16(p_in, world) &&
+                        world_->resolve_peers(mine_out, count * es, p_out) &&
+                        p_out[root] != nullptr &&
+                        reinterpret_cast<uintptr_t>(p_out[root]) % 16 == 0;
+        if (ok) {
+            for (int r = 0; r < world; ++r) {
+                if (r != root) { p_out[r] = p_in[r]; }  // never written: only [root] is used
+            }
+            AllReduceCall k;
+            k.dt = dt;
+            k.op = op;
+            k.root = root;
+            k.has_scale = scale != 1.0;
+            k.scale = scale;
+            k.peer_data = p_in;
+            k.peer_push = p_out;
+            k.count = count;
+            k.algo = count * es >= (64u << 20) ? kAlgoTwoShotTma : kAlgoTwoShot;
+            launch_ar(k, stream);
+            return;
+        }
+    }
     const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
     std::vector<const void *> src(vr);
     std::vector<void *> dst(vr);
@@ -485,6 +615,69 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
     }
 }
 
+// Same arena offset on every virtual rank, 16-byte aligned: the buffer can be
+// addressed on every peer without any copy.
+size_t DeviceSession::symmetric_offset(const void *const *ptrs) const
+{
+    const int vr = world_->vranks();
+    if (ptrs == nullptr || ptrs[0] == nullptr) { return SIZE_MAX; }
+    const size_t off = world_->offset_of(ptrs[0], 0);
+    if (off == SIZE_MAX || off % 16 != 0) { return SIZE_MAX; }
+    for (int v = 1; v < vr; ++v) {
+        if (ptrs[v] == nullptr || world_->offset_of(ptrs[v], v) != off) { return SIZE_MAX; }
+    }
+    return off;
+}
+
+// Runs the chunks of a staged all_gather / broadcast with their local unpack on
+// a second stream: while chunk k is copied out of its slot, chunk k+1 is on the
+// links.  A chunk's push may start only when every rank has unpacked the chunk
+// that used the slot before, hence the start barrier from the third chunk on
+// (each rank's launch already waits for its own unpack).
+void DeviceSession::run_gather_chunks(std::vector<GatherCall> &calls,
+                                      const std::vector<std::vector<void *>> &dsts,
+                                      int blocks_n, size_t stride, void *stream)
+{
+    ensure_pipeline();
+    cudaStream_t main_s = static_cast<cudaStream_t>(stream);
+    cudaStream_t unpack_s = static_cast<cudaStream_t>(unpack_stream_);
+    auto ev = [](void *e) { return static_cast<cudaEvent_t>(e); };
+    const int rank = world_->rank();
+    bool used[2] = {false, false};
+    for (size_t k = 0; k < calls.size(); ++k) {
+        GatherCall &g = calls[k];
+        g.off = world_->next_staging_slot();
+        const int slot = static_cast<int>((g.off - kDataOffset) / world_->staging_bytes()) & 1;
+        if (used[slot]) {
+            rt_check(cudaStreamWaitEvent(main_s, ev(unpacked_ev_[slot]), 0), "cudaStreamWaitEvent");
+            g.start_barrier = true;
+        }
+        g.dst = nullptr;  // unpacked by the copy kernel below
+        // posted stores fill the links from few SMs; the rest belong to the unpack
+        // of the previous chunk, which runs at the same time
+        if (g.blocks <= 0) { g.blocks = 40; }
+        launch_check(world_->gather(g, stream), "gather (chunk)");
+        ++launches_;
+        rt_check(cudaEventRecord(ev(reduced_ev_[slot]), main_s), "cudaEventRecord");
+        rt_check(cudaStreamWaitEvent(unpack_s, ev(reduced_ev_[slot]), 0), "cudaStreamWaitEvent");
+        launch_check(world_->unpack_blocks(world_->ptr(rank, g.off), dsts[k][0], g.bytes,
+                                           g.sym_stride, stride, blocks_n, unpack_s),
+                     "unpack (chunk)");
+        ++launches_;
+        rt_check(cudaEventRecord(ev(unpacked_ev_[slot]), unpack_s), "cudaEventRecord");
+        used[slot] = true;
+    }
+    for (int i = 0; i < 2; ++i) {
+        if (used[i]) {
+            rt_check(cudaStreamWaitEvent(main_s, ev(unpacked_ev_[i]), 0), "cudaStreamWaitEvent");
+        }
+    }
+    // as at the end of run_pipelined: no rank may push into a slot that its owner
+    // is still unpacking
+    launch_check(world_->barrier(stream), "barrier (end of pipeline)");
+    ++launches_;
+}
+
 void DeviceSession::all_gather(const void *const *in, void *const *out, size_t count, int dt,
                                void *stream)
 {
@@ -493,22 +686,81 @@ void DeviceSession::all_gather(const void *const *in, void *const *out, size_t c
     const size_t bytes = count * elem_size(dt);
     if (bytes == 0) { return; }
     const int vr = world_->vranks();
-    const size_t slot = world_->staging_bytes();
-    std::vector<const void *> src(vr);
-    std::vector<void *> dst(vr);
-    for (size_t done = 0; done < bytes; done += slot) {
-        const size_t nbytes = std::min(slot, bytes - done);
+    const int world = world_->world();
+
+    // zero-copy: the output lives in the symmetric heap and blocks start on
+    // 16-byte boundaries; every rank stores its block straight into every output
+    const size_t out_off = symmetric_offset(out);
+    if (out_off != SIZE_MAX && bytes % 16 == 0 && world > 1) {
+        std::vector<const void *> src(vr);
         for (int v = 0; v < vr; ++v) {
-            src[v] = static_cast<const char *>(in[v]) + done;
-            dst[v] = static_cast<char *>(out[v]) + done;
+            const char *own = static_cast<const char *>(out[v]) +
+                              static_cast<size_t>(world_->rank() + v) * bytes;
+            src[v] = (in[v] == own) ? nullptr : in[v];  // already in place
         }
         GatherCall g;
-        g.off = world_->next_staging_slot();
+        g.off = out_off;
         g.src = src.data();
-        g.dst = dst.data();
-        g.bytes = nbytes;
+        g.bytes = bytes;
+        g.sym_stride = bytes;
+        g.start_barrier = true;  // peers write into memory this rank may still be reading
+        g.algo = kGatherPush;
+        launch_check(world_->gather(g, stream), "all_gather");
+        ++launches_;
+        return;
+    }
+
+    if (bytes % 16 == 0 && registered_path(bytes * static_cast<size_t>(world), stream)) {
+        void *p_out[kMaxRanks];
+        if (world_->resolve_peers(out, bytes * static_cast<size_t>(world), p_out) &&
+            all_aligned16(p_out, world)) {
+            const char *own = static_cast<const char *>(out[0]) +
+                              static_cast<size_t>(world_->rank()) * bytes;
+            const void *src[1] = {in[0] == own ? nullptr : in[0]};
+            GatherCall g;
+            g.peer_data = p_out;
+            g.src = src;
+            g.bytes = bytes;
+            g.sym_stride = bytes;
+            g.start_barrier = true;
+            g.algo = kGatherPush;
+            launch_check(world_->gather(g, stream), "all_gather");
+            ++launches_;
+            return;
+        }
+    }
+
+    // staged: a slot holds one block of every rank
+    const bool in_capture = capturing(stream);
+    const size_t slot = world_->staging_bytes();
+    const size_t chunk = std::max<size_t>(16, slot / static_cast<size_t>(world) / 16 * 16);
+    std::vector<GatherCall> calls;
+    std::vector<std::vector<const void *>> srcs;
+    std::vector<std::vector<void *>> dsts;
+    for (size_t done = 0; done < bytes; done += chunk) {
+        srcs.emplace_back(vr);
+        dsts.emplace_back(vr);
+        for (int v = 0; v < vr; ++v) {
+            srcs.back()[v] = static_cast<const char *>(in[v]) + done;
+            dsts.back()[v] = static_cast<char *>(out[v]) + done;
+        }
+        GatherCall g;
+        g.bytes = std::min(chunk, bytes - done);
+        g.sym_stride = (g.bytes + 15) / 16 * 16;
         g.stride = bytes;
-        g.end_barrier = capturing(stream);
+        g.end_barrier = in_capture;
+        calls.push_back(g);
+    }
+    for (size_t k = 0; k < calls.size(); ++k) {
+        calls[k].src = srcs[k].data();
+        calls[k].dst = dsts[k].data();
+    }
+    if (calls.size() >= 2 && vr == 1 && world > 1 && !in_capture) {
+        run_gather_chunks(calls, dsts, world, bytes, stream);
+        return;
+    }
+    for (GatherCall &g : calls) {
+        g.off = world_->next_staging_slot();
         launch_check(world_->gather(g, stream), "all_gather");
         ++launches_;
     }
@@ -523,23 +775,77 @@ void DeviceSession::broadcast(const void *const *in, void *const *out, size_t co
     const size_t bytes = count * elem_size(dt);
     if (bytes == 0) { return; }
     const int vr = world_->vranks();
-    const size_t slot = world_->staging_bytes();
-    std::vector<const void *> src(vr);
-    std::vector<void *> dst(vr);
-    for (size_t done = 0; done < bytes; done += slot) {
-        const size_t nbytes = std::min(slot, bytes - done);
+    const int world = world_->world();
+
+    // zero-copy: the destination lives in the symmetric heap; root stores into it
+    // on every rank (one multimem.st pass with NVLS)
+    const size_t out_off = symmetric_offset(out);
+    if (out_off != SIZE_MAX && world > 1) {
+        std::vector<const void *> src(vr);
         for (int v = 0; v < vr; ++v) {
-            src[v] = (in != nullptr && in[v] != nullptr) ? static_cast<const char *>(in[v]) + done
-                                                          : nullptr;
-            dst[v] = static_cast<char *>(out[v]) + done;
+            const bool has_in = in != nullptr && in[v] != nullptr;
+            src[v] = (!has_in || in[v] == out[v]) ? nullptr : in[v];
         }
         GatherCall g;
-        g.off = world_->next_staging_slot();
+        g.off = out_off;
         g.src = src.data();
-        g.dst = dst.data();
-        g.bytes = nbytes;
+        g.bytes = bytes;
         g.root = root;
-        g.end_barrier = capturing(stream);
+        g.start_barrier = true;
+        if (bytes < (256u << 10)) { g.algo = kGatherPush; }  // small: root stores to every peer
+        launch_check(world_->gather(g, stream), "broadcast");
+        ++launches_;
+        return;
+    }
+
+    if (registered_path(bytes, stream)) {
+        void *p_out[kMaxRanks];
+        if (world_->resolve_peers(out, bytes, p_out) && all_aligned16(p_out, world)) {
+            const bool has_in = in != nullptr && in[0] != nullptr;
+            const void *src[1] = {(!has_in || in[0] == out[0]) ? nullptr : in[0]};
+            GatherCall g;
+            g.peer_data = p_out;
+            g.src = src;
+            g.bytes = bytes;
+            g.root = root;
+            g.start_barrier = true;
+            g.algo = world > 2 ? kBcastScatter : kGatherPush;
+            launch_check(world_->gather(g, stream), "broadcast");
+            ++launches_;
+            return;
+        }
+    }
+
+    const bool in_capture = capturing(stream);
+    const size_t slot = world_->staging_bytes();
+    std::vector<GatherCall> calls;
+    std::vector<std::vector<const void *>> srcs;
+    std::vector<std::vector<void *>> dsts;
+    for (size_t done = 0; done < bytes; done += slot) {
+        srcs.emplace_back(vr);
+        dsts.emplace_back(vr);
+        for (int v = 0; v < vr; ++v) {
+            srcs.back()[v] = (in != nullptr && in[v] != nullptr)
+                                 ? static_cast<const char *>(in[v]) + done
+                                 : nullptr;
+            dsts.back()[v] = static_cast<char *>(out[v]) + done;
+        }
+        GatherCall g;
+        g.bytes = std::min(slot, bytes - done);
+        g.root = root;
+        g.end_barrier = in_capture;
+        calls.push_back(g);
+    }
+    for (size_t k = 0; k < calls.size(); ++k) {
+        calls[k].src = srcs[k].data();
+        calls[k].dst = dsts[k].data();
+    }
+    if (calls.size() >= 2 && vr == 1 && world > 1 && !in_capture) {
+        run_gather_chunks(calls, dsts, 1, 0, stream);
+        return;
+    }
+    for (GatherCall &g : calls) {
+        g.off = world_->next_staging_slot();
         launch_check(world_->gather(g, stream), "broadcast");
         ++launches_;
     }

@@ -75,6 +75,19 @@ class DeviceSession
                    void *stream);
     void barrier(void *stream);
 
+    // Knobs of the session (register_min_bytes) and of its world (see
+    // DeviceWorld::set_knob).  register_min_bytes: collectives on ordinary device
+    // buffers of at least this many bytes have the buffers' allocations mapped
+    // on every peer (DeviceWorld::resolve_peers) and run zero-copy on them
+    // instead of staging through the arena; negative: never (the default, also
+    // STDML_COLLECTIVE_REGISTER_MIN_BYTES).  Such buffers must stay allocated
+    // until drop_registrations() or the end of the session, and every rank must
+    // make the same choice between in-place and out-of-place for a call.
+    void set_knob(const std::string &name, long long value);
+    // Collective: unmap every registered peer buffer (before memory that was
+    // used in registered calls is freed).
+    void drop_registrations();
+
     // Throws DeviceTimeout if a kernel reported a wait that ran out.
     void check();
     // Kernel launches issued so far (all kinds).
@@ -96,6 +109,10 @@ class DeviceSession
     // overlap the NVLink phase of its neighbours.
     void run_pipelined(std::vector<AllReduceCall> &calls, void *stream);
     void ensure_pipeline();
+    size_t symmetric_offset(const void *const *ptrs) const;
+    void run_gather_chunks(std::vector<GatherCall> &calls,
+                           const std::vector<std::vector<void *>> &dsts, int blocks_n,
+                           size_t stride, void *stream);
     const GroupPlan &plan_group(size_t n, const void *const *ins, void *const *outs,
                                 const size_t *counts, int dt, int user_dt);
 
@@ -108,6 +125,8 @@ class DeviceSession
     std::map<std::string, GroupPlan> plans_;
     std::vector<void *> table_mem_;
     unsigned long long launches_ = 0;
+    size_t register_min_bytes_ = SIZE_MAX;     // STDML_COLLECTIVE_REGISTER_MIN_BYTES
+    bool registered_path(size_t bytes, void *stream) const;
     size_t pipeline_min_bytes_ = 512u << 20;   // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
     size_t pipeline_chunk_bytes_ = 32u << 20;  // STDML_COLLECTIVE_PIPELINE_CHUNK_BYTES (smallest chunk)
     // pipeline resources (created on first use)

@@ -52,6 +52,7 @@ struct Driver {
     decltype(&cuMulticastBindMem) MulticastBindMem = nullptr;
     decltype(&cuMulticastUnbind) MulticastUnbind = nullptr;
     decltype(&cuMulticastGetGranularity) MulticastGetGranularity = nullptr;
+    decltype(&cuMemGetAddressRange) MemGetAddressRange = nullptr;
     bool ok = false;
     bool multicast = false;
 
@@ -85,6 +86,7 @@ struct Driver {
                     load("cuMulticastBindMem", MulticastBindMem) &&
                     load("cuMulticastUnbind", MulticastUnbind) &&
                     load("cuMulticastGetGranularity", MulticastGetGranularity);
+        (void)load("cuMemGetAddressRange", MemGetAddressRange);
     }
 
     std::string err(CUresult r) const
@@ -146,18 +148,35 @@ class World final : public DeviceWorld
     StatusBlock *status_host_ = nullptr;
     StatusBlock *status_dev_ = nullptr;
 
+    // registered user memory: what this rank has exported (by base address) and
+    // what it has imported from each peer (by that peer's base address)
+    struct Exported {
+        cudaIpcMemHandle_t handle;
+        size_t size = 0;
+        bool announced = false;  // the peers have seen this handle already
+    };
+    struct Imported {
+        cudaIpcMemHandle_t handle;
+        size_t size = 0;
+        void *mapped = nullptr;
+    };
+    std::map<uintptr_t, Exported> exported_;
+    std::vector<std::map<uintptr_t, Imported>> imported_;  // per peer
+
     std::unique_ptr<LocalRendezvous> rdv_;
     int num_sms_ = 148;
     int max_blocks_ = 128;
     size_t oneshot_max_ = 0;       // 0: measured default for this world size
     size_t nvls_oneshot_max_ = 0;  // 0: measured default for this world size
-    size_t tma_min_ = 1u << 20;            // STDML_COLLECTIVE_TMA_MIN_BYTES (-1: never)
+    size_t tma_min_ = 64u << 20;           // STDML_COLLECTIVE_TMA_MIN_BYTES (-1: never)
     size_t tma_over_nvls_min_ = SIZE_MAX;  // STDML_COLLECTIVE_TMA_OVER_NVLS_MIN_BYTES
     int nvls_blocks_ = 0;                  // STDML_COLLECTIVE_NVLS_BLOCKS
     int tma_blocks_ = 0;                   // STDML_COLLECTIVE_TMA_BLOCKS
-    unsigned int tma_tile_vec_ = 0;        // STDML_COLLECTIVE_TMA_TILE_VEC (0: one vector per thread)
+    unsigned int tma_tile_vec_ = 0;        // STDML_COLLECTIVE_TMA_TILE_VEC (0: 1024, two vectors per thread)
     int nvls_variant_ = kNvlsPipe4;        // STDML_COLLECTIVE_NVLS_VARIANT
     bool debug_checks_ = false;            // STDML_COLLECTIVE_DEBUG
+    size_t gather_push_min_ = 64u << 10;  // STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES
+    bool gather_mc_ = true;               // STDML_COLLECTIVE_GATHER_MC: all_gather through the switch
     int debug_inject_ = 0;  // tests: hand the next all_reduce kernel arguments that its
                             // own checks must refuse (1: misaligned offset, 2: offset
                             // inside the signal pad); implies debug_checks for that launch
@@ -205,6 +224,8 @@ class World final : public DeviceWorld
         if (const char *e = std::getenv("STDML_COLLECTIVE_NVLS_VARIANT")) {
             nvls_variant_ = std::max(0, std::min(kNvlsVariants - 1, std::atoi(e)));
         }
+        env_bytes("STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES", gather_push_min_);
+        if (const char *e = std::getenv("STDML_COLLECTIVE_GATHER_MC")) { gather_mc_ = std::atoi(e) != 0; }
         if (const char *e = std::getenv("STDML_COLLECTIVE_DEBUG")) {
             debug_checks_ = std::atoi(e) != 0;
         }
@@ -305,6 +326,10 @@ class World final : public DeviceWorld
             tma_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "tma_over_nvls_min_bytes") {
             tma_over_nvls_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "gather_push_min_bytes") {
+            gather_push_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "gather_mc") {
+            gather_mc_ = value != 0;
         } else if (name == "debug_checks") {
             debug_checks_ = value != 0;
         } else if (name == "debug_inject") {
@@ -312,6 +337,137 @@ class World final : public DeviceWorld
         } else {
             throw std::invalid_argument("device world: unknown knob '" + name + "'");
         }
+    }
+
+    // ------------------------------------------------------------ registration
+    struct RegRecord {
+        int ok;      // this rank's buffer can be exported (or it passed none)
+        int fresh;   // the handle below has not been announced before
+        unsigned long long base, size, offset;
+        cudaIpcMemHandle_t handle;
+    };
+
+    bool resolve_peers(const void *const *ptrs, size_t bytes, void **peer_ptrs) override
+    {
+        for (int r = 0; r < opt_.world; ++r) { peer_ptrs[r] = nullptr; }
+        if (opt_.loopback) {
+            for (int v = 0; v < vranks_; ++v) { peer_ptrs[v] = const_cast<void *>(ptrs[v]); }
+            return true;
+        }
+        void *mine = const_cast<void *>(ptrs[0]);
+        if (opt_.world == 1) {
+            peer_ptrs[0] = mine;
+            return true;
+        }
+        RegRecord rec;
+        std::memset(&rec, 0, sizeof(rec));
+        rec.ok = 1;
+        if (mine != nullptr) {
+            rec.ok = 0;
+            Driver &d = driver();
+            CUdeviceptr base = 0;
+            size_t size = 0;
+            if (d.MemGetAddressRange != nullptr &&
+                d.MemGetAddressRange(&base, &size, reinterpret_cast<CUdeviceptr>(mine)) ==
+                    CUDA_SUCCESS &&
+                reinterpret_cast<uintptr_t>(mine) + bytes <= static_cast<uintptr_t>(base) + size) {
+                auto it = exported_.find(static_cast<uintptr_t>(base));
+                if (it != exported_.end() && it->second.size != size) {
+                    exported_.erase(it);  // the address was freed and allocated again
+                    it = exported_.end();
+                }
+                if (it == exported_.end()) {
+                    Exported e;
+                    if (cudaIpcGetMemHandle(&e.handle, reinterpret_cast<void *>(base)) ==
+                        cudaSuccess) {
+                        e.size = size;
+                        it = exported_.emplace(static_cast<uintptr_t>(base), e).first;
+                    } else {
+                        (void)cudaGetLastError();  // e.g. memory from the VMM allocator
+                    }
+                }
+                if (it != exported_.end()) {
+                    rec.ok = 1;
+                    rec.fresh = it->second.announced ? 0 : 1;
+                    rec.base = static_cast<unsigned long long>(base);
+                    rec.size = size;
+                    rec.offset = reinterpret_cast<uintptr_t>(mine) - static_cast<uintptr_t>(base);
+                    rec.handle = it->second.handle;
+                }
+            }
+        }
+        std::vector<std::vector<char>> all;
+        rdv_->all_gather(&rec, sizeof(rec), all);
+        bool everyone = true, any_fresh = false;
+        std::vector<RegRecord> recs(opt_.world);
+        for (int r = 0; r < opt_.world; ++r) {
+            std::memcpy(&recs[r], all[r].data(), sizeof(RegRecord));
+            everyone = everyone && recs[r].ok != 0;
+            any_fresh = any_fresh || recs[r].fresh != 0;
+        }
+        if (!everyone) { return false; }
+        if (mine != nullptr) { exported_[static_cast<uintptr_t>(rec.base)].announced = true; }
+        imported_.resize(opt_.world);
+        bool imported_all = true;
+        for (int r = 0; r < opt_.world; ++r) {
+            if (r == opt_.rank) {
+                peer_ptrs[r] = mine;
+                continue;
+            }
+            const RegRecord &pr = recs[r];
+            if (pr.base == 0) { continue; }  // that rank passed no buffer
+            auto &table = imported_[r];
+            auto it = table.find(static_cast<uintptr_t>(pr.base));
+            if (it != table.end() &&
+                (it->second.size != pr.size ||
+                 std::memcmp(&it->second.handle, &pr.handle, sizeof(pr.handle)) != 0)) {
+                (void)cudaIpcCloseMemHandle(it->second.mapped);  // a new allocation at that address
+                table.erase(it);
+                it = table.end();
+            }
+            if (it == table.end()) {
+                Imported im;
+                im.handle = pr.handle;
+                im.size = pr.size;
+                if (cudaIpcOpenMemHandle(&im.mapped, pr.handle, cudaIpcMemLazyEnablePeerAccess) !=
+                    cudaSuccess) {
+                    (void)cudaGetLastError();
+                    imported_all = false;
+                    continue;
+                }
+                it = table.emplace(static_cast<uintptr_t>(pr.base), im).first;
+            }
+            peer_ptrs[r] = static_cast<char *>(it->second.mapped) + pr.offset;
+        }
+        // every handle was seen before: every import above came from the tables
+        if (any_fresh || !imported_all) { imported_all = rdv_->all_agree(imported_all); }
+        return imported_all;
+    }
+
+    void drop_registrations() override
+    {
+        if (opt_.loopback || opt_.world == 1) { return; }
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        rdv_->barrier();  // nobody has a kernel on these mappings any more
+        close_imports();
+        exported_.clear();
+        rdv_->barrier();
+    }
+
+    size_t registrations() const override
+    {
+        size_t n = 0;
+        for (const auto &t : imported_) { n += t.size(); }
+        return n;
+    }
+
+    void close_imports()
+    {
+        for (auto &table : imported_) {
+            for (auto &kv : table) { (void)cudaIpcCloseMemHandle(kv.second.mapped); }
+            table.clear();
+        }
+        (void)cudaGetLastError();
     }
 
     // ------------------------------------------------------- algorithm table
@@ -369,8 +525,19 @@ class World final : public DeviceWorld
         const size_t esize = sizes[c.dt];
         const size_t bytes = c.count * esize;
         const size_t nvec = (bytes + 15) / 16;
-        if (c.off % 16 != 0 || c.off < kDataOffset || c.off + nvec * 16 > arena_bytes_) {
+        const bool registered = c.peer_data != nullptr;
+        if (!registered &&
+            (c.off % 16 != 0 || c.off < kDataOffset || c.off + nvec * 16 > arena_bytes_)) {
             throw std::invalid_argument("all_reduce: symmetric buffer outside the arena");
+        }
+        if (registered) {
+            for (int r = 0; r < opt_.world; ++r) {
+                if (c.peer_data[r] == nullptr ||
+                    reinterpret_cast<uintptr_t>(c.peer_data[r]) % 16 != 0) {
+                    throw std::invalid_argument("all_reduce: registered buffers must be mapped "
+                                                "on every rank and 16-byte aligned");
+                }
+            }
         }
         const int user_dt = c.user_dtype < 0 ? c.dt : c.user_dtype;
         if (user_dt != c.dt && !((c.dt == 8 || c.dt == 9) && user_dt == 10)) {
@@ -387,7 +554,7 @@ class World final : public DeviceWorld
             c.phases == kPhaseAll) {
             // alone on the GPU: one scaled copy, straight from the source to the
             // destination (the arena buffer stands in for whichever is absent)
-            char *sym = base_[0] + c.off;
+            char *sym = registered ? static_cast<char *>(c.peer_data[0]) : base_[0] + c.off;
             const void *from = (c.src != nullptr && c.src[0] != nullptr) ? c.src[0] : sym;
             void *to = (c.dst != nullptr && c.dst[0] != nullptr) ? c.dst[0] : sym;
             return launch_local_scale(from, to, c.count, c.dt, c.scale, c.has_scale ? 1 : 0,
@@ -400,6 +567,9 @@ class World final : public DeviceWorld
         const bool nvls = (algo == kAlgoNvls || algo == kAlgoNvlsOneShot);
         if (!owner && any_dst_null && c.table == nullptr && c.root < 0) {
             throw std::invalid_argument("all_reduce: one-shot algorithms need a destination");
+        }
+        if (nvls && registered) {
+            throw std::invalid_argument("all_reduce: NVLS needs a buffer in the symmetric arena");
         }
         if (nvls && (!has_nvls() || !nvls_supported(c.dt, c.op))) {
             throw std::invalid_argument("all_reduce: NVLS not available for this dtype/op/world");
@@ -428,7 +598,23 @@ class World final : public DeviceWorld
             a.dst[v] = c.dst != nullptr ? c.dst[v] : nullptr;
             a.table[v] = c.table != nullptr ? c.table[v] : nullptr;
         }
-        a.off = c.off;
+        for (int r = 0; r < opt_.world; ++r) {
+            a.data[r] = registered ? static_cast<char *>(c.peer_data[r]) : base_[r] + c.off;
+            a.push[r] = (registered && c.peer_push != nullptr)
+                            ? static_cast<char *>(c.peer_push[r])
+                            : a.data[r];
+        }
+        if (registered && c.peer_push != nullptr) {
+            for (int r = 0; r < opt_.world; ++r) {
+                const bool needed = c.root < 0 || c.root == r;
+                if ((needed && a.push[r] == nullptr) ||
+                    reinterpret_cast<uintptr_t>(a.push[r]) % 16 != 0) {
+                    throw std::invalid_argument("all_reduce: registered outputs must be mapped "
+                                                "and 16-byte aligned");
+                }
+            }
+        }
+        a.off = registered ? 0 : c.off;
         a.count = c.count;
         a.nvec = nvec;
         a.ntable = c.ntable;
@@ -470,8 +656,17 @@ class World final : public DeviceWorld
     {
         if (c.bytes == 0) { return 0; }
         const size_t nvec = (c.bytes + 15) / 16;
-        if (c.off % 16 != 0 || c.off < kDataOffset || c.off + nvec * 16 > arena_bytes_) {
-            throw std::invalid_argument("gather: symmetric buffer outside the arena");
+        const bool registered = c.peer_data != nullptr;
+        const bool all_gather = c.root < 0;
+        if (c.sym_stride % 16 != 0) {
+            throw std::invalid_argument("gather: blocks of a region start on 16-byte boundaries");
+        }
+        const size_t span = all_gather
+                                ? static_cast<size_t>(opt_.world - 1) * c.sym_stride + nvec * 16
+                                : nvec * 16;
+        if (!registered &&
+            (c.off % 16 != 0 || c.off < kDataOffset || c.off + span > arena_bytes_)) {
+            throw std::invalid_argument("gather: symmetric region outside the arena");
         }
         GatherArgs a;
         std::memset(&a, 0, sizeof(a));
@@ -479,26 +674,55 @@ class World final : public DeviceWorld
             a.src[v] = c.src != nullptr ? c.src[v] : nullptr;
             a.dst[v] = c.dst != nullptr ? c.dst[v] : nullptr;
         }
-        a.off = c.off;
+        for (int r = 0; r < opt_.world; ++r) {
+            a.data[r] = registered ? static_cast<char *>(c.peer_data[r]) : base_[r] + c.off;
+            if (a.data[r] == nullptr || reinterpret_cast<uintptr_t>(a.data[r]) % 16 != 0) {
+                throw std::invalid_argument("gather: regions must be mapped and 16-byte aligned");
+            }
+        }
+        a.off = registered ? 0 : c.off;
         a.bytes = c.bytes;
+        a.sym_stride = c.sym_stride;
         a.stride = c.stride != 0 ? c.stride : c.bytes;
         a.root = c.root;
+        a.start_barrier = c.start_barrier ? 1 : 0;
         a.end_barrier = c.end_barrier ? 1 : 0;
-        a.algo = kBcastPull;
-        if (c.root >= 0 && opt_.world > 2) {
-            // measured: pulling from root costs (n-1) copies on root's links
-            if (c.algo >= 0) {
-                a.algo = c.algo;
-            } else if (c.bytes >= (256u << 10)) {
-                a.algo = has_nvls() ? kBcastNvls : kBcastScatter;
-            }
-            if (a.algo == kBcastNvls && !has_nvls()) {
-                throw std::invalid_argument("broadcast: NVLS is not available");
-            }
+        // with two GPUs the switch has nothing to add (measured: multimem.st 340 GB/s
+        // against 640 GB/s for plain stores at 256 MB)
+        const bool mc_possible = has_nvls() && !registered && opt_.world > 2;
+        if (c.algo >= 0) {
+            a.algo = c.algo;
+        } else if (all_gather) {
+            // measured: posted stores beat peer loads once the message is past the
+            // latency-bound sizes
+            a.algo = (opt_.world > 1 && c.bytes >= gather_push_min_) ? kGatherPush : kBcastPull;
+        } else if (opt_.world > 1 && c.bytes >= (256u << 10)) {
+            // pulling from root costs (n-1) copies on root's links
+            a.algo = mc_possible ? kBcastNvls : (opt_.world > 2 ? kBcastScatter : kGatherPush);
+        } else {
+            a.algo = kBcastPull;
+        }
+        if (a.algo == kBcastNvls && !mc_possible) {
+            throw std::invalid_argument("broadcast: NVLS needs the multicast mapping of the arena");
+        }
+        a.use_mc = c.use_mc >= 0 ? (c.use_mc != 0 && mc_possible) : (mc_possible && gather_mc_);
+        if (all_gather && a.algo == kBcastPull && c.src != nullptr && c.sym_stride == 0) {
+            // one block per region: block p is read at p * 0
         }
         int blocks = c.blocks > 0 ? c.blocks : pick_blocks(nvec, kAlgoOneShot);
         if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
         return launch_gather(make_ctx(), a, blocks, vranks_, stream);
+    }
+
+    int unpack_blocks(const void *region, void *dst, size_t bytes, size_t sym_stride,
+                      size_t stride, int blocks_n, void *stream) override
+    {
+        if (bytes == 0 || blocks_n <= 0) { return 0; }
+        const size_t nvec = (bytes + 15) / 16;
+        const int grid = static_cast<int>(std::min<size_t>(
+            std::max<size_t>(1, nvec / (static_cast<size_t>(kThreads) * 4)),
+            static_cast<size_t>(2 * num_sms_)));
+        return launch_unpack_blocks(region, dst, bytes, sym_stride, stride, blocks_n, grid, stream);
     }
 
     int barrier(void *stream) override
@@ -898,6 +1122,7 @@ class World final : public DeviceWorld
                 // a peer is gone; carry on with local cleanup
             }
         }
+        close_imports();
         release_vmm();
         for (void *q : opened_) { (void)cudaIpcCloseMemHandle(q); }
         opened_.clear();

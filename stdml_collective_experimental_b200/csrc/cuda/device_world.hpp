@@ -48,6 +48,13 @@ struct DeviceStatus {
 // (1 for a real world, `world` for a loopback world).
 struct AllReduceCall {
     size_t off = 0;  // arena byte offset of the symmetric buffer
+    // Instead of `off`: the buffer of every rank of the world (world() entries) as
+    // mapped in this process: a user buffer registered with register_buffer().
+    // No NVLS then (the multicast mapping covers the arena only).
+    void *const *peer_data = nullptr;
+    // With peer_data: where the owner algorithms store results instead (world()
+    // entries; reduce-to-root needs [root] only).  Null: into peer_data itself.
+    void *const *peer_push = nullptr;
     const void *const *src = nullptr;
     void *const *dst = nullptr;
     const GroupEntry *const *table = nullptr;  // device pointers, one per vrank
@@ -66,14 +73,19 @@ struct AllReduceCall {
 };
 
 struct GatherCall {
-    size_t off = 0;
-    const void *const *src = nullptr;
-    void *const *dst = nullptr;
-    size_t bytes = 0;
-    size_t stride = 0;  // all_gather: distance between rank blocks in dst (0: bytes)
+    size_t off = 0;  // arena offset of the symmetric region (a staging slot or a heap buffer)
+    // Instead of `off`: every rank's region as mapped here (registered user buffers).
+    void *const *peer_data = nullptr;
+    const void *const *src = nullptr;  // per vrank; null entry: block already in place
+    void *const *dst = nullptr;        // per vrank; null entry: result stays in the region
+    size_t bytes = 0;       // per rank block
+    size_t sym_stride = 0;  // all_gather: distance between rank blocks in the region
+    size_t stride = 0;      // all_gather: distance between rank blocks in dst (0: bytes)
     int root = -1;
     int blocks = 0;
-    int algo = -1;  // broadcast: -1 pick, else kBcast*
+    int algo = -1;       // -1 pick, else kBcast* / kGatherPush
+    int use_mc = -1;     // -1 pick; push through the switch (needs NVLS and an arena region)
+    bool start_barrier = false;  // the region is live memory of its owner (zero-copy)
     bool end_barrier = false;
 };
 
@@ -99,6 +111,20 @@ class DeviceWorld
     // Offset of `p` inside the arena of virtual rank `vr`, or SIZE_MAX.
     virtual size_t offset_of(const void *p, int vr = 0) const = 0;
 
+    // Registration of ordinary device memory (collective; every rank passes its
+    // own buffer, or null for "none from me").  `ptrs` has vranks() entries,
+    // `peer_ptrs` receives world() entries: rank r's buffer as mapped in this
+    // process (own buffers as they are, null where a rank passed null).  The
+    // base allocation of each buffer is exported once as a CUDA IPC handle over
+    // the local rendezvous and stays mapped on the peers until
+    // drop_registrations() or the end of the world: the owner must not free it
+    // before.  Returns false, on every rank alike, when some rank cannot export
+    // (memory that did not come from cudaMalloc) or import; callers then stage.
+    virtual bool resolve_peers(const void *const *ptrs, size_t bytes, void **peer_ptrs) = 0;
+    // Collective: unmaps every peer buffer imported so far.
+    virtual void drop_registrations() = 0;
+    virtual size_t registrations() const = 0;  // peer allocations mapped now
+
     // Symmetric heap: every rank must make the same calls in the same order.
     // Returns an arena offset (256-byte aligned).  Throws std::bad_alloc.
     virtual size_t alloc(size_t bytes) = 0;
@@ -113,6 +139,9 @@ class DeviceWorld
     // arguments that the kernels could not run.
     virtual int all_reduce(const AllReduceCall &c, void *stream) = 0;
     virtual int gather(const GatherCall &c, void *stream) = 0;
+    // Local copy of `blocks_n` gathered blocks out of a region into user memory.
+    virtual int unpack_blocks(const void *region, void *dst, size_t bytes, size_t sym_stride,
+                              size_t stride, int blocks_n, void *stream) = 0;
     virtual int barrier(void *stream) = 0;
     // Loopback worlds only: launch the barrier for the first `rows` virtual
     // ranks.  With rows < world the missing ranks never arrive, so the wait

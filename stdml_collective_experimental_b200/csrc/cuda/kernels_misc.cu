@@ -136,9 +136,11 @@ void launch_barrier(const CommCtx &ctx, int vranks, void *stream)
     barrier_kernel<<<1, kThreads, 0, s>>>(ctx);
 }
 
-// One block per rank of `bytes` bytes.  all_gather: every rank packs its block
-// into its arena slot, then pulls every peer's slot into dst + peer * stride.
-// broadcast: three ways to get root's data to everybody, see kBcast*.
+// all_gather and broadcast.  Data moves between GPUs either by pull (16-byte
+// peer loads: small messages, one barrier) or by push (posted 16-byte stores, or
+// multimem.st through the switch, into every rank's symmetric region: large
+// messages; stores are not bound by the round trip that loads pay).  With a
+// destination outside the region the kernel ends with a local unpack.
 __device__ __forceinline__ void copy_span_to_user(char *out, unsigned long long bytes,
                                                   const char *from, const Span &sp)
 {
@@ -158,6 +160,33 @@ __device__ __forceinline__ void copy_span_to_user(char *out, unsigned long long 
     }
 }
 
+// Vectors [sp.lo, sp.hi) of one block: read them from `src` (user memory, any
+// alignment, `bytes` long) or from `sym` (16-byte vectors) and hand each to
+// put(v, x), four loads in flight per thread.
+template <typename Put>
+__device__ __forceinline__ void for_each_block_vec(const void *src, const char *sym,
+                                                   unsigned long long bytes, const Span &sp,
+                                                   Put put)
+{
+    const bool al = src != nullptr && ptr_aligned16(src);
+    unsigned long long v = sp.lo + threadIdx.x;
+    for (; v + 3ull * kThreads < sp.hi; v += 4ull * kThreads) {
+        uint4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const unsigned long long vu = v + u * kThreads;
+            x[u] = src != nullptr ? load_user_vec<DT_U8>(src, false, vu, bytes, al)
+                                  : ld_arena_v4(sym + vu * 16ull);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { put(v + u * kThreads, x[u]); }
+    }
+    for (; v < sp.hi; v += kThreads) {
+        put(v, src != nullptr ? load_user_vec<DT_U8>(src, false, v, bytes, al)
+                              : ld_arena_v4(sym + v * 16ull));
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
     gather_kernel(const __grid_constant__ CommCtx ctx, const __grid_constant__ GatherArgs a)
 {
@@ -171,72 +200,97 @@ __global__ void __launch_bounds__(kThreads)
 
     const unsigned long long nvec = (a.bytes + 15ull) / 16ull;
     const Span whole = span_of(nvec, 1, 0, nb, b);
-    char *mine = ctx.base[rank] + a.off;
+    char *mine = a.data[rank];
     const void *src = a.src[vr];
     char *dst = static_cast<char *>(a.dst[vr]);
     const bool bcast = a.root >= 0;
     const bool is_root = a.root == rank;
 
-    if (bcast && a.algo == kBcastNvls) {
-        // root stores every vector once; the switch replicates it into all slots
+    if (a.start_barrier) {
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+    }
+
+    if (a.algo == kGatherPush && !bcast) {
+        // ---- all_gather, push: my block goes into block `rank` of every region
+        const unsigned long long at = static_cast<unsigned long long>(rank) * a.sym_stride;
+        for_each_block_vec(src, mine + at, a.bytes, whole,
+                           [&](unsigned long long v, const uint4 &x) {
+                               if (a.use_mc) {
+                                   mm_st_v4(ctx.mc_base + a.off + at + v * 16ull, x);
+                                   return;
+                               }
+                               for (int i = 0; i < world; ++i) {
+                                   const int r = (rank + 1 + i) % world;  // own region last
+                                   if (r == rank && src == nullptr) { continue; }  // in place
+                                   st_arena_v4(a.data[r] + at + v * 16ull, x);
+                               }
+                           });
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (dst != nullptr) {
+            for (int i = 0; i < world; ++i) {
+                const int p = (rank + i) % world;
+                copy_span_to_user(dst + static_cast<unsigned long long>(p) * a.stride, a.bytes,
+                                  mine + static_cast<unsigned long long>(p) * a.sym_stride, whole);
+            }
+        }
+    } else if (bcast && (a.algo == kBcastNvls || a.algo == kGatherPush)) {
+        // ---- broadcast, push: root stores every vector into every region, through
+        // the switch (one store, replicated) or peer by peer
         if (is_root) {
-            const bool al = src != nullptr && ptr_aligned16(src);
-            unsigned long long v = whole.lo + threadIdx.x;
-            for (; v + 3ull * kThreads < whole.hi; v += 4ull * kThreads) {
-                uint4 x[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const unsigned long long vu = v + u * kThreads;
-                    x[u] = src != nullptr ? load_user_vec<DT_U8>(src, false, vu, a.bytes, al)
-                                          : ld_arena_v4(mine + vu * 16ull);
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    mm_st_v4(ctx.mc_base + a.off + (v + u * kThreads) * 16ull, x[u]);
-                }
-            }
-            for (; v < whole.hi; v += kThreads) {
-                const uint4 x = src != nullptr ? load_user_vec<DT_U8>(src, false, v, a.bytes, al)
-                                               : ld_arena_v4(mine + v * 16ull);
-                mm_st_v4(ctx.mc_base + a.off + v * 16ull, x);
-            }
+            const bool mc = a.use_mc || a.algo == kBcastNvls;
+            for_each_block_vec(src, mine, a.bytes, whole,
+                               [&](unsigned long long v, const uint4 &x) {
+                                   if (mc) {
+                                       mm_st_v4(ctx.mc_base + a.off + v * 16ull, x);
+                                       return;
+                                   }
+                                   for (int i = 0; i < world; ++i) {
+                                       const int r = (rank + 1 + i) % world;
+                                       if (r == rank && src == nullptr) { continue; }
+                                       st_arena_v4(a.data[r] + v * 16ull, x);
+                                   }
+                               });
         }
         if (!peer_barrier(ctx, rank, &sync)) { return; }
         if (dst != nullptr) { copy_span_to_user(dst, a.bytes, mine, whole); }
     } else if (bcast && a.algo == kBcastScatter) {
-        // root packs; rank r fetches slice r from root; then everybody fetches
-        // every slice from its holder, so root's links carry ~2 copies, not n-1
-        if (is_root && src != nullptr) {
-            const bool al = ptr_aligned16(src);
-            for (int s = 0; s < world; ++s) {
-                const Span sp = span_of(nvec, world, s, nb, b);
-                for (unsigned long long v = sp.lo + threadIdx.x; v < sp.hi; v += kThreads) {
-                    st_arena_v4(mine + v * 16ull, load_user_vec<DT_U8>(src, false, v, a.bytes, al));
-                }
-            }
-        }
-        if (!peer_barrier(ctx, rank, &sync)) { return; }
-        if (!is_root) {
-            const Span sp = span_of(nvec, world, rank, nb, b);
-            const char *from = ctx.base[a.root] + a.off;
-            for (unsigned long long v = sp.lo + threadIdx.x; v < sp.hi; v += kThreads) {
-                st_arena_v4(mine + v * 16ull, ld_arena_v4(from + v * 16ull));
-            }
-        }
-        if (!peer_barrier(ctx, rank, &sync)) { return; }
-        if (dst != nullptr) {
+        // ---- broadcast without the switch: root stores slice r into rank r's
+        // region (its own slice into its own), then every rank stores the slice it
+        // holds into all the other regions
+        if (is_root) {
             for (int i = 0; i < world; ++i) {
-                const int s = (rank + i) % world;  // own slice first, then round the ranks
+                const int s = (rank + 1 + i) % world;
+                if (s == rank && src == nullptr) { continue; }
                 const Span sp = span_of(nvec, world, s, nb, b);
-                copy_span_to_user(dst, a.bytes, ctx.base[s] + a.off, sp);
+                for_each_block_vec(src, mine, a.bytes, sp,
+                                   [&](unsigned long long v, const uint4 &x) {
+                                       st_arena_v4(a.data[s] + v * 16ull, x);
+                                   });
             }
         }
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        {
+            const Span sp = span_of(nvec, world, rank, nb, b);
+            for_each_block_vec(nullptr, mine, a.bytes, sp,
+                               [&](unsigned long long v, const uint4 &x) {
+                                   for (int i = 1; i < world; ++i) {
+                                       const int r = (rank + i) % world;
+                                       if (r == a.root) { continue; }  // root has it all
+                                       st_arena_v4(a.data[r] + v * 16ull, x);
+                                   }
+                               });
+        }
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (dst != nullptr) { copy_span_to_user(dst, a.bytes, mine, whole); }
     } else {
+        // ---- pull (small messages): pack, one barrier, read the peers' regions
         if (src != nullptr && (!bcast || is_root)) {
-            const bool al = ptr_aligned16(src);
-            for (unsigned long long v = whole.lo + threadIdx.x; v < whole.hi; v += kThreads) {
-                st_arena_v4(mine + v * 16ull, load_user_vec<DT_U8>(src, false, v, a.bytes, al));
-            }
+            const unsigned long long at =
+                bcast ? 0ull : static_cast<unsigned long long>(rank) * a.sym_stride;
+            for_each_block_vec(src, mine, a.bytes, whole,
+                               [&](unsigned long long v, const uint4 &x) {
+                                   st_arena_v4(mine + at + v * 16ull, x);
+                               });
         }
         if (!peer_barrier(ctx, rank, &sync)) { return; }
         if (dst != nullptr) {
@@ -245,7 +299,9 @@ __global__ void __launch_bounds__(kThreads)
                 // start with the next rank so that peers do not all read the same GPU first
                 const int p = bcast ? a.root : (rank + 1 + i) % world;
                 char *out = bcast ? dst : dst + static_cast<unsigned long long>(p) * a.stride;
-                copy_span_to_user(out, a.bytes, ctx.base[p] + a.off, whole);
+                const unsigned long long at =
+                    bcast ? 0ull : static_cast<unsigned long long>(p) * a.sym_stride;
+                copy_span_to_user(out, a.bytes, a.data[p] + at, whole);
             }
         }
     }
@@ -254,6 +310,30 @@ __global__ void __launch_bounds__(kThreads)
         if (!peer_barrier(ctx, rank, &sync)) { return; }
     }
     sync_end(ctx, rank, &sync);
+}
+
+// Local copy of gathered blocks out of a region into user memory: the unpack
+// of a chunk, run on its own stream while the next chunk is on the links.
+__global__ void __launch_bounds__(kThreads)
+    unpack_blocks_kernel(const char *region, char *dst, unsigned long long bytes,
+                         unsigned long long sym_stride, unsigned long long stride, int blocks_n)
+{
+    const unsigned long long nvec = (bytes + 15ull) / 16ull;
+    const Span whole = span_of(nvec, 1, 0, static_cast<int>(gridDim.x), static_cast<int>(blockIdx.x));
+    for (int p = 0; p < blocks_n; ++p) {
+        copy_span_to_user(dst + static_cast<unsigned long long>(p) * stride, bytes,
+                          region + static_cast<unsigned long long>(p) * sym_stride, whole);
+    }
+}
+
+int launch_unpack_blocks(const void *region, void *dst, unsigned long long bytes,
+                         unsigned long long sym_stride, unsigned long long stride, int blocks_n,
+                         int grid, void *stream)
+{
+    unpack_blocks_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const char *>(region), static_cast<char *>(dst), bytes, sym_stride, stride,
+        blocks_n);
+    return static_cast<int>(cudaGetLastError());
 }
 
 int launch_gather(const CommCtx &ctx, const GatherArgs &a, int blocks, int vranks, void *stream)

@@ -70,6 +70,40 @@ int setup_device(int dev)
 
 using namespace stdml::collective::cuda;
 
+// Copies the device-resident status block back to the host: one asynchronous
+// copy into the caller's own array and a wait for `stream`.  Nothing allocates.
+extern "C" int stdmlc_all_reduce_noalloc_status(int *out7, void *stream)
+{
+    if (out7 == nullptr) { return fail(2, "stdmlc_all_reduce_noalloc_status: null output"); }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return fail(1, "stdmlc_all_reduce_noalloc_status: no current CUDA device");
+    }
+    for (int i = 0; i < 7; ++i) { out7[i] = 0; }
+    if (g_status_ptr[dev] == nullptr) { return 0; }  // never called on this device: healthy
+    StatusBlock st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(&st, g_status_ptr[dev], sizeof(st), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) { e = cudaStreamSynchronize(s); }
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(1, std::string("stdmlc_all_reduce_noalloc_status: ") + cudaGetErrorString(e));
+    }
+    out7[0] = st.code;
+    out7[1] = st.rank;
+    out7[2] = st.block;
+    out7[3] = st.peer;
+    out7[4] = st.phase;
+    out7[5] = static_cast<int>(st.want);
+    out7[6] = static_cast<int>(st.have);
+    if (st.code == kStatusTimeout) {
+        return fail(4, "stdmlc_all_reduce_noalloc: a bounded wait of the last call ran out "
+                       "(two calls overlapping on the GPU?); its outputs are incomplete");
+    }
+    return st.code == kStatusOk ? 0 : fail(1, "stdmlc_all_reduce_noalloc: the last call failed");
+}
+
 extern "C" int stdmlc_all_reduce_noalloc(const void *const *in, void *const *out, int nranks,
                                          unsigned long long count, int dt, int op, double scale,
                                          void *stream)
@@ -135,6 +169,7 @@ extern "C" int stdmlc_all_reduce_noalloc(const void *const *in, void *const *out
         a.src[r] = in[r];
         a.dst[r] = out[r];
     }
+    for (int r = 0; r < nranks; ++r) { a.data[r] = a.push[r] = ctx.base[r] + kDataOffset; }
     a.off = kDataOffset;
     a.count = count;
     a.nvec = (bytes + 15) / 16;

@@ -46,7 +46,19 @@
  * The call is asynchronous: it returns after enqueuing a memset and one
  * cooperative kernel launch on `stream` (NULL = the legacy default stream).
  * It calls no cudaMalloc, cudaFree, cudaHostAlloc, nor any allocating library
- * routine.  Returns 0 on success. */
+ * routine.  Returns 0 on success.
+ *
+ * Learning of a failure: every wait inside the kernel is bounded (2 s).  A wait
+ * that runs out (in practice: two calls overlapping on the GPU, against the
+ * rule above) makes the kernel's blocks return early; the call itself returned
+ * 0 long before.  The record of that is kept in device memory, because this
+ * entry point may not allocate the pinned host memory that the regular
+ * sessions use for it.  stdmlc_all_reduce_noalloc_status(out7, stream) copies
+ * it back (one cudaMemcpyAsync on `stream` and a wait for that stream; no
+ * allocation either): out7 = {code, rank, block, peer, phase, want, have},
+ * code 0 = the calls enqueued on `stream` so far all completed.  It returns 0
+ * when healthy and STDMLC_ERR_TIMEOUT (4) after a wait that ran out; the next
+ * stdmlc_all_reduce_noalloc call clears the record. */
 #ifndef STDML_COLLECTIVE_NOALLOC_ALL_REDUCE_H
 #define STDML_COLLECTIVE_NOALLOC_ALL_REDUCE_H
 #ifdef __cplusplus
@@ -60,6 +72,8 @@ extern "C" {
 int stdmlc_all_reduce_noalloc(const void *const *in, void *const *out, int nranks,
                               unsigned long long count, int dt, int op, double scale,
                               void *stream);
+
+int stdmlc_all_reduce_noalloc_status(int *out7, void *stream);
 
 #ifdef __cplusplus
 }

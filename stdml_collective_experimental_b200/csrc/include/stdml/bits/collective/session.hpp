@@ -42,6 +42,7 @@ namespace stdml::collective
 namespace cuda
 {
 class DeviceSession;
+class NcclP2P;
 }
 
 class session
@@ -51,6 +52,8 @@ class session
     std::unique_ptr<cuda::DeviceSession> device_;
     bool device_tried_ = false;
     std::shared_ptr<std::mutex> device_mu_ = std::make_shared<std::mutex>();  // guards device_'s creation
+    std::unique_ptr<cuda::NcclP2P> p2p_;  // device send / recv, created by the first such call
+    cuda::NcclP2P *p2p();
     int spin_polls_ = 0;  // looks at a mailbox before a receiver sleeps (see session.cpp)
     bool established_ = false;  // the constructor's barrier has completed
     // Two-level execution for members on several hosts (built on first use,
@@ -195,8 +198,22 @@ class session
                         std::string name = "", void *stream = nullptr);
     void all_to_all(const void *input, void *output, size_t count, dtype dt,
                     std::string name = "", void *stream = nullptr);
+    // Host buffers: the rendezvous message of the TCP path.  Device buffers: NCCL
+    // send / recv on a stream of this session's own (libnccl is opened at run
+    // time; the two ranks of a pair build a communicator of two on first use).
+    // Both return when the buffer may be reused (send) or holds the data (recv);
+    // as with MPI, two ranks that send to each other first and receive second
+    // may wait for each other for ever: order the calls, or use the async forms.
     void recv(void *output, size_t count, dtype dt, size_t target, std::string name = "");
     void send(const void *input, size_t count, dtype dt, size_t target, std::string name = "");
+    // Device buffers: the transfer is enqueued behind the work that `stream`
+    // holds now and runs beside the collectives; the task finishes when the GPU
+    // has done it.  Host buffers: the call blocks as above and returns a
+    // finished task.
+    std::unique_ptr<task> async_send(const void *input, size_t count, dtype dt, size_t target,
+                                     std::string name = "", void *stream = nullptr);
+    std::unique_ptr<task> async_recv(void *output, size_t count, dtype dt, size_t target,
+                                     std::string name = "", void *stream = nullptr);
 
     bool consistent(const void *ptr, size_t size);
 

@@ -418,6 +418,32 @@ int stdmlc_session_all_reduce_async(void *s, const void *in, void *out, unsigned
     });
 }
 
+// send / recv that return a task (see session::async_send): device buffers are
+// enqueued behind `stream` and run beside the collectives
+int stdmlc_session_send_async(void *s, const void *in, unsigned long long count, int dt, int target,
+                              const char *name, void *stream, void **task)
+{
+    *task = nullptr;
+    return host_guarded([&] {
+        *task = SS(s)
+                    .async_send(in, count, static_cast<sc::dtype>(dt), static_cast<size_t>(target),
+                                name ? name : "", stream)
+                    .release();
+    });
+}
+
+int stdmlc_session_recv_async(void *s, void *out, unsigned long long count, int dt, int source,
+                              const char *name, void *stream, void **task)
+{
+    *task = nullptr;
+    return host_guarded([&] {
+        *task = SS(s)
+                    .async_recv(out, count, static_cast<sc::dtype>(dt), static_cast<size_t>(source),
+                                name ? name : "", stream)
+                    .release();
+    });
+}
+
 int stdmlc_task_poll(void *task, int *finished)
 {
     return host_guarded([&] {

@@ -18,6 +18,7 @@
 #include <stdml/bits/collective/stat.hpp>
 
 #include "../cuda/device_session.hpp"
+#include "../cuda/nccl_p2p.hpp"
 
 namespace stdml::collective
 {
@@ -1071,9 +1072,70 @@ void session::all_to_all(const void *input, void *output, size_t count, dtype dt
     if (first) { std::rethrow_exception(first); }
 }
 
+cuda::NcclP2P *session::p2p()
+{
+    std::lock_guard<std::mutex> lk(*device_mu_);
+    if (p2p_) { return p2p_.get(); }
+    int local = 0;
+    for (size_t r = 0; r < rank_; ++r) {
+        if (peers_[r].ipv4 == peers_[rank_].ipv4) { ++local; }
+    }
+    if (const auto v = parse_env_int("STDML_COLLECTIVE_DEVICE_ID")) {
+        local = static_cast<int>(*v);
+    } else if (const auto l = parse_env_int("LOCAL_RANK")) {
+        local = static_cast<int>(*l);
+    }
+    const int ndev = cuda::cuda_device_count();
+    if (ndev <= 0) { throw std::runtime_error("device send/recv needs a CUDA device"); }
+    // the communicator id of a pair travels as an ordinary host message
+    auto exchange = [this](int peer, bool i_send, void *id, size_t size) {
+        if (i_send) {
+            send(id, size, u8, static_cast<size_t>(peer), "stdml::nccl::id");
+        } else {
+            recv(id, size, u8, static_cast<size_t>(peer), "stdml::nccl::id");
+        }
+    };
+    p2p_ = std::make_unique<cuda::NcclP2P>(static_cast<int>(rank_), local % ndev, exchange);
+    return p2p_.get();
+}
+
+std::unique_ptr<task> session::async_send(const void *input, size_t count, dtype dt, size_t target,
+                                          std::string name, void *stream)
+{
+    if (target >= peers_.size()) { throw std::out_of_range("send: no such rank"); }
+    if (count > 0 && cuda::pointer_kind(input) == 1) {
+        ensure_usable("send");
+        cuda::NcclP2P *p = p2p();
+        p->send(input, count, static_cast<int>(dt), static_cast<int>(target), stream, nullptr);
+        return std::make_unique<event_task>(p->stream());
+    }
+    send(input, count, dt, target, std::move(name));
+    return std::make_unique<noop_task>();
+}
+
+std::unique_ptr<task> session::async_recv(void *output, size_t count, dtype dt, size_t target,
+                                          std::string name, void *stream)
+{
+    if (target >= peers_.size()) { throw std::out_of_range("recv: no such rank"); }
+    if (count > 0 && cuda::pointer_kind(output) == 1) {
+        ensure_usable("recv");
+        cuda::NcclP2P *p = p2p();
+        p->recv(output, count, static_cast<int>(dt), static_cast<int>(target), stream, nullptr);
+        return std::make_unique<event_task>(p->stream());
+    }
+    recv(output, count, dt, target, std::move(name));
+    return std::make_unique<noop_task>();
+}
+
 void session::send(const void *input, size_t count, dtype dt, size_t target, std::string name)
 {
     if (target >= peers_.size()) { throw std::out_of_range("send: no such rank"); }
+    if (count > 0 && cuda::pointer_kind(input) == 1) {
+        // a device address means nothing to a socket: NCCL moves it, and the call
+        // returns when the GPU has sent it
+        async_send(input, count, dt, target, std::move(name), nullptr)->finish();
+        return;
+    }
     const std::string tag = versioned(*this, "stdml::p2p::" + name);
     client_pool_->require(conn_collective)
         ->send(peers_[target], tag.c_str(), input, count * dtype_size(dt),
@@ -1084,6 +1146,10 @@ void session::recv(void *output, size_t count, dtype dt, size_t target, std::str
 {
     if (target >= peers_.size()) { throw std::out_of_range("recv: no such rank"); }
     ensure_usable("recv");
+    if (count > 0 && cuda::pointer_kind(output) == 1) {
+        async_recv(output, count, dt, target, std::move(name), nullptr)->finish();
+        return;
+    }
     const std::string tag = versioned(*this, "stdml::p2p::" + name);
     take_into(target, tag, output, count * dtype_size(dt), "recv");
 }

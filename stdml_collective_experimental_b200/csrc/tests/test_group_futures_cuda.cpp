@@ -68,8 +68,12 @@ int main()
     }
     // warm the device path up (its first call builds the arena) so that the
     // launch count below belongs to the group alone
-    sess.all_reduce(bufs[m - 1], bufs[m - 1], counts[m - 1], f32, stdml::collective::max, "warm");
+    void *scratch = nullptr;
+    CUDA_OK(cudaMalloc(&scratch, 4096));
+    CUDA_OK(cudaMemset(scratch, 0, 4096));
+    sess.all_reduce(scratch, scratch, 1024, f32, stdml::collective::max, "warm");
     CUDA_OK(cudaDeviceSynchronize());
+    cudaFree(scratch);
     const unsigned long long before = sess.device_launches();
 
     std::vector<std::promise<workspace>> promises(m);

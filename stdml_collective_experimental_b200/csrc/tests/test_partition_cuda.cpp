@@ -160,15 +160,17 @@ int main()
         t2.world = 2;
         EXPECT(select_algo(t2, 8 << 20, true, false) == kAlgoOneShot);  // the switch adds nothing at 2
         EXPECT(select_algo(t2, 1 << 30, true, false) == kAlgoTwoShotTma);  // large: bulk-copy pulls
+        EXPECT(select_algo(t2, 32 << 20, true, true) == kAlgoTwoShot);
         t2.tma_min = SIZE_MAX;
         EXPECT(select_algo(t2, 1 << 30, true, false) == kAlgoTwoShot);
         AlgoTuning t4 = t8;
         t4.world = 4;
         t4.has_nvls = false;
         EXPECT(select_algo(t4, 1 << 20, true, false) == kAlgoOneShot);
+        EXPECT(select_algo(t4, (1 << 20) + 16, true, false) == kAlgoTwoShot);
+        t4.tma_min = 1u << 20;
         EXPECT(select_algo(t4, (1 << 20) + 16, true, false) == kAlgoTwoShotTma);
         t4.tma_min = 64u << 20;
-        EXPECT(select_algo(t4, (1 << 20) + 16, true, false) == kAlgoTwoShot);
         EXPECT(select_algo(t4, 64u << 20, true, true) == kAlgoTwoShotTma);
         t8.tma_over_nvls_min = 32u << 20;  // NVLS worlds may prefer it from some size up
         EXPECT(select_algo(t8, 16u << 20, true, true) == kAlgoNvls);

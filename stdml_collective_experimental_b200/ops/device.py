@@ -179,8 +179,19 @@ class DeviceSession:
     def set_knob(self, name, value):
         """Named tuning knob, same value on every rank: nvls_variant (0..3),
         nvls_blocks, tma_blocks, tma_tile_vec, tma_min_bytes,
-        tma_over_nvls_min_bytes (negative: never), debug_checks."""
+        tma_over_nvls_min_bytes (negative: never), gather_push_min_bytes, gather_mc,
+        pipeline_min_bytes, debug_checks, and register_min_bytes: collectives on
+        ordinary CUDA tensors of at least that many bytes map the tensors'
+        allocations on every peer (CUDA IPC, cached per allocation) and run
+        zero-copy on them; negative: never (the default).  Tensors used that way
+        must stay allocated until drop_registrations() or close()."""
         _native.check(self._lib.stdmlc_dw_set_knob(self._h, name.encode(), int(value)))
+
+    def drop_registrations(self):
+        """Collective: unmap every peer allocation that registered calls mapped.
+        Call it before such memory goes back to the driver (for torch tensors:
+        before torch.cuda.empty_cache())."""
+        _native.check(self._lib.stdmlc_dw_drop_registrations(self._h))
 
     # ---------------------------------------------------------- symmetric heap
     def symm_empty(self, shape, dtype=torch.float32):

@@ -62,6 +62,8 @@ def _lib():
         lib.stdmlc_cluster_resize_json.argtypes = [c.c_char_p, u64, c.c_char_p, u64]
         lib.stdmlc_session_all_reduce_async.argtypes = [vp, vp, vp, u64, c.c_int, c.c_int,
                                                         c.c_char_p, vp, vpp]
+        lib.stdmlc_session_send_async.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p, vp, vpp]
+        lib.stdmlc_session_recv_async.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p, vp, vpp]
         lib.stdmlc_task_poll.argtypes = [vp, c.POINTER(c.c_int)]
         lib.stdmlc_task_finish.argtypes = [vp]
         lib.stdmlc_task_destroy.argtypes = [vp]
@@ -296,15 +298,45 @@ class Session:
         return o
 
     def send(self, tensor, target, name=""):
+        """Returns when the tensor may be reused.  CPU tensors: the TCP rendezvous
+        message; CUDA tensors: NCCL send on the session's transfer stream, after the
+        work the current stream holds."""
+        if tensor.is_cuda:
+            self.send_async(tensor, target, name).wait()
+            return
         t = _checked(tensor, "send")
         _native.check(self._lib.stdmlc_session_send(
             self._h, t.data_ptr(), t.numel(), dtype_code(t.dtype), target, name.encode()))
 
     def recv(self, out, source, name=""):
+        if out.is_cuda:
+            return self.recv_async(out, source, name).wait()
         o = _checked(out, "recv")
         _native.check(self._lib.stdmlc_session_recv(
             self._h, o.data_ptr(), o.numel(), dtype_code(o.dtype), source, name.encode()))
         return o
+
+    def send_async(self, tensor, target, name=""):
+        """Start a send and return a Task (CUDA tensors: runs beside the collectives
+        on a stream of its own; CPU tensors: done when this returns)."""
+        t = _checked(tensor, "send_async")
+        h = ctypes.c_void_p()
+        _native.check(self._lib.stdmlc_session_send_async(
+            self._h, t.data_ptr(), t.numel(), dtype_code(t.dtype), int(target), name.encode(),
+            _stream_of(t), ctypes.byref(h)))
+        task = Task(h, (t,))
+        self._tasks.add(task)
+        return task
+
+    def recv_async(self, out, source, name=""):
+        o = _checked(out, "recv_async")
+        h = ctypes.c_void_p()
+        _native.check(self._lib.stdmlc_session_recv_async(
+            self._h, o.data_ptr(), o.numel(), dtype_code(o.dtype), int(source), name.encode(),
+            _stream_of(o), ctypes.byref(h)))
+        task = Task(h, (o,))
+        self._tasks.add(task)
+        return task
 
     def barrier(self):
         _native.check(self._lib.stdmlc_session_barrier(self._h))

@@ -165,6 +165,112 @@ def main():
     torch.cuda.synchronize()
     sess.check()
 
+    # ---- registered execution: ordinary tensors, their allocations mapped on every
+    # peer, no staging (the launch count tells: one launch whatever the size)
+    sess.set_knob("register_min_bytes", 0)
+    for dtype in (torch.float32, torch.bfloat16, torch.int32):
+        for n in (1000, 3_000_004):
+            host = inputs(world, n, dtype, seed=n + 9, exact=True)
+            want = reduce_many(host, "sum")
+            x = host[rank].cuda()
+            before = sess.launches
+            sess.all_reduce(x)  # in place
+            torch.cuda.synchronize()
+            sess.check()
+            assert sess.launches == before + 1, "registered calls are one launch"
+            assert bits_equal(x.cpu(), want), ("registered in place", dtype, n)
+            x = host[rank].cuda()
+            y = torch.empty_like(x)
+            sess.all_reduce(x, out=y, scale=0.5 if dtype.is_floating_point else None)
+            torch.cuda.synchronize()
+            assert bits_equal(y.cpu(), reduce_many(host, "sum", 0.5 if dtype.is_floating_point else 1.0))
+            assert bits_equal(x.cpu(), host[rank]), "out of place must not touch the input"
+            for root in sorted({0, world - 1}):
+                r_out = torch.full((n,), 3, dtype=dtype, device="cuda")
+                sess.reduce(x, out=r_out, root=root)
+                torch.cuda.synchronize()
+                sess.check()
+                assert bits_equal(x.cpu(), host[rank])
+                if rank == root:
+                    assert bits_equal(r_out.cpu(), want), ("registered reduce", dtype, n, root)
+                else:
+                    assert torch.all(r_out == 3)
+                b = host[rank].cuda()
+                sess.broadcast(b, root=root)
+                torch.cuda.synchronize()
+                assert bits_equal(b.cpu(), host[root]), ("registered broadcast", dtype, n, root)
+            if (n * x.element_size()) % 16 == 0:
+                g_out = torch.empty(n * world, dtype=dtype, device="cuda")
+                before = sess.launches
+                sess.all_gather(x, g_out)
+                torch.cuda.synchronize()
+                sess.check()
+                assert sess.launches == before + 1
+                assert bits_equal(g_out.cpu(), torch.cat(host)), ("registered all_gather", dtype, n)
+    sess.drop_registrations()
+    sess.set_knob("register_min_bytes", -1)
+    x = torch.ones(1000, device="cuda")
+    sess.all_reduce(x)  # staged again
+    torch.cuda.synchronize()
+    assert torch.all(x == world)
+
+    # ---- the same three on symmetric buffers (zero-copy: pushed straight into the
+    # destinations, through the switch where there is one), and a message of
+    # several staging slots (chunks unpacked on a second stream)
+    for n in (4, 1000, 1_000_004):
+        host = inputs(world, n, torch.int32, seed=n + 1)
+        out = sess.symm_empty(n * world, torch.int32)
+        out.fill_(-1)
+        before = sess.launches
+        sess.all_gather(host[rank].cuda(), out)
+        torch.cuda.synchronize()
+        sess.check()
+        assert sess.launches == before + 1 and torch.equal(out.cpu(), torch.cat(host)), n
+        for use_mc in (0, 1):
+            sess.set_knob("gather_mc", use_mc)
+            out.fill_(-1)
+            sess.all_gather(host[rank].cuda(), out)
+            torch.cuda.synchronize()
+            assert torch.equal(out.cpu(), torch.cat(host)), (n, use_mc)
+        sess.symm_free(out)
+        sym = sess.symm_empty(n, torch.int32)
+        for root in sorted({0, world - 1}):
+            sym.copy_(host[rank])
+            sess.broadcast(sym, root=root)
+            torch.cuda.synchronize()
+            assert torch.equal(sym.cpu(), host[root]), (n, root)
+            sym.copy_(host[rank])
+            r_out = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+            sess.reduce(sym, out=r_out, root=root)
+            torch.cuda.synchronize()
+            sess.check()
+            assert torch.equal(sym.cpu(), host[rank])
+            if rank == root:
+                assert torch.equal(r_out.cpu(), reduce_many(host, "sum"))
+            else:
+                assert torch.all(r_out == -7)
+        fsym = sess.symm_empty(n, torch.float32)
+        fhost = inputs(world, n, torch.float32, seed=n, exact=True)
+        fsym.copy_(fhost[rank])
+        f_out = torch.zeros(n, device="cuda")
+        sess.reduce(fsym, out=f_out, root=0, scale=0.5)  # f32 sum: the switch reduces for root
+        torch.cuda.synchronize()
+        if rank == 0:
+            assert bits_equal(f_out.cpu(), reduce_many(fhost, "sum", 0.5))
+        sess.symm_free(fsym)
+        sess.symm_free(sym)
+    n = 5_000_001  # 20 MB per rank through 4 MB slots
+    host = inputs(world, n, torch.int32, seed=77)
+    out = torch.empty(n * world, dtype=torch.int32, device="cuda")
+    sess.all_gather(host[rank].cuda(), out)
+    b = host[rank].cuda()
+    sess.broadcast(b, root=world - 1)
+    sess.all_reduce(out[:1000])  # a staged call right after the pipelines: the slots are free
+    torch.cuda.synchronize()
+    sess.check()
+    assert torch.equal(out[1000:].cpu(), torch.cat(host)[1000:]) and torch.equal(b.cpu(), host[world - 1])
+    assert torch.equal(out[:1000].cpu(), torch.cat(host)[:1000] * world)
+
     # ---- the collectives as torch custom ops
     from stdml_collective_experimental_b200.ops import torch_ops
     torch_ops.set_default_session(sess)

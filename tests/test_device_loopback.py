@@ -343,6 +343,124 @@ def test_broadcast_and_reduce(sess, n):
     sess.check()
 
 
+@pytest.mark.parametrize("n", [4, 1000, 300_004])
+def test_zero_copy_all_gather_broadcast_reduce_on_symmetric_buffers(sess, n):
+    """Output (all_gather, broadcast) or input (reduce) in the symmetric heap: one
+    launch, no staging; blocks are pushed straight into every rank's buffer."""
+    w = sess.world
+    host = make_inputs(w, n, torch.int32, seed=n + 3)
+    out = sess.symm_empty(n * w, torch.int32)
+    outs = out if sess.vranks > 1 else [out]
+    for o in outs:
+        o.fill_(-1)
+    ins = [h.cuda() for h in host]
+    before = sess.launches
+    sess.all_gather(ins if sess.vranks > 1 else ins[0], out)
+    torch.cuda.synchronize()
+    sess.check()
+    assert sess.launches == before + 1 or w == 1  # alone: a plain copy through the slots
+    for r in range(w):
+        assert torch.equal(outs[r].cpu(), torch.cat(host)), r
+    # in place: every rank's block already sits in its own output
+    for r in range(w):
+        outs[r].fill_(-1)
+        outs[r][r * n:(r + 1) * n].copy_(host[r])
+    views = [outs[r][r * n:(r + 1) * n] for r in range(w)]
+    sess.all_gather(views if sess.vranks > 1 else views[0], out)
+    torch.cuda.synchronize()
+    for r in range(w):
+        assert torch.equal(outs[r].cpu(), torch.cat(host)), (r, "in place")
+    sess.symm_free(out)
+
+    for root in sorted({0, w - 1}):
+        sym = sess.symm_empty(n, torch.int32)
+        syms = sym if sess.vranks > 1 else [sym]
+        for r in range(w):
+            syms[r].copy_(host[r])
+        sess.broadcast(sym, root=root)  # in place on a symmetric buffer
+        torch.cuda.synchronize()
+        sess.check()
+        for r in range(w):
+            assert torch.equal(syms[r].cpu(), host[root]), (root, r)
+        # from an ordinary tensor on root into symmetric buffers everywhere
+        for t in syms:
+            t.fill_(-5)
+        sess.broadcast(ins if sess.vranks > 1 else ins[0], out=sym, root=root)
+        torch.cuda.synchronize()
+        for r in range(w):
+            assert torch.equal(syms[r].cpu(), host[root]), (root, r, "out of place")
+        # reduce: symmetric inputs, ordinary output on root only
+        for r in range(w):
+            syms[r].copy_(host[r])
+        res = [torch.full((n,), -7, dtype=torch.int32, device="cuda") for _ in range(w)]
+        sess.reduce(sym, out=res if sess.vranks > 1 else res[0], root=root)
+        torch.cuda.synchronize()
+        sess.check()
+        for r in range(w):
+            if r == root:
+                assert torch.equal(res[r].cpu(), reduce_many(host, "sum"))
+            else:
+                assert bool((res[r] == -7).all())
+            assert torch.equal(syms[r].cpu(), host[r]), "reduce must leave its inputs alone"
+        sess.symm_free(sym)
+
+
+@pytest.mark.parametrize("algo_knob", [0, 1 << 40])
+def test_all_gather_push_and_pull_agree(sess, algo_knob):
+    sess.set_knob("gather_push_min_bytes", algo_knob)  # 0: always push; huge: always pull
+    try:
+        for n in (3, 1000, 70_001):
+            host = make_inputs(sess.world, n, torch.int16, seed=n)
+            outs = [torch.empty(n * sess.world, dtype=torch.int16, device="cuda")
+                    for _ in range(sess.world)]
+            ins = [h.cuda() for h in host]
+            sess.all_gather(ins if sess.vranks > 1 else ins[0],
+                            outs if sess.vranks > 1 else outs[0])
+            torch.cuda.synchronize()
+            sess.check()
+            for r in range(sess.world):
+                assert torch.equal(outs[r].cpu(), torch.cat(host)), (n, r)
+    finally:
+        sess.set_knob("gather_push_min_bytes", 64 << 10)
+
+
+def test_kernels_against_plain_pytorch_arithmetic(sess):
+    """An oracle that shares nothing with the library: the same reductions done by
+    PyTorch in float32 / float64 on the host.  all_reduce (every algorithm), the
+    fused group with the 1/world scale, and the bf16 wire format for f32 tensors."""
+    w = sess.world
+    g = torch.Generator().manual_seed(42)
+    n = 100_003
+    host = [torch.rand(n, generator=g) * 2 - 1 for _ in range(w)]
+    exact = torch.stack([h.double() for h in host]).sum(0)
+    f32 = host[0].clone()
+    for h in host[1:]:
+        f32 += h  # rank-ascending float32 adds: what the peer-load kernels do
+    for algo in ("oneshot", "twoshot") + (("twoshot_tma",) if w > 1 else ()):
+        dev = [h.cuda() for h in host]
+        sess.all_reduce(dev if sess.vranks > 1 else dev[0], algo=algo)
+        torch.cuda.synchronize()
+        sess.check()
+        for r in range(w):
+            assert torch.equal(dev[r].cpu(), f32), algo
+            assert torch.allclose(dev[r].cpu().double(), exact, rtol=0, atol=w * 2.0 ** -23)
+    sizes = [3, 1000, 70_001, 17]
+    hosts = [[torch.rand(m, generator=g) * 2 - 1 for m in sizes] for _ in range(w)]
+    dev = [[t.cuda() for t in hosts[r]] for r in range(w)]
+    sess.group_all_reduce(dev if sess.vranks > 1 else dev[0], scale=1.0 / w)
+    dev16 = [[t.cuda() for t in hosts[r]] for r in range(w)]
+    sess.group_all_reduce(dev16 if sess.vranks > 1 else dev16[0], scale=1.0 / w,
+                          wire_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    sess.check()
+    for i in range(len(sizes)):
+        mean = torch.stack([hosts[r][i].double() for r in range(w)]).mean(0)
+        for r in range(w):
+            assert torch.allclose(dev[r][i].cpu().double(), mean, rtol=0, atol=2.0 ** -22)
+            # bf16 wire: every operand rounded to 8 bits of mantissa, then the mean rounded
+            assert torch.allclose(dev16[r][i].cpu().double(), mean, rtol=0, atol=3 * 2.0 ** -8)
+
+
 def test_barrier_and_launch_count(sess):
     before = sess.launches
     for _ in range(5):

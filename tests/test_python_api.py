@@ -31,6 +31,18 @@ def test_python_peer_session(n, strategy, base, native_lib):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
 
 
+def test_resnet50_gradient_set_over_a_ring_of_four(native_lib):
+    """The "CPU plumbing" acceptance case, as specified: 4 processes, ring, the 161
+    f32 tensors of ResNet-50, N(0, 1) values seeded per rank, against a host sum."""
+    n, base = 4, 12170
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "config1_worker.py"), str(r),
+                               str(n), str(base)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(n)]
+    outs = collect(procs, 600)
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
+
+
 @pytest.mark.parametrize("strategy,base", [("star", 12140), ("ring", 12150)])
 def test_python_peer_failure_is_an_exception(strategy, base, native_lib):
     n = 3

@@ -277,3 +277,56 @@ def test_data_parallel_buckets_and_gradient_accumulation_on_cpu(monkeypatch):
             assert torch.allclose(p.grad, dict(ref.named_parameters())[n].grad, atol=1e-6), n
     dp.close()
     assert all(p.grad is None for p in dp.params)
+
+
+def test_host_reducer_against_plain_pytorch_reductions():
+    """reduce_many is the oracle of every device test, so it is itself checked
+    against reductions that share no code with it: float64 / int64 PyTorch
+    arithmetic.  Integers, min and max must agree exactly; float sums and
+    products within one rounding of the output type per accumulation step."""
+    from stdml_collective_experimental_b200.utils.oracle import reduce_many
+    g = torch.Generator().manual_seed(0)
+    eps = {torch.float32: 2.0 ** -23, torch.float64: 2.0 ** -52, torch.bfloat16: 2.0 ** -7,
+           torch.float16: 2.0 ** -10}
+    for world in (1, 2, 3, 8):
+        for dtype in (torch.float32, torch.float64, torch.bfloat16, torch.float16, torch.int8,
+                      torch.int16, torch.int32, torch.int64, torch.uint8):
+            n = 1027
+            if dtype.is_floating_point:
+                xs = [(torch.rand(n, generator=g) + 0.5).to(dtype) for _ in range(world)]
+            else:
+                info = torch.iinfo(dtype)
+                xs = [torch.randint(max(info.min, -50), min(info.max, 50) + 1, (n,),
+                                    generator=g).to(dtype) for _ in range(world)]
+            wide = torch.stack([x.double() if dtype.is_floating_point else x.long() for x in xs])
+            for op in ("sum", "min", "max", "prod") + (() if dtype.is_floating_point else ("bit_xor",)):
+                got = reduce_many(xs, op)
+                assert got.dtype == dtype
+                if op == "min":
+                    assert torch.equal(got, wide.min(0).values.to(dtype)), (dtype, op, world)
+                elif op == "max":
+                    assert torch.equal(got, wide.max(0).values.to(dtype)), (dtype, op, world)
+                elif op == "bit_xor":
+                    want = wide[0]
+                    for w in wide[1:]:
+                        want = want ^ w
+                    assert torch.equal(got, want.to(dtype)), (dtype, world)
+                elif not dtype.is_floating_point:
+                    want = wide.sum(0) if op == "sum" else wide.prod(0)
+                    bits = torch.iinfo(dtype).bits  # integer results wrap around
+                    if dtype == torch.uint8:
+                        want = want % 256
+                    elif bits < 64:  # (values this small never leave int64)
+                        want = (want + (1 << (bits - 1))) % (1 << bits) - (1 << (bits - 1))
+                    assert torch.equal(got.long(), want), (dtype, op, world)
+                else:
+                    want = wide.sum(0) if op == "sum" else wide.prod(0)
+                    # 16-bit floats: accumulated in f32, rounded once; others: one rounding a step
+                    steps = 1 if dtype in (torch.bfloat16, torch.float16) else world
+                    tol = eps[dtype] * steps * 1.01
+                    assert torch.allclose(got.double(), want, rtol=tol, atol=0), (dtype, op, world)
+            if dtype.is_floating_point:
+                got = reduce_many(xs, "sum", 1.0 / 3.0)
+                want = wide.sum(0) / 3.0
+                steps = 2 if dtype in (torch.bfloat16, torch.float16) else world + 1
+                assert torch.allclose(got.double(), want, rtol=eps[dtype] * steps * 1.01, atol=0)

@@ -19,6 +19,7 @@ pytestmark = pytest.mark.gpu
 
 from stdml_collective_experimental_b200 import DeviceSession, _native  # noqa: E402
 from stdml_collective_experimental_b200.ops.device import dtype_code, op_code  # noqa: E402
+from stdml_collective_experimental_b200.utils.oracle import reduce_many  # noqa: E402
 
 MAX_BYTES = 512 << 10
 MAX_RANKS = 8
@@ -32,6 +33,16 @@ def entry_point():
                    ctypes.c_ulonglong, ctypes.c_int, ctypes.c_int, ctypes.c_double,
                    ctypes.c_void_p]
     return lib, fn
+
+
+def status(lib):
+    """(return code, the seven status words) of the calls enqueued so far."""
+    fn = lib.stdmlc_all_reduce_noalloc_status
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
+    out = (ctypes.c_int * 7)()
+    rc = fn(out, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    return rc, tuple(out)
 
 
 def ptrs(tensors):
@@ -49,6 +60,7 @@ def call(fn, ins, outs, op, scale):
     (8, torch.bfloat16, "sum", 262_144, 1.0),     # exactly the size limit
     (2, torch.int32, "max", 17, 1.0),
     (3, torch.float16, "prod", 4099, 1.0),
+    (6, torch.float64, "sum", 10_007, 1.0 / 3.0),  # a scale that is not a float
 ])
 def test_noalloc_matches_device_session_twice(world, dtype, op, n, scale):
     lib, fn = entry_point()
@@ -69,9 +81,20 @@ def test_noalloc_matches_device_session_twice(world, dtype, op, n, scale):
             assert rc == 0, lib.stdmlc_last_error().decode()
             torch.cuda.synchronize()
             sess.check()
+            assert status(lib) == (0, (0, 0, 0, 0, 0, 0, 0)), "no bounded wait ran out"
+            # two oracles that share no code with the kernel: the host reducer
+            # (bit for bit) and a plain float64 PyTorch reduction (within rounding)
+            cpu_want = reduce_many(host, op, scale)
+            wide = torch.stack([h.double() for h in host])
+            wide = {"sum": wide.sum(0), "max": wide.max(0).values,
+                    "prod": wide.prod(0)}[op] * scale
+            tol = {torch.float32: 1e-6, torch.float64: 1e-14, torch.bfloat16: 1e-2,
+                   torch.float16: 2e-3, torch.int32: 0}[dtype]
             for r in range(world):
                 assert torch.equal(got[r].view(torch.uint8), want[r].view(torch.uint8)), \
                     (round_, r)
+                assert torch.equal(got[r].cpu().view(torch.uint8), cpu_want.view(torch.uint8))
+                assert torch.allclose(got[r].cpu().double(), wide, rtol=tol, atol=tol)
                 assert torch.equal(ins[r].cpu(), host[r]), "inputs must stay untouched"
         # in place: out[r] == in[r]
         ins = [h.cuda() for h in host]
