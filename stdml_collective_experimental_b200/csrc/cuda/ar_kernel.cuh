@@ -315,13 +315,17 @@ __device__ __forceinline__ void nvls_span(const CommCtx &ctx, unsigned long long
 }
 
 // ---- pack: user memory -> own arena buffer (the parts peers' block b read)
-template <int DT>
+// span_at(s): the part of shard s that THIS block index serves.  The barriers
+// pair blocks with the same index across ranks, so a block must pack exactly
+// what the peers' block of the same index will read, and unpack exactly what
+// they wrote.
+template <int DT, typename SpanAt>
 __device__ __forceinline__ void pack_phase(const AllReduceArgs &a, const GroupEntry *tab,
                                            const GroupEntry &single, char *mine, int shards,
-                                           int nb, int b, bool user_f32)
+                                           bool user_f32, SpanAt span_at)
 {
     for (int s = 0; s < shards; ++s) {
-        const Span sp = span_of(a.nvec, shards, s, nb, b);
+        const Span sp = span_at(s);
         for_each_entry<DT>(
             tab, a.ntable, single, sp.lo, sp.hi,
             [&](const GroupEntry &e, unsigned long long lo, unsigned long long hi) {
@@ -349,13 +353,13 @@ __device__ __forceinline__ void pack_phase(const AllReduceArgs &a, const GroupEn
 }
 
 // ---- unpack: own arena buffer -> user memory (owner algorithms only)
-template <int DT>
+template <int DT, typename SpanAt>
 __device__ __forceinline__ void unpack_phase(const AllReduceArgs &a, const GroupEntry *tab,
                                              const GroupEntry &single, const char *mine,
-                                             int shards, int nb, int b, bool user_f32)
+                                             int shards, bool user_f32, SpanAt span_at)
 {
     for (int s = 0; s < shards; ++s) {
-        const Span sp = span_of(a.nvec, shards, s, nb, b);
+        const Span sp = span_at(s);
         for_each_entry<DT>(
             tab, a.ntable, single, sp.lo, sp.hi,
             [&](const GroupEntry &e, unsigned long long lo, unsigned long long hi) {
@@ -471,7 +475,8 @@ __global__ void __launch_bounds__(kThreads)
     single.count = a.count;
 
     if ((phases & kPhasePack) != 0 && (tab != nullptr || single.src != nullptr)) {
-        pack_phase<DT>(a, tab, single, mine, shards, nb, b, user_f32);
+        pack_phase<DT>(a, tab, single, mine, shards, user_f32,
+                       [&](int s) { return span_of(a.nvec, shards, s, nb, b); });
     }
 
     if (do_reduce && !peer_barrier(ctx, rank, &sync)) { return; }
@@ -518,7 +523,8 @@ __global__ void __launch_bounds__(kThreads)
 
     if ((phases & kPhaseUnpack) != 0 && owner_algo && computes &&
         (tab != nullptr || single.dst != nullptr)) {
-        unpack_phase<DT>(a, tab, single, a.push[rank], shards, nb, b, user_f32);
+        unpack_phase<DT>(a, tab, single, a.push[rank], shards, user_f32,
+                         [&](int s) { return span_of(a.nvec, shards, s, nb, b); });
     }
 
     if (do_reduce) { sync_end(ctx, rank, &sync); }
@@ -710,6 +716,7 @@ __device__ __forceinline__ bool tma_reduce_span(const CommCtx &ctx, const AllRed
 // dtype and op, rank-ascending order); the other modes are the NVLS loops
 // (kNvls*: the switch reduces, multimem.st spreads the result).
 constexpr int kOwnerTma = 16;
+constexpr int kOwnerHybrid = 17;  // NVLS (pipelined, 4 vectors) on one part, peer loads on the rest
 
 template <int DT, int OP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -744,8 +751,23 @@ __global__ void __launch_bounds__(kThreads, 1)
     single.voff = 0;
     single.count = a.count;
 
+    // the part of shard s that blocks with this index serve (see pack_phase)
+    auto span_at = [&](int s) {
+        if constexpr (MODE == kOwnerHybrid) {
+            const int nbn = a.hybrid_nvls_blocks;
+            const unsigned long long n1 = a.hybrid_split_vec;
+            if (b < nbn) { return span_of(n1, world, s, nbn, b); }
+            Span t = span_of(a.nvec - n1, world, s, nb - nbn, b - nbn);
+            t.lo += n1;
+            t.hi += n1;
+            return t;
+        } else {
+            return span_of(a.nvec, world, s, nb, b);
+        }
+    };
+
     if ((phases & kPhasePack) != 0 && (tab != nullptr || single.src != nullptr)) {
-        pack_phase<DT>(a, tab, single, mine, world, nb, b, user_f32);
+        pack_phase<DT>(a, tab, single, mine, world, user_f32, span_at);
         // the packed data is read by bulk copies (async proxy) of the peers
         if constexpr (MODE == kOwnerTma) { fence_async_proxy(); }
     }
@@ -767,6 +789,27 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (!tma_reduce_span<DT, OP>(ctx, a, rank, sp.lo, sp.hi, ring, bars, &sync, push)) {
                 return;
             }
+        } else if constexpr (MODE == kOwnerHybrid) {
+            // vectors [0, n1): the switch reduces and replicates; [n1, nvec): this
+            // rank loads its shard from every peer and stores the result to every
+            // peer.  Different CTAs, one launch, one pair of barriers.
+            const Span mine_sp = span_at(rank);
+            if (b < a.hybrid_nvls_blocks) {
+                auto push = [&](unsigned long long v, const uint4 &x) {
+                    mm_st_v4(ctx.mc_base + a.off + v * 16ull, x);
+                };
+                nvls_span<DT, OP, kNvlsPipe4>(ctx, a.off, mine_sp.lo, mine_sp.hi, a.scale,
+                                              a.has_scale != 0, push);
+            } else {
+                auto push = [&](unsigned long long v, const uint4 &x) {
+                    for (int i = 0; i < world; ++i) {
+                        const int r = (rank + i) % world;
+                        st_arena_v4(a.push[r] + v * 16ull, x);
+                    }
+                };
+                reduce_span<DT, OP>(ctx, a.data, mine_sp.lo, mine_sp.hi, a.scale,
+                                    a.has_scale != 0, push);
+            }
         } else {
             auto push = [&](unsigned long long v, const uint4 &x) {
                 if (a.root >= 0) {
@@ -781,7 +824,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     if ((phases & kPhaseUnpack) != 0 && computes && (tab != nullptr || single.dst != nullptr)) {
-        unpack_phase<DT>(a, tab, single, a.push[rank], world, nb, b, user_f32);
+        unpack_phase<DT>(a, tab, single, a.push[rank], world, user_f32, span_at);
     }
 
     if (do_reduce) { sync_end(ctx, rank, &sync); }
@@ -826,6 +869,12 @@ int launch_one(const CommCtx &ctx, const AllReduceArgs &a, int blocks, int vrank
         const unsigned int smem = static_cast<unsigned int>(a.tma_stages) *
                                   static_cast<unsigned int>(ctx.world) * a.tma_tile_vec * 16u;
         return launch_owner<DT, OP, kOwnerTma>(ctx, a, grid, vranks, smem, stream);
+    }
+    if (a.algo == kAlgoNvlsHybrid) {
+        if constexpr (nvls_ok<DT, OP>()) {
+            return launch_owner<DT, OP, kOwnerHybrid>(ctx, a, grid, vranks, 0u, stream);
+        }
+        return -1;
     }
     if (a.algo == kAlgoNvls) {
         if constexpr (nvls_ok<DT, OP>()) {

@@ -30,6 +30,13 @@ constexpr int kThreads = 512;     // block size of every collective kernel
 // remembers how many barriers block b has passed, so that launches need no
 // host-side counter and all ranks agree as long as they launch the same
 // sequence of grids.
+//
+// One pad per world means: the collectives of a world run on the GPU one at a
+// time, in the same order on every rank.  Two kernels of one world running side
+// by side (two streams, no dependency) would count each other's arrivals.  The
+// session enforces the order (DeviceSession::order_after_previous: a call that
+// arrives on another stream than the previous one first waits for that
+// stream); code that launches through DeviceWorld directly must do the same.
 struct SignalPad {
     uint32_t flag[kMaxBlocks][kMaxRanks];
     uint32_t epoch[kMaxBlocks];
@@ -75,14 +82,18 @@ enum : int {
     kAlgoTwoShotTma = 4,   // two-shot whose pulls are bulk async copies (TMA) of every
                            // rank's tile into a shared-memory ring; results leave as
                            // plain 16-byte stores
-    kAlgoCount = 5,
+    kAlgoNvlsHybrid = 5,   // most of each shard through the switch (NVLS), the rest by
+                           // peer loads and stores from other CTAs of the same launch:
+                           // the two kinds of traffic load the links differently
+    kAlgoCount = 6,
 };
 
 // Owner algorithms: rank r reduces shard r and writes the result into every
 // rank's symmetric buffer, so they can run in place.
 STDML_HD inline bool is_owner_algo(int algo)
 {
-    return algo == kAlgoTwoShot || algo == kAlgoNvls || algo == kAlgoTwoShotTma;
+    return algo == kAlgoTwoShot || algo == kAlgoNvls || algo == kAlgoTwoShotTma ||
+           algo == kAlgoNvlsHybrid;
 }
 
 // Shared-memory ring of the bulk-copy two-shot kernel: `stages` slots, each
@@ -146,6 +157,8 @@ struct AllReduceArgs {
     int nvls_variant; // inner loop of the NVLS reduce: see kNvls* below
     int tma_stages;   // kAlgoTwoShotTma: slots of the shared-memory ring
     unsigned int tma_tile_vec;  // kAlgoTwoShotTma: vectors per rank per tile
+    int hybrid_nvls_blocks;  // kAlgoNvlsHybrid: CTAs [0, this) take the NVLS region
+    unsigned long long hybrid_split_vec;  // kAlgoNvlsHybrid: vectors [0, this) are the NVLS region
     int debug_checks; // != 0: validate offsets / table / alignment in the kernel and
                       // report kStatusBadArgs instead of touching memory
 };

@@ -78,6 +78,7 @@ DeviceSession::~DeviceSession()
     }
     for (void *p : table_mem_) { (void)cudaFree(p); }
     table_mem_.clear();
+    if (order_ev_ != nullptr) { (void)cudaEventDestroy(static_cast<cudaEvent_t>(order_ev_)); }
     (void)cudaGetLastError();
 }
 
@@ -121,6 +122,26 @@ bool all_aligned16(void *const *p, int n, bool allow_null = false)
     return true;
 }
 }  // namespace
+
+void DeviceSession::order_after_previous(void *stream)
+{
+    if (have_last_stream_ && last_stream_ != stream && !capturing(stream) &&
+        !capturing(last_stream_)) {
+        if (order_ev_ == nullptr) {
+            cudaEvent_t e;
+            rt_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+            order_ev_ = e;
+        }
+        rt_check(cudaEventRecord(static_cast<cudaEvent_t>(order_ev_),
+                                 static_cast<cudaStream_t>(last_stream_)),
+                 "cudaEventRecord");
+        rt_check(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream),
+                                     static_cast<cudaEvent_t>(order_ev_), 0),
+                 "cudaStreamWaitEvent");
+    }
+    last_stream_ = stream;
+    have_last_stream_ = true;
+}
 
 void DeviceSession::check()
 {
@@ -225,6 +246,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
+    order_after_previous(stream);
     if (count == 0) { return; }
     const size_t es = elem_size(dt);
     const int vr = world_->vranks();
@@ -348,6 +370,7 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
+    order_after_previous(stream);
     if (count == 0) { return; }
     if (root < 0 || root >= world_->world()) { throw std::invalid_argument("reduce: bad root"); }
     const size_t es = elem_size(dt);
@@ -360,21 +383,37 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
     const bool by_switch = world_->has_nvls() && nvls_supported(dt, op) && world_->world() > 2;
     if (in_off != SIZE_MAX && world_->world() > 1 && (by_switch || count * es <= (1u << 20))) {
         std::vector<void *> dsts(vr);
-        for (int v = 0; v < vr; ++v) {
-            dsts[v] = (out != nullptr && out[v] != nullptr) ? out[v] : nullptr;
+        const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
+        const bool small = count * es <= (1u << 20);
+        for (size_t done = 0; done < count; done += small ? count : slot_elems) {
+            const size_t n = small ? count : std::min(slot_elems, count - done);
+            for (int v = 0; v < vr; ++v) {
+                dsts[v] = (out != nullptr && out[v] != nullptr)
+                              ? static_cast<char *>(out[v]) + done * es
+                              : nullptr;
+            }
+            AllReduceCall k;
+            k.dt = dt;
+            k.op = op;
+            k.root = root;
+            k.has_scale = scale != 1.0;
+            k.scale = scale;
+            k.off = in_off + done * es;
+            k.dst = dsts.data();
+            k.count = n;
+            if (small) {
+                // root alone reads everything (through the switch when it can)
+                k.end_barrier = true;  // the inputs stay untouched until root has read them
+                k.algo = by_switch ? kAlgoNvlsOneShot : kAlgoOneShot;
+            } else {
+                // every rank has the switch reduce its shard and stores it into root's
+                // staging slot, from where root copies it out: one GPU alone cannot
+                // draw the switch's full rate, eight together can
+                k.algo = kAlgoNvls;
+                k.push_off = world_->next_staging_slot();
+            }
+            launch_ar(k, stream);
         }
-        AllReduceCall k;
-        k.dt = dt;
-        k.op = op;
-        k.root = root;
-        k.has_scale = scale != 1.0;
-        k.scale = scale;
-        k.off = in_off;
-        k.dst = dsts.data();
-        k.count = count;
-        k.end_barrier = true;  // the inputs stay untouched until root has read them
-        k.algo = by_switch ? kAlgoNvlsOneShot : kAlgoOneShot;
-        launch_ar(k, stream);
         return;
     }
     if (registered_path(count * es, stream)) {
@@ -436,7 +475,9 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         if (n * es <= (1u << 20) || world_->world() <= 2) {
             k.algo = kAlgoOneShot;
         } else if (world_->has_nvls() && nvls_supported(dt, op)) {
-            k.algo = kAlgoNvlsOneShot;  // root alone pulls the switch-reduced data
+            // owners have the switch reduce their shard and store it to root (measured:
+            // one GPU pulling everything through the switch stops near 370 GB/s)
+            k.algo = kAlgoNvls;
         } else {
             k.algo = kAlgoTwoShot;
         }
@@ -533,6 +574,7 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
+    order_after_previous(stream);
     if (n == 0) { return; }
     const size_t es = elem_size(dt);
     const int vr = world_->vranks();
@@ -683,6 +725,7 @@ void DeviceSession::all_gather(const void *const *in, void *const *out, size_t c
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
+    order_after_previous(stream);
     const size_t bytes = count * elem_size(dt);
     if (bytes == 0) { return; }
     const int vr = world_->vranks();
@@ -771,6 +814,7 @@ void DeviceSession::broadcast(const void *const *in, void *const *out, size_t co
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
+    order_after_previous(stream);
     if (root < 0 || root >= world_->world()) { throw std::invalid_argument("broadcast: bad root"); }
     const size_t bytes = count * elem_size(dt);
     if (bytes == 0) { return; }
@@ -855,6 +899,7 @@ void DeviceSession::barrier(void *stream)
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
     check();
+    order_after_previous(stream);
     launch_check(world_->barrier(stream), "barrier");
     ++launches_;
 }

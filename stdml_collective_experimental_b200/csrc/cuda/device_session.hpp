@@ -125,6 +125,14 @@ class DeviceSession
     std::map<std::string, GroupPlan> plans_;
     std::vector<void *> table_mem_;
     unsigned long long launches_ = 0;
+    // One signal pad serves the whole session, so its collectives must run on
+    // the GPU one after the other, in the order issued.  On one stream that is
+    // stream order; when a call comes in on another stream than the previous
+    // one, it is made to wait for everything the previous stream holds.
+    void order_after_previous(void *stream);
+    void *last_stream_ = nullptr;
+    bool have_last_stream_ = false;
+    void *order_ev_ = nullptr;
     size_t register_min_bytes_ = SIZE_MAX;     // STDML_COLLECTIVE_REGISTER_MIN_BYTES
     bool registered_path(size_t bytes, void *stream) const;
     size_t pipeline_min_bytes_ = 512u << 20;   // STDML_COLLECTIVE_PIPELINE_MIN_BYTES

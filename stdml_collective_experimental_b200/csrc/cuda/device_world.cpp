@@ -1,6 +1,7 @@
 #include "device_world.hpp"
 
 #include <algorithm>
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -131,6 +132,8 @@ class World final : public DeviceWorld
     size_t staging_off_[2] = {0, 0};
     unsigned long long staged_ops_ = 0;
     OffsetHeap heap_;
+    double setup_ms_[4] = {0, 0, 0, 0};
+    std::map<size_t, size_t> guarded_;  // offset handed out -> bytes between its guard bands
     std::string backend_;
 
     std::vector<char *> base_;  // per rank
@@ -176,7 +179,11 @@ class World final : public DeviceWorld
     int nvls_variant_ = kNvlsPipe4;        // STDML_COLLECTIVE_NVLS_VARIANT
     bool debug_checks_ = false;            // STDML_COLLECTIVE_DEBUG
     size_t gather_push_min_ = 64u << 10;  // STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES
-    bool gather_mc_ = true;               // STDML_COLLECTIVE_GATHER_MC: all_gather through the switch
+    bool gather_mc_ = false;  // STDML_COLLECTIVE_GATHER_MC: all_gather through the switch (measured
+                              // at 8 GPUs: plain stores 653-660 GB/s, multimem.st 614-625)
+    int hybrid_permille_ = 150;        // share of a hybrid call that goes by peer loads (knob hybrid_permille)
+    int hybrid_twoshot_blocks_ = 64;   // CTAs of that share (knob hybrid_twoshot_blocks)
+    static constexpr unsigned long long kHybridGranule = 32;  // the spans' own granule
     int debug_inject_ = 0;  // tests: hand the next all_reduce kernel arguments that its
                             // own checks must refuse (1: misaligned offset, 2: offset
                             // inside the signal pad); implies debug_checks for that launch
@@ -250,8 +257,10 @@ class World final : public DeviceWorld
                 setup_loopback();
             } else {
                 if (o.world > 1) {
+                    const auto t0 = std::chrono::steady_clock::now();
                     rdv_ = std::make_unique<LocalRendezvous>(o.key, o.rank, o.world,
                                                              o.setup_timeout_ms);
+                    setup_ms_[0] = ms_since(t0);
                 }
                 setup_real();
             }
@@ -272,6 +281,10 @@ class World final : public DeviceWorld
     bool has_nvls() const override { return mc_base_ != nullptr; }
     const char *backend() const override { return backend_.c_str(); }
     size_t arena_bytes() const override { return arena_bytes_; }
+    void setup_ms(double out[4]) const override
+    {
+        for (int i = 0; i < 4; ++i) { out[i] = setup_ms_[i]; }
+    }
     size_t staging_bytes() const override { return opt_.staging_bytes; }
 
     void *ptr(int r, size_t off) const override
@@ -297,8 +310,62 @@ class World final : public DeviceWorld
         return SIZE_MAX;
     }
 
-    size_t alloc(size_t bytes) override { return heap_.alloc(bytes); }
-    void release(size_t off) override { heap_.release(off); }
+    // Every heap allocation sits between two guard bands filled with a known
+    // word; release() reads them back and reports a band that changed (a kernel,
+    // ours or the user's, that wrote outside its buffer).  Peers write into this
+    // arena too, so the bands of every rank's copy tell on remote writers as well.
+    static constexpr size_t kGuardBytes = 256;
+    static constexpr unsigned char kGuardByte = 0xA5;
+
+    size_t alloc(size_t bytes) override
+    {
+        const size_t body = round_up(std::max<size_t>(bytes, 16), 256);
+        const size_t off = heap_.alloc(body + 2 * kGuardBytes);
+        for (int r = 0; r < opt_.world; ++r) {
+            if (!opt_.loopback && r != opt_.rank) { continue; }  // each rank paints its own
+            rt_check(cudaMemset(base_[r] + off, kGuardByte, kGuardBytes), "cudaMemset(guard)");
+            rt_check(cudaMemset(base_[r] + off + kGuardBytes + body, kGuardByte, kGuardBytes),
+                     "cudaMemset(guard)");
+        }
+        rt_check(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+        guarded_[off + kGuardBytes] = body;
+        return off + kGuardBytes;
+    }
+
+    void release(size_t off) override
+    {
+        const auto it = guarded_.find(off);
+        if (it == guarded_.end()) {
+            throw std::invalid_argument("device world: release() of an offset that alloc() did "
+                                        "not return");
+        }
+        const size_t body = it->second;
+        guarded_.erase(it);
+        std::string damage;
+        unsigned char band[kGuardBytes];
+        for (int r = 0; r < opt_.world; ++r) {
+            if (!opt_.loopback && r != opt_.rank) { continue; }
+            for (int side = 0; side < 2; ++side) {
+                const char *at = base_[r] + (side == 0 ? off - kGuardBytes : off + body);
+                if (cudaMemcpy(band, at, kGuardBytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    continue;
+                }
+                for (size_t i = 0; i < kGuardBytes; ++i) {
+                    if (band[i] != kGuardByte) {
+                        damage += " rank " + std::to_string(r) + (side == 0 ? " below" : " above") +
+                                  " (first changed byte " + std::to_string(i) + ")";
+                        break;
+                    }
+                }
+            }
+        }
+        heap_.release(off - kGuardBytes);
+        if (!damage.empty()) {
+            throw std::runtime_error("device world: the guard bands of the symmetric buffer at "
+                                     "offset " + std::to_string(off) + " were overwritten:" + damage);
+        }
+    }
 
     size_t next_staging_slot() override { return staging_off_[(staged_ops_++) & 1ull]; }
 
@@ -330,6 +397,10 @@ class World final : public DeviceWorld
             gather_push_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "gather_mc") {
             gather_mc_ = value != 0;
+        } else if (name == "hybrid_permille") {
+            hybrid_permille_ = static_cast<int>(std::max<long long>(0, std::min<long long>(1000, value)));
+        } else if (name == "hybrid_twoshot_blocks") {
+            hybrid_twoshot_blocks_ = static_cast<int>(std::max<long long>(1, std::min<long long>(512, value)));
         } else if (name == "debug_checks") {
             debug_checks_ = value != 0;
         } else if (name == "debug_inject") {
@@ -564,7 +635,11 @@ class World final : public DeviceWorld
         if (algo < 0) { algo = pick_algo(bytes, c.dt, c.op, any_dst_null); }
         if (algo >= kAlgoCount) { throw std::invalid_argument("all_reduce: unknown algorithm"); }
         const bool owner = is_owner_algo(algo);
-        const bool nvls = (algo == kAlgoNvls || algo == kAlgoNvlsOneShot);
+        const bool nvls =
+            (algo == kAlgoNvls || algo == kAlgoNvlsOneShot || algo == kAlgoNvlsHybrid);
+        if (algo == kAlgoNvlsHybrid && c.root >= 0) {
+            throw std::invalid_argument("all_reduce: the hybrid algorithm has no reduce-to-root form");
+        }
         if (!owner && any_dst_null && c.table == nullptr && c.root < 0) {
             throw std::invalid_argument("all_reduce: one-shot algorithms need a destination");
         }
@@ -602,7 +677,12 @@ class World final : public DeviceWorld
             a.data[r] = registered ? static_cast<char *>(c.peer_data[r]) : base_[r] + c.off;
             a.push[r] = (registered && c.peer_push != nullptr)
                             ? static_cast<char *>(c.peer_push[r])
-                            : a.data[r];
+                            : ((!registered && c.push_off != 0) ? base_[r] + c.push_off : a.data[r]);
+        }
+        if (!registered && c.push_off != 0 &&
+            (c.push_off % 16 != 0 || c.push_off < kDataOffset ||
+             c.push_off + nvec * 16 > arena_bytes_)) {
+            throw std::invalid_argument("all_reduce: result region outside the arena");
         }
         if (registered && c.peer_push != nullptr) {
             for (int r = 0; r < opt_.world; ++r) {
@@ -638,6 +718,16 @@ class World final : public DeviceWorld
         if (algo == kAlgoTwoShotTma) {
             unsigned int smem = 0;
             tma_geometry(opt_.world, tma_tile_vec_, &a.tma_stages, &a.tma_tile_vec, &smem);
+        }
+        if (algo == kAlgoNvlsHybrid) {
+            const int nbn = nvls_blocks_ > 0 ? nvls_blocks_ : 24;
+            int nbt = hybrid_twoshot_blocks_;
+            if (vranks_ > 1) { nbt = std::max(1, std::min(nbt, num_sms_ / vranks_ - nbn)); }
+            if (c.blocks <= 0) { blocks = std::min(nbn + nbt, kMaxBlocks); }
+            a.hybrid_nvls_blocks = std::max(1, std::min(nbn, blocks - 1));
+            const unsigned long long keep =
+                nvec * static_cast<unsigned long long>(1000 - hybrid_permille_) / 1000ull;
+            a.hybrid_split_vec = std::min<unsigned long long>(keep / kHybridGranule * kHybridGranule, nvec);
         }
         if ((c.phases & kPhaseReduce) == 0) {
             // a local copy phase: no peer waits, any grid will do
@@ -789,11 +879,18 @@ class World final : public DeviceWorld
         rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
     }
 
+    static double ms_since(std::chrono::steady_clock::time_point t0)
+    {
+        return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0)
+            .count();
+    }
+
     void setup_real()
     {
         const bool want_vmm = opt_.backend == "auto" || opt_.backend == "vmm";
         bool vmm_ok = false;
         std::string why;
+        auto t0 = std::chrono::steady_clock::now();
         if (want_vmm) {
             try {
                 vmm_ok = setup_vmm_local(why);
@@ -802,12 +899,17 @@ class World final : public DeviceWorld
                 why = e.what();
             }
         }
+        setup_ms_[1] = ms_since(t0);
         // every rank must take the same path
         if (rdv_) { vmm_ok = rdv_->all_agree(vmm_ok); }
         if (vmm_ok) {
             backend_ = "vmm";
+            t0 = std::chrono::steady_clock::now();
             exchange_vmm();
+            setup_ms_[2] = ms_since(t0);
+            t0 = std::chrono::steady_clock::now();
             if (opt_.enable_nvls && opt_.world > 1) { setup_multicast(); }
+            setup_ms_[3] = ms_since(t0);
         } else {
             if (opt_.backend == "vmm") {
                 throw std::runtime_error("device world: VMM backend unavailable: " + why);

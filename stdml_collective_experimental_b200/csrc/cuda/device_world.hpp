@@ -48,6 +48,10 @@ struct DeviceStatus {
 // (1 for a real world, `world` for a loopback world).
 struct AllReduceCall {
     size_t off = 0;  // arena byte offset of the symmetric buffer
+    // Owner algorithms: store the results at this arena offset instead of over the
+    // operands (0: in place).  Lets a reduce-to-root read symmetric inputs where
+    // they are and deliver into root's staging slot.
+    size_t push_off = 0;
     // Instead of `off`: the buffer of every rank of the world (world() entries) as
     // mapped in this process: a user buffer registered with register_buffer().
     // No NVLS then (the multicast mapping covers the arena only).
@@ -102,6 +106,11 @@ class DeviceWorld
     virtual bool has_nvls() const = 0;
     virtual const char *backend() const = 0;
     virtual size_t arena_bytes() const = 0;
+    // Where the set-up time of this world went, in milliseconds: [0] the local
+    // rendezvous (UNIX-socket mesh among the ranks), [1] allocating and mapping
+    // this rank's arena, [2] exchanging handles and mapping the peers' arenas,
+    // [3] creating and binding the NVLS multicast object.
+    virtual void setup_ms(double out[4]) const = 0;
     virtual size_t staging_bytes() const = 0;
 
     // Address of arena offset `off` of rank `r` as mapped here / of the

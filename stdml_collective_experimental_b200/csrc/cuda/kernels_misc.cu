@@ -262,9 +262,13 @@ __global__ void __launch_bounds__(kThreads)
                 const int s = (rank + 1 + i) % world;
                 if (s == rank && src == nullptr) { continue; }
                 const Span sp = span_of(nvec, world, s, nb, b);
+                // from user memory root also fills its own region completely (nobody
+                // sends root anything), so that its unpack below finds the whole block
+                const bool also_mine = src != nullptr && s != rank;
                 for_each_block_vec(src, mine, a.bytes, sp,
                                    [&](unsigned long long v, const uint4 &x) {
                                        st_arena_v4(a.data[s] + v * 16ull, x);
+                                       if (also_mine) { st_arena_v4(mine + v * 16ull, x); }
                                    });
             }
         }
@@ -281,7 +285,14 @@ __global__ void __launch_bounds__(kThreads)
                                });
         }
         if (!peer_barrier(ctx, rank, &sync)) { return; }
-        if (dst != nullptr) { copy_span_to_user(dst, a.bytes, mine, whole); }
+        if (dst != nullptr) {
+            // slice by slice, with the partition the writers used: the barriers only
+            // vouch for what blocks of this index wrote
+            for (int i = 0; i < world; ++i) {
+                const int s = (rank + i) % world;
+                copy_span_to_user(dst, a.bytes, mine, span_of(nvec, world, s, nb, b));
+            }
+        }
     } else {
         // ---- pull (small messages): pack, one barrier, read the peers' regions
         if (src != nullptr && (!bcast || is_root)) {

@@ -145,6 +145,18 @@ class session
 
     void barrier();
 
+    // Device memory in this session's symmetric heap (collective: every rank makes
+    // the same calls in the same order; the heap belongs to this membership and
+    // goes with it on a resize).  Collectives on such buffers are zero-copy: no
+    // staging, one launch.  Size of the heap: STDML_COLLECTIVE_HEAP_MB.
+    void *symm_alloc(size_t bytes);
+    void symm_free(void *p);
+
+    // Milliseconds the device world of this membership took to set up (zeros
+    // before the first device call): rendezvous among the ranks, own arena,
+    // peers' arenas, NVLS multicast.
+    void device_setup_ms(double out[4]) const;
+
     // Kernels this session has launched on the device so far (0 before its first
     // device call): lets callers and tests see how many launches a call cost.
     unsigned long long device_launches() const;

@@ -332,6 +332,27 @@ int stdmlc_session_recv(void *s, void *out, unsigned long long count, int dt, in
     });
 }
 
+int stdmlc_session_symm_alloc(void *s, unsigned long long bytes, void **out)
+{
+    *out = nullptr;
+    return host_guarded([&] { *out = SS(s).symm_alloc(bytes); });
+}
+
+int stdmlc_session_symm_free(void *s, void *p)
+{
+    return host_guarded([&] { SS(s).symm_free(p); });
+}
+
+int stdmlc_session_device_setup_ms(void *s, double *out4)
+{
+    return host_guarded([&] { SS(s).device_setup_ms(out4); });
+}
+
+int stdmlc_session_device_launches(void *s, unsigned long long *out)
+{
+    return host_guarded([&] { *out = SS(s).device_launches(); });
+}
+
 int stdmlc_session_barrier(void *s)
 {
     return host_guarded([&] { SS(s).barrier(); });

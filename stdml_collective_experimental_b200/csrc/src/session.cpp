@@ -1182,6 +1182,27 @@ bool session::on_device(const void *a, const void *b) const
     return ka == 1;
 }
 
+void *session::symm_alloc(size_t bytes)
+{
+    cuda::DeviceWorld &w = device()->world();
+    return w.ptr(w.rank(), w.alloc(bytes));
+}
+
+void session::symm_free(void *p)
+{
+    cuda::DeviceWorld &w = device()->world();
+    const size_t off = w.offset_of(p, 0);
+    if (off == SIZE_MAX) { throw std::invalid_argument("symm_free: not a symmetric buffer"); }
+    w.release(off);
+}
+
+void session::device_setup_ms(double out[4]) const
+{
+    std::lock_guard<std::mutex> lk(*device_mu_);
+    for (int i = 0; i < 4; ++i) { out[i] = 0.0; }
+    if (device_) { device_->world().setup_ms(out); }
+}
+
 unsigned long long session::device_launches() const
 {
     std::lock_guard<std::mutex> lk(*device_mu_);

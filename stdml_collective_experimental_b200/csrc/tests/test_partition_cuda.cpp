@@ -184,7 +184,7 @@ int main()
         t8.oneshot_max = 0;
         // grids: one vector ... 1 GiB
         EXPECT(select_blocks(t8, 1, kAlgoNvls) == 1);
-        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoNvls) == 32);
+        EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoNvls) == 24);
         EXPECT(select_blocks(t8, (8ull << 20) / 16, kAlgoNvls) == 32);  // 1 MB per rank / 32 KB per CTA
         EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoTwoShot) == 128);
         EXPECT(select_blocks(t8, (1ull << 30) / 16, kAlgoOneShot) == 128);

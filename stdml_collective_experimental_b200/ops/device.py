@@ -19,7 +19,7 @@ from .. import _native
 
 ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_NVLS_ONESHOT, ALGO_TWOSHOT_TMA = 0, 1, 2, 3, 4
 _ALGOS = {None: -1, "auto": -1, "oneshot": 0, "twoshot": 1, "nvls": 2, "nvls_oneshot": 3,
-          "twoshot_tma": 4}
+          "twoshot_tma": 4, "nvls_hybrid": 5}
 
 _DTYPES = {
     torch.int8: 0, torch.int16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4,

@@ -55,6 +55,10 @@ def _lib():
         lib.stdmlc_session_send.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_recv.argtypes = [vp, vp, u64, c.c_int, c.c_int, c.c_char_p]
         lib.stdmlc_session_barrier.argtypes = [vp]
+        lib.stdmlc_session_symm_alloc.argtypes = [vp, u64, vpp]
+        lib.stdmlc_session_symm_free.argtypes = [vp, vp]
+        lib.stdmlc_session_device_launches.argtypes = [vp, c.POINTER(u64)]
+        lib.stdmlc_session_device_setup_ms.argtypes = [vp, c.POINTER(c.c_double)]
         lib.stdmlc_session_consistent.argtypes = [vp, vp, u64, c.POINTER(c.c_int)]
         lib.stdmlc_peer_resize.argtypes = [vp, vp, c.c_longlong, c.c_char_p, c.POINTER(c.c_int),
                                            c.POINTER(c.c_int)]
@@ -340,6 +344,37 @@ class Session:
 
     def barrier(self):
         _native.check(self._lib.stdmlc_session_barrier(self._h))
+
+    def symm_empty(self, numel, dtype=torch.float32, device=None):
+        """A CUDA tensor in this session's symmetric heap (collective: every rank
+        makes the same calls in the same order).  Collectives on it are zero-copy;
+        a group of such tensors laid back to back is one fused in-place launch.
+        The heap belongs to this membership: after Peer.resize() or recover()
+        allocate again (the old tensors must not be used any more)."""
+        from ..ops.device import _RawCuda
+        nbytes = max(16, int(numel) * torch.empty((), dtype=dtype).element_size())
+        p = ctypes.c_void_p()
+        _native.check(self._lib.stdmlc_session_symm_alloc(self._h, nbytes, ctypes.byref(p)))
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        raw = torch.as_tensor(_RawCuda(p.value, nbytes, self), device=dev)
+        return raw.view(dtype)[:numel]
+
+    def symm_free(self, tensor):
+        _native.check(self._lib.stdmlc_session_symm_free(self._h, ctypes.c_void_p(tensor.data_ptr())))
+
+    @property
+    def device_setup_ms(self):
+        """Where the set-up of this membership's device world went (milliseconds)."""
+        out = (ctypes.c_double * 4)()
+        _native.check(self._lib.stdmlc_session_device_setup_ms(self._h, out))
+        return {"rendezvous": out[0], "own_arena": out[1], "peer_arenas": out[2],
+                "multicast": out[3]}
+
+    @property
+    def device_launches(self):
+        v = ctypes.c_ulonglong()
+        _native.check(self._lib.stdmlc_session_device_launches(self._h, ctypes.byref(v)))
+        return int(v.value)
 
     def consistent(self, data):
         """True when every rank holds the same bytes."""

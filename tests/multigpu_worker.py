@@ -41,7 +41,7 @@ def main():
                                   wait_timeout_ms=20000)
     assert sess.rank == rank and sess.world == world
     info = f"backend={sess.backend} nvls={sess.has_nvls}"
-    algos = ["oneshot", "twoshot", "twoshot_tma"] + (["nvls", "nvls_oneshot"] if sess.has_nvls else [])
+    algos = ["oneshot", "twoshot", "twoshot_tma"] + (["nvls", "nvls_oneshot", "nvls_hybrid"] if sess.has_nvls else [])
 
     # ---- all_reduce: dtype x op x size, default algorithm choice (staged path)
     for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int32,
@@ -81,7 +81,7 @@ def main():
                     assert bits_equal(got, want), (algo, dtype, n)
 
     # ---- zero-copy symmetric buffers, every owner algorithm
-    for algo in [a for a in algos if a in ("twoshot", "twoshot_tma", "nvls")]:
+    for algo in [a for a in algos if a in ("twoshot", "twoshot_tma", "nvls", "nvls_hybrid")]:
         n = 1_000_003
         host = inputs(world, n, torch.float32, seed=99, exact=True)
         want = reduce_many(host, "sum")
@@ -270,6 +270,25 @@ def main():
     sess.check()
     assert torch.equal(out[1000:].cpu(), torch.cat(host)[1000:]) and torch.equal(b.cpu(), host[world - 1])
     assert torch.equal(out[:1000].cpu(), torch.cat(host)[:1000] * world)
+
+    # ---- ranks that reach a collective at very different times (0 - 50 ms apart, a
+    # different rank late every time): the device-side waits are bounded by seconds,
+    # so lateness of this order must change nothing
+    import random
+    import time
+    rnd = random.Random(1000 + rank)
+    x = torch.empty(100_000, device="cuda")
+    for it in range(12):
+        time.sleep(rnd.random() * 0.05)
+        x.fill_(float(rank + it))
+        sess.all_reduce(x)
+        g_in = torch.full((1000,), float(rank), device="cuda")
+        g_out = torch.empty(1000 * world, device="cuda")
+        sess.all_gather(g_in, g_out)
+        torch.cuda.synchronize()
+        sess.check()
+        assert torch.all(x == world * (world - 1) / 2 + world * it), ("skew", it)
+        assert g_out[::1000].tolist() == [float(r) for r in range(world)]
 
     # ---- the collectives as torch custom ops
     from stdml_collective_experimental_b200.ops import torch_ops

@@ -547,7 +547,8 @@ def test_large_staged_messages_are_pipelined_on_three_streams(world, monkeypatch
         s.all_reduce(dev, out=out, scale=0.5)
         torch.cuda.synchronize()
         s.check()
-        assert s.launches - before == 3 * 6, "6 slot-sized chunks, three launches each"
+        assert s.launches - before == 3 * 6 + 1, \
+                "6 slot-sized chunks, three launches each, and the barrier that ends a pipeline"
         for r in range(world):
             assert same(out[r].cpu(), want) and same(dev[r].cpu(), host[r])
         # a fused group above the threshold takes the same route
