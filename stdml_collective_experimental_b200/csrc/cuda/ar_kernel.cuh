@@ -391,12 +391,28 @@ __device__ __forceinline__ void unpack_phase(const AllReduceArgs &a, const Group
 // running.  Checked: the symmetric buffer lies inside the data region and is
 // 16-byte aligned, the table is sorted, starts at 0 and stays inside the
 // buffer, the ring geometry fits the shared memory it was given.
+// The range rules of the in-kernel checks, as plain functions (also run on the
+// CPU by the tests): entry i of a table ends inside the buffer and before the
+// next entry starts; a buffer offset is 16-byte aligned and past the signal pad
+// (or 0 for registered buffers, which have no arena offset).
+template <int DT>
+__host__ __device__ __forceinline__ bool table_entry_in_range(const GroupEntry *tab, int i, int n,
+                                                           unsigned long long nvec)
+{
+    const unsigned long long end = tab[i].voff + entry_nvec<DT>(tab[i].count);
+    return end <= nvec && (i + 1 >= n || tab[i + 1].voff >= end);
+}
+
+__host__ __device__ __forceinline__ bool buffer_offset_ok(unsigned long long off)
+{
+    return off % 16ull == 0ull && (off >= kDataOffset || off == 0ull);
+}
+
 template <int DT>
 __device__ __forceinline__ bool args_look_sane(const CommCtx &ctx, const AllReduceArgs &a,
                                                const GroupEntry *tab, unsigned int dyn_smem)
 {
-    bool ok = (a.off % 16ull == 0ull) && (a.off >= kDataOffset || a.off == 0ull) &&
-              ctx.world >= 1 && ctx.world <= kMaxRanks && a.algo >= 0 && a.algo < kAlgoCount &&
+    bool ok = buffer_offset_ok(a.off) && ctx.world >= 1 && ctx.world <= kMaxRanks && a.algo >= 0 && a.algo < kAlgoCount &&
               a.root < ctx.world && a.nvec > 0;
     for (int r = 0; ok && r < ctx.world; ++r) {
         // every rank's buffer: mapped, 16-byte aligned, and (arena buffers) past the pad
@@ -408,8 +424,7 @@ __device__ __forceinline__ bool args_look_sane(const CommCtx &ctx, const AllRedu
     if (ok && tab != nullptr) {
         ok = a.ntable > 0 && tab[0].voff == 0;
         for (int i = threadIdx.x; ok && i < a.ntable; i += kThreads) {
-            const unsigned long long end = tab[i].voff + entry_nvec<DT>(tab[i].count);
-            if (end > a.nvec || (i + 1 < a.ntable && tab[i + 1].voff < end)) { ok = false; }
+            ok = table_entry_in_range<DT>(tab, i, a.ntable, a.nvec);
         }
     }
     if (ok && a.algo == kAlgoTwoShotTma) {

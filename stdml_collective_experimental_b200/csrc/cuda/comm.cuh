@@ -191,6 +191,7 @@ struct GatherArgs {
     int end_barrier;    // the region is reused by the next call (captured staged calls)
     int algo;           // see kGather* / kBcast*
     int use_mc;         // push through the switch (multimem.st) instead of one store per peer
+    int rounds;         // kBcastPipelined: pieces per block and slice
 };
 
 enum : int {
@@ -201,6 +202,9 @@ enum : int {
                         // to all others (root's links carry ~2 copies, not n-1)
     kGatherPush = 3,    // every rank stores its block into every rank's region; broadcast:
                         // root stores the block into every rank's region
+    kBcastPipelined = 4,  // kBcastScatter in rounds: root signals each round, the holders
+                          // forward their part of it while root sends the next one, so
+                          // root's links and everybody else's are busy at the same time
 };
 
 // kernels_misc.cu

@@ -385,6 +385,18 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         std::vector<void *> dsts(vr);
         const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
         const bool small = count * es <= (1u << 20);
+        // several slots: root copies chunk k out of its slot on a second stream while
+        // the owners already reduce chunk k + 1 into the other slot
+        const bool overlap = !small && count > slot_elems && vr == 1 && !capturing(stream);
+        const bool i_am_root = world_->rank() == root;
+        cudaStream_t main_s = static_cast<cudaStream_t>(stream);
+        cudaStream_t unpack_s = nullptr;
+        auto ev = [](void *e) { return static_cast<cudaEvent_t>(e); };
+        bool used[2] = {false, false};
+        if (overlap) {
+            ensure_pipeline();
+            unpack_s = static_cast<cudaStream_t>(unpack_stream_);
+        }
         for (size_t done = 0; done < count; done += small ? count : slot_elems) {
             const size_t n = small ? count : std::min(slot_elems, count - done);
             for (int v = 0; v < vr; ++v) {
@@ -405,14 +417,45 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
                 // root alone reads everything (through the switch when it can)
                 k.end_barrier = true;  // the inputs stay untouched until root has read them
                 k.algo = by_switch ? kAlgoNvlsOneShot : kAlgoOneShot;
-            } else {
-                // every rank has the switch reduce its shard and stores it into root's
-                // staging slot, from where root copies it out: one GPU alone cannot
-                // draw the switch's full rate, eight together can
-                k.algo = kAlgoNvls;
-                k.push_off = world_->next_staging_slot();
+                launch_ar(k, stream);
+                continue;
             }
+            // every rank has the switch reduce its shard and stores it into root's
+            // staging slot, from where root copies it out: one GPU alone cannot
+            // draw the switch's full rate, eight together can
+            k.algo = kAlgoNvls;
+            k.push_off = world_->next_staging_slot();
+            if (!overlap) {
+                launch_ar(k, stream);
+                continue;
+            }
+            const int slot =
+                static_cast<int>((k.push_off - kDataOffset) / world_->staging_bytes()) & 1;
+            if (used[slot]) {
+                rt_check(cudaStreamWaitEvent(main_s, ev(unpacked_ev_[slot]), 0), "cudaStreamWaitEvent");
+            }
+            void *root_dst = dsts[0];
+            dsts[0] = nullptr;  // copied out below, beside the next chunk
             launch_ar(k, stream);
+            rt_check(cudaEventRecord(ev(reduced_ev_[slot]), main_s), "cudaEventRecord");
+            rt_check(cudaStreamWaitEvent(unpack_s, ev(reduced_ev_[slot]), 0), "cudaStreamWaitEvent");
+            if (i_am_root && root_dst != nullptr) {
+                launch_check(world_->unpack_blocks(world_->ptr(world_->rank(), k.push_off), root_dst,
+                                                   n * es, 0, 0, 1, unpack_s),
+                             "unpack (reduce chunk)");
+                ++launches_;
+            }
+            rt_check(cudaEventRecord(ev(unpacked_ev_[slot]), unpack_s), "cudaEventRecord");
+            used[slot] = true;
+        }
+        if (overlap) {
+            for (int i = 0; i < 2; ++i) {
+                if (used[i]) {
+                    rt_check(cudaStreamWaitEvent(main_s, ev(unpacked_ev_[i]), 0), "cudaStreamWaitEvent");
+                }
+            }
+            launch_check(world_->barrier(stream), "barrier (end of pipeline)");
+            ++launches_;
         }
         return;
     }
@@ -448,15 +491,19 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         }
     }
     const size_t slot_elems = world_->staging_bytes() / 16 * (16 / es);
-    std::vector<const void *> src(vr);
-    std::vector<void *> dst(vr);
+    const bool in_capture = capturing(stream);
+    std::vector<std::vector<const void *>> srcs;
+    std::vector<std::vector<void *>> dsts;
+    std::vector<AllReduceCall> calls;
     for (size_t done = 0; done < count; done += slot_elems) {
         const size_t n = std::min(slot_elems, count - done);
+        srcs.emplace_back(vr);
+        dsts.emplace_back(vr);
         for (int v = 0; v < vr; ++v) {
-            src[v] = static_cast<const char *>(in[v]) + done * es;
-            dst[v] = (out != nullptr && out[v] != nullptr)
-                         ? static_cast<char *>(out[v]) + done * es
-                         : nullptr;
+            srcs.back()[v] = static_cast<const char *>(in[v]) + done * es;
+            dsts.back()[v] = (out != nullptr && out[v] != nullptr)
+                                 ? static_cast<char *>(out[v]) + done * es
+                                 : nullptr;
         }
         AllReduceCall k;
         k.dt = dt;
@@ -464,23 +511,31 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
         k.root = root;
         k.has_scale = scale != 1.0;
         k.scale = scale;
-        k.off = world_->next_staging_slot();
-        k.src = src.data();
-        k.dst = dst.data();
         k.count = n;
-        k.end_barrier = capturing(stream);
-        // small (or two ranks): root pulls everything; large: the switch reduces
-        // for root, or owners reduce their shard and store it to root only,
-        // which spreads the reads over all links
+        k.end_barrier = in_capture;
+        // small (or two ranks): root pulls everything; large: owners reduce their
+        // shard (through the switch where it can) and store it to root only, which
+        // spreads the reads over all links
         if (n * es <= (1u << 20) || world_->world() <= 2) {
             k.algo = kAlgoOneShot;
         } else if (world_->has_nvls() && nvls_supported(dt, op)) {
-            // owners have the switch reduce their shard and store it to root (measured:
-            // one GPU pulling everything through the switch stops near 370 GB/s)
+            // (measured: one GPU pulling everything through the switch stops near 370 GB/s)
             k.algo = kAlgoNvls;
         } else {
             k.algo = kAlgoTwoShot;
         }
+        calls.push_back(k);
+    }
+    for (size_t i = 0; i < calls.size(); ++i) {
+        calls[i].src = srcs[i].data();
+        calls[i].dst = dsts[i].data();
+    }
+    if (calls.size() >= 2 && world_->world() > 2 && vr == 1 && !in_capture) {
+        run_pipelined(calls, stream);  // pack / reduce / unpack of neighbouring chunks overlap
+        return;
+    }
+    for (AllReduceCall &k : calls) {
+        k.off = world_->next_staging_slot();
         launch_ar(k, stream);
     }
 }
@@ -697,7 +752,7 @@ void DeviceSession::run_gather_chunks(std::vector<GatherCall> &calls,
         g.dst = nullptr;  // unpacked by the copy kernel below
         // posted stores fill the links from few SMs; the rest belong to the unpack
         // of the previous chunk, which runs at the same time
-        if (g.blocks <= 0) { g.blocks = 40; }
+        if (g.blocks <= 0) { g.blocks = 64; }
         launch_check(world_->gather(g, stream), "gather (chunk)");
         ++launches_;
         rt_check(cudaEventRecord(ev(reduced_ev_[slot]), main_s), "cudaEventRecord");
@@ -853,7 +908,6 @@ void DeviceSession::broadcast(const void *const *in, void *const *out, size_t co
             g.bytes = bytes;
             g.root = root;
             g.start_barrier = true;
-            g.algo = world > 2 ? kBcastScatter : kGatherPush;
             launch_check(world_->gather(g, stream), "broadcast");
             ++launches_;
             return;

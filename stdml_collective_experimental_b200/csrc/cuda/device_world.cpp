@@ -178,6 +178,7 @@ class World final : public DeviceWorld
     unsigned int tma_tile_vec_ = 0;        // STDML_COLLECTIVE_TMA_TILE_VEC (0: 1024, two vectors per thread)
     int nvls_variant_ = kNvlsPipe4;        // STDML_COLLECTIVE_NVLS_VARIANT
     bool debug_checks_ = false;            // STDML_COLLECTIVE_DEBUG
+    size_t bcast_pipelined_min_ = 8u << 20;  // STDML_COLLECTIVE_BCAST_PIPELINED_MIN_BYTES
     size_t gather_push_min_ = 64u << 10;  // STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES
     bool gather_mc_ = false;  // STDML_COLLECTIVE_GATHER_MC: all_gather through the switch (measured
                               // at 8 GPUs: plain stores 653-660 GB/s, multimem.st 614-625)
@@ -232,6 +233,7 @@ class World final : public DeviceWorld
             nvls_variant_ = std::max(0, std::min(kNvlsVariants - 1, std::atoi(e)));
         }
         env_bytes("STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES", gather_push_min_);
+        env_bytes("STDML_COLLECTIVE_BCAST_PIPELINED_MIN_BYTES", bcast_pipelined_min_);
         if (const char *e = std::getenv("STDML_COLLECTIVE_GATHER_MC")) { gather_mc_ = std::atoi(e) != 0; }
         if (const char *e = std::getenv("STDML_COLLECTIVE_DEBUG")) {
             debug_checks_ = std::atoi(e) != 0;
@@ -393,6 +395,8 @@ class World final : public DeviceWorld
             tma_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "tma_over_nvls_min_bytes") {
             tma_over_nvls_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "bcast_pipelined_min_bytes") {
+            bcast_pipelined_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "gather_push_min_bytes") {
             gather_push_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "gather_mc") {
@@ -786,6 +790,8 @@ class World final : public DeviceWorld
             // measured: posted stores beat peer loads once the message is past the
             // latency-bound sizes
             a.algo = (opt_.world > 1 && c.bytes >= gather_push_min_) ? kGatherPush : kBcastPull;
+        } else if (opt_.world > 2 && c.bytes >= bcast_pipelined_min_) {
+            a.algo = kBcastPipelined;
         } else if (opt_.world > 1 && c.bytes >= (256u << 10)) {
             // pulling from root costs (n-1) copies on root's links
             a.algo = mc_possible ? kBcastNvls : (opt_.world > 2 ? kBcastScatter : kGatherPush);
@@ -801,6 +807,13 @@ class World final : public DeviceWorld
         }
         int blocks = c.blocks > 0 ? c.blocks : pick_blocks(nvec, kAlgoOneShot);
         if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
+        if (a.algo == kBcastPipelined) {
+            // about 16 KB per piece: long enough to fill the links, short enough that
+            // the holders start forwarding early
+            const size_t per_block_slice = nvec / static_cast<size_t>(opt_.world - 1) /
+                                           static_cast<size_t>(std::max(1, blocks));
+            a.rounds = static_cast<int>(std::max<size_t>(1, std::min<size_t>(32, per_block_slice / 1024)));
+        }
         return launch_gather(make_ctx(), a, blocks, vranks_, stream);
     }
 

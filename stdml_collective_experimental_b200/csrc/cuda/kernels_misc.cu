@@ -293,6 +293,58 @@ __global__ void __launch_bounds__(kThreads)
                 copy_span_to_user(dst, a.bytes, mine, span_of(nvec, world, s, nb, b));
             }
         }
+    } else if (bcast && a.algo == kBcastPipelined) {
+        // ---- the same in rounds, with the block cut into world - 1 slices, one per
+        // non-root rank (root holds everything already and forwards nothing, so
+        // its links carry the message exactly once).  Block b's part of a slice is
+        // cut into `rounds` pieces.  Root sends piece k of every slice to its
+        // holder and signals; a holder waits for signal k and forwards its piece k
+        // to the other non-root ranks while root is already sending piece k + 1.
+        const int rounds = a.rounds > 0 ? a.rounds : 1;
+        const int ns = world - 1;
+        auto piece = [&](int j, int k) {
+            const Span sp = span_of(nvec, ns, j, nb, b);
+            const unsigned long long groups = (sp.hi - sp.lo + kSpanGranule - 1) / kSpanGranule;
+            Span r;
+            r.lo = sp.lo + groups * static_cast<unsigned long long>(k) / rounds * kSpanGranule;
+            r.hi = sp.lo + groups * static_cast<unsigned long long>(k + 1) / rounds * kSpanGranule;
+            r.lo = r.lo < sp.hi ? r.lo : sp.hi;
+            r.hi = r.hi < sp.hi ? r.hi : sp.hi;
+            return r;
+        };
+        const int my_slice = (rank - a.root - 1 + world) % world;  // non-root ranks
+        for (int k = 0; k < rounds; ++k) {
+            if (is_root) {
+                for (int j = 0; j < ns; ++j) {
+                    const int holder = (rank + 1 + j) % world;
+                    for_each_block_vec(src, mine, a.bytes, piece(j, k),
+                                       [&](unsigned long long v, const uint4 &x) {
+                                           st_arena_v4(a.data[holder] + v * 16ull, x);
+                                           // from user memory root fills its own region too,
+                                           // for its unpack below
+                                           if (src != nullptr) { st_arena_v4(mine + v * 16ull, x); }
+                                       });
+                }
+                signal_from(ctx, rank, &sync, k);
+            } else {
+                if (!wait_for(ctx, rank, a.root, &sync, k)) { return; }
+                for_each_block_vec(nullptr, mine, a.bytes, piece(my_slice, k),
+                                   [&](unsigned long long v, const uint4 &x) {
+                                       for (int i = 1; i < world; ++i) {
+                                           const int r = (rank + i) % world;
+                                           if (r == a.root) { continue; }
+                                           st_arena_v4(a.data[r] + v * 16ull, x);
+                                       }
+                                   });
+            }
+        }
+        rounds_done(&sync, rounds);
+        if (!peer_barrier(ctx, rank, &sync)) { return; }
+        if (dst != nullptr) {
+            for (int j = 0; j < ns; ++j) {
+                copy_span_to_user(dst, a.bytes, mine, span_of(nvec, ns, (my_slice + j) % ns, nb, b));
+            }
+        }
     } else {
         // ---- pull (small messages): pack, one barrier, read the peers' regions
         if (src != nullptr && (!bcast || is_root)) {

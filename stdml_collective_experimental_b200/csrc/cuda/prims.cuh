@@ -147,6 +147,58 @@ __device__ __forceinline__ bool peer_barrier(const CommCtx &ctx, int rank, Block
     return ok;
 }
 
+// One-way signals on the barrier's flags, for kernels in which one rank feeds
+// the others in rounds.  signal_from(): this block of `rank` tells block
+// blockIdx.x of every rank that everything its threads stored so far is in
+// place (value = epoch + round + 1).  wait_for(): the others wait for it, with
+// the barrier's limits.  After `rounds` rounds every rank calls rounds_done(),
+// so that the next full barrier of all ranks starts from the same epoch.
+__device__ __forceinline__ void signal_from(const CommCtx &ctx, int rank, BlockSync *s, int round)
+{
+    __syncthreads();
+    const int p = static_cast<int>(threadIdx.x);
+    if (p < ctx.world) {
+        st_release_sys_u32(&pad_of(ctx, p)->flag[blockIdx.x][rank],
+                           s->epoch + static_cast<uint32_t>(round) + 1u);
+    }
+}
+
+__device__ __forceinline__ bool wait_for(const CommCtx &ctx, int rank, int src, BlockSync *s,
+                                         int round)
+{
+    if (threadIdx.x == 0) {
+        const uint32_t target = s->epoch + static_cast<uint32_t>(round) + 1u;
+        const uint32_t *f = &pad_of(ctx, rank)->flag[blockIdx.x][src];
+        unsigned int spins = 0;
+        unsigned long long t0 = 0;
+        for (;;) {
+            const uint32_t seen = ld_acquire_sys_u32(f);
+            if (static_cast<int32_t>(seen - target) >= 0) { break; }
+            ++spins;
+            if ((spins & 127u) == 0u) {
+                const unsigned long long now = global_ns();
+                if (t0 == 0) { t0 = now; }
+                if (now - t0 > ctx.timeout_ns || spins >= ctx.max_spins) {
+                    report_timeout(ctx, rank, src, target, seen, 32 + round);
+                    *reinterpret_cast<volatile int *>(&s->failed) = 1;
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const bool ok = (*reinterpret_cast<volatile int *>(&s->failed) == 0);
+    __syncthreads();
+    return ok;
+}
+
+__device__ __forceinline__ void rounds_done(BlockSync *s, int rounds)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) { s->epoch += static_cast<uint32_t>(rounds); }
+    __syncthreads();
+}
+
 // ------------------------------------------------------------- dtype traits
 template <int DT>
 struct Tr;

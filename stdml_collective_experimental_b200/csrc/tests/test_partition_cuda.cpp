@@ -220,6 +220,19 @@ int main()
             }
         }
     }
+    {   // the rules of the in-kernel argument checks
+        EXPECT(buffer_offset_ok(kDataOffset) && buffer_offset_ok(kDataOffset + 4096) && buffer_offset_ok(0));
+        EXPECT(!buffer_offset_ok(kDataOffset + 8) && !buffer_offset_ok(64) && !buffer_offset_ok(kDataOffset - 16));
+        GroupEntry tab[3];
+        for (auto &e : tab) { e.src = nullptr; e.dst = nullptr; }
+        tab[0].voff = 0;  tab[0].count = 10;   // 3 vectors of f32
+        tab[1].voff = 3;  tab[1].count = 4;    // 1 vector
+        tab[2].voff = 4;  tab[2].count = 1;
+        for (int i = 0; i < 3; ++i) { EXPECT(table_entry_in_range<DT_F32>(tab, i, 3, 5)); }
+        EXPECT(!table_entry_in_range<DT_F32>(tab, 2, 3, 4));   // runs past the buffer
+        tab[1].voff = 2;                                       // overlaps its predecessor
+        EXPECT(!table_entry_in_range<DT_F32>(tab, 0, 3, 5));
+    }
     EXPECT(entry_nvec<DT_BF16>(9) == 2 && entry_nvec<DT_U8>(16) == 1 && entry_nvec<DT_F64>(3) == 2);
     std::printf("test-partition: %s\n", failures == 0 ? "OK" : "FAILED");
     return failures == 0 ? 0 : 1;

@@ -259,15 +259,49 @@ def main():
             assert bits_equal(f_out.cpu(), reduce_many(fhost, "sum", 0.5))
         sess.symm_free(fsym)
         sess.symm_free(sym)
+    # the broadcast in rounds (the default above 8 MB from three ranks up), forced at
+    # every size here
+    sess.set_knob("bcast_pipelined_min_bytes", 0)
+    for n in (1, 5000, 3_000_001):
+        host = inputs(world, n, torch.int32, seed=n + 5)
+        for root in sorted({0, world - 1}):
+            b = host[rank].cuda()
+            sess.broadcast(b, root=root)
+            sym = sess.symm_empty(n, torch.int32)
+            sym.copy_(host[rank])
+            sess.broadcast(sym, root=root)
+            torch.cuda.synchronize()
+            sess.check()
+            assert torch.equal(b.cpu(), host[root]) and torch.equal(sym.cpu(), host[root]), (n, root)
+            sess.symm_free(sym)
+    sess.set_knob("bcast_pipelined_min_bytes", 8 << 20)
     n = 5_000_001  # 20 MB per rank through 4 MB slots
     host = inputs(world, n, torch.int32, seed=77)
     out = torch.empty(n * world, dtype=torch.int32, device="cuda")
     sess.all_gather(host[rank].cuda(), out)
     b = host[rank].cuda()
     sess.broadcast(b, root=world - 1)
+    r_int = torch.full((n,), -3, dtype=torch.int32, device="cuda")
+    sess.reduce(host[rank].cuda(), out=r_int, root=world - 1)   # several slots: three-stream pipeline
+    fhost = inputs(world, n, torch.float32, seed=78, exact=True)
+    r_f = torch.zeros(n, device="cuda")
+    sess.reduce(fhost[rank].cuda(), out=r_f, root=0)
+    fsym = sess.symm_empty(n, torch.float32)                     # symmetric input, several slots
+    fsym.copy_(fhost[rank])
+    r_s = torch.zeros(n, device="cuda")
+    sess.reduce(fsym, out=r_s, root=0, scale=0.5)
     sess.all_reduce(out[:1000])  # a staged call right after the pipelines: the slots are free
     torch.cuda.synchronize()
     sess.check()
+    if rank == world - 1:
+        assert torch.equal(r_int.cpu(), reduce_many(host, "sum"))
+    else:
+        assert torch.all(r_int == -3)
+    if rank == 0:
+        assert bits_equal(r_f.cpu(), reduce_many(fhost, "sum"))
+        assert bits_equal(r_s.cpu(), reduce_many(fhost, "sum", 0.5))
+    assert bits_equal(fsym.cpu(), fhost[rank])
+    sess.symm_free(fsym)
     assert torch.equal(out[1000:].cpu(), torch.cat(host)[1000:]) and torch.equal(b.cpu(), host[world - 1])
     assert torch.equal(out[:1000].cpu(), torch.cat(host)[:1000] * world)
 

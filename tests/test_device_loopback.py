@@ -405,6 +405,36 @@ def test_zero_copy_all_gather_broadcast_reduce_on_symmetric_buffers(sess, n):
         sess.symm_free(sym)
 
 
+def test_broadcast_in_rounds(sess):
+    """The pipelined broadcast (root sends in rounds and signals, holders forward
+    while root goes on) at sizes from one vector to many rounds, staged and on
+    symmetric buffers, from both ends of the rank range."""
+    if sess.world < 3:
+        pytest.skip("used from three ranks up")
+    sess.set_knob("bcast_pipelined_min_bytes", 0)
+    try:
+        for n in (1, 17, 5000, 300_001, 2_000_003):
+            host = make_inputs(sess.world, n, torch.float32, seed=n + 1)
+            for root in sorted({0, sess.world - 1}):
+                dev = [h.cuda() for h in host]
+                sess.broadcast(dev, root=root)
+                if n * 4 <= (4 << 20):
+                    sym = sess.symm_empty(n, torch.float32)
+                    for r in range(sess.world):
+                        sym[r].copy_(host[r])
+                    sess.broadcast(sym, root=root)
+                torch.cuda.synchronize()
+                sess.check()
+                for r in range(sess.world):
+                    assert torch.equal(dev[r].cpu(), host[root]), (n, root, r)
+                    if n * 4 <= (4 << 20):
+                        assert torch.equal(sym[r].cpu(), host[root]), (n, root, r, "symmetric")
+                if n * 4 <= (4 << 20):
+                    sess.symm_free(sym)
+    finally:
+        sess.set_knob("bcast_pipelined_min_bytes", 8 << 20)
+
+
 @pytest.mark.parametrize("algo_knob", [0, 1 << 40])
 def test_all_gather_push_and_pull_agree(sess, algo_knob):
     sess.set_knob("gather_push_min_bytes", algo_knob)  # 0: always push; huge: always pull

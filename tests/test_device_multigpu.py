@@ -22,8 +22,11 @@ def run_world(n, port, extra_env=None, timeout=600, worker="multigpu_worker.py")
            os.path.join(HERE, worker)]
     res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                          timeout=timeout)
-    assert res.returncode == 0, res.stdout[-4000:]
-    assert res.stdout.count("OK rank") == n, res.stdout[-4000:]
+    if res.returncode != 0 or res.stdout.count("OK rank") != n:
+        # the workers' own tracebacks come long before the launcher's epilogue
+        lines = res.stdout.splitlines()
+        first = next((i for i, line in enumerate(lines) if "Traceback" in line), max(0, len(lines) - 60))
+        raise AssertionError("\n".join(lines[first:first + 60]) + "\n...\n" + res.stdout[-1500:])
     return res.stdout
 
 
