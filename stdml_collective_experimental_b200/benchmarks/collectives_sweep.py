@@ -59,7 +59,7 @@ def main():
         ms = timed(lambda: dist.reduce(r_in.clone(), 0), iters, 5, dev)
         row["nccl_reduce_incl_clone"] = {"us": ms * 1e3}
         # registered: the same ordinary tensors, no staging
-        sess.set_knob("register_min_bytes", 0)
+        sess.set_knob("register_min_bytes", 4 << 20)  # below: staged, the handle exchange costs more than it saves
         out.zero_()
         ms = timed(lambda: sess.all_gather(x, out), iters, 5, dev)
         ok = all(float(out[r * n]) == r and float(out[(r + 1) * n - 1]) == r for r in range(world))

@@ -89,6 +89,14 @@ void DeviceSession::set_knob(const std::string &name, long long value)
         register_min_bytes_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         return;
     }
+    if (name == "chunk_push_blocks") {
+        chunk_push_blocks_ = static_cast<int>(std::max<long long>(1, std::min<long long>(kMaxBlocks, value)));
+        return;
+    }
+    if (name == "chunk_unpack_blocks") {
+        chunk_unpack_blocks_ = static_cast<int>(std::max<long long>(0, std::min<long long>(kMaxBlocks, value)));
+        return;
+    }
     if (name == "pipeline_min_bytes") {
         pipeline_min_bytes_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         return;
@@ -752,13 +760,14 @@ void DeviceSession::run_gather_chunks(std::vector<GatherCall> &calls,
         g.dst = nullptr;  // unpacked by the copy kernel below
         // posted stores fill the links from few SMs; the rest belong to the unpack
         // of the previous chunk, which runs at the same time
-        if (g.blocks <= 0) { g.blocks = 64; }
+        if (g.blocks <= 0) { g.blocks = chunk_push_blocks_; }
         launch_check(world_->gather(g, stream), "gather (chunk)");
         ++launches_;
         rt_check(cudaEventRecord(ev(reduced_ev_[slot]), main_s), "cudaEventRecord");
         rt_check(cudaStreamWaitEvent(unpack_s, ev(reduced_ev_[slot]), 0), "cudaStreamWaitEvent");
         launch_check(world_->unpack_blocks(world_->ptr(rank, g.off), dsts[k][0], g.bytes,
-                                           g.sym_stride, stride, blocks_n, unpack_s),
+                                           g.sym_stride, stride, blocks_n, unpack_s,
+                                           chunk_unpack_blocks_),
                      "unpack (chunk)");
         ++launches_;
         rt_check(cudaEventRecord(ev(unpacked_ev_[slot]), unpack_s), "cudaEventRecord");

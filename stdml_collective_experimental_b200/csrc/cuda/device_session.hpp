@@ -134,6 +134,8 @@ class DeviceSession
     bool have_last_stream_ = false;
     void *order_ev_ = nullptr;
     size_t register_min_bytes_ = SIZE_MAX;     // STDML_COLLECTIVE_REGISTER_MIN_BYTES
+    int chunk_push_blocks_ = 64;    // grid of a chunk's push while the previous chunk is unpacked (knob)
+    int chunk_unpack_blocks_ = 0;   // grid of that unpack (0: as many as the copy wants) (knob)
     bool registered_path(size_t bytes, void *stream) const;
     size_t pipeline_min_bytes_ = 512u << 20;   // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
     size_t pipeline_chunk_bytes_ = 32u << 20;  // STDML_COLLECTIVE_PIPELINE_CHUNK_BYTES (smallest chunk)

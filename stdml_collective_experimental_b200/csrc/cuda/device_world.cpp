@@ -818,13 +818,14 @@ class World final : public DeviceWorld
     }
 
     int unpack_blocks(const void *region, void *dst, size_t bytes, size_t sym_stride,
-                      size_t stride, int blocks_n, void *stream) override
+                      size_t stride, int blocks_n, void *stream, int want_grid) override
     {
         if (bytes == 0 || blocks_n <= 0) { return 0; }
         const size_t nvec = (bytes + 15) / 16;
-        const int grid = static_cast<int>(std::min<size_t>(
+        int grid = static_cast<int>(std::min<size_t>(
             std::max<size_t>(1, nvec / (static_cast<size_t>(kThreads) * 4)),
             static_cast<size_t>(2 * num_sms_)));
+        if (want_grid > 0) { grid = std::min(grid, want_grid); }
         return launch_unpack_blocks(region, dst, bytes, sym_stride, stride, blocks_n, grid, stream);
     }
 

@@ -150,7 +150,7 @@ class DeviceWorld
     virtual int gather(const GatherCall &c, void *stream) = 0;
     // Local copy of `blocks_n` gathered blocks out of a region into user memory.
     virtual int unpack_blocks(const void *region, void *dst, size_t bytes, size_t sym_stride,
-                              size_t stride, int blocks_n, void *stream) = 0;
+                              size_t stride, int blocks_n, void *stream, int grid = 0) = 0;
     virtual int barrier(void *stream) = 0;
     // Loopback worlds only: launch the barrier for the first `rows` virtual
     // ranks.  With rows < world the missing ranks never arrive, so the wait

@@ -224,18 +224,31 @@ class StdmlProcessGroup(dist.ProcessGroup):
                 t.copy_(d)
         return _DoneWork(tensors)
 
+    # gather, scatter and all_to_all are built from point-to-point messages in
+    # which ranks may all send before any of them receives.  Host messages are
+    # buffered, so that is fine there; device transfers (NCCL kernels) would wait
+    # for each other for ever.  CUDA tensors of these three calls therefore travel
+    # as host messages (a copy out and a copy in); they are not hot paths.
+    @staticmethod
+    def _wire(t):
+        return t.detach().cpu().contiguous() if t.is_cuda else StdmlProcessGroup._dense(t)
+
+    @staticmethod
+    def _landing(o):
+        return torch.empty(o.shape, dtype=o.dtype, device="cpu")
+
     def gather(self, output_tensors, input_tensors, opts=None):
         root = getattr(opts, "rootRank", 0)
         name = self._name("ga")
         for k, inp in enumerate(input_tensors):
             if self._rank != root:
-                self.sess.send(self._dense(inp), root, name=f"{name}/{k}")
+                self.sess.send(self._wire(inp), root, name=f"{name}/{k}")
                 continue
             for r, o in enumerate(output_tensors[k]):
                 if r == root:
                     o.copy_(inp)
                 else:
-                    d = torch.empty_like(o, memory_format=torch.contiguous_format)
+                    d = self._landing(o)
                     self.sess.recv(d, r, name=f"{name}/{k}")
                     o.copy_(d)
         return _DoneWork(output_tensors)
@@ -249,9 +262,9 @@ class StdmlProcessGroup(dist.ProcessGroup):
                     if r == root:
                         out.copy_(t)
                     else:
-                        self.sess.send(self._dense(t), r, name=f"{name}/{k}")
+                        self.sess.send(self._wire(t), r, name=f"{name}/{k}")
             else:
-                d = torch.empty_like(out, memory_format=torch.contiguous_format)
+                d = self._landing(out)
                 self.sess.recv(d, root, name=f"{name}/{k}")
                 out.copy_(d)
         return _DoneWork(output_tensors)
@@ -260,12 +273,12 @@ class StdmlProcessGroup(dist.ProcessGroup):
         name = self._name("a2a")
         for r, t in enumerate(input_tensors):
             if r != self._rank:
-                self.sess.send(self._dense(t), r, name=name)
+                self.sess.send(self._wire(t), r, name=name)
         for r, o in enumerate(output_tensors):
             if r == self._rank:
                 o.copy_(input_tensors[r])
             else:
-                d = torch.empty_like(o, memory_format=torch.contiguous_format)
+                d = self._landing(o)
                 self.sess.recv(d, r, name=name)
                 o.copy_(d)
         return _DoneWork(output_tensors)

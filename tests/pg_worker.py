@@ -1,5 +1,6 @@
-"""One rank of the torch.distributed backend test (spawned by test_python_api.py):
-every torch.distributed collective on CPU tensors through backend "stdml", then
+"""One rank of the torch.distributed backend test (spawned by test_python_api.py,
+and with a fourth argument "cuda" by test_device_multigpu.py): every
+torch.distributed collective through backend "stdml" on CPU (or CUDA) tensors, then
 DistributedDataParallel against single-process training on the joint batch."""
 import os
 import sys
@@ -19,12 +20,21 @@ def make_model():
 
 
 def data(rank):
-    g = torch.Generator().manual_seed(500 + rank)
-    return torch.randn(8, 12, generator=g), torch.randn(8, 4, generator=g)
+    g = torch.Generator(device="cpu").manual_seed(500 + rank)
+    x = torch.randn(8, 12, generator=g, device="cpu")
+    y = torch.randn(8, 4, generator=g, device="cpu")
+    dev = torch.get_default_device()
+    return x.to(dev), y.to(dev)
 
 
 def main():
     rank, n, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+    if len(sys.argv) > 4 and sys.argv[4] == "cuda":
+        # the same calls on CUDA tensors: one GPU per rank, every factory call below
+        # then makes device tensors and the backend takes the NVLink kernels
+        os.environ["STDML_COLLECTIVE_DEVICE_ID"] = str(rank)
+        torch.cuda.set_device(rank)
+        torch.set_default_device(torch.device("cuda", rank))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     dist.init_process_group("stdml", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=n)
     assert dist.get_backend() == "stdml" and dist.get_rank() == rank and dist.get_world_size() == n

@@ -50,6 +50,27 @@ def test_data_parallel_matches_single_process_training():
     run_world(2, 29641, worker="ddp_worker.py")
 
 
+def test_torch_distributed_backend_on_cuda_tensors():
+    """Backend "stdml" of torch.distributed with CUDA tensors on two GPUs: the
+    collectives run on this library's kernels, DistributedDataParallel trains."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    n, port = 2, 29881
+    env = dict(os.environ, STDML_COLLECTIVE_BASE_PORT="10900")
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "pg_worker.py"), str(r), str(n),
+                               str(port), "cuda"], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(n)]
+    try:
+        outs = [p.communicate(timeout=300)[0] for p in procs]
+    except subprocess.TimeoutExpired:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        raise
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"rank {r} OK" in o, o[-3000:]
+
+
 def test_elastic_resize_on_gpus():
     """2 -> 1 -> 2 workers with CUDA tensors through Peer/Session: every membership
     gets a fresh device world (arenas, mappings, multicast); the survivor keeps
