@@ -801,6 +801,11 @@ class World final : public DeviceWorld
         if (a.algo == kBcastNvls && !mc_possible) {
             throw std::invalid_argument("broadcast: NVLS needs the multicast mapping of the arena");
         }
+        if (a.algo == kBcastPull && c.start_barrier) {
+            // zero-copy pull: the peers read live memory of its owner, who may only go
+            // on once they are done
+            a.end_barrier = 1;
+        }
         a.use_mc = c.use_mc >= 0 ? (c.use_mc != 0 && mc_possible) : (mc_possible && gather_mc_);
         if (all_gather && a.algo == kBcastPull && c.src != nullptr && c.sym_stride == 0) {
             // one block per region: block p is read at p * 0

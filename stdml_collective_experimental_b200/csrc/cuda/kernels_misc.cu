@@ -356,14 +356,19 @@ __global__ void __launch_bounds__(kThreads)
                                });
         }
         if (!peer_barrier(ctx, rank, &sync)) { return; }
-        if (dst != nullptr) {
+        // without a user destination the region itself is the destination (zero-copy
+        // on registered or symmetric memory): what is already in place is skipped
+        if (dst != nullptr || !bcast || !is_root) {
             const int count = bcast ? 1 : world;
             for (int i = 0; i < count; ++i) {
                 // start with the next rank so that peers do not all read the same GPU first
                 const int p = bcast ? a.root : (rank + 1 + i) % world;
-                char *out = bcast ? dst : dst + static_cast<unsigned long long>(p) * a.stride;
+                if (dst == nullptr && p == rank) { continue; }
                 const unsigned long long at =
                     bcast ? 0ull : static_cast<unsigned long long>(p) * a.sym_stride;
+                char *out = dst != nullptr
+                                ? (bcast ? dst : dst + static_cast<unsigned long long>(p) * a.stride)
+                                : mine + at;
                 copy_span_to_user(out, a.bytes, a.data[p] + at, whole);
             }
         }

@@ -64,6 +64,25 @@ int main()
     CUDA_OK(cudaMemcpy(host.data(), y, 16, cudaMemcpyDeviceToHost));
     bad += host[0] != 1.0f;
 
+    // gradients that live in the session's symmetric heap: tensors laid back to
+    // back are reduced in place by ONE launch, nothing is packed or unpacked
+    const size_t sizes[3] = {4096, 100000, 12};  // multiples of 4 floats: 16-byte boundaries
+    float *heap = static_cast<float *>(sess.symm_alloc((4096 + 100000 + 12) * sizeof(float)));
+    std::vector<float> ones(4096 + 100000 + 12, float(r + 1));
+    CUDA_OK(cudaMemcpy(heap, ones.data(), ones.size() * sizeof(float), cudaMemcpyHostToDevice));
+    std::vector<workspace> in_heap;
+    size_t at = 0;
+    for (const size_t s : sizes) {
+        in_heap.push_back(workspace{heap + at, heap + at, s, f32, sum, "h" + std::to_string(at)});
+        at += s;
+    }
+    const unsigned long long before = sess.device_launches();
+    sess.group_all_reduce(in_heap, 1.0 / n);
+    CUDA_OK(cudaMemcpy(ones.data(), heap, ones.size() * sizeof(float), cudaMemcpyDeviceToHost));
+    bad += ones[0] != (n + 1) / 2.0f || ones.back() != (n + 1) / 2.0f;
+    bad += sess.device_launches() - before != 1;
+    sess.symm_free(heap);
+
     std::printf("rank %d/%d on device memory: %s\n", r, n, bad == 0 ? "OK" : "WRONG");
     cudaFree(x);
     cudaFree(y);

@@ -330,3 +330,25 @@ def test_host_reducer_against_plain_pytorch_reductions():
                 want = wide.sum(0) / 3.0
                 steps = 2 if dtype in (torch.bfloat16, torch.float16) else world + 1
                 assert torch.allclose(got.double(), want, rtol=eps[dtype] * steps * 1.01, atol=0)
+
+
+def test_elastic_benchmark_refuses_to_drop_members_with_nvls_on(monkeypatch):
+    """A rank must not leave a GPU job while its arena is bound to a multicast
+    object: schedules that shrink need STDML_COLLECTIVE_NVLS=0, and say so."""
+    import pytest
+    from stdml_collective_experimental_b200.benchmarks import elastic
+    assert elastic.shrinks(8, {50: 4, 100: 6, 150: 8})
+    assert elastic.shrinks(4, {10: 6, 20: 5})
+    assert not elastic.shrinks(2, {3: 4, 9: 4})
+    assert not elastic.shrinks(6, {10: 4}, from_step=11)  # a joiner that arrives after the shrink
+
+    class FakeSess:
+        size = 8
+
+    class FakePeer:
+        self_id = "127.0.0.1:1"
+
+    monkeypatch.delenv("STDML_COLLECTIVE_NVLS", raising=False)
+    with pytest.raises(SystemExit) as e:
+        elastic.run(None, FakePeer(), FakeSess(), {50: 4}, True, None)
+    assert "STDML_COLLECTIVE_NVLS=0" in str(e.value)
