@@ -4,7 +4,7 @@ by ONE driver source (baseline/resize_driver.cpp) that uses only the public API
 the two share: peer::from_env, join_elastic, all_reduce, peer::resize(sess,
 config_provider).
 
-    python baseline/measure_resize.py [--impl reference|ours] [--schedule 8,4,6,8]
+    python baseline/measure_resize.py [--impl reference --reference <its source tree> | --impl ours] [--schedule 8,4,6,8]
 
 The reference's elastic launcher needs a Go toolchain, which is not available
 offline, but its peer::resize(sess, config_provider) overload is plain C++.  This
@@ -61,7 +61,8 @@ def build(reference, out_bin):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--schedule", default="8,4,6,8")
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("STDML_REFERENCE_SRC", ""),
+                    help="source tree of the reference implementation (or $STDML_REFERENCE_SRC)")
     ap.add_argument("--impl", default="reference", choices=["reference", "ours"])
     args = ap.parse_args()
     sizes = [int(x) for x in args.schedule.split(",")]

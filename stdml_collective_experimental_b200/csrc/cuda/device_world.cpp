@@ -446,20 +446,24 @@ class World final : public DeviceWorld
                 d.MemGetAddressRange(&base, &size, reinterpret_cast<CUdeviceptr>(mine)) ==
                     CUDA_SUCCESS &&
                 reinterpret_cast<uintptr_t>(mine) + bytes <= static_cast<uintptr_t>(base) + size) {
+                // The handle is asked for on every call: an allocation that was freed and
+                // made again at the same address and size has another handle, and only
+                // a fresh look tells (the driver call costs microseconds).
                 auto it = exported_.find(static_cast<uintptr_t>(base));
-                if (it != exported_.end() && it->second.size != size) {
-                    exported_.erase(it);  // the address was freed and allocated again
-                    it = exported_.end();
-                }
-                if (it == exported_.end()) {
-                    Exported e;
-                    if (cudaIpcGetMemHandle(&e.handle, reinterpret_cast<void *>(base)) ==
-                        cudaSuccess) {
+                cudaIpcMemHandle_t now;
+                if (cudaIpcGetMemHandle(&now, reinterpret_cast<void *>(base)) == cudaSuccess) {
+                    if (it == exported_.end() || it->second.size != size ||
+                        std::memcmp(&it->second.handle, &now, sizeof(now)) != 0) {
+                        Exported e;
+                        e.handle = now;
                         e.size = size;
-                        it = exported_.emplace(static_cast<uintptr_t>(base), e).first;
-                    } else {
-                        (void)cudaGetLastError();  // e.g. memory from the VMM allocator
+                        exported_[static_cast<uintptr_t>(base)] = e;  // not announced yet
+                        it = exported_.find(static_cast<uintptr_t>(base));
                     }
+                } else {
+                    (void)cudaGetLastError();  // e.g. memory from the VMM allocator
+                    if (it != exported_.end()) { exported_.erase(it); }
+                    it = exported_.end();
                 }
                 if (it != exported_.end()) {
                     rec.ok = 1;

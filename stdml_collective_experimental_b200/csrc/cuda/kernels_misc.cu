@@ -29,38 +29,40 @@ int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op
 }
 
 // A world of one GPU: all_reduce degenerates to out = scale * in.  No peers, no
-// barrier, no arena: a light grid-stride copy with many loads in flight.
+// barrier, no arena: a copy in which every block walks contiguous 32 KB tiles
+// (8 vectors per thread in flight), so that DRAM pages and TLB entries are used
+// up before the block moves on.
+constexpr int kLocalThreads = 256;
+constexpr int kLocalUnroll = 8;
+
 template <int DT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kLocalThreads)
     local_scale_kernel(const void *src, void *dst,
                        unsigned long long count, double scale, int has_scale)
 {
     constexpr unsigned long long N = lanes_of<DT>();
+    constexpr unsigned long long kTile = static_cast<unsigned long long>(kLocalThreads) * kLocalUnroll;
     const unsigned long long nvec = (count + N - 1) / N;
+    const unsigned long long ntiles = (nvec + kTile - 1) / kTile;
     const bool al = ptr_aligned16(src) && ptr_aligned16(dst);
-    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-    unsigned long long v = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    constexpr int U = 8;
-    for (; v + (U - 1) * stride < nvec; v += U * stride) {
-        uint4 x[U];
+    for (unsigned long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const unsigned long long v0 = t * kTile + threadIdx.x;
+        uint4 x[kLocalUnroll];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            x[u] = load_user_vec<DT>(src, false, v + u * stride, count, al);
+        for (int u = 0; u < kLocalUnroll; ++u) {
+            const unsigned long long v = v0 + static_cast<unsigned long long>(u) * kLocalThreads;
+            if (v < nvec) { x[u] = load_user_vec<DT>(src, false, v, count, al); }
         }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if constexpr (Tr<DT>::is_float) {
-                if (has_scale) { x[u] = scale_vec<DT>(x[u], scale); }
+        for (int u = 0; u < kLocalUnroll; ++u) {
+            const unsigned long long v = v0 + static_cast<unsigned long long>(u) * kLocalThreads;
+            if (v < nvec) {
+                if constexpr (Tr<DT>::is_float) {
+                    if (has_scale) { x[u] = scale_vec<DT>(x[u], scale); }
+                }
+                store_user_vec<DT>(dst, false, v, count, al, x[u]);
             }
-            store_user_vec<DT>(dst, false, v + u * stride, count, al, x[u]);
         }
-    }
-    for (; v < nvec; v += stride) {
-        uint4 x = load_user_vec<DT>(src, false, v, count, al);
-        if constexpr (Tr<DT>::is_float) {
-            if (has_scale) { x = scale_vec<DT>(x, scale); }
-        }
-        store_user_vec<DT>(dst, false, v, count, al, x);
     }
 }
 
@@ -70,12 +72,13 @@ static int launch_local_dt(const void *src, void *dst, unsigned long long count,
 {
     constexpr unsigned long long N = lanes_of<DT>();
     const unsigned long long nvec = (count + N - 1) / N;
-    unsigned long long blocks = (nvec + 256ull * 8 - 1) / (256ull * 8);
-    const unsigned long long cap = static_cast<unsigned long long>(sms) * 8;
+    const unsigned long long tile = static_cast<unsigned long long>(kLocalThreads) * kLocalUnroll;
+    unsigned long long blocks = (nvec + tile - 1) / tile;
+    const unsigned long long cap = static_cast<unsigned long long>(sms) * 8;  // 8 resident CTAs per SM
     if (blocks > cap) { blocks = cap; }
     if (blocks < 1) { blocks = 1; }
-    local_scale_kernel<DT><<<static_cast<unsigned int>(blocks), 256, 0, s>>>(src, dst, count, scale,
-                                                                             has_scale);
+    local_scale_kernel<DT><<<static_cast<unsigned int>(blocks), kLocalThreads, 0, s>>>(
+        src, dst, count, scale, has_scale);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -101,3 +101,17 @@ def test_distributed_optimizer_matches_single_process_training(native_lib):
     outs = collect(procs, 300)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
+
+
+def test_resize_latency_harness_on_this_library(native_lib):
+    """The driver that times peer::resize(sess, config_provider) for both
+    implementations, compiled against this library: shrink 4 -> 2, grow 2 -> 3."""
+    import json
+    root = os.path.dirname(HERE)
+    res = subprocess.run([sys.executable, os.path.join(root, "baseline", "measure_resize.py"),
+                          "--impl", "ours", "--schedule", "4,2,3"], stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["finished"] and [(e["from"], e["to"]) for e in line["resizes"]] == [(4, 2), (2, 3)]
+    assert all(e["ms"] < 2000 for e in line["resizes"])
