@@ -140,12 +140,16 @@ void DeviceSession::order_after_previous(void *stream)
             rt_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
             order_ev_ = e;
         }
-        rt_check(cudaEventRecord(static_cast<cudaEvent_t>(order_ev_),
-                                 static_cast<cudaStream_t>(last_stream_)),
-                 "cudaEventRecord");
-        rt_check(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream),
-                                     static_cast<cudaEvent_t>(order_ev_), 0),
-                 "cudaStreamWaitEvent");
+        // the previous stream may have been destroyed by its owner since (then all of
+        // its work has been submitted and completed or abandoned): nothing to wait for
+        if (cudaEventRecord(static_cast<cudaEvent_t>(order_ev_),
+                            static_cast<cudaStream_t>(last_stream_)) == cudaSuccess) {
+            rt_check(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream),
+                                         static_cast<cudaEvent_t>(order_ev_), 0),
+                     "cudaStreamWaitEvent");
+        } else {
+            (void)cudaGetLastError();
+        }
     }
     last_stream_ = stream;
     have_last_stream_ = true;

@@ -179,6 +179,7 @@ class World final : public DeviceWorld
     int nvls_variant_ = kNvlsPipe4;        // STDML_COLLECTIVE_NVLS_VARIANT
     bool debug_checks_ = false;            // STDML_COLLECTIVE_DEBUG
     size_t bcast_pipelined_min_ = 8u << 20;  // STDML_COLLECTIVE_BCAST_PIPELINED_MIN_BYTES
+    size_t bcast_piece_vec_ = 1024;          // vectors per round, block and slice (knob bcast_piece_vec)
     size_t gather_push_min_ = 64u << 10;  // STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES
     bool gather_mc_ = false;  // STDML_COLLECTIVE_GATHER_MC: all_gather through the switch (measured
                               // at 8 GPUs: plain stores 653-660 GB/s, multimem.st 614-625)
@@ -395,6 +396,8 @@ class World final : public DeviceWorld
             tma_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "tma_over_nvls_min_bytes") {
             tma_over_nvls_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "bcast_piece_vec") {
+            bcast_piece_vec_ = static_cast<size_t>(std::max<long long>(32, value));
         } else if (name == "bcast_pipelined_min_bytes") {
             bcast_pipelined_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "gather_push_min_bytes") {
@@ -821,7 +824,8 @@ class World final : public DeviceWorld
             // the holders start forwarding early
             const size_t per_block_slice = nvec / static_cast<size_t>(opt_.world - 1) /
                                            static_cast<size_t>(std::max(1, blocks));
-            a.rounds = static_cast<int>(std::max<size_t>(1, std::min<size_t>(32, per_block_slice / 1024)));
+            a.rounds = static_cast<int>(std::max<size_t>(
+                1, std::min<size_t>(32, per_block_slice / std::max<size_t>(32, bcast_piece_vec_))));
         }
         return launch_gather(make_ctx(), a, blocks, vranks_, stream);
     }
