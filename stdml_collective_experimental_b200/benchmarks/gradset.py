@@ -8,6 +8,9 @@ N(0, 1e-3) seeded per rank, averaged over the ranks:
   ours/arena   gradients live in the symmetric heap: ONE fused in-place launch
   ours/staged  gradients are ordinary CUDA tensors: pack + reduce + unpack fused,
                one launch per staging slot (descriptor table)
+  ours/registered  the same ordinary tensors with register_min_bytes = 0: their
+               allocations are mapped on every peer once, then ONE launch reduces
+               them where they lie (no pack, no unpack)
   nccl/flat    ncclAllReduce on one flattened bucket + a separate scale kernel
   nccl/coalesced  torch's coalesced all_reduce over the tensor list + _foreach_mul_
 busBW = 2(n-1)/n * set bytes / t.  The link roofline is 770 GB/s per direction
@@ -120,6 +123,22 @@ def main():
                        args.iters, 3, dev, world)
             row["ours_staged_bf16_wire"] = {"ms": ms, "busbw_equiv": bus(ms)}
         if world > 1:
+            sess.set_knob("register_min_bytes", 0)
+            for t, v in zip(loose, ref_parts):
+                t.copy_(v[:t.numel()])  # a known value again: every rank holds the mean
+            sess.group_all_reduce(loose)  # sum of n equal means = n * mean
+            torch.cuda.synchronize()
+            sess.check()
+            err_r = max(float((loose[i].float() - world * ref_parts[i][:sizes[i]].float()).abs().max())
+                        for i in picks)
+            row["verified"] = bool(ok and err_r <= world * tol * mag + 1e-9)
+            l0 = sess.launches
+            ms = timed(lambda: sess.group_all_reduce(loose, scale=scale), args.iters, 3, dev, world)
+            row["ours_registered"] = {"ms": ms, "busbw": bus(ms),
+                                      "launches_per_call": (sess.launches - l0) // (args.iters + 3)}
+            sess.drop_registrations()
+            sess.set_knob("register_min_bytes", -1)
+
             def nccl_flat():
                 dist.all_reduce(plain_flat)
                 plain_flat.mul_(scale)

@@ -172,6 +172,27 @@ enum : int {
     kNvlsVariants = 4,
 };
 
+// A fused group on REGISTERED tensors: every tensor of every rank is addressed
+// through its own peer mapping, nothing is packed.  Entry i covers the vectors
+// [voff, voff + ceil(count / lanes)) of the group's flat index space.
+struct PeerEntry {
+    char *in[kMaxRanks];   // tensor i of rank r as mapped here (operands)
+    char *out[kMaxRanks];  // where rank r wants the result (often the same memory)
+    unsigned long long voff;
+    unsigned long long count;  // elements
+};
+
+struct GroupPeerArgs {
+    const PeerEntry *table;  // device memory, sorted by voff, entry 0 at 0
+    int ntable;
+    unsigned long long nvec;  // vectors of the flat index space
+    int has_scale;
+    double scale;
+    // bulk-copy variant (see tma_geometry): 0 stages = plain peer loads
+    int tma_stages;
+    unsigned int tma_tile_vec;
+};
+
 enum : int { kPhasePack = 1, kPhaseReduce = 2, kPhaseUnpack = 4, kPhaseAll = 7 };
 
 struct GatherArgs {
@@ -218,6 +239,9 @@ int launch_unpack_blocks(const void *region, void *dst, unsigned long long bytes
 int launch_all_reduce(const CommCtx &ctx, const AllReduceArgs &a, int dt, int op,
                       int blocks, int vranks, void *stream);
 bool nvls_supported(int dt, int op);
+// kernels_group_peer.cu: two-shot over a table of registered tensors
+int launch_group_peer(const CommCtx &ctx, const GroupPeerArgs &a, int dt, int op, int blocks,
+                      int vranks, void *stream);
 // world of one GPU: dst = scale * src (integers: copy), no arena involved
 int launch_local_scale(const void *src, void *dst, unsigned long long count, int dt, double scale,
                        int has_scale, int sms, void *stream);

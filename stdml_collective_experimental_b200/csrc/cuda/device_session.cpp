@@ -78,6 +78,7 @@ DeviceSession::~DeviceSession()
     }
     for (void *p : table_mem_) { (void)cudaFree(p); }
     table_mem_.clear();
+    forget_peer_plans();
     if (order_ev_ != nullptr) { (void)cudaEventDestroy(static_cast<cudaEvent_t>(order_ev_)); }
     (void)cudaGetLastError();
 }
@@ -107,7 +108,16 @@ void DeviceSession::set_knob(const std::string &name, long long value)
 void DeviceSession::drop_registrations()
 {
     std::lock_guard<std::recursive_mutex> lk(mu_);
-    world_->drop_registrations();
+    world_->drop_registrations();  // waits for the device first
+    forget_peer_plans();           // their tables hold addresses of the mappings just closed
+}
+
+void DeviceSession::forget_peer_plans()
+{
+    for (auto &kv : peer_plans_) {
+        if (kv.second.dev != nullptr) { (void)cudaFree(kv.second.dev); }
+    }
+    peer_plans_.clear();
 }
 
 // Registered (zero-copy on user memory) execution applies to real multi-GPU
@@ -587,6 +597,8 @@ const DeviceSession::GroupPlan &DeviceSession::plan_group(size_t n, const void *
     key.append(reinterpret_cast<const char *>(counts), sizeof(size_t) * n);
     key.append(reinterpret_cast<const char *>(&dt), sizeof(dt));
     key.append(reinterpret_cast<const char *>(&user_dt), sizeof(user_dt));
+    key.append(reinterpret_cast<const char *>(&pipeline_min_bytes_), sizeof(pipeline_min_bytes_));
+    key.append(reinterpret_cast<const char *>(&pipeline_chunk_bytes_), sizeof(pipeline_chunk_bytes_));
     auto it = plans_.find(key);
     if (it != plans_.end()) { return it->second; }
     if (plans_.size() >= 64) {  // bounded cache; cudaFree waits for work in flight
@@ -598,7 +610,17 @@ const DeviceSession::GroupPlan &DeviceSession::plan_group(size_t n, const void *
     const size_t es = elem_size(dt);                          // wire element
     const size_t ues = user_dt >= 0 ? elem_size(user_dt) : es;  // user element
     const size_t lanes = 16 / es;
-    const size_t cap = world_->staging_bytes() / 16;  // vectors per slot
+    size_t cap = world_->staging_bytes() / 16;  // vectors per slot
+    if (world_->world() > 1) {
+        // a set large enough for the three-stream pipeline is cut finer than a slot
+        // (about 1/8 of it per chunk), so that pack, reduce and unpack of
+        // neighbouring chunks overlap from early on
+        size_t total_vec = 0;
+        for (size_t i = 0; i < n; ++i) { total_vec += (counts[i] + lanes - 1) / lanes; }
+        if (total_vec * 16 >= pipeline_min_bytes_) {
+            cap = std::min(cap, std::max(pipeline_chunk_bytes_ / 16, (total_vec + 7) / 8));
+        }
+    }
 
     using Piece = GroupPiece;
     const std::vector<std::vector<Piece>> chunks = plan_group_pieces(n, counts, lanes, cap);
@@ -633,6 +655,95 @@ const DeviceSession::GroupPlan &DeviceSession::plan_group(size_t n, const void *
         plan.chunks.push_back(std::move(per_rank));
     }
     return plans_.emplace(std::move(key), std::move(plan)).first->second;
+}
+
+bool DeviceSession::group_registered(size_t n, const void *const *ins, void *const *outs,
+                                     const size_t *counts, int dt, int op, double scale,
+                                     void *stream)
+{
+    const int world = world_->world();
+    const int vr = world_->vranks();
+    const size_t es = elem_size(dt);
+    const size_t lanes = 16 / es;
+    // the key: this rank's pointers and sizes, and the allocations behind them (an
+    // allocation freed and made again at the same address has another id)
+    std::string key;
+    key.reserve((4 * vr * n + n + 1) * sizeof(void *));
+    key.append(reinterpret_cast<const char *>(ins), sizeof(void *) * n * vr);
+    key.append(reinterpret_cast<const char *>(outs), sizeof(void *) * n * vr);
+    key.append(reinterpret_cast<const char *>(counts), sizeof(size_t) * n);
+    key.append(reinterpret_cast<const char *>(&dt), sizeof(dt));
+    for (size_t k = 0; k < n * static_cast<size_t>(vr); ++k) {
+        const unsigned long long a = world_->buffer_id(ins[k]);
+        const unsigned long long b = outs[k] == ins[k] ? a : world_->buffer_id(outs[k]);
+        key.append(reinterpret_cast<const char *>(&a), sizeof(a));
+        key.append(reinterpret_cast<const char *>(&b), sizeof(b));
+    }
+    auto it = peer_plans_.find(key);
+    const bool reuse = world_->all_same(it != peer_plans_.end() ? it->second.stamp : 0ull);
+    if (!reuse) {
+        // some rank has a new set (or a new allocation under an old one): all build
+        if (it != peer_plans_.end()) {
+            if (it->second.dev != nullptr) { (void)cudaFree(it->second.dev); }
+            peer_plans_.erase(it);
+        }
+        if (peer_plans_.size() >= 64) { forget_peer_plans(); }  // bounded; cudaFree waits for work in flight
+        PeerPlan plan;
+        plan.stamp = ++peer_plan_builds_;
+        std::vector<size_t> bytes(n);
+        for (size_t i = 0; i < n; ++i) { bytes[i] = counts[i] * es; }
+        std::vector<void *> p_in(n * world), p_out(n * world);
+        bool same = true;
+        for (size_t k = 0; k < n * static_cast<size_t>(vr) && same; ++k) { same = ins[k] == outs[k]; }
+        // (a rank whose outputs are its inputs still joins both exchanges when another
+        // rank's are not: the number of exchanges must not depend on local facts)
+        same = world_->all_same(same ? 1ull : 2ull) && same;
+        bool ok = world_->resolve_many(n, ins, bytes.data(), p_in.data()) &&
+                  all_aligned16(p_in.data(), static_cast<int>(n) * world);
+        if (ok && !same) {
+            ok = world_->resolve_many(n, reinterpret_cast<const void *const *>(outs), bytes.data(),
+                                      p_out.data()) &&
+                 all_aligned16(p_out.data(), static_cast<int>(n) * world);
+        }
+        ok = world_->all_same(ok ? 1ull : 2ull) && ok;
+        if (ok) {
+            std::vector<PeerEntry> host(n);
+            size_t voff = 0;
+            for (size_t i = 0; i < n; ++i) {
+                std::memset(&host[i], 0, sizeof(PeerEntry));
+                for (int r = 0; r < world; ++r) {
+                    host[i].in[r] = static_cast<char *>(p_in[i * world + r]);
+                    host[i].out[r] = static_cast<char *>(same ? p_in[i * world + r] : p_out[i * world + r]);
+                }
+                host[i].voff = voff;
+                host[i].count = counts[i];
+                voff += (counts[i] + lanes - 1) / lanes;
+            }
+            // empty tensors would break the search for an entry by its first vector
+            host.erase(std::remove_if(host.begin(), host.end(),
+                                      [](const PeerEntry &e) { return e.count == 0; }),
+                       host.end());
+            plan.nvec = voff;
+            plan.n = static_cast<int>(host.size());
+            if (!host.empty()) {
+                void *dev = nullptr;
+                rt_check(cudaMalloc(&dev, host.size() * sizeof(PeerEntry)), "cudaMalloc(table)");
+                rt_check(cudaMemcpy(dev, host.data(), host.size() * sizeof(PeerEntry),
+                                    cudaMemcpyHostToDevice),
+                         "cudaMemcpy(table)");
+                plan.dev = static_cast<PeerEntry *>(dev);
+            } else {
+                return true;  // nothing to reduce
+            }
+        }
+        it = peer_plans_.emplace(std::move(key), plan).first;
+    }
+    const PeerPlan &plan = it->second;
+    if (plan.dev == nullptr) { return false; }
+    launch_check(world_->group_peer(plan.dev, plan.n, plan.nvec, dt, op, scale, stream),
+                 "group_all_reduce(registered)");
+    ++launches_;
+    return true;
 }
 
 void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *const *outs,
@@ -678,6 +789,16 @@ void DeviceSession::group_all_reduce(size_t n, const void *const *ins, void *con
         if (c.algo < 0) { c.algo = world_->pick_algo(total, dt, op, true); }
         launch_ar(c, stream);
         return;
+    }
+
+    if (user_dt < 0 && (algo < 0 || algo == kAlgoTwoShot)) {
+        size_t bytes = 0;
+        for (size_t i = 0; i < n; ++i) { bytes += counts[i] * es; }
+        // (a loopback world runs it too: there every "peer" pointer is a local one)
+        if (world_->world() > 1 && bytes >= register_min_bytes_ && !capturing(stream) &&
+            group_registered(n, ins, outs, counts, dt, op, scale, stream)) {
+            return;
+        }
     }
 
     const GroupPlan &plan = plan_group(n, ins, outs, counts, dt, user_dt);

@@ -54,6 +54,7 @@ struct Driver {
     decltype(&cuMulticastUnbind) MulticastUnbind = nullptr;
     decltype(&cuMulticastGetGranularity) MulticastGetGranularity = nullptr;
     decltype(&cuMemGetAddressRange) MemGetAddressRange = nullptr;
+    decltype(&cuPointerGetAttribute) PointerGetAttribute = nullptr;
     bool ok = false;
     bool multicast = false;
 
@@ -88,6 +89,7 @@ struct Driver {
                     load("cuMulticastUnbind", MulticastUnbind) &&
                     load("cuMulticastGetGranularity", MulticastGetGranularity);
         (void)load("cuMemGetAddressRange", MemGetAddressRange);
+        (void)load("cuPointerGetAttribute", PointerGetAttribute);
     }
 
     std::string err(CUresult r) const
@@ -179,6 +181,7 @@ class World final : public DeviceWorld
     int nvls_variant_ = kNvlsPipe4;        // STDML_COLLECTIVE_NVLS_VARIANT
     bool debug_checks_ = false;            // STDML_COLLECTIVE_DEBUG
     size_t bcast_pipelined_min_ = 8u << 20;  // STDML_COLLECTIVE_BCAST_PIPELINED_MIN_BYTES
+    size_t group_bulk_min_ = 4u << 20;       // registered groups: bulk copies from here (knob group_bulk_min_bytes)
     size_t bcast_piece_vec_ = 1024;          // vectors per round, block and slice (knob bcast_piece_vec)
     size_t gather_push_min_ = 64u << 10;  // STDML_COLLECTIVE_GATHER_PUSH_MIN_BYTES
     bool gather_mc_ = false;  // STDML_COLLECTIVE_GATHER_MC: all_gather through the switch (measured
@@ -396,6 +399,8 @@ class World final : public DeviceWorld
             tma_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "tma_over_nvls_min_bytes") {
             tma_over_nvls_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
+        } else if (name == "group_bulk_min_bytes") {
+            group_bulk_min_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         } else if (name == "bcast_piece_vec") {
             bcast_piece_vec_ = static_cast<size_t>(std::max<long long>(32, value));
         } else if (name == "bcast_pipelined_min_bytes") {
@@ -425,105 +430,161 @@ class World final : public DeviceWorld
         cudaIpcMemHandle_t handle;
     };
 
-    bool resolve_peers(const void *const *ptrs, size_t bytes, void **peer_ptrs) override
+    // What this rank tells the others about one of its buffers.
+    RegRecord make_record(void *mine, size_t bytes)
     {
-        for (int r = 0; r < opt_.world; ++r) { peer_ptrs[r] = nullptr; }
-        if (opt_.loopback) {
-            for (int v = 0; v < vranks_; ++v) { peer_ptrs[v] = const_cast<void *>(ptrs[v]); }
-            return true;
-        }
-        void *mine = const_cast<void *>(ptrs[0]);
-        if (opt_.world == 1) {
-            peer_ptrs[0] = mine;
-            return true;
-        }
         RegRecord rec;
         std::memset(&rec, 0, sizeof(rec));
         rec.ok = 1;
-        if (mine != nullptr) {
-            rec.ok = 0;
-            Driver &d = driver();
-            CUdeviceptr base = 0;
-            size_t size = 0;
-            if (d.MemGetAddressRange != nullptr &&
-                d.MemGetAddressRange(&base, &size, reinterpret_cast<CUdeviceptr>(mine)) ==
-                    CUDA_SUCCESS &&
-                reinterpret_cast<uintptr_t>(mine) + bytes <= static_cast<uintptr_t>(base) + size) {
-                // The handle is asked for on every call: an allocation that was freed and
-                // made again at the same address and size has another handle, and only
-                // a fresh look tells (the driver call costs microseconds).
-                auto it = exported_.find(static_cast<uintptr_t>(base));
-                cudaIpcMemHandle_t now;
-                if (cudaIpcGetMemHandle(&now, reinterpret_cast<void *>(base)) == cudaSuccess) {
-                    if (it == exported_.end() || it->second.size != size ||
-                        std::memcmp(&it->second.handle, &now, sizeof(now)) != 0) {
-                        Exported e;
-                        e.handle = now;
-                        e.size = size;
-                        exported_[static_cast<uintptr_t>(base)] = e;  // not announced yet
-                        it = exported_.find(static_cast<uintptr_t>(base));
-                    }
-                } else {
-                    (void)cudaGetLastError();  // e.g. memory from the VMM allocator
-                    if (it != exported_.end()) { exported_.erase(it); }
-                    it = exported_.end();
+        if (mine == nullptr) { return rec; }
+        rec.ok = 0;
+        Driver &d = driver();
+        CUdeviceptr base = 0;
+        size_t size = 0;
+        if (d.MemGetAddressRange != nullptr &&
+            d.MemGetAddressRange(&base, &size, reinterpret_cast<CUdeviceptr>(mine)) ==
+                CUDA_SUCCESS &&
+            reinterpret_cast<uintptr_t>(mine) + bytes <= static_cast<uintptr_t>(base) + size) {
+            // The handle is asked for on every call: an allocation that was freed and
+            // made again at the same address and size has another handle, and only
+            // a fresh look tells (the driver call costs microseconds).
+            auto it = exported_.find(static_cast<uintptr_t>(base));
+            cudaIpcMemHandle_t now;
+            if (cudaIpcGetMemHandle(&now, reinterpret_cast<void *>(base)) == cudaSuccess) {
+                if (it == exported_.end() || it->second.size != size ||
+                    std::memcmp(&it->second.handle, &now, sizeof(now)) != 0) {
+                    Exported e;
+                    e.handle = now;
+                    e.size = size;
+                    exported_[static_cast<uintptr_t>(base)] = e;  // not announced yet
+                    it = exported_.find(static_cast<uintptr_t>(base));
                 }
-                if (it != exported_.end()) {
-                    rec.ok = 1;
-                    rec.fresh = it->second.announced ? 0 : 1;
-                    rec.base = static_cast<unsigned long long>(base);
-                    rec.size = size;
-                    rec.offset = reinterpret_cast<uintptr_t>(mine) - static_cast<uintptr_t>(base);
-                    rec.handle = it->second.handle;
-                }
+            } else {
+                (void)cudaGetLastError();  // e.g. memory from the VMM allocator
+                if (it != exported_.end()) { exported_.erase(it); }
+                it = exported_.end();
+            }
+            if (it != exported_.end()) {
+                rec.ok = 1;
+                rec.fresh = it->second.announced ? 0 : 1;
+                rec.base = static_cast<unsigned long long>(base);
+                rec.size = size;
+                rec.offset = reinterpret_cast<uintptr_t>(mine) - static_cast<uintptr_t>(base);
+                rec.handle = it->second.handle;
             }
         }
+        return rec;
+    }
+
+    // Rank r's buffer as mapped here (null: that rank passed none, or the import failed,
+    // which clears *imported_all).
+    void *import_record(int r, const RegRecord &pr, bool *imported_all)
+    {
+        if (pr.base == 0) { return nullptr; }
+        auto &table = imported_[r];
+        auto it = table.find(static_cast<uintptr_t>(pr.base));
+        if (it != table.end() &&
+            (it->second.size != pr.size ||
+             std::memcmp(&it->second.handle, &pr.handle, sizeof(pr.handle)) != 0)) {
+            (void)cudaIpcCloseMemHandle(it->second.mapped);  // a new allocation at that address
+            table.erase(it);
+            it = table.end();
+        }
+        if (it == table.end()) {
+            Imported im;
+            im.handle = pr.handle;
+            im.size = pr.size;
+            if (cudaIpcOpenMemHandle(&im.mapped, pr.handle, cudaIpcMemLazyEnablePeerAccess) !=
+                cudaSuccess) {
+                (void)cudaGetLastError();
+                *imported_all = false;
+                return nullptr;
+            }
+            it = table.emplace(static_cast<uintptr_t>(pr.base), im).first;
+        }
+        return static_cast<char *>(it->second.mapped) + pr.offset;
+    }
+
+    bool resolve_peers(const void *const *ptrs, size_t bytes, void **peer_ptrs) override
+    {
+        return resolve_many(1, ptrs, &bytes, peer_ptrs);
+    }
+
+    bool resolve_many(size_t n, const void *const *ptrs, const size_t *bytes,
+                      void **peer_ptrs) override
+    {
+        const int world = opt_.world;
+        for (size_t k = 0; k < n * static_cast<size_t>(world); ++k) { peer_ptrs[k] = nullptr; }
+        if (opt_.loopback) {
+            for (size_t i = 0; i < n; ++i) {
+                for (int v = 0; v < vranks_; ++v) {
+                    peer_ptrs[i * world + v] = const_cast<void *>(ptrs[v * n + i]);
+                }
+            }
+            return true;
+        }
+        if (world == 1) {
+            for (size_t i = 0; i < n; ++i) { peer_ptrs[i] = const_cast<void *>(ptrs[i]); }
+            return true;
+        }
+        std::vector<RegRecord> mine(n);
+        for (size_t i = 0; i < n; ++i) { mine[i] = make_record(const_cast<void *>(ptrs[i]), bytes[i]); }
         std::vector<std::vector<char>> all;
-        rdv_->all_gather(&rec, sizeof(rec), all);
+        rdv_->all_gather(mine.data(), n * sizeof(RegRecord), all);
         bool everyone = true, any_fresh = false;
-        std::vector<RegRecord> recs(opt_.world);
-        for (int r = 0; r < opt_.world; ++r) {
-            std::memcpy(&recs[r], all[r].data(), sizeof(RegRecord));
-            everyone = everyone && recs[r].ok != 0;
-            any_fresh = any_fresh || recs[r].fresh != 0;
+        for (int r = 0; r < world && everyone; ++r) {
+            everyone = all[r].size() == n * sizeof(RegRecord);  // the same set on every rank
         }
         if (!everyone) { return false; }
-        if (mine != nullptr) { exported_[static_cast<uintptr_t>(rec.base)].announced = true; }
-        imported_.resize(opt_.world);
+        std::vector<RegRecord> recs(n * static_cast<size_t>(world));
+        for (int r = 0; r < world; ++r) {
+            for (size_t i = 0; i < n; ++i) {
+                RegRecord &pr = recs[i * world + r];
+                std::memcpy(&pr, all[r].data() + i * sizeof(RegRecord), sizeof(RegRecord));
+                everyone = everyone && pr.ok != 0;
+                any_fresh = any_fresh || pr.fresh != 0;
+            }
+        }
+        if (!everyone) { return false; }
+        for (size_t i = 0; i < n; ++i) {
+            if (ptrs[i] != nullptr) { exported_[static_cast<uintptr_t>(mine[i].base)].announced = true; }
+        }
+        imported_.resize(world);
         bool imported_all = true;
-        for (int r = 0; r < opt_.world; ++r) {
-            if (r == opt_.rank) {
-                peer_ptrs[r] = mine;
-                continue;
+        for (size_t i = 0; i < n; ++i) {
+            for (int r = 0; r < world; ++r) {
+                peer_ptrs[i * world + r] =
+                    r == opt_.rank ? const_cast<void *>(ptrs[i])
+                                   : import_record(r, recs[i * world + r], &imported_all);
             }
-            const RegRecord &pr = recs[r];
-            if (pr.base == 0) { continue; }  // that rank passed no buffer
-            auto &table = imported_[r];
-            auto it = table.find(static_cast<uintptr_t>(pr.base));
-            if (it != table.end() &&
-                (it->second.size != pr.size ||
-                 std::memcmp(&it->second.handle, &pr.handle, sizeof(pr.handle)) != 0)) {
-                (void)cudaIpcCloseMemHandle(it->second.mapped);  // a new allocation at that address
-                table.erase(it);
-                it = table.end();
-            }
-            if (it == table.end()) {
-                Imported im;
-                im.handle = pr.handle;
-                im.size = pr.size;
-                if (cudaIpcOpenMemHandle(&im.mapped, pr.handle, cudaIpcMemLazyEnablePeerAccess) !=
-                    cudaSuccess) {
-                    (void)cudaGetLastError();
-                    imported_all = false;
-                    continue;
-                }
-                it = table.emplace(static_cast<uintptr_t>(pr.base), im).first;
-            }
-            peer_ptrs[r] = static_cast<char *>(it->second.mapped) + pr.offset;
         }
         // every handle was seen before: every import above came from the tables
         if (any_fresh || !imported_all) { imported_all = rdv_->all_agree(imported_all); }
         return imported_all;
+    }
+
+    bool all_same(unsigned long long token) override
+    {
+        if (opt_.loopback || opt_.world == 1) { return token != 0; }
+        std::vector<std::vector<char>> all;
+        rdv_->all_gather(&token, sizeof(token), all);
+        bool same = token != 0;
+        for (const auto &x : all) {
+            same = same && x.size() == sizeof(token) && std::memcmp(x.data(), &token, sizeof(token)) == 0;
+        }
+        return same;
+    }
+
+    unsigned long long buffer_id(const void *p) const override
+    {
+        Driver &d = driver();
+        unsigned long long id = 0;
+        if (p == nullptr || d.PointerGetAttribute == nullptr ||
+            d.PointerGetAttribute(&id, CU_POINTER_ATTRIBUTE_BUFFER_ID,
+                                  reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS) {
+            return 0;
+        }
+        return id;
     }
 
     void drop_registrations() override
@@ -821,13 +882,40 @@ class World final : public DeviceWorld
         if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
         if (a.algo == kBcastPipelined) {
             // about 16 KB per piece: long enough to fill the links, short enough that
-            // the holders start forwarding early
+            // the holders start forwarding early; at most 9 rounds (8 GPUs, 256 MB:
+            // 9 rounds 454 us, 18 rounds 501 us, 4 rounds 497 us)
             const size_t per_block_slice = nvec / static_cast<size_t>(opt_.world - 1) /
                                            static_cast<size_t>(std::max(1, blocks));
             a.rounds = static_cast<int>(std::max<size_t>(
-                1, std::min<size_t>(32, per_block_slice / std::max<size_t>(32, bcast_piece_vec_))));
+                1, std::min<size_t>(9, per_block_slice / std::max<size_t>(32, bcast_piece_vec_))));
         }
         return launch_gather(make_ctx(), a, blocks, vranks_, stream);
+    }
+
+    int group_peer(const PeerEntry *table, int ntable, size_t nvec, int dt, int op, double scale,
+                   void *stream) override
+    {
+        if (dt < 0 || dt > DT_F64_) { throw std::invalid_argument("group_peer: bad dtype"); }
+        if (table == nullptr || ntable <= 0 || nvec == 0) { return 0; }
+        GroupPeerArgs a;
+        std::memset(&a, 0, sizeof(a));
+        a.table = table;
+        a.ntable = ntable;
+        a.nvec = nvec;
+        a.has_scale = scale != 1.0 ? 1 : 0;
+        a.scale = scale;
+        // bulk copies from 4 MB up (where the single-buffer sweep shows them ahead
+        // of plain peer loads), unless the knob says otherwise
+        const bool bulk = group_bulk_min_ != SIZE_MAX && nvec * 16 >= group_bulk_min_;
+        int blocks = pick_blocks(nvec, bulk ? kAlgoTwoShotTma : kAlgoTwoShot);
+        if (bulk) {
+            unsigned int smem = 0;
+            tma_geometry(opt_.world, tma_tile_vec_, &a.tma_stages, &a.tma_tile_vec, &smem);
+            blocks = std::min(blocks, num_sms_);
+        }
+        if (vranks_ > 1) { blocks = std::min(blocks, std::max(1, num_sms_ / vranks_)); }
+        blocks = std::min(blocks, kMaxBlocks);
+        return launch_group_peer(make_ctx(), a, dt, op, blocks, vranks_, stream);
     }
 
     int unpack_blocks(const void *region, void *dst, size_t bytes, size_t sym_stride,

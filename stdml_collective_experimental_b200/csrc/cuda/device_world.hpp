@@ -130,6 +130,16 @@ class DeviceWorld
     // before.  Returns false, on every rank alike, when some rank cannot export
     // (memory that did not come from cudaMalloc) or import; callers then stage.
     virtual bool resolve_peers(const void *const *ptrs, size_t bytes, void **peer_ptrs) = 0;
+    // The same for n buffers with ONE exchange: ptrs[v * n + i] is buffer i of
+    // (virtual) rank v, peer_ptrs[i * world + r] buffer i of rank r as mapped here.
+    virtual bool resolve_many(size_t n, const void *const *ptrs, const size_t *bytes,
+                              void **peer_ptrs) = 0;
+    // Collective: true when every rank passed the same non-zero token (8 bytes
+    // over the local rendezvous; how cached plans are confirmed before reuse).
+    virtual bool all_same(unsigned long long token) = 0;
+    // A number that identifies the allocation behind `p` and is never used twice
+    // in a process (0: not a device allocation the driver knows).
+    virtual unsigned long long buffer_id(const void *p) const = 0;
     // Collective: unmaps every peer buffer imported so far.
     virtual void drop_registrations() = 0;
     virtual size_t registrations() const = 0;  // peer allocations mapped now
@@ -148,6 +158,9 @@ class DeviceWorld
     // arguments that the kernels could not run.
     virtual int all_reduce(const AllReduceCall &c, void *stream) = 0;
     virtual int gather(const GatherCall &c, void *stream) = 0;
+    // Two-shot all-reduce over a table of registered tensors (see PeerEntry).
+    virtual int group_peer(const PeerEntry *table, int ntable, size_t nvec, int dt, int op,
+                           double scale, void *stream) = 0;
     // Local copy of `blocks_n` gathered blocks out of a region into user memory.
     virtual int unpack_blocks(const void *region, void *dst, size_t bytes, size_t sym_stride,
                               size_t stride, int blocks_n, void *stream, int grid = 0) = 0;

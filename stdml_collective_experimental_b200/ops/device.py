@@ -180,7 +180,9 @@ class DeviceSession:
         """Named tuning knob, same value on every rank: nvls_variant (0..3),
         nvls_blocks, tma_blocks, tma_tile_vec, tma_min_bytes,
         tma_over_nvls_min_bytes (negative: never), gather_push_min_bytes, gather_mc,
-        pipeline_min_bytes, debug_checks, and register_min_bytes: collectives on
+        pipeline_min_bytes, debug_checks, group_bulk_min_bytes (registered groups of
+        at least that many bytes load their operands with bulk asynchronous copies;
+        negative: never), and register_min_bytes: collectives on
         ordinary CUDA tensors of at least that many bytes map the tensors'
         allocations on every peer (CUDA IPC, cached per allocation) and run
         zero-copy on them; negative: never (the default).  Tensors used that way

@@ -207,7 +207,43 @@ def main():
                 sess.check()
                 assert sess.launches == before + 1
                 assert bits_equal(g_out.cpu(), torch.cat(host)), ("registered all_gather", dtype, n)
+    # a set of separately allocated tensors: one launch on the tensors themselves, the
+    # table of peer pointers kept between calls and rebuilt when one rank's tensors move
+    sizes = [3, 1000, 7, 250_001, 64, 1_000_003, 1]
+    for dtype in (torch.float32, torch.bfloat16):
+        host = [[inputs(1, n, dtype, seed=100 * r + i)[0] for i, n in enumerate(sizes)]
+                for r in range(world)]
+        want = [reduce_many([host[r][i] for r in range(world)], "sum", 0.5)
+                for i in range(len(sizes))]
+        keep = []
+        for step in range(5):
+            # (step 4: 16-byte peer loads instead of bulk copies into shared memory)
+            sess.set_knob("group_bulk_min_bytes", -1 if step == 4 else 0)
+            if step < 2 or rank == step % world:  # steps 2 and 3: one rank has new tensors
+                dev = [t.cuda() for t in host[rank]]
+                keep.append(dev)  # (earlier sets stay allocated: peers may still map them)
+            else:
+                for t, h in zip(dev, host[rank]):
+                    t.copy_(h)
+            before = sess.launches
+            sess.group_all_reduce(dev, scale=0.5)
+            torch.cuda.synchronize()
+            sess.check()
+            assert sess.launches == before + 1, "registered group: one launch"
+            for i in range(len(sizes)):
+                assert bits_equal(dev[i].cpu(), want[i]), ("registered group", dtype, step, i)
+        outs = [torch.full((n + 8,), 3, dtype=dtype, device="cuda") for n in sizes]
+        for t, h in zip(dev, host[rank]):
+            t.copy_(h)
+        sess.group_all_reduce(dev, outs=[o[:n] for o, n in zip(outs, sizes)], scale=0.5)
+        torch.cuda.synchronize()
+        sess.check()
+        for i, n in enumerate(sizes):
+            assert bits_equal(outs[i][:n].cpu(), want[i]) and torch.all(outs[i][n:] == 3)
+            assert bits_equal(dev[i].cpu(), host[rank][i])
+    sess.set_knob("group_bulk_min_bytes", 4 << 20)
     sess.drop_registrations()
+    del keep
     sess.set_knob("register_min_bytes", -1)
     x = torch.ones(1000, device="cuda")
     sess.all_reduce(x)  # staged again

@@ -255,6 +255,73 @@ def test_group_all_reduce_fused(sess, dtype):
     sess.check()
 
 
+@pytest.mark.parametrize("bulk", [False, True])
+@pytest.mark.parametrize("dtype,op,scale", [
+    (torch.float32, "sum", 0.125), (torch.bfloat16, "sum", None), (torch.int32, "max", None),
+    (torch.float64, "prod", 1.0 / 3.0), (torch.int8, "bit_xor", None), (torch.float16, "min", None),
+])
+def test_group_all_reduce_on_registered_loose_tensors(sess, dtype, op, scale, bulk):
+    """Separately allocated tensors, reduced where they lie: one launch, no staging.
+    `bulk`: operands come in by bulk asynchronous copies into a shared-memory ring
+    (the default from 4 MB up), else by 16-byte peer loads."""
+    if sess.world == 1:
+        pytest.skip("needs peers")
+    sess.set_knob("group_bulk_min_bytes", 0 if bulk else -1)
+    sizes = [1, 7, 768, 3, 2304, 590_000, 5, 64, 1000, 123_457, 2, 768]
+    host = [[make_inputs(1, n, dtype, seed=31 * r + i, small=op == "prod")[0]
+             for i, n in enumerate(sizes)] for r in range(sess.world)]
+    want = [reduce_many([host[r][i] for r in range(sess.world)], op, scale)
+            for i in range(len(sizes))]
+    sess.set_knob("register_min_bytes", 0)
+    try:
+        # in place, twice (the second call reuses the table of peer pointers)
+        for _ in range(2):
+            dev = [[t.cuda() for t in host[r]] for r in range(sess.world)]
+            before = sess.launches
+            sess.group_all_reduce(dev if sess.vranks > 1 else dev[0], op=op, scale=scale)
+            torch.cuda.synchronize()
+            sess.check()
+            assert sess.launches == before + 1
+            for r in range(sess.world):
+                for i in range(len(sizes)):
+                    assert same(dev[r][i].cpu(), want[i]), (r, i)
+        # out of place: inputs stay, outputs carry the result and nothing beyond their end
+        dev = [[t.cuda() for t in host[r]] for r in range(sess.world)]
+        pad = 16
+        outs = [[torch.full((n + pad,), 3, dtype=dtype, device="cuda") for n in sizes]
+                for _ in range(sess.world)]
+        views = [[o[:n] for o, n in zip(outs[r], sizes)] for r in range(sess.world)]
+        before = sess.launches
+        sess.group_all_reduce(dev if sess.vranks > 1 else dev[0],
+                              outs=views if sess.vranks > 1 else views[0], op=op, scale=scale)
+        torch.cuda.synchronize()
+        sess.check()
+        assert sess.launches == before + 1
+        for r in range(sess.world):
+            for i, n in enumerate(sizes):
+                assert same(views[r][i].cpu(), want[i]), (r, i)
+                assert bool((outs[r][i][n:] == 3).all()), "wrote past the end of a tensor"
+                assert torch.equal(dev[r][i].cpu(), host[r][i]), "inputs must stay untouched"
+        # a tensor that does not start on a 16-byte boundary sends the set the staged way
+        dev = [[t.cuda() for t in host[r]] for r in range(sess.world)]
+        for r in range(sess.world):
+            odd = torch.empty(sizes[5] + 1, dtype=dtype, device="cuda")[1:]
+            if odd.data_ptr() % 16 != 0:
+                odd.copy_(host[r][5])
+                dev[r][5] = odd
+        before = sess.launches
+        sess.group_all_reduce(dev if sess.vranks > 1 else dev[0], op=op, scale=scale)
+        torch.cuda.synchronize()
+        sess.check()
+        assert sess.launches > before
+        for r in range(sess.world):
+            for i in range(len(sizes)):
+                assert same(dev[r][i].cpu(), want[i]), (r, i)
+    finally:
+        sess.set_knob("register_min_bytes", -1)
+        sess.set_knob("group_bulk_min_bytes", 4 << 20)
+
+
 def test_group_all_reduce_bf16_wire_for_f32_grads(sess):
     sizes = [5, 4096, 33, 100_000]
     g = torch.Generator().manual_seed(2)
