@@ -154,7 +154,7 @@ class DeviceSession
                                     // 8 GPUs, 64 MB per rank: 128 / 96 gave 850 us where 64 / 0 gave 956)
     int chunk_unpack_blocks_ = 96;   // grid of that unpack (0: as many as the copy wants) (knob)
     bool registered_path(size_t bytes, void *stream) const;
-    size_t pipeline_min_bytes_ = 128u << 20;   // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
+    size_t pipeline_min_bytes_ = 256u << 20;   // STDML_COLLECTIVE_PIPELINE_MIN_BYTES
     size_t pipeline_chunk_bytes_ = 32u << 20;  // STDML_COLLECTIVE_PIPELINE_CHUNK_BYTES (smallest chunk)
     // pipeline resources (created on first use)
     void *pack_stream_ = nullptr;
