@@ -24,20 +24,30 @@ def staged_group(args, sess, dtype, es):
     ranks = [[torch.full((s,), float(r + 1), dtype=dtype, device="cuda") for s in sizes]
              for r in range(args.world)]
     arg = ranks if args.world > 1 else ranks[0]
+    if args.registered:
+        # reduced where they lie (group_peer_kernel): no pack, no unpack
+        sess.set_knob("register_min_bytes", 0)
+        if args.bulk_min_bytes is not None:
+            sess.set_knob("group_bulk_min_bytes", args.bulk_min_bytes)
     torch.cuda.synchronize()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(args.iters + 1)]
     e[0].record()
     for i in range(args.iters):
-        sess.group_all_reduce(arg, scale=1.0 / args.world, algo=args.algo)
+        sess.group_all_reduce(arg, scale=1.0 / args.world,
+                              algo=None if args.registered else args.algo)
         e[i + 1].record()
     torch.cuda.synchronize()
     sess.check()
     times = [e[i].elapsed_time(e[i + 1]) for i in range(args.iters)]
     nbytes = sum(sizes) * es
-    # per rank: pack (read + write), reduce (read world, write world, amortised: read + write), unpack (read + write)
-    hbm = 6 * args.world * nbytes
+    # per rank: pack (read + write), reduce (read world, write world, amortised: read + write), unpack (read + write);
+    # registered: the reduce alone
+    hbm = (2 if args.registered else 6) * args.world * nbytes
     best = min(times[1:]) if len(times) > 1 else times[0]
-    print(json.dumps({"world": args.world, "tensors": k, "set_mb": nbytes / 2**20, "algo": args.algo,
+    want = sum(range(1, args.world + 1)) / args.world
+    assert args.iters > 1 or all(abs(float(t[-1]) - want) < 1e-3 for t in ranks[0]), "wrong result"
+    print(json.dumps({"world": args.world, "tensors": k, "set_mb": nbytes / 2**20,
+                      "algo": "registered" if args.registered else args.algo,
                       "ms_per_call": times, "best_ms": best, "hbm_bytes_per_call": hbm,
                       "achieved_gb_s": hbm / (best * 1e-3) / 1e9}))
     sess.close()
@@ -88,6 +98,10 @@ def main():
     ap.add_argument("--staged-group", type=int, default=0,
                     help="N > 0: reduce N separately allocated tensors per rank (pack + reduce + "
                          "unpack through a descriptor table) instead of one symmetric buffer")
+    ap.add_argument("--registered", action="store_true",
+                    help="with --staged-group: register the tensors instead of staging them")
+    ap.add_argument("--bulk-min-bytes", type=int, default=None,
+                    help="with --registered: the group_bulk_min_bytes knob (-1: peer loads only)")
     args = ap.parse_args()
     dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
     es = 4 if args.dtype == "f32" else 2
