@@ -228,6 +228,7 @@ class World final : public DeviceWorld
         };
         env_bytes("STDML_COLLECTIVE_TMA_MIN_BYTES", tma_min_);
         env_bytes("STDML_COLLECTIVE_TMA_OVER_NVLS_MIN_BYTES", tma_over_nvls_min_);
+        env_bytes("STDML_COLLECTIVE_GROUP_BULK_MIN_BYTES", group_bulk_min_);
         if (const char *e = std::getenv("STDML_COLLECTIVE_NVLS_BLOCKS")) { nvls_blocks_ = std::atoi(e); }
         if (const char *e = std::getenv("STDML_COLLECTIVE_TMA_BLOCKS")) { tma_blocks_ = std::atoi(e); }
         if (const char *e = std::getenv("STDML_COLLECTIVE_TMA_TILE_VEC")) {

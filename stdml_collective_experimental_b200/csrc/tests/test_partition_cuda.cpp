@@ -4,10 +4,12 @@
 // that holds a vector.  compute-sanitizer is not available for the device
 // code, so the arithmetic that decides every address is exercised here.
 #include <cstdio>
+#include <cstring>
 #include <random>
 #include <vector>
 
 #include "../cuda/ar_kernel.cuh"
+#include "../cuda/group_walk.cuh"
 #include "../cuda/device_session.hpp"
 #include "../cuda/algo_table.hpp"
 #include "../cuda/offset_heap.hpp"
@@ -49,6 +51,54 @@ int main()
             EXPECT(len_max - len_min <= 2 * kSpanGranule);
         }
         EXPECT(expect == nvec);
+    }
+    // registered groups: over all ranks and blocks, the tiles of the walk cover every whole
+    // vector of every tensor exactly once, in order, never across a tensor boundary and
+    // never longer than a tile; the ragged last vectors are left to the element-wise tail
+    for (int trial = 0; trial < 600; ++trial) {
+        constexpr unsigned long long N = 4;  // f32 lanes
+        const int n = 1 + static_cast<int>(rng() % 120);
+        std::vector<PeerEntry> tab;
+        unsigned long long voff = 0;
+        for (int i = 0; i < n; ++i) {
+            PeerEntry e;
+            std::memset(&e, 0, sizeof(e));
+            e.voff = voff;
+            e.count = 1 + rng() % (i % 7 == 0 ? 300000 : 900);  // (empty tensors never enter a table)
+            voff += (e.count + N - 1) / N;
+            tab.push_back(e);
+        }
+        GroupPeerArgs a;
+        std::memset(&a, 0, sizeof(a));
+        a.table = tab.data();
+        a.ntable = n;
+        a.nvec = voff;
+        const int world = 1 + static_cast<int>(rng() % 8);
+        const int nb = 1 + static_cast<int>(rng() % 40);
+        const unsigned int tile_vec = 32u << (rng() % 6);
+        std::vector<unsigned long long> next(n, 0);  // first vector of each tensor not covered yet
+        for (int r = 0; r < world; ++r) {
+            for (int b = 0; b < nb; ++b) {
+                const Span sp = span_of(a.nvec, world, r, nb, b);
+                if (sp.lo >= sp.hi) { continue; }
+                TileCursor c;
+                c.i = find_peer_entry(a.table, a.ntable, sp.lo);
+                c.v = c.end = 0;
+                EXPECT(tab[c.i].voff <= sp.lo);
+                if (!cursor_enter<N>(a, sp, &c)) { continue; }
+                Tile t;
+                while (cursor_next<N>(a, sp, &c, tile_vec, &t)) {
+                    const int i = static_cast<int>(t.e - tab.data());
+                    EXPECT(i >= 0 && i < n);
+                    EXPECT(t.nv >= 1 && t.nv <= tile_vec);
+                    EXPECT(t.v0 == next[i]);                         // in order, no gap, no overlap
+                    EXPECT(t.v0 + t.nv <= tab[i].count / N);         // whole vectors of this tensor only
+                    EXPECT(tab[i].voff + t.v0 >= sp.lo && tab[i].voff + t.v0 + t.nv <= sp.hi);
+                    next[i] = t.v0 + t.nv;
+                }
+            }
+        }
+        for (int i = 0; i < n; ++i) { EXPECT(next[i] == tab[i].count / N); }
     }
     // descriptor tables: the entry found for v really contains v (or is the
     // last one starting at or before v when v falls into padding-free gaps)
