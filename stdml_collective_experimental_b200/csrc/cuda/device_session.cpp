@@ -328,7 +328,7 @@ void DeviceSession::all_reduce(const void *const *in, void *const *out, size_t c
             c.count = count;
             c.algo = algo >= 0 ? algo : world_->pick_algo(count * es, dt, op, true);
             if (c.algo == kAlgoNvls) {  // the multicast mapping covers the arena only
-                c.algo = count * es >= (64u << 20) ? kAlgoTwoShotTma : kAlgoTwoShot;
+                c.algo = world_->pick_peer_algo(count * es);
             }
             launch_ar(c, stream);
             return;
@@ -507,7 +507,7 @@ void DeviceSession::reduce(const void *const *in, void *const *out, size_t count
             k.peer_data = p_in;
             k.peer_push = p_out;
             k.count = count;
-            k.algo = count * es >= (64u << 20) ? kAlgoTwoShotTma : kAlgoTwoShot;
+            k.algo = world_->pick_peer_algo(count * es);
             launch_ar(k, stream);
             return;
         }

@@ -637,6 +637,11 @@ class World final : public DeviceWorld
         return select_algo(tuning(), bytes, nvls_supported(dt, op), need_owner);
     }
 
+    int pick_peer_algo(size_t bytes) const override
+    {
+        return select_algo(tuning(), bytes, false, true);
+    }
+
     int pick_blocks(size_t nvec, int algo) const override
     {
         return select_blocks(tuning(), nvec, algo);

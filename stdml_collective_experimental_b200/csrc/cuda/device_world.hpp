@@ -152,6 +152,8 @@ class DeviceWorld
     virtual size_t next_staging_slot() = 0;
 
     virtual int pick_algo(size_t bytes, int dt, int op, bool need_owner) const = 0;
+    // The owner algorithm for buffers outside the arena (no in-switch reduction there).
+    virtual int pick_peer_algo(size_t bytes) const = 0;
     virtual int pick_blocks(size_t nvec, int algo) const = 0;
 
     // Launches.  Return 0 or a cudaError_t; throw std::invalid_argument on
