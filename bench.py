@@ -386,8 +386,20 @@ def loopback_kernel_block(args, sizes, steps, warmup, world=8):
                 "kernel": "owner_kernel (bulk-copy two-shot), one cooperative launch per step"}
 
 
+def keep_stdout_for_the_result():
+    """Libraries write to file descriptor 1 on their own (NCCL prints its version there when
+    NCCL_DEBUG is set in the environment).  The contract is ONE JSON line on stdout, so
+    everything else that this process or its children write to fd 1 goes to stderr, and
+    only print() reaches the real stdout."""
+    sys.stdout.flush()
+    real = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real, "w", buffering=1)
+
+
 def main():
     args = parse_args()
+    keep_stdout_for_the_result()
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
