@@ -24,6 +24,7 @@ import torch
 
 from ..models.gradsets import gradset_sizes
 from ..parallel import Peer
+from ..parallel.peer import standby_wait
 
 
 def main():
@@ -40,6 +41,8 @@ def main():
         schedule[int(k)] = int(v)
 
     use_cuda = args.device == "cuda"
+    # a warm standby (launcher option -spares) learns here which worker, and so which GPU, it is
+    standby_wait()
     if use_cuda:
         dev_id = int(os.environ.get("STDML_COLLECTIVE_DEVICE_ID", os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(dev_id % torch.cuda.device_count())

@@ -17,7 +17,7 @@ int main(int argc, char *argv[])
     if (!stdml::collective::parse_runner_args(argc, argv, opt, error)) {
         std::fprintf(stderr, "%s: %s\nusage: %s -np N [-strategy STAR|RING] [-w] "
                              "[-builtin-config-port P] [-config-server URL] [-logdir DIR] [-q] "
-                             "[-runner-port P] [-port-range P] [-env K=V] "
+                             "[-runner-port P] [-port-range P] [-env K=V] [-spares N] "
                              "[-H ip:slots,ip:slots -self ip] prog [args...]\n",
                      argv[0], error.c_str(), argv[0]);
         return 2;

@@ -6,6 +6,7 @@
 #include <functional>
 #include <memory>
 #include <optional>
+#include <string>
 
 #include <stdml/bits/collective/address.hpp>
 #include <stdml/bits/collective/config.hpp>
@@ -16,6 +17,13 @@
 
 namespace stdml::collective
 {
+// Warm standby hand-over (launcher option -spares): when this process was started
+// without an identity, waits for the launcher to provide one, exports it into
+// the environment and returns it as "NAME=VALUE\n" lines; returns "" at once in
+// every other process.  peer::from_env() calls it first; programs that read the
+// environment themselves before that (a device index, say) call it earlier.
+std::string standby_wait();
+
 class peer
 {
     system_config config_;

@@ -38,6 +38,11 @@ struct runner_options {
     std::string config_server_url;   // external config server instead
     std::string logdir;              // per-worker <ip>.<port>.{stdout,stderr}.log
     bool quiet = false;
+    // Elastic growth without the start-up cost of a worker: keep this many warm
+    // standby processes (the same program, run up to its peer::from_env(), where
+    // it waits for an identity on a pipe from this launcher).  A worker that joins
+    // is then a standby that is told who it is, not a fresh process.
+    size_t spares = 0;
     std::vector<std::string> command;  // program and arguments
     std::vector<std::pair<std::string, std::string>> extra_env;
 };
@@ -66,13 +71,26 @@ class runner
     size_t version_ = 0;
     std::mutex mu_;
     std::map<uint64_t, int> pids_;  // worker hash -> pid
+    struct standby {
+        int pid;
+        int fd;  // write end of its identity pipe
+    };
+    std::vector<standby> standbys_;
     int failed_ = 0;
     std::unique_ptr<http_server> http_;
     std::unique_ptr<rchan::conn_handler> handler_;
     std::unique_ptr<rchan::server> server_;
     std::string stored_config_;  // what the config server returns
 
+    // the environment contract of one worker (what peer::from_env() reads)
+    std::vector<std::pair<std::string, std::string>> identity(const peer_id &worker,
+                                                              const cluster_config &cluster,
+                                                              size_t version) const;
     void spawn(const peer_id &worker, const cluster_config &cluster, size_t version);
+    void spawn_standby();
+    // true: a standby took the identity and is now that worker
+    bool hand_over(const peer_id &worker, const cluster_config &cluster, size_t version);
+    void dismiss_standbys();
     void reap(bool block);
     void stop_workers();
 };

@@ -96,6 +96,23 @@ sc::session &SS(void *h)
 }  // namespace
 
 extern "C" {
+// Warm standby hand-over: copies the identity ("NAME=VALUE\n" lines) into buf and
+// returns its length; 0 when this process is not a standby (the usual case).
+long long stdmlc_standby_wait(char *buf, unsigned long long cap)
+{
+    try {
+        const std::string block = sc::standby_wait();
+        if (buf != nullptr && cap > 0) {
+            const size_t n = std::min<size_t>(block.size(), static_cast<size_t>(cap) - 1);
+            std::memcpy(buf, block.data(), n);
+            buf[n] = '\0';
+        }
+        return static_cast<long long>(block.size());
+    } catch (...) {
+        return -1;
+    }
+}
+
 int stdmlc_peer_from_env(void **out)
 {
     *out = nullptr;

@@ -187,8 +187,46 @@ peer peer::from_torchrun_env()
                      parse_kungfu_startegy(std::getenv("KUNGFU_ALLREDUCE_STRATEGY")));
 }
 
+// A warm standby (started by the launcher with -spares) has run its program up
+// to here without an identity.  It waits for the launcher to write one into
+// its pipe ("NAME=VALUE" lines, an empty line at the end), puts it into the
+// environment and goes on as a worker that joins.  End of file instead means
+// that it was never needed: the process ends quietly.
+std::string standby_wait()
+{
+    const char *spec = std::getenv("STDML_COLLECTIVE_STANDBY_FD");
+    if (spec == nullptr || *spec == '\0') { return ""; }
+    const int fd = std::atoi(spec);
+    ::unsetenv("STDML_COLLECTIVE_STANDBY_FD");
+    std::string block;
+    char buf[512];
+    for (;;) {
+        const ssize_t n = ::read(fd, buf, sizeof(buf));
+        if (n < 0 && errno == EINTR) { continue; }
+        if (n <= 0) { break; }
+        block.append(buf, static_cast<size_t>(n));
+        if (block.size() >= 2 && block.compare(block.size() - 2, 2, "\n\n") == 0) { break; }
+    }
+    ::close(fd);
+    if (block.size() < 2 || block.compare(block.size() - 2, 2, "\n\n") != 0) {
+        std::fflush(nullptr);
+        ::_exit(0);  // dismissed
+    }
+    size_t at = 0;
+    while (at < block.size()) {
+        const size_t nl = block.find('\n', at);
+        const std::string line = block.substr(at, nl - at);
+        at = nl + 1;
+        const size_t eq = line.find('=');
+        if (eq == std::string::npos || eq == 0) { continue; }
+        ::setenv(line.substr(0, eq).c_str(), line.substr(eq + 1).c_str(), 1);
+    }
+    return block;
+}
+
 peer peer::from_env()
 {
+    (void)standby_wait();
     if (std::getenv("KUNGFU_SELF_SPEC") != nullptr) { return from_kungfu_env(); }
     if (std::getenv("OMPI_COMM_WORLD_SIZE") != nullptr) { return from_ompi_env(); }
     if (std::getenv("WORLD_SIZE") != nullptr && std::getenv("RANK") != nullptr) {

@@ -112,7 +112,9 @@ std::string runner::config_url() const
     return "";
 }
 
-void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t version)
+std::vector<std::pair<std::string, std::string>> runner::identity(const peer_id &worker,
+                                                                  const cluster_config &cluster,
+                                                                  size_t version) const
 {
     std::string peers;
     for (size_t i = 0; i < cluster.workers.size(); ++i) {
@@ -122,7 +124,47 @@ void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t 
     for (size_t i = 0; i < cluster.runners.size(); ++i) {
         runners += (i ? "," : "") + cluster.runners[i].str();
     }
+    std::vector<std::pair<std::string, std::string>> env;
+    env.emplace_back("KUNGFU_SELF_SPEC", worker.str());
+    env.emplace_back("KUNGFU_INIT_PEERS", peers);
+    env.emplace_back("KUNGFU_INIT_RUNNERS", runners);
+    env.emplace_back("KUNGFU_INIT_CLUSTER_VERSION", std::to_string(version));
+    env.emplace_back("KUNGFU_ALLREDUCE_STRATEGY", strategy_name(opt_.strat));
     const std::string url = config_url();
+    if (!url.empty()) { env.emplace_back("KUNGFU_CONFIG_SERVER", url); }
+    // a worker keeps its GPU for life: the index follows its port, not its rank
+    env.emplace_back("STDML_COLLECTIVE_DEVICE_ID",
+                     std::to_string(worker.port - opt_.worker_base_port));
+    return env;
+}
+
+namespace
+{
+void redirect_output(const std::string &logdir, const std::string &name)
+{
+    if (logdir.empty()) { return; }
+    ::mkdir(logdir.c_str(), 0755);
+    const std::string base = logdir + "/" + name;
+    const int out = ::open((base + ".stdout.log").c_str(), O_WRONLY | O_CREAT | O_APPEND, 0644);
+    const int err = ::open((base + ".stderr.log").c_str(), O_WRONLY | O_CREAT | O_APPEND, 0644);
+    if (out >= 0) { ::dup2(out, 1); }
+    if (err >= 0) { ::dup2(err, 2); }
+}
+
+[[noreturn]] void exec_command(const std::vector<std::string> &command)
+{
+    std::vector<char *> argv;
+    for (auto &a : command) { argv.push_back(const_cast<char *>(a.c_str())); }
+    argv.push_back(nullptr);
+    ::execvp(argv[0], argv.data());
+    std::fprintf(stderr, "runner: cannot exec %s: %s\n", argv[0], std::strerror(errno));
+    ::_exit(127);
+}
+}  // namespace
+
+void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t version)
+{
+    const auto env = identity(worker, cluster, version);
     const pid_t pid = ::fork();
     if (pid < 0) { throw std::runtime_error("runner: fork failed"); }
     if (pid == 0) {
@@ -130,36 +172,108 @@ void runner::spawn(const peer_id &worker, const cluster_config &cluster, size_t 
         // joiners are started from a short-lived connection thread)
         std::signal(SIGINT, SIG_DFL);
         std::signal(SIGTERM, SIG_DFL);
-        ::setenv("KUNGFU_SELF_SPEC", worker.str().c_str(), 1);
-        ::setenv("KUNGFU_INIT_PEERS", peers.c_str(), 1);
-        ::setenv("KUNGFU_INIT_RUNNERS", runners.c_str(), 1);
-        ::setenv("KUNGFU_INIT_CLUSTER_VERSION", std::to_string(version).c_str(), 1);
-        ::setenv("KUNGFU_ALLREDUCE_STRATEGY", strategy_name(opt_.strat), 1);
-        if (!url.empty()) { ::setenv("KUNGFU_CONFIG_SERVER", url.c_str(), 1); }
-        // a worker keeps its GPU for life: the index follows its port, not its rank
-        ::setenv("STDML_COLLECTIVE_DEVICE_ID",
-                 std::to_string(worker.port - opt_.worker_base_port).c_str(), 1);
+        std::signal(SIGPIPE, SIG_DFL);
+        for (const auto &s : standbys_) { ::close(s.fd); }  // not this worker's to hold open
+        for (const auto &kv : env) { ::setenv(kv.first.c_str(), kv.second.c_str(), 1); }
         for (const auto &kv : opt_.extra_env) { ::setenv(kv.first.c_str(), kv.second.c_str(), 1); }
-        if (!opt_.logdir.empty()) {
-            ::mkdir(opt_.logdir.c_str(), 0755);
-            const std::string base = opt_.logdir + "/" + worker.hostname() + "." +
-                                     std::to_string(worker.port);
-            const int out = ::open((base + ".stdout.log").c_str(), O_WRONLY | O_CREAT | O_APPEND, 0644);
-            const int err = ::open((base + ".stderr.log").c_str(), O_WRONLY | O_CREAT | O_APPEND, 0644);
-            if (out >= 0) { ::dup2(out, 1); }
-            if (err >= 0) { ::dup2(err, 2); }
-        }
-        std::vector<char *> argv;
-        for (auto &a : opt_.command) { argv.push_back(const_cast<char *>(a.c_str())); }
-        argv.push_back(nullptr);
-        ::execvp(argv[0], argv.data());
-        std::fprintf(stderr, "runner: cannot exec %s: %s\n", argv[0], std::strerror(errno));
-        ::_exit(127);
+        redirect_output(opt_.logdir, worker.hostname() + "." + std::to_string(worker.port));
+        exec_command(opt_.command);
     }
     pids_[worker.hash()] = pid;
     if (!opt_.quiet) {
         log(PRINT) << "[runner] started worker" << worker.str() << "pid" << pid << "version"
                    << version;
+    }
+}
+
+// A standby is the worker program without an identity: it runs up to its
+// peer::from_env() (interpreter start, imports, model set-up), where it reads
+// its identity from the pipe whose write end stays here.  End of file on that
+// pipe (this launcher is done, or gone) makes it exit quietly.
+void runner::spawn_standby()
+{
+    int fds[2];
+    if (::pipe(fds) != 0) { return; }
+    const pid_t pid = ::fork();
+    if (pid < 0) {
+        ::close(fds[0]);
+        ::close(fds[1]);
+        return;
+    }
+    if (pid == 0) {
+        std::signal(SIGINT, SIG_DFL);
+        std::signal(SIGTERM, SIG_DFL);
+        std::signal(SIGPIPE, SIG_DFL);
+        ::close(fds[1]);
+        for (const auto &s : standbys_) { ::close(s.fd); }
+        for (const char *name : {"KUNGFU_SELF_SPEC", "KUNGFU_INIT_PEERS", "KUNGFU_INIT_RUNNERS",
+                                 "KUNGFU_INIT_CLUSTER_VERSION", "STDML_COLLECTIVE_DEVICE_ID"}) {
+            ::unsetenv(name);
+        }
+        ::setenv("STDML_COLLECTIVE_STANDBY_FD", std::to_string(fds[0]).c_str(), 1);
+        for (const auto &kv : opt_.extra_env) { ::setenv(kv.first.c_str(), kv.second.c_str(), 1); }
+        redirect_output(opt_.logdir, "standby." + std::to_string(::getpid()));
+        exec_command(opt_.command);
+    }
+    ::close(fds[0]);
+    ::fcntl(fds[1], F_SETFD, FD_CLOEXEC);
+    standbys_.push_back(standby{static_cast<int>(pid), fds[1]});
+    if (!opt_.quiet) { log(PRINT) << "[runner] standby pid" << pid << "is warming up"; }
+}
+
+bool runner::hand_over(const peer_id &worker, const cluster_config &cluster, size_t version)
+{
+    while (!standbys_.empty()) {
+        const standby s = standbys_.front();
+        standbys_.erase(standbys_.begin());
+        std::string block;
+        for (const auto &kv : identity(worker, cluster, version)) {
+            block += kv.first + "=" + kv.second + "\n";
+        }
+        block += "\n";
+        size_t sent = 0;
+        bool ok = true;
+        while (sent < block.size()) {
+            const ssize_t n = ::write(s.fd, block.data() + sent, block.size() - sent);
+            if (n <= 0) {
+                if (n < 0 && errno == EINTR) { continue; }
+                ok = false;  // the standby is gone (EPIPE): try the next one
+                break;
+            }
+            sent += static_cast<size_t>(n);
+        }
+        ::close(s.fd);
+        if (!ok) { continue; }
+        pids_[worker.hash()] = s.pid;
+        if (!opt_.quiet) {
+            log(PRINT) << "[runner] standby pid" << s.pid << "becomes worker" << worker.str()
+                       << "version" << version;
+        }
+        return true;
+    }
+    return false;
+}
+
+// End of file on their pipes: standbys that were never needed exit by themselves.
+void runner::dismiss_standbys()
+{
+    std::vector<standby> all;
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        all.swap(standbys_);
+    }
+    for (const auto &s : all) { ::close(s.fd); }
+    for (const auto &s : all) {
+        bool gone = false;
+        for (int waited_ms = 0; waited_ms < 3000 && !gone; waited_ms += 20) {
+            gone = ::waitpid(s.pid, nullptr, WNOHANG) == s.pid;
+            if (!gone) { std::this_thread::sleep_for(std::chrono::milliseconds(20)); }
+        }
+        if (!gone) {
+            // still importing: it has not reached its read yet, do not wait for that
+            ::kill(s.pid, SIGTERM);
+            ::waitpid(s.pid, nullptr, 0);
+        }
     }
 }
 
@@ -170,6 +284,20 @@ void runner::reap(bool block)
         const pid_t pid = ::waitpid(-1, &status, block ? 0 : WNOHANG);
         if (pid <= 0) { return; }
         std::lock_guard<std::mutex> lk(mu_);
+        bool was_standby = false;
+        for (auto it = standbys_.begin(); it != standbys_.end(); ++it) {
+            if (it->pid == pid) {  // died while warming up: no worker was lost
+                ::close(it->fd);
+                standbys_.erase(it);
+                was_standby = true;
+                break;
+            }
+        }
+        if (was_standby) {
+            if (!opt_.quiet) { log(PRINT) << "[runner] standby pid" << pid << "ended early"; }
+            if (block) { return; }
+            continue;
+        }
         for (auto it = pids_.begin(); it != pids_.end(); ++it) {
             if (it->second == pid) {
                 pids_.erase(it);
@@ -238,8 +366,9 @@ void runner::on_update(size_t version, const cluster_config &next)
             }
             pids_.erase(running);
         }
-        spawn(w, next, version);
+        if (!hand_over(w, next, version)) { spawn(w, next, version); }
     }
+    while (opt_.watch && standbys_.size() < opt_.spares) { spawn_standby(); }
     // removed workers learn `detached` from their own resize() and exit by themselves
 }
 
@@ -276,6 +405,7 @@ int runner::run()
         for (const auto &w : cluster_.workers) {
             if (w.ipv4 == opt_.self.ipv4) { spawn(w, cluster_, 0); }  // other hosts' runners start theirs
         }
+        while (opt_.watch && standbys_.size() < opt_.spares) { spawn_standby(); }
     }
     // A runner of a several-host elastic job may have no worker of its own for a
     // while (its host was shrunk away) and must still be there when the job
@@ -285,6 +415,7 @@ int runner::run()
     int silent_checks = 0;
     std::signal(SIGINT, on_stop_signal);
     std::signal(SIGTERM, on_stop_signal);
+    std::signal(SIGPIPE, SIG_IGN);  // a standby that died shows as EPIPE on its pipe
     for (;;) {
         if (g_stop_signal != 0) {
             stop_workers();
@@ -316,6 +447,7 @@ int runner::run()
         std::this_thread::sleep_for(std::chrono::milliseconds(500));
     }
     if (server_) { server_->stop(); }
+    dismiss_standbys();
     if (http_) { http_->stop(); }
     return failed_;
 }
@@ -372,6 +504,10 @@ bool parse_runner_args(int argc, char *argv[], runner_options &o, std::string &e
             o.watch = true;
         } else if (a == "-q") {
             o.quiet = true;
+        } else if (a == "-spares") {
+            const char *v = need("-spares");
+            if (!v) { return false; }
+            o.spares = static_cast<size_t>(std::max(0, std::atoi(v)));
         } else if (a == "-builtin-config-port") {
             const char *v = need("-builtin-config-port");
             if (!v) { return false; }

@@ -15,6 +15,8 @@ counter becomes the maximum over the new members and the resize hook runs
 `should_stop()` become true.  An unplanned loss surfaces as `PeerFailure`;
 `state.recover()` then rebuilds the session from the members that still answer.
 """
+import time
+
 import torch
 
 from .peer import Peer
@@ -29,6 +31,7 @@ class ElasticState:
         self.max_progress = max_progress
         self.progress = 0
         self.detached = False
+        self.last_resize_ms = None  # duration of the last advance() that changed the membership
         self._synced = False
         self._needs_state = self.sess.version > 0  # joined a running job
         self._hook = None
@@ -62,6 +65,7 @@ class ElasticState:
     def advance(self):
         self._sync()
         self.progress += 1
+        t0 = time.perf_counter()
         if self._get_cluster is not None:
             wanted = self._get_cluster()
             if wanted is None:
@@ -75,6 +79,9 @@ class ElasticState:
             self._synced = False
             self._needs_state = True
             self._sync()
+            # what the members that stay pay for a change of membership: agreement, the new
+            # session (which waits for every joiner to arrive) and the state hand-over
+            self.last_resize_ms = (time.perf_counter() - t0) * 1e3
 
     def recover(self):
         """After a PeerFailure in the loop body (or in advance()): carry on with the

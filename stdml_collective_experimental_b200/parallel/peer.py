@@ -10,6 +10,7 @@ reduce / gather / send / recv / consistent / barrier and the elastic
 `peer.resize(sess, ...)`.  CUDA tensors are enqueued on the current CUDA stream.
 """
 import ctypes
+import os
 import json
 import weakref
 
@@ -391,6 +392,27 @@ class Session:
         return bool(same.value)
 
 
+def standby_wait():
+    """Warm standby hand-over (launcher option -spares N): a process that the launcher
+    started without an identity waits here until it is told which worker it is, and
+    the identity is put into os.environ; every other process returns at once.
+    Peer.from_env() calls it; call it earlier if the program reads the environment
+    (a device index, say) before that.  Returns the identity as a dict."""
+    lib = _lib()
+    lib.stdmlc_standby_wait.restype = ctypes.c_longlong
+    lib.stdmlc_standby_wait.argtypes = [ctypes.c_char_p, ctypes.c_ulonglong]
+    buf = ctypes.create_string_buffer(1 << 16)
+    n = lib.stdmlc_standby_wait(buf, len(buf))
+    got = {}
+    if n > 0:
+        for line in buf.value.decode().splitlines():
+            k, eq, v = line.partition("=")
+            if eq and k:
+                os.environ[k] = v
+                got[k] = v
+    return got
+
+
 class Peer:
     def __init__(self, handle):
         self._h = handle
@@ -398,6 +420,7 @@ class Peer:
 
     @classmethod
     def from_env(cls):
+        standby_wait()
         h = ctypes.c_void_p()
         _native.check(_lib().stdmlc_peer_from_env(ctypes.byref(h)))
         return cls(h)

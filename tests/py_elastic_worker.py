@@ -11,6 +11,7 @@ from stdml_collective_experimental_b200 import PeerFailure  # noqa: E402
 from stdml_collective_experimental_b200.parallel.elastic import ElasticState  # noqa: E402
 from stdml_collective_experimental_b200.parallel.peer import resized_cluster  # noqa: E402
 import json  # noqa: E402
+import time  # noqa: E402
 import urllib.request  # noqa: E402
 
 
@@ -26,6 +27,8 @@ def main():
     die = [a[len("--die="):].split(":") for a in args if a.startswith("--die=")]
     die_port, die_step = (int(die[0][0]), int(die[0][1])) if die else (-1, -1)
     schedule = dict(tuple(map(int, a.split(":"))) for a in args if not a.startswith("--"))
+    step_ms = [int(a[len("--step-ms="):]) for a in args if a.startswith("--step-ms=")]
+    report = "--report" in args
     weights = torch.zeros(256)
     state = ElasticState(max_progress=max_step)
     state.on_resize(lambda s: s.broadcast(weights, name="state", root=state.state_root))
@@ -40,7 +43,13 @@ def main():
             weights += g / state.sess.size
             if state.sess.rank == 0 and step in schedule:
                 propose(state.sess, schedule[step])
+            if step_ms:
+                time.sleep(step_ms[0] * 1e-3)  # stands for the compute of a step
+            before = state.sess.size
             state.advance()
+            if report and not state.detached and state.sess.size != before and state.sess.rank == 0:
+                print(f"resize {before} -> {state.sess.size} took {state.last_resize_ms:.0f} ms",
+                      flush=True)
         except PeerFailure:
             print(f"lost {state.recover()} member(s)", flush=True)
     if state.detached:

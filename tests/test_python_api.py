@@ -69,6 +69,29 @@ def test_python_elastic_state_under_the_runner(native_lib):
     assert res.stdout.count("weight 36.0 OK") == 2 and res.stdout.count("detached") == 1
 
 
+def test_python_elastic_growth_takes_warm_standbys(native_lib):
+    """-spares 2: the launcher keeps two copies of the worker program warm (run up to
+    Peer.from_env()); a growth hands them their identities instead of starting processes,
+    and standbys that were never needed end quietly with the job."""
+    from stdml_collective_experimental_b200 import _native
+    runner = os.path.join(_native.CSRC, "build", "bin", "stdml_collective_run")
+    cmd = [runner, "-np", "2", "-w", "-spares", "2", "-builtin-config-port", "0", "-runner-port",
+           "38286", "-port-range", "10560", sys.executable,
+           os.path.join(HERE, "py_elastic_worker.py"), "30", "--report", "--step-ms=250",
+           "16:4", "24:3"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         timeout=600)
+    out = res.stdout
+    assert res.returncode == 0, out[-3000:]
+    assert out.count("becomes worker") == 2, out[-3000:]        # both joiners were standbys
+    assert out.count("started worker") == 2, out[-3000:]        # only the first two were started cold
+    assert out.count("weight 465.0 OK") == 3 and out.count("detached") == 1, out[-3000:]
+    took = [float(line.split("took")[1].split()[0]) for line in out.splitlines()
+            if line.startswith("resize 2 -> 4")]
+    assert len(took) == 1
+    print("growth with warm standbys took", took[0], "ms")
+
+
 def test_python_elastic_state_recovers_from_a_crash(native_lib):
     from stdml_collective_experimental_b200 import _native
     runner = os.path.join(_native.CSRC, "build", "bin", "stdml_collective_run")
