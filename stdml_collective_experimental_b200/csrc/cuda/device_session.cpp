@@ -718,9 +718,12 @@ bool DeviceSession::group_registered(size_t n, const void *const *ins, void *con
             if (!host.empty()) {
                 void *dev = nullptr;
                 rt_check(cudaMalloc(&dev, host.size() * sizeof(PeerEntry)), "cudaMalloc(table)");
-                rt_check(cudaMemcpy(dev, host.data(), host.size() * sizeof(PeerEntry),
-                                    cudaMemcpyHostToDevice),
-                         "cudaMemcpy(table)");
+                if (cudaMemcpy(dev, host.data(), host.size() * sizeof(PeerEntry),
+                               cudaMemcpyHostToDevice) != cudaSuccess) {
+                    (void)cudaFree(dev);
+                    rt_check(cudaGetLastError(), "cudaMemcpy(table)");
+                    throw std::runtime_error("group_all_reduce: cannot upload the table of peer pointers");
+                }
                 plan.dev = static_cast<PeerEntry *>(dev);
             } else {
                 return true;  // nothing to reduce

@@ -83,6 +83,32 @@ int main()
     bad += sess.device_launches() - before != 1;
     sess.symm_free(heap);
 
+    // separately allocated tensors, registered: their allocations are mapped on every
+    // peer once, then ONE launch reduces them where they lie (no staging)
+    if (n > 1) {
+        sess.device_set_knob("register_min_bytes", 0);
+        float *t[3] = {nullptr, nullptr, nullptr};
+        const size_t len[3] = {1000, 77, 300001};
+        std::vector<workspace> loose;
+        for (int i = 0; i < 3; ++i) {
+            CUDA_OK(cudaMalloc(&t[i], len[i] * sizeof(float)));
+            std::vector<float> v(len[i], float(r + 1));
+            CUDA_OK(cudaMemcpy(t[i], v.data(), len[i] * sizeof(float), cudaMemcpyHostToDevice));
+            loose.push_back(workspace{t[i], t[i], len[i], f32, sum, "l" + std::to_string(i)});
+        }
+        const unsigned long long l0 = sess.device_launches();
+        sess.group_all_reduce(loose, 1.0 / n);
+        for (int i = 0; i < 3; ++i) {
+            std::vector<float> v(len[i]);
+            CUDA_OK(cudaMemcpy(v.data(), t[i], len[i] * sizeof(float), cudaMemcpyDeviceToHost));
+            bad += v[0] != (n + 1) / 2.0f || v.back() != (n + 1) / 2.0f;
+        }
+        bad += sess.device_launches() - l0 != 1;
+        sess.device_drop_registrations();  // before the tensors are freed
+        sess.device_set_knob("register_min_bytes", -1);
+        for (float *p : t) { cudaFree(p); }
+    }
+
     std::printf("rank %d/%d on device memory: %s\n", r, n, bad == 0 ? "OK" : "WRONG");
     cudaFree(x);
     cudaFree(y);

@@ -157,6 +157,15 @@ class session
     // peers' arenas, NVLS multicast.
     void device_setup_ms(double out[4]) const;
 
+    // A named tuning knob of the device plane, the same value on every rank
+    // (e.g. "register_min_bytes": collectives on ordinary device buffers of at
+    // least that size map the buffers' allocations on every peer and run on
+    // them in place; a group of separately allocated tensors is then one
+    // launch).  device_drop_registrations() is collective and unmaps what
+    // registered calls mapped; buffers used that way must stay allocated until then.
+    void device_set_knob(const std::string &name, long long value);
+    void device_drop_registrations();
+
     // Kernels this session has launched on the device so far (0 before its first
     // device call): lets callers and tests see how many launches a call cost.
     unsigned long long device_launches() const;

@@ -365,6 +365,16 @@ int stdmlc_session_device_setup_ms(void *s, double *out4)
     return host_guarded([&] { SS(s).device_setup_ms(out4); });
 }
 
+int stdmlc_session_device_set_knob(void *s, const char *name, long long value)
+{
+    return host_guarded([&] { SS(s).device_set_knob(name ? name : "", value); });
+}
+
+int stdmlc_session_device_drop_registrations(void *s)
+{
+    return host_guarded([&] { SS(s).device_drop_registrations(); });
+}
+
 int stdmlc_session_device_launches(void *s, unsigned long long *out)
 {
     return host_guarded([&] { *out = SS(s).device_launches(); });

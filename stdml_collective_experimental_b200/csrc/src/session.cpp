@@ -1203,6 +1203,16 @@ void session::device_setup_ms(double out[4]) const
     if (device_) { device_->world().setup_ms(out); }
 }
 
+void session::device_set_knob(const std::string &name, long long value)
+{
+    device()->set_knob(name, value);
+}
+
+void session::device_drop_registrations()
+{
+    device()->drop_registrations();
+}
+
 unsigned long long session::device_launches() const
 {
     std::lock_guard<std::mutex> lk(*device_mu_);

@@ -59,6 +59,8 @@ def _lib():
         lib.stdmlc_session_symm_alloc.argtypes = [vp, u64, vpp]
         lib.stdmlc_session_symm_free.argtypes = [vp, vp]
         lib.stdmlc_session_device_launches.argtypes = [vp, c.POINTER(u64)]
+        lib.stdmlc_session_device_set_knob.argtypes = [vp, c.c_char_p, c.c_longlong]
+        lib.stdmlc_session_device_drop_registrations.argtypes = [vp]
         lib.stdmlc_session_device_setup_ms.argtypes = [vp, c.POINTER(c.c_double)]
         lib.stdmlc_session_consistent.argtypes = [vp, vp, u64, c.POINTER(c.c_int)]
         lib.stdmlc_peer_resize.argtypes = [vp, vp, c.c_longlong, c.c_char_p, c.POINTER(c.c_int),
@@ -370,6 +372,16 @@ class Session:
         _native.check(self._lib.stdmlc_session_device_setup_ms(self._h, out))
         return {"rendezvous": out[0], "own_arena": out[1], "peer_arenas": out[2],
                 "multicast": out[3]}
+
+    def device_set_knob(self, name, value):
+        """A tuning knob of the device plane (see DeviceSession.set_knob), the same value
+        on every rank; e.g. ("register_min_bytes", 0): CUDA tensors are used in place
+        through peer mappings of their allocations, a group of them is one launch."""
+        _native.check(self._lib.stdmlc_session_device_set_knob(self._h, name.encode(), int(value)))
+
+    def device_drop_registrations(self):
+        """Collective: unmap what registered calls mapped (before freeing such tensors)."""
+        _native.check(self._lib.stdmlc_session_device_drop_registrations(self._h))
 
     @property
     def device_launches(self):
