@@ -24,6 +24,8 @@ def propose(sess, new_size):
 def main():
     max_step = int(sys.argv[1])
     args = sys.argv[2:]
+    if "--standby-dies" in args and os.environ.get("STDML_COLLECTIVE_STANDBY_FD"):
+        sys.exit(0)  # a standby that does not survive its warm-up
     die = [a[len("--die="):].split(":") for a in args if a.startswith("--die=")]
     die_port, die_step = (int(die[0][0]), int(die[0][1])) if die else (-1, -1)
     schedule = dict(tuple(map(int, a.split(":"))) for a in args if not a.startswith("--"))

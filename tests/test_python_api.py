@@ -92,6 +92,22 @@ def test_python_elastic_growth_takes_warm_standbys(native_lib):
     print("growth with warm standbys took", took[0], "ms")
 
 
+def test_python_elastic_growth_survives_dead_standbys(native_lib):
+    """Standbys that ended during their warm-up are skipped: the joiners are started cold."""
+    from stdml_collective_experimental_b200 import _native
+    runner = os.path.join(_native.CSRC, "build", "bin", "stdml_collective_run")
+    cmd = [runner, "-np", "2", "-w", "-spares", "1", "-builtin-config-port", "0", "-runner-port",
+           "38288", "-port-range", "10580", sys.executable,
+           os.path.join(HERE, "py_elastic_worker.py"), "12", "--standby-dies", "--step-ms=100",
+           "6:3"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         timeout=600)
+    out = res.stdout
+    assert res.returncode == 0, out[-3000:]
+    assert out.count("becomes worker") == 0 and out.count("started worker") == 3, out[-3000:]
+    assert out.count("weight 78.0 OK") == 3, out[-3000:]
+
+
 def test_python_elastic_state_recovers_from_a_crash(native_lib):
     from stdml_collective_experimental_b200 import _native
     runner = os.path.join(_native.CSRC, "build", "bin", "stdml_collective_run")
