@@ -1,5 +1,7 @@
 #include "local_rendezvous.hpp"
 
+#include <algorithm>
+
 #include <cerrno>
 #include <chrono>
 #include <cstring>
@@ -218,11 +220,18 @@ void LocalRendezvous::all_gather(const void *mine, size_t size,
 {
     out.assign(world_, std::vector<char>(size));
     if (size > 0) { std::memcpy(out[rank_].data(), mine, size); }
-    for (int p = 0; p < world_; ++p) {
-        if (p != rank_) { send_bytes(p, mine, size); }
-    }
-    for (int p = 0; p < world_; ++p) {
-        if (p != rank_) { recv_bytes(p, out[p].data(), size); }
+    // Every rank sends before it receives, so what is in flight per socket must fit
+    // the socket's buffer: large contributions (a table of a few thousand buffer
+    // registrations) go in pieces, each exchanged completely before the next.
+    constexpr size_t kPiece = 32u << 10;
+    for (size_t at = 0; at < size; at += kPiece) {
+        const size_t piece = std::min(kPiece, size - at);
+        for (int p = 0; p < world_; ++p) {
+            if (p != rank_) { send_bytes(p, static_cast<const char *>(mine) + at, piece); }
+        }
+        for (int p = 0; p < world_; ++p) {
+            if (p != rank_) { recv_bytes(p, out[p].data() + at, piece); }
+        }
     }
 }
 

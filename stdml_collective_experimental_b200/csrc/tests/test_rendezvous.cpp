@@ -42,6 +42,21 @@ static int rank_main(const std::string &key, int r, int np)
         std::memcpy(&v, all[p].data(), sizeof(v));
         CHECK(v == 100 + p);
     }
+    // a contribution far larger than a socket buffer (every rank sends before it receives)
+    {
+        std::vector<unsigned char> big((3u << 20) + 7);
+        for (size_t i = 0; i < big.size(); ++i) { big[i] = static_cast<unsigned char>(i * 31 + r); }
+        rdv.all_gather(big.data(), big.size(), all);
+        for (int p = 0; p < np; ++p) {
+            CHECK(all[p].size() == big.size());
+            bool same = true;
+            for (size_t i = 0; i < big.size() && same; i += 4093) {
+                same = static_cast<unsigned char>(all[p][i]) == static_cast<unsigned char>(i * 31 + p);
+            }
+            CHECK(same);
+        }
+        rdv.all_gather(nullptr, 0, all);  // nothing to say is fine too
+    }
     // descriptors: everybody shares a page that names its owner
     const int mfd = ::memfd_create("rdv-test", MFD_CLOEXEC);
     REQUIRE(mfd >= 0);
