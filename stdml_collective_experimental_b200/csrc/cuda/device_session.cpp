@@ -90,6 +90,10 @@ void DeviceSession::set_knob(const std::string &name, long long value)
         register_min_bytes_ = value < 0 ? SIZE_MAX : static_cast<size_t>(value);
         return;
     }
+    if (name == "register_verify") {
+        register_verify_ = value != 0;
+        return;
+    }
     if (name == "chunk_push_blocks") {
         chunk_push_blocks_ = static_cast<int>(std::max<long long>(1, std::min<long long>(kMaxBlocks, value)));
         return;
@@ -663,7 +667,7 @@ bool DeviceSession::group_registered(size_t n, const void *const *ins, void *con
     key.append(reinterpret_cast<const char *>(outs), sizeof(void *) * n * vr);
     key.append(reinterpret_cast<const char *>(counts), sizeof(size_t) * n);
     key.append(reinterpret_cast<const char *>(&dt), sizeof(dt));
-    for (size_t k = 0; k < n * static_cast<size_t>(vr); ++k) {
+    for (size_t k = 0; register_verify_ && k < n * static_cast<size_t>(vr); ++k) {
         const unsigned long long a = world_->buffer_id(ins[k]);
         const unsigned long long b = outs[k] == ins[k] ? a : world_->buffer_id(outs[k]);
         key.append(reinterpret_cast<const char *>(&a), sizeof(a));

@@ -135,6 +135,11 @@ class DeviceSession
     };
     std::map<std::string, PeerPlan> peer_plans_;
     unsigned long long peer_plan_builds_ = 0;
+    // Look up the allocation id behind every tensor on every call (one driver query
+    // per tensor), so that a tensor freed and allocated again at the same address
+    // is noticed.  Knob register_verify = 0 trusts the addresses instead (for sets of
+    // thousands of tensors in allocations that are never freed).
+    bool register_verify_ = true;
     void forget_peer_plans();
     // Returns false when the set has to be staged (decided alike on every rank).
     bool group_registered(size_t n, const void *const *ins, void *const *outs,

@@ -182,7 +182,8 @@ class DeviceSession:
         tma_over_nvls_min_bytes (negative: never), gather_push_min_bytes, gather_mc,
         pipeline_min_bytes, debug_checks, group_bulk_min_bytes (registered groups of
         at least that many bytes load their operands with bulk asynchronous copies;
-        negative: never), and register_min_bytes: collectives on
+        negative: never), register_verify (0: a registered group trusts its tensors'
+        addresses instead of looking up their allocation ids on every call), and register_min_bytes: collectives on
         ordinary CUDA tensors of at least that many bytes map the tensors'
         allocations on every peer (CUDA IPC, cached per allocation) and run
         zero-copy on them; negative: never (the default).  Tensors used that way
