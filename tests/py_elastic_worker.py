@@ -2,7 +2,10 @@
 import os
 import sys
 
-import torch
+if "--standby-dies" in sys.argv and os.environ.get("STDML_COLLECTIVE_STANDBY_FD"):
+    sys.exit(0)  # a standby that does not survive its warm-up (gone long before the job grows)
+
+import torch  # noqa: E402
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
@@ -24,8 +27,6 @@ def propose(sess, new_size):
 def main():
     max_step = int(sys.argv[1])
     args = sys.argv[2:]
-    if "--standby-dies" in args and os.environ.get("STDML_COLLECTIVE_STANDBY_FD"):
-        sys.exit(0)  # a standby that does not survive its warm-up
     die = [a[len("--die="):].split(":") for a in args if a.startswith("--die=")]
     die_port, die_step = (int(die[0][0]), int(die[0][1])) if die else (-1, -1)
     schedule = dict(tuple(map(int, a.split(":"))) for a in args if not a.startswith("--"))
