@@ -66,21 +66,38 @@ sockaddr_in to_sockaddr(const peer_id &id)
 }
 
 // Second back-end: ranks of one host may talk over abstract UNIX-domain stream
-// sockets instead of TCP loopback (STDML_COLLECTIVE_TRANSPORT=unix).  The
-// framing is identical; only dialling and listening differ.  Every server
-// listens on both, so mixed settings still connect.
-bool prefer_shared_memory()
+// sockets instead of TCP loopback.  The framing is identical; only dialling
+// and listening differ.  Every server listens on both, so mixed settings still
+// connect.  STDML_COLLECTIVE_TRANSPORT = tcp | unix | shm | auto; unset means
+// auto: peers of this host are dialled over a UNIX socket with a shared-memory
+// ring (without one where none can be made).  unix: no ring; shm: the ring is
+// required.  In all three a peer whose UNIX socket does not answer (it listens
+// on TCP only, or lives in another network namespace) is dialled over TCP.
+enum class transport_mode { tcp, unix_socket, shm, automatic };
+
+transport_mode transport()
 {
-    static const bool on = safe_getenv("STDML_COLLECTIVE_TRANSPORT") == "shm";
-    return on;
+    static const transport_mode m = [] {
+        const std::string v = safe_getenv("STDML_COLLECTIVE_TRANSPORT");
+        if (v == "tcp") { return transport_mode::tcp; }
+        if (v == "unix") { return transport_mode::unix_socket; }
+        if (v == "shm") { return transport_mode::shm; }
+        return transport_mode::automatic;
+    }();
+    return m;
 }
 
-bool prefer_unix_sockets()
+// (automatic mode) a ring could not be set up once: plain UNIX sockets from then on
+std::atomic<bool> g_ring_unavailable{false};
+
+bool prefer_shared_memory()
 {
-    static const bool on =
-        safe_getenv("STDML_COLLECTIVE_TRANSPORT") == "unix" || prefer_shared_memory();
-    return on;
+    const transport_mode m = transport();
+    return m == transport_mode::shm ||
+           (m == transport_mode::automatic && !g_ring_unavailable.load(std::memory_order_relaxed));
 }
+
+bool prefer_unix_sockets() { return transport() != transport_mode::tcp; }
 
 // Third back-end (STDML_COLLECTIVE_TRANSPORT=shm): the dialler of a UNIX-domain
 // connection announces a ring with this bit of conn_header::type, creates it
@@ -385,43 +402,56 @@ std::unique_ptr<connection> connection::dial(const peer_id remote, const conn_ty
     const int64_t limit = patience_ms >= 0 ? std::max<int64_t>(patience_ms, 1) : connect_timeout_ms();
     const sockaddr_in addr = to_sockaddr(remote);
     int wait_ms = 2;
+    const bool same_host =
+        remote.ipv4 == local.ipv4 || local.ipv4 == 0 || (remote.ipv4 >> 24) == 127u;
+    const bool automatic = transport() == transport_mode::automatic;
     for (;;) {
-        const bool local_peer = prefer_unix_sockets() &&
-                                (remote.ipv4 == local.ipv4 || local.ipv4 == 0 ||
-                                 (remote.ipv4 >> 24) == 127u);
-        const int fd = ::socket(local_peer ? AF_UNIX : AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
-        if (fd < 0) { throw std::runtime_error("rchan: socket() failed"); }
-        mark_reusable(fd);
-        int rc;
-        if (local_peer) {
-            sockaddr_un ua;
-            const socklen_t ul = to_unix_addr(remote, ua);
-            rc = ::connect(fd, reinterpret_cast<const sockaddr *>(&ua), ul);
-        } else {
-            rc = ::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr));
-        }
-        if (rc == 0) {
-            tune_socket(fd);
-            const bool want_ring = local_peer && prefer_shared_memory();
-            const uint16_t wire_type =
-                static_cast<uint16_t>(type) | (want_ring ? conn_type_ring_bit : uint16_t(0));
-            conn_header h{wire_type, local.port, local.ipv4};
-            connection_ack ack{};
-            iovec iov{&h, sizeof(h)};
-            if (write_iov(fd, &iov, 1) && read_exact(fd, &ack, sizeof(ack))) {
-                if (!want_ring) {
-                    return std::unique_ptr<connection>(new connection_impl(fd, type, remote));
-                }
-                if (auto ring = offer_ring(fd)) {
-                    return std::unique_ptr<connection>(
-                        new connection_impl(fd, type, remote, std::move(ring)));
-                }
-                ::close(fd);
-                throw std::runtime_error("rchan: cannot set up a shared-memory ring to " +
-                                         remote.str());
+        // one round: the UNIX socket of a peer of this host first, then TCP (a peer
+        // elsewhere, or one that listens on TCP only)
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            const bool local_peer = attempt == 0 && prefer_unix_sockets() && same_host;
+            if (attempt == 0 && !local_peer) { continue; }              // nothing to try before TCP
+            const int fd =
+                ::socket(local_peer ? AF_UNIX : AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+            if (fd < 0) { throw std::runtime_error("rchan: socket() failed"); }
+            mark_reusable(fd);
+            int rc;
+            if (local_peer) {
+                sockaddr_un ua;
+                const socklen_t ul = to_unix_addr(remote, ua);
+                rc = ::connect(fd, reinterpret_cast<const sockaddr *>(&ua), ul);
+            } else {
+                rc = ::connect(fd, reinterpret_cast<const sockaddr *>(&addr), sizeof(addr));
             }
+            if (rc == 0) {
+                tune_socket(fd);
+                const bool want_ring = local_peer && prefer_shared_memory();
+                const uint16_t wire_type = static_cast<uint16_t>(type) |
+                                           (want_ring ? conn_type_ring_bit : uint16_t(0));
+                conn_header h{wire_type, local.port, local.ipv4};
+                connection_ack ack{};
+                iovec iov{&h, sizeof(h)};
+                if (write_iov(fd, &iov, 1) && read_exact(fd, &ack, sizeof(ack))) {
+                    if (!want_ring) {
+                        return std::unique_ptr<connection>(new connection_impl(fd, type, remote));
+                    }
+                    if (auto ring = offer_ring(fd)) {
+                        return std::unique_ptr<connection>(
+                            new connection_impl(fd, type, remote, std::move(ring)));
+                    }
+                    ::close(fd);
+                    if (automatic) {
+                        // no shared memory to be had here: dial again, without a ring
+                        g_ring_unavailable.store(true, std::memory_order_relaxed);
+                        attempt = -1;
+                        continue;
+                    }
+                    throw std::runtime_error("rchan: cannot set up a shared-memory ring to " +
+                                             remote.str());
+                }
+            }
+            ::close(fd);
         }
-        ::close(fd);
         const auto waited =
             std::chrono::duration_cast<std::chrono::milliseconds>(clock::now() - t0).count();
         if (limit > 0 && waited > limit) {
@@ -636,7 +666,9 @@ class server_impl final : public server
             throw std::runtime_error("rchan: cannot bind " + self_.str() + ": " + why);
         }
         if (::listen(listen_fd_, 128) != 0) { throw std::runtime_error("rchan: listen() failed"); }
-        unix_fd_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        // (a rank that is told to speak TCP only listens on TCP only, like a rank of
+        // the reference; its peers' diallers then fall back to TCP)
+        unix_fd_ = prefer_unix_sockets() ? ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0) : -1;
         if (unix_fd_ >= 0) {
             sockaddr_un ua;
             const socklen_t ul = to_unix_addr(self_, ua);

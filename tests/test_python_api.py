@@ -31,6 +31,26 @@ def test_python_peer_session(n, strategy, base, native_lib):
         assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
 
 
+def test_ranks_with_different_transports_meet(native_lib):
+    """Ranks 0 and 2 take the default (UNIX socket + shared-memory ring for same-host peers,
+    TCP when that does not answer), rank 1 speaks and listens on TCP only, rank 3 insists on
+    plain UNIX sockets: every pair still connects, in both directions."""
+    n, base = 4, 12180
+    modes = {1: "tcp", 3: "unix"}
+    procs = []
+    for r in range(n):
+        env = dict(os.environ)
+        env.pop("STDML_COLLECTIVE_TRANSPORT", None)
+        if r in modes:
+            env["STDML_COLLECTIVE_TRANSPORT"] = modes[r]
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "py_rank_worker.py"),
+                                       str(r), str(n), str(base), "ring"], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = collect(procs, 300)
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"rank {r} OK" in o, o[-2000:]
+
+
 def test_resnet50_gradient_set_over_a_ring_of_four(native_lib):
     """The "CPU plumbing" acceptance case, as specified: 4 processes, ring, the 161
     f32 tensors of ResNet-50, N(0, 1) values seeded per rank, against a host sum."""
