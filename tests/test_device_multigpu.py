@@ -14,6 +14,12 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+# These tests are about the device plane.  Their host control plane runs over TCP loopback,
+# the transport they were validated with on GPU boxes; the transport that the host path
+# picks by itself is covered by the CPU tests.
+os.environ.setdefault("STDML_COLLECTIVE_TRANSPORT", "tcp")
+
+
 def run_world(n, port, extra_env=None, timeout=600, worker="multigpu_worker.py"):
     env = dict(os.environ)
     env.update(extra_env or {})
