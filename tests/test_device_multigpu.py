@@ -17,11 +17,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # These tests are about the device plane.  Their host control plane runs over TCP loopback,
 # the transport they were validated with on GPU boxes; the transport that the host path
 # picks by itself is covered by the CPU tests.
-os.environ.setdefault("STDML_COLLECTIVE_TRANSPORT", "tcp")
+CONTROL_PLANE = {"STDML_COLLECTIVE_TRANSPORT": os.environ.get("STDML_COLLECTIVE_TRANSPORT", "tcp")}
 
 
 def run_world(n, port, extra_env=None, timeout=600, worker="multigpu_worker.py"):
-    env = dict(os.environ)
+    env = dict(os.environ, **CONTROL_PLANE)
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
@@ -62,7 +62,7 @@ def test_torch_distributed_backend_on_cuda_tensors():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     n, port = 2, 29881
-    env = dict(os.environ, STDML_COLLECTIVE_BASE_PORT="10900")
+    env = dict(os.environ, STDML_COLLECTIVE_BASE_PORT="10900", **CONTROL_PLANE)
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "pg_worker.py"), str(r), str(n),
                                str(port), "cuda"], env=env, stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(n)]
@@ -91,7 +91,8 @@ def test_elastic_resize_on_gpus():
         _native.build()
     # a rank leaves between steps: no multicast binding may be live then, neither
     # NCCL's nor the library's own
-    env = dict(os.environ, PYTHONPATH=root, NCCL_NVLS_ENABLE="0", STDML_COLLECTIVE_NVLS="0")
+    env = dict(os.environ, PYTHONPATH=root, NCCL_NVLS_ENABLE="0", STDML_COLLECTIVE_NVLS="0",
+               **CONTROL_PLANE)
     cmd = [runner, "-q", "-np", "2", "-w", "-builtin-config-port", "0", "-runner-port", "38181",
            "-port-range", "10300", sys.executable, "-m",
            "stdml_collective_experimental_b200.benchmarks.elastic", "--model", "resnet50",
