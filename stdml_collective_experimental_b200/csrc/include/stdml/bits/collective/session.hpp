@@ -117,7 +117,7 @@ class session
     liveness *liveness_;               // owned by peer; may be null (no failure detection)
 
     session(system_config config, size_t version, size_t rank, peer_list peers, peer_list runners,
-            mailbox *mailbox, slotbox *slotbox, rchan::client_pool *client_pool,
+            mailbox *eager_box, slotbox *posted_box, rchan::client_pool *client_pool,
             strategy s = star, liveness *live = nullptr, std::string scope = "");
     ~session();
 

@@ -59,12 +59,12 @@ int forced_algo(const system_config &c)
 }  // namespace
 
 session::session(system_config config, size_t version, size_t rank, peer_list peers,
-                 peer_list runners, mailbox *mailbox, slotbox *slotbox,
+                 peer_list runners, mailbox *eager_box, slotbox *posted_box,
                  rchan::client_pool *client_pool, strategy s, liveness *live, std::string scope)
     : scope_(std::move(scope)), config_(std::move(config)), version_(version), rank_(rank), peers_(std::move(peers)),
       runners_(std::move(runners)), strategy_(s),
-      all_reduce_topo_(make_graph_pair_list(s, peers_.size())), mailbox_(mailbox),
-      slotbox_(slotbox), client_pool_(client_pool), liveness_(live)
+      all_reduce_topo_(make_graph_pair_list(s, peers_.size())), mailbox_(eager_box),
+      slotbox_(posted_box), client_pool_(client_pool), liveness_(live)
 {
     if (rank_ >= peers_.size()) { throw std::invalid_argument("session: rank outside the peer list"); }
     if (config_.thread_pool_size > 0 &&
