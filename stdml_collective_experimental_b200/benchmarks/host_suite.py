@@ -78,7 +78,7 @@ def main():
     ap.add_argument("--workloads", default="1024x100,16384x100,102400x100,262144x10,resnet50,vgg16")
     ap.add_argument("--out", default="")
     ap.add_argument("--strategies", default="RING,STAR",
-                    help="comma list of RING, STAR, BINARY_TREE (the reference knows the first two)")
+                    help="comma list of RING, STAR, BINARY_TREE, CLIQUE (the reference knows the first two)")
     args = ap.parse_args()
     # "sweep" stands for the reference's AxB list (testdata/test-set-1.txt there)
     args.workloads = ",".join(",".join(SWEEP) if w == "sweep" else w

@@ -15,7 +15,7 @@ int main(int argc, char *argv[])
     stdml::collective::runner_options opt;
     std::string error;
     if (!stdml::collective::parse_runner_args(argc, argv, opt, error)) {
-        std::fprintf(stderr, "%s: %s\nusage: %s -np N [-strategy STAR|RING] [-w] "
+        std::fprintf(stderr, "%s: %s\nusage: %s -np N [-strategy STAR|RING|BINARY_TREE|CLIQUE] [-w] "
                              "[-builtin-config-port P] [-config-server URL] [-logdir DIR] [-q] "
                              "[-runner-port P] [-port-range P] [-env K=V] [-spares N] "
                              "[-H ip:slots,ip:slots -self ip] prog [args...]\n",

@@ -71,6 +71,7 @@ enum strategy {
     star,
     ring,
     binary_tree,  // the reference lists it and leaves it commented out (topology.hpp:85-89 there)
+    clique,       // one star per rank; KungFu's name for it (the reference has no such strategy)
 };
 
 // star rooted at `root`: edges root -> i
@@ -81,7 +82,9 @@ graph_builder start_broadcast_graph_builder(size_t n, size_t root);
 // binary_tree: n pairs; pair r is a complete binary tree over the ranks renumbered
 // from r (rank (r + k) % n is node k, whose parent is node (k - 1) / 2): log2(n)
 // hops instead of the ring's n - 1, two children per node instead of the star's
-// n - 1 at the root.
+// n - 1 at the root.  clique: n pairs; pair r is the star rooted at r, so the
+// chunks of a tensor (and the tensors of a set) spread their roots over all
+// ranks: two hops like the star, the ring's even load per rank.
 graph_pair_list make_graph_pair_list(strategy s, size_t n);
 
 const char *strategy_name(strategy s);

@@ -130,7 +130,7 @@ int stdmlc_peer_create(void **out, int rank, const char *peers_csv, int strategy
             throw std::invalid_argument("peer: malformed peer list");
         }
         *out = new sc::peer(sc::peer::from_list(static_cast<size_t>(rank), *peers,
-                                                strategy == 1 ? sc::ring : strategy == 2 ? sc::binary_tree : sc::star, version,
+                                                strategy == 1 ? sc::ring : strategy == 2 ? sc::binary_tree : strategy == 3 ? sc::clique : sc::star, version,
                                                 *runners));
     });
 }
@@ -207,7 +207,7 @@ int stdmlc_session_info(void *s, int what, unsigned long long *out)
             *out = ss.version();
             break;
         case 3:
-            *out = ss.get_strategy() == sc::ring ? 1 : ss.get_strategy() == sc::binary_tree ? 2 : 0;
+            *out = ss.get_strategy() == sc::ring ? 1 : ss.get_strategy() == sc::binary_tree ? 2 : ss.get_strategy() == sc::clique ? 3 : 0;
             break;
         default:
             throw std::invalid_argument("session_info: unknown item");

@@ -113,6 +113,7 @@ strategy parse_kungfu_startegy(const char *s)
     std::string v(s);
     for (auto &c : v) { c = static_cast<char>(std::toupper(static_cast<unsigned char>(c))); }
     if (v == "BINARY_TREE" || v == "TREE") { return binary_tree; }
+    if (v == "CLIQUE") { return clique; }
     return v == "RING" ? ring : star;
 }
 

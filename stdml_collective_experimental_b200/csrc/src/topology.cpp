@@ -72,6 +72,8 @@ graph_pair_list make_graph_pair_list(strategy s, size_t n)
         for (size_t r = 0; r < n; ++r) { l.pairs.push_back(ring_pair(n, r)); }
     } else if (s == binary_tree && n > 1) {
         for (size_t r = 0; r < n; ++r) { l.pairs.push_back(tree_pair(n, r)); }
+    } else if (s == clique && n > 1) {
+        for (size_t r = 0; r < n; ++r) { l.pairs.push_back(star_pair(n, r)); }
     } else {
         l.pairs.push_back(star_pair(n, 0));
     }
@@ -80,6 +82,6 @@ graph_pair_list make_graph_pair_list(strategy s, size_t n)
 
 const char *strategy_name(strategy s)
 {
-    return s == ring ? "RING" : s == binary_tree ? "BINARY_TREE" : "STAR";
+    return s == ring ? "RING" : s == binary_tree ? "BINARY_TREE" : s == clique ? "CLIQUE" : "STAR";
 }
 }  // namespace stdml::collective

@@ -116,6 +116,21 @@ static void test_topology()
             }
         }
     }
+    // clique: the star, once per rank as root
+    for (size_t n : {2u, 5u}) {
+        const auto cl = make_graph_pair_list(clique, n);
+        CHECK(cl.pairs.size() == n);
+        for (size_t r = 0; r < n; ++r) {
+            const graph &g = cl.pairs[r].reduce_graph, &b = cl.pairs[r].broadcast_graph;
+            CHECK(g.self_loop(r) && g.prevs(r).size() == n - 1 && g.nexts(r).empty());
+            CHECK(b.nexts(r).size() == n - 1 && b.prevs(r).empty());
+            for (size_t v = 0; v < n; ++v) {
+                if (v != r) { CHECK(g.nexts(v).size() == 1 && g.nexts(v)[0] == r && b.prevs(v)[0] == r); }
+            }
+        }
+    }
+    CHECK(make_graph_pair_list(clique, 1).pairs.size() == 1);
+    CHECK(std::string(strategy_name(clique)) == "CLIQUE" && parse_kungfu_startegy("clique") == clique);
     CHECK(std::string(strategy_name(binary_tree)) == "BINARY_TREE" &&
           parse_kungfu_startegy("tree") == binary_tree && parse_kungfu_startegy("Ring") == ring &&
           parse_kungfu_startegy(nullptr) == star);

@@ -164,7 +164,7 @@ class Session:
 
     @property
     def strategy(self):
-        return {1: "ring", 2: "binary_tree"}.get(self._info(3), "star")
+        return {1: "ring", 2: "binary_tree", 3: "clique"}.get(self._info(3), "star")
 
     @property
     def cluster(self):
@@ -443,7 +443,7 @@ class Peer:
         h = ctypes.c_void_p()
         _native.check(_lib().stdmlc_peer_create(
             ctypes.byref(h), rank, ",".join(peers).encode(),
-            {"ring": 1, "binary_tree": 2, "tree": 2}.get(strategy.lower(), 0),
+            {"ring": 1, "binary_tree": 2, "tree": 2, "clique": 3}.get(strategy.lower(), 0),
             version, ",".join(runners).encode()))
         return cls(h)
 

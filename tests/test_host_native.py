@@ -207,6 +207,11 @@ def test_failure_detection_with_the_tree_strategy():
     assert "np=5: OK" in run("test_shutdown", 5, env={"KUNGFU_ALLREDUCE_STRATEGY": "BINARY_TREE"})
 
 
+def test_failure_detection_with_the_clique_strategy():
+    # a star per rank: every rank is a root for some chunks and a leaf for the others
+    assert "np=4: OK" in run("test_shutdown", 4, env={"KUNGFU_ALLREDUCE_STRATEGY": "CLIQUE"})
+
+
 def test_shutdown_and_host_side_failure_detection():
     # clean teardown after 100 collectives; a rank that leaves between steps and a rank
     # that never joins both end in exceptions on the others, not in a hang
@@ -224,7 +229,7 @@ def test_public_headers_compile_as_cxx17():
 
 @pytest.mark.parametrize("np_,strategy", [(16, "STAR"), (16, "RING"), (7, "RING"),
                                           (4, "BINARY_TREE"), (7, "BINARY_TREE"),
-                                          (16, "BINARY_TREE")])
+                                          (16, "BINARY_TREE"), (4, "CLIQUE"), (7, "CLIQUE")])
 def test_collectives_many_ranks(np_, strategy):
     # the reference's CI sweeps np = 1..16 (t:37-57 there)
     assert f"np={np_}: OK" in run("test_collectives", np_,
