@@ -21,7 +21,7 @@ def collect(procs, timeout):
 
 
 @pytest.mark.parametrize("n,strategy,base", [(1, "star", 12100), (3, "star", 12110),
-                                             (4, "ring", 12120)])
+                                             (4, "ring", 12120), (3, "clique", 12130)])
 def test_python_peer_session(n, strategy, base, native_lib):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "py_rank_worker.py"), str(r),
                                str(n), str(base), strategy], stdout=subprocess.PIPE,
