@@ -188,6 +188,17 @@ def test_elastic_state_follows_config_server():
     assert out.count("weight 45.0 (want 45.0) OK") == 3 and out.count("detached") == 1
 
 
+def test_elastic_growth_from_warm_standbys_cxx_workers():
+    # -spares 2: the joiners of both growth steps are standbys that waited in
+    # peer::from_env(); nothing but the first two workers is started cold, and the
+    # standbys that were never used end with the job
+    out = run("stdml_collective_run", "-np", 2, "-w", "-spares", 2, "-builtin-config-port", 0,
+              "-runner-port", 38387, "-port-range", 10640, os.path.join(BIN, "example_elastic"),
+              "--max-step=12", "3:2", "6:3", "9:4", timeout=300)
+    assert out.count("becomes worker") == 2 and out.count("started worker") == 2, out
+    assert out.count("weight 78.0 (want 78.0) OK") == 4, out
+
+
 def test_elastic_state_survives_a_crash_and_grows_back():
     # the worker on port 10601 dies at step 3; the others recover (version 1, two
     # members), rank 0 asks for three again at step 6 and the runner starts a
